@@ -1,0 +1,33 @@
+// Internal interfaces between the convolution translation units.
+#pragma once
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+
+namespace dcg {
+
+enum ConvKind { kConvFwd = 0, kConvDx = 1, kConvDk = 2 };
+
+// CUDA-core fp32 kernels, any shape (conv_generic.cu).
+int conv_fwd_generic(const dcg_conv_desc& d, const float* x, const float* k, float* y,
+                     const EpilogueArgs& ep, cudaStream_t stream);
+int conv_dx_generic(const dcg_conv_desc& d, const float* dy, const float* k, float* dx,
+                    const EpilogueArgs& ep, cudaStream_t stream);
+int conv_dk_generic(const dcg_conv_desc& d, const float* x, const float* dy, float* dk,
+                    cudaStream_t stream);
+
+// tcgen05 TF32 implicit-GEMM kernels (conv_tc.cu).  *_supported tells whether the
+// tensor path takes the shape; *_workspace its scratch need in bytes.
+bool conv_tc_supported(const dcg_conv_desc& d, int kind);
+size_t conv_tc_workspace(const dcg_conv_desc& d, int kind);
+int conv_tc_fwd(const dcg_conv_desc& d, const float* x, const float* k, float* y,
+                const EpilogueArgs& ep, void* ws, size_t ws_bytes, cudaStream_t stream);
+int conv_tc_dx(const dcg_conv_desc& d, const float* dy, const float* k, float* dx,
+               const EpilogueArgs& ep, void* ws, size_t ws_bytes, cudaStream_t stream);
+int conv_tc_dk(const dcg_conv_desc& d, const float* x, const float* dy, float* dk,
+               void* ws, size_t ws_bytes, cudaStream_t stream);
+
+// Shape validation shared by the entry points: 0 or a negative dcg_status.
+int conv_check_desc(const dcg_conv_desc* d, const char* who);
+
+}  // namespace dcg

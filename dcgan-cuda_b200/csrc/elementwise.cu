@@ -1,0 +1,565 @@
+// Memory-bound operators around the convolutions: bias add + activation,
+// activation gradients, element-wise add / axpy, column and row sums, losses.
+//
+// All of them are HBM-bound streaming kernels: 128-bit loads and stores where
+// the pointers and sizes allow it, grid-stride loops, grids sized as a multiple
+// of the SM count.  Reductions use a fixed tree so results are deterministic.
+#include "common.cuh"
+
+namespace dcg {
+namespace {
+
+constexpr int kThreads = 256;
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+inline int stream_grid(size_t work_items, int per_block = kThreads, int waves = 8)
+{
+    size_t blocks = (work_items + per_block - 1) / per_block;
+    size_t cap = (size_t)sm_count() * waves;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+// ---- z = a + bias[col]; act(z) ---------------------------------------------
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads)
+bias_act_kernel(const float* __restrict__ a, const float* __restrict__ bias,
+                float* __restrict__ z_out, float* __restrict__ act_out,
+                size_t total, unsigned cols, int act, float alpha)
+{
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (VEC) {
+        const size_t n4 = total >> 2;
+        for (; i < n4; i += stride) {
+            float4 v = __ldg(reinterpret_cast<const float4*>(a) + i);
+            if (bias) {
+                const unsigned col = (unsigned)((i << 2) % cols);
+                const float4 b = __ldg(reinterpret_cast<const float4*>(bias + col));
+                v.x = __fadd_rn(v.x, b.x); v.y = __fadd_rn(v.y, b.y);
+                v.z = __fadd_rn(v.z, b.z); v.w = __fadd_rn(v.w, b.w);
+            }
+            if (z_out) reinterpret_cast<float4*>(z_out)[i] = v;
+            if (act_out) {
+                v.x = act_apply(v.x, act, alpha); v.y = act_apply(v.y, act, alpha);
+                v.z = act_apply(v.z, act, alpha); v.w = act_apply(v.w, act, alpha);
+                reinterpret_cast<float4*>(act_out)[i] = v;
+            }
+        }
+    } else {
+        for (; i < total; i += stride) {
+            float v = __ldg(a + i);
+            if (bias) v = __fadd_rn(v, __ldg(bias + (i % cols)));
+            if (z_out) z_out[i] = v;
+            if (act_out) act_out[i] = act_apply(v, act, alpha);
+        }
+    }
+}
+
+// ---- out = dout * act'(gate) -----------------------------------------------
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads)
+act_grad_kernel(const float* __restrict__ gate, const float* __restrict__ dout,
+                float* __restrict__ out, size_t total, int act, float alpha)
+{
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (VEC) {
+        const size_t n4 = total >> 2;
+        for (; i < n4; i += stride) {
+            const float4 g = __ldg(reinterpret_cast<const float4*>(gate) + i);
+            const float4 d = __ldg(reinterpret_cast<const float4*>(dout) + i);
+            float4 r;
+            r.x = act_grad_apply(g.x, d.x, act, alpha); r.y = act_grad_apply(g.y, d.y, act, alpha);
+            r.z = act_grad_apply(g.z, d.z, act, alpha); r.w = act_grad_apply(g.w, d.w, act, alpha);
+            reinterpret_cast<float4*>(out)[i] = r;
+        }
+    } else {
+        for (; i < total; i += stride)
+            out[i] = act_grad_apply(__ldg(gate + i), __ldg(dout + i), act, alpha);
+    }
+}
+
+// ---- out = a + b ; out += coeff * dv ----------------------------------------
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads)
+add_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
+           size_t total)
+{
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (VEC) {
+        const size_t n4 = total >> 2;
+        for (; i < n4; i += stride) {
+            const float4 x = __ldg(reinterpret_cast<const float4*>(a) + i);
+            const float4 y = __ldg(reinterpret_cast<const float4*>(b) + i);
+            reinterpret_cast<float4*>(out)[i] =
+                make_float4(__fadd_rn(x.x, y.x), __fadd_rn(x.y, y.y), __fadd_rn(x.z, y.z),
+                            __fadd_rn(x.w, y.w));
+        }
+    } else {
+        for (; i < total; i += stride) out[i] = __fadd_rn(__ldg(a + i), __ldg(b + i));
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+update_kernel(const float* __restrict__ dv, float* __restrict__ out,
+              const float* __restrict__ coeff, size_t total)
+{
+    const float c = __ldg(coeff);
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride)
+        out[i] = __fadd_rn(out[i], __fmul_rn(c, __ldg(dv + i)));
+}
+
+// ---- column sums (bias gradient) ---------------------------------------------
+// Stage 1: block (tx over column groups, ty over rows) reduces a slab of rows
+// into partial[slab][cols]; stage 2 sums the slabs in order.  VEC: a column
+// group is one float4.
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads)
+colsum_partial_kernel(const float* __restrict__ a, float* __restrict__ partial,
+                      size_t rows, unsigned cols, unsigned rows_per_slab, int tx_count)
+{
+    extern __shared__ float smem[];  // [ty_count][tx_count * (VEC ? 4 : 1)]
+    const int ty_count = blockDim.x / tx_count;
+    const int tx = threadIdx.x % tx_count;
+    const int ty = threadIdx.x / tx_count;
+    const unsigned groups = VEC ? cols / 4 : cols;
+    const unsigned group = blockIdx.x * tx_count + tx;
+    const size_t r0 = (size_t)blockIdx.y * rows_per_slab;
+    size_t r1 = r0 + rows_per_slab;
+    if (r1 > rows) r1 = rows;
+
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (group < groups) {
+        for (size_t r = r0 + ty; r < r1; r += ty_count) {
+            if (VEC) {
+                const float4 v = __ldg(reinterpret_cast<const float4*>(a + r * cols) + group);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            } else {
+                acc.x += __ldg(a + r * cols + group);
+            }
+        }
+    }
+    constexpr int W = VEC ? 4 : 1;
+    float* mine = smem + ((size_t)ty * tx_count + tx) * W;
+    mine[0] = acc.x;
+    if (VEC) { mine[1] = acc.y; mine[2] = acc.z; mine[3] = acc.w; }
+    __syncthreads();
+    for (int s = ty_count >> 1; s > 0; s >>= 1) {
+        if (ty < s) {
+            const float* other = smem + ((size_t)(ty + s) * tx_count + tx) * W;
+#pragma unroll
+            for (int q = 0; q < W; ++q) mine[q] += other[q];
+        }
+        __syncthreads();
+    }
+    if (ty == 0 && group < groups) {
+        float* dst = partial + (size_t)blockIdx.y * cols + (size_t)group * W;
+#pragma unroll
+        for (int q = 0; q < W; ++q) dst[q] = mine[q];
+    }
+}
+
+__global__ void colsum_final_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                                    unsigned slabs, unsigned cols)
+{
+    const unsigned c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    float s = 0.f;
+    for (unsigned k = 0; k < slabs; ++k) s += partial[(size_t)k * cols + c];
+    out[c] = s;
+}
+
+// ---- row sums: one warp per row -----------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+rowsum_kernel(const float* __restrict__ a, float* __restrict__ out, size_t rows, size_t cols)
+{
+    const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= rows) return;
+    float s = 0.f;
+    for (size_t c = lane; c < cols; c += 32) s += __ldg(a + warp * cols + c);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) out[warp] = s;
+}
+
+// ---- block-wide deterministic sum ----------------------------------------------
+__device__ __forceinline__ float block_sum(float v, float* red /* [32] */)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = (threadIdx.x < nwarps) ? red[threadIdx.x] : 0.f;
+    if (warp == 0) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    }
+    __syncthreads();
+    return v;  // valid in warp 0
+}
+
+// mean_i( x>=0 ? x - x*y + log(1+exp(-x)) : -x*y + log(1+exp(x)) ), src/cpu/ops.hxx:440-452
+__global__ void __launch_bounds__(512)
+sigmoid_xent_kernel(const float* __restrict__ y, const float* __restrict__ x,
+                    float* __restrict__ out, size_t n)
+{
+    __shared__ float red[32];
+    float s = 0.f;
+    for (size_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const float xi = __ldg(x + i), yi = __ldg(y + i);
+        s += xi >= 0.f ? xi - xi * yi + logf(1.f + expf(-xi)) : -xi * yi + logf(1.f + expf(xi));
+    }
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) out[0] = s / (float)n;
+}
+
+__global__ void __launch_bounds__(kThreads)
+sigmoid_xent_grad_kernel(const float* __restrict__ y, const float* __restrict__ x,
+                         float* __restrict__ out, size_t n)
+{
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        out[i] = (act_apply(__ldg(x + i), DCG_ACT_SIGMOID, 0.f) - __ldg(y + i)) / (float)n;
+}
+
+__global__ void __launch_bounds__(512)
+mse_kernel(const float* __restrict__ y, const float* __restrict__ y_hat, float* __restrict__ out,
+           size_t n)
+{
+    __shared__ float red[32];
+    float s = 0.f;
+    for (size_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const float d = __ldg(y + i) - __ldg(y_hat + i);
+        s += d * d;
+    }
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) out[0] = s / (float)n;
+}
+
+__global__ void __launch_bounds__(kThreads)
+mse_grad_kernel(const float* __restrict__ y, const float* __restrict__ y_hat,
+                float* __restrict__ out, size_t n, float coeff)
+{
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        out[i] = __fmul_rn(coeff, __fsub_rn(__ldg(y_hat + i), __ldg(y + i)));
+}
+
+// ---- softmax family: one warp per row (src/cpu/ops.hxx:129-186,418-430) ---------
+// mode 0: softmax, 1: log_softmax, 2: (softmax - y)/rows
+__global__ void __launch_bounds__(kThreads)
+softmax_rows_kernel(const float* __restrict__ a, const float* __restrict__ y,
+                    float* __restrict__ out, size_t rows, size_t cols, int mode)
+{
+    const size_t row = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float* ar = a + row * cols;
+    float mx = -INFINITY;
+    for (size_t c = lane; c < cols; c += 32) mx = fmaxf(mx, __ldg(ar + c));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float s = 0.f;
+    for (size_t c = lane; c < cols; c += 32) s += expf(__ldg(ar + c) - mx);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float logsum = mx + logf(s);
+    for (size_t c = lane; c < cols; c += 32) {
+        const float v = __ldg(ar + c);
+        float r;
+        if (mode == 0) r = expf(v - mx) / s;
+        else if (mode == 1) r = v - logsum;
+        else r = (expf(v - mx) / s - __ldg(y + row * cols + c)) / (float)rows;
+        out[row * cols + c] = r;
+    }
+}
+
+// -(1/rows) sum_ij y_ij (logit_ij - logsumexp_i)
+__global__ void __launch_bounds__(512)
+softmax_xent_kernel(const float* __restrict__ y, const float* __restrict__ logits,
+                    float* __restrict__ out, size_t rows, size_t cols)
+{
+    __shared__ float red[32];
+    float acc = 0.f;
+    for (size_t r = threadIdx.x; r < rows; r += blockDim.x) {
+        const float* lr = logits + r * cols;
+        float mx = lr[0];
+        for (size_t c = 1; c < cols; ++c) mx = fmaxf(mx, lr[c]);
+        float e = 0.f;
+        for (size_t c = 0; c < cols; ++c) e += expf(lr[c] - mx);
+        const float logsum = mx + logf(e);
+        for (size_t c = 0; c < cols; ++c) acc += y[r * cols + c] * (lr[c] - logsum);
+    }
+    acc = block_sum(acc, red);
+    if (threadIdx.x == 0) out[0] = -acc / (float)rows;
+}
+
+// Count of rows whose first maximum sits at the same column in both matrices.
+// Integer counting keeps the result exact whatever the reduction order.
+__global__ void __launch_bounds__(512)
+argmax_acc_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                  float* __restrict__ out, size_t rows, size_t cols)
+{
+    __shared__ unsigned count;
+    if (threadIdx.x == 0) count = 0;
+    __syncthreads();
+    unsigned mine = 0;
+    for (size_t r = threadIdx.x; r < rows; r += blockDim.x) {
+        const float* ar = a + r * cols;
+        const float* br = b + r * cols;
+        size_t ia = 0, ib = 0;
+        for (size_t c = 1; c < cols; ++c) {
+            if (ar[c] > ar[ia]) ia = c;
+            if (br[c] > br[ib]) ib = c;
+        }
+        mine += (ia == ib);
+    }
+    atomicAdd(&count, mine);
+    __syncthreads();
+    if (threadIdx.x == 0) out[0] = (float)count;
+}
+
+}  // namespace
+}  // namespace dcg
+
+using namespace dcg;
+
+extern "C" int dcg_bias_act(const float* a, const float* bias, float* z_out, float* act_out,
+                            size_t rows, size_t cols, int act, float alpha, dcg_stream_t stream)
+{
+    DCG_CHECK_ARG(a && (z_out || act_out), "dcg_bias_act: null input or no output");
+    DCG_CHECK_ARG(cols > 0 && cols <= 0xffffffffu, "dcg_bias_act: bad cols %zu", cols);
+    DCG_CHECK_ARG(act >= DCG_ACT_NONE && act <= DCG_ACT_SIGMOID, "dcg_bias_act: unknown act %d", act);
+    const size_t total = rows * cols;
+    if (total == 0) return DCG_OK;
+    const bool vec = (cols % 4 == 0) && aligned16(a) && (!bias || aligned16(bias)) &&
+                     (!z_out || aligned16(z_out)) && (!act_out || aligned16(act_out));
+    if (vec)
+        bias_act_kernel<true><<<stream_grid(total / 4), kThreads, 0, as_stream(stream)>>>(
+            a, bias, z_out, act_out, total, (unsigned)cols, act, alpha);
+    else
+        bias_act_kernel<false><<<stream_grid(total), kThreads, 0, as_stream(stream)>>>(
+            a, bias, z_out, act_out, total, (unsigned)cols, act, alpha);
+    DCG_LAUNCH_CHECK("bias_act_kernel");
+    return DCG_OK;
+}
+
+extern "C" int dcg_act_fwd(const float* a, float* out, size_t n, int act, float alpha,
+                           dcg_stream_t stream)
+{
+    DCG_CHECK_ARG(a && out, "dcg_act_fwd: null pointer");
+    return dcg_bias_act(a, nullptr, nullptr, out, n / 4 * 4 == n ? n / 4 : n, n / 4 * 4 == n ? 4 : 1,
+                        act, alpha, stream);
+}
+
+extern "C" int dcg_act_grad(const float* gate, const float* dout, float* out, size_t n, int act,
+                            float alpha, dcg_stream_t stream)
+{
+    DCG_CHECK_ARG(gate && dout && out, "dcg_act_grad: null pointer");
+    DCG_CHECK_ARG(act >= DCG_ACT_NONE && act <= DCG_ACT_SIGMOID, "dcg_act_grad: unknown act %d", act);
+    if (n == 0) return DCG_OK;
+    const bool vec = (n % 4 == 0) && aligned16(gate) && aligned16(dout) && aligned16(out);
+    if (vec)
+        act_grad_kernel<true><<<stream_grid(n / 4), kThreads, 0, as_stream(stream)>>>(gate, dout, out, n, act, alpha);
+    else
+        act_grad_kernel<false><<<stream_grid(n), kThreads, 0, as_stream(stream)>>>(gate, dout, out, n, act, alpha);
+    DCG_LAUNCH_CHECK("act_grad_kernel");
+    return DCG_OK;
+}
+
+extern "C" int dcg_add(const float* a, const float* b, float* out, size_t n, dcg_stream_t stream)
+{
+    DCG_CHECK_ARG(a && b && out, "dcg_add: null pointer");
+    if (n == 0) return DCG_OK;
+    const bool vec = (n % 4 == 0) && aligned16(a) && aligned16(b) && aligned16(out);
+    if (vec)
+        add_kernel<true><<<stream_grid(n / 4), kThreads, 0, as_stream(stream)>>>(a, b, out, n);
+    else
+        add_kernel<false><<<stream_grid(n), kThreads, 0, as_stream(stream)>>>(a, b, out, n);
+    DCG_LAUNCH_CHECK("add_kernel");
+    return DCG_OK;
+}
+
+extern "C" int dcg_update(const float* dv, float* out, const float* coeff, size_t n,
+                          dcg_stream_t stream)
+{
+    DCG_CHECK_ARG(dv && out && coeff, "dcg_update: null pointer");
+    if (n == 0) return DCG_OK;
+    update_kernel<<<stream_grid(n), kThreads, 0, as_stream(stream)>>>(dv, out, coeff, n);
+    DCG_LAUNCH_CHECK("update_kernel");
+    return DCG_OK;
+}
+
+namespace {
+struct ColsumPlan {
+    bool vec;
+    int tx_count;       // threads along column groups
+    unsigned groups;    // column groups (float4s or floats)
+    unsigned grid_x;    // column-group tiles
+    unsigned slabs;     // row slabs = grid_y
+    unsigned rows_per_slab;
+};
+
+ColsumPlan colsum_plan(size_t rows, size_t cols, bool ptr_aligned)
+{
+    ColsumPlan p;
+    p.vec = (cols % 4 == 0) && ptr_aligned;
+    p.groups = (unsigned)(p.vec ? cols / 4 : cols);
+    int tx = 1;
+    while (tx < 32 && (unsigned)tx < p.groups) tx <<= 1;
+    p.tx_count = tx;
+    p.grid_x = (p.groups + tx - 1) / tx;
+    const int ty = kThreads / tx;
+    // enough slabs to fill the machine a few times over, each at least 4 row passes deep
+    size_t want = ((size_t)sm_count() * 4 + p.grid_x - 1) / p.grid_x;
+    size_t max_slabs = (rows + (size_t)ty * 4 - 1) / ((size_t)ty * 4);
+    if (max_slabs < 1) max_slabs = 1;
+    if (want > max_slabs) want = max_slabs;
+    if (want < 1) want = 1;
+    p.rows_per_slab = (unsigned)((rows + want - 1) / want);
+    if (p.rows_per_slab < 1) p.rows_per_slab = 1;
+    p.slabs = (unsigned)((rows + p.rows_per_slab - 1) / p.rows_per_slab);
+    if (p.slabs < 1) p.slabs = 1;
+    return p;
+}
+}  // namespace
+
+extern "C" size_t dcg_colsum_workspace_bytes(size_t rows, size_t cols)
+{
+    // Sized for the larger of the vector / scalar plans (pointer alignment is unknown here).
+    const ColsumPlan a = colsum_plan(rows, cols, true), b = colsum_plan(rows, cols, false);
+    const unsigned slabs = a.slabs > b.slabs ? a.slabs : b.slabs;
+    return (size_t)slabs * cols * sizeof(float);
+}
+
+extern "C" int dcg_colsum(const float* a, float* out, size_t rows, size_t cols, void* workspace,
+                          size_t workspace_bytes, dcg_stream_t stream)
+{
+    DCG_CHECK_ARG(a && out, "dcg_colsum: null pointer");
+    DCG_CHECK_ARG(cols > 0 && cols <= 0x7fffffffu && rows > 0, "dcg_colsum: bad shape %zu x %zu", rows, cols);
+    const ColsumPlan p = colsum_plan(rows, cols, aligned16(a));
+    const size_t need = (size_t)p.slabs * cols * sizeof(float);
+    float* partial;
+    if (p.slabs == 1) {
+        partial = out;  // a single slab writes the result directly
+    } else {
+        if (!workspace || workspace_bytes < need)
+            return fail(DCG_ERR_WORKSPACE, "dcg_colsum: workspace %zu < %zu bytes", workspace_bytes, need);
+        partial = static_cast<float*>(workspace);
+    }
+    const dim3 grid(p.grid_x, p.slabs);
+    const size_t smem = (size_t)kThreads * (p.vec ? 4 : 1) * sizeof(float);
+    if (p.vec)
+        colsum_partial_kernel<true><<<grid, kThreads, smem, as_stream(stream)>>>(
+            a, partial, rows, (unsigned)cols, p.rows_per_slab, p.tx_count);
+    else
+        colsum_partial_kernel<false><<<grid, kThreads, smem, as_stream(stream)>>>(
+            a, partial, rows, (unsigned)cols, p.rows_per_slab, p.tx_count);
+    DCG_LAUNCH_CHECK("colsum_partial_kernel");
+    if (p.slabs > 1) {
+        colsum_final_kernel<<<(unsigned)((cols + 127) / 128), 128, 0, as_stream(stream)>>>(
+            partial, out, p.slabs, (unsigned)cols);
+        DCG_LAUNCH_CHECK("colsum_final_kernel");
+    }
+    return DCG_OK;
+}
+
+extern "C" int dcg_rowsum(const float* a, float* out, size_t rows, size_t cols, dcg_stream_t stream)
+{
+    DCG_CHECK_ARG(a && out && rows > 0 && cols > 0, "dcg_rowsum: bad arguments");
+    const size_t blocks = (rows * 32 + kThreads - 1) / kThreads;
+    rowsum_kernel<<<(unsigned)blocks, kThreads, 0, as_stream(stream)>>>(a, out, rows, cols);
+    DCG_LAUNCH_CHECK("rowsum_kernel");
+    return DCG_OK;
+}
+
+extern "C" int dcg_sigmoid_xent(const float* y, const float* logits, float* out, size_t n,
+                                dcg_stream_t stream)
+{
+    DCG_CHECK_ARG(y && logits && out && n > 0, "dcg_sigmoid_xent: bad arguments");
+    sigmoid_xent_kernel<<<1, 512, 0, as_stream(stream)>>>(y, logits, out, n);
+    DCG_LAUNCH_CHECK("sigmoid_xent_kernel");
+    return DCG_OK;
+}
+
+extern "C" int dcg_sigmoid_xent_grad(const float* y, const float* logits, float* out, size_t n,
+                                     dcg_stream_t stream)
+{
+    DCG_CHECK_ARG(y && logits && out && n > 0, "dcg_sigmoid_xent_grad: bad arguments");
+    sigmoid_xent_grad_kernel<<<stream_grid(n), kThreads, 0, as_stream(stream)>>>(y, logits, out, n);
+    DCG_LAUNCH_CHECK("sigmoid_xent_grad_kernel");
+    return DCG_OK;
+}
+
+extern "C" int dcg_mse(const float* y, const float* y_hat, float* out, size_t rows, size_t cols,
+                       dcg_stream_t stream)
+{
+    DCG_CHECK_ARG(y && y_hat && out && rows * cols > 0, "dcg_mse: bad arguments");
+    mse_kernel<<<1, 512, 0, as_stream(stream)>>>(y, y_hat, out, rows * cols);
+    DCG_LAUNCH_CHECK("mse_kernel");
+    return DCG_OK;
+}
+
+extern "C" int dcg_mse_grad(const float* y, const float* y_hat, float* out, size_t n,
+                            dcg_stream_t stream)
+{
+    DCG_CHECK_ARG(y && y_hat && out && n > 0, "dcg_mse_grad: bad arguments");
+    mse_grad_kernel<<<stream_grid(n), kThreads, 0, as_stream(stream)>>>(y, y_hat, out, n,
+                                                                        (float)(2. / (double)n));
+    DCG_LAUNCH_CHECK("mse_grad_kernel");
+    return DCG_OK;
+}
+
+static int softmax_rows(const float* a, const float* y, float* out, size_t rows, size_t cols,
+                        int mode, dcg_stream_t stream)
+{
+    DCG_CHECK_ARG(a && out && rows > 0 && cols > 0, "softmax: bad arguments");
+    const size_t blocks = (rows * 32 + kThreads - 1) / kThreads;
+    softmax_rows_kernel<<<(unsigned)blocks, kThreads, 0, as_stream(stream)>>>(a, y, out, rows, cols, mode);
+    DCG_LAUNCH_CHECK("softmax_rows_kernel");
+    return DCG_OK;
+}
+
+extern "C" int dcg_softmax(const float* a, float* out, size_t rows, size_t cols, dcg_stream_t stream)
+{
+    return softmax_rows(a, nullptr, out, rows, cols, 0, stream);
+}
+
+extern "C" int dcg_log_softmax(const float* a, float* out, size_t rows, size_t cols,
+                               dcg_stream_t stream)
+{
+    return softmax_rows(a, nullptr, out, rows, cols, 1, stream);
+}
+
+extern "C" int dcg_softmax_xent_grad(const float* y, const float* logits, float* out, size_t rows,
+                                     size_t cols, dcg_stream_t stream)
+{
+    DCG_CHECK_ARG(y, "dcg_softmax_xent_grad: null labels");
+    return softmax_rows(logits, y, out, rows, cols, 2, stream);
+}
+
+extern "C" int dcg_softmax_xent(const float* y, const float* logits, float* out, size_t rows,
+                                size_t cols, dcg_stream_t stream)
+{
+    DCG_CHECK_ARG(y && logits && out && rows > 0 && cols > 0, "dcg_softmax_xent: bad arguments");
+    softmax_xent_kernel<<<1, 512, 0, as_stream(stream)>>>(y, logits, out, rows, cols);
+    DCG_LAUNCH_CHECK("softmax_xent_kernel");
+    return DCG_OK;
+}
+
+extern "C" int dcg_argmax_acc(const float* y, const float* y_hat, float* out, size_t rows,
+                              size_t cols, dcg_stream_t stream)
+{
+    DCG_CHECK_ARG(y && y_hat && out && rows > 0 && cols > 0, "dcg_argmax_acc: bad arguments");
+    argmax_acc_kernel<<<1, 512, 0, as_stream(stream)>>>(y, y_hat, out, rows, cols);
+    DCG_LAUNCH_CHECK("argmax_acc_kernel");
+    return DCG_OK;
+}

@@ -1,0 +1,311 @@
+/*
+ * dcgan_b200 - C ABI of the B200 (sm_100a) convolution / Adam hot path that
+ * replaces the GPU backend (src/gpu) of obs145628/dcgan-cuda.
+ *
+ * Conventions
+ *   - every pointer named x, k, y, dy, dx, dk, bias, ... is a DEVICE pointer to
+ *     fp32 data unless the comment says "host";
+ *   - activations are NHWC, conv2d kernels HWIO [kh][kw][Cin][Cout],
+ *     conv2d_transpose kernels [kh][kw][Cout][Cin] (the layouts of the
+ *     reference's ops, src/ops/conv2d.cu, src/ops/conv2d-transpose.cu);
+ *   - every entry point returns a dcg_status (0 = ok, negative = error), is
+ *     asynchronous on the given stream, never synchronises the device and
+ *     never allocates: scratch memory is passed in as (workspace, bytes);
+ *   - dcg_last_error() returns a human-readable message for the last non-zero
+ *     status returned on the calling thread.
+ *
+ * File:line citations name the reference interface each entry point replaces.
+ */
+#ifndef DCGAN_B200_H
+#define DCGAN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* dcg_stream_t; /* a cudaStream_t; NULL = the default stream */
+
+enum dcg_status {
+    DCG_OK = 0,
+    DCG_ERR_INVALID = -1,     /* bad argument (null pointer, non-positive size, unknown enum) */
+    DCG_ERR_CUDA = -2,        /* a CUDA runtime/driver call failed */
+    DCG_ERR_WORKSPACE = -3,   /* workspace too small / missing */
+    DCG_ERR_UNSUPPORTED = -4, /* shape outside what the requested path supports */
+    DCG_ERR_DEVICE = -5       /* a kernel reported an error through its status word */
+};
+
+enum dcg_act {
+    DCG_ACT_NONE = 0,
+    DCG_ACT_LEAKY = 1,   /* x<0 ? alpha*x : x        (src/gpu/relu.cu:26-37)   */
+    DCG_ACT_RELU = 2,    /* x<0 ? 0 : x              (src/gpu/relu.cu:39-48)   */
+    DCG_ACT_TANH = 3,    /* 2/(1+exp(-2x)) - 1       (src/gpu/sigmoid.cu:113)  */
+    DCG_ACT_SIGMOID = 4  /* 1/(1+exp(-x))            (src/gpu/sigmoid.cu:21)   */
+};
+
+enum dcg_precision {
+    DCG_PREC_TF32 = 0,   /* tcgen05 kind::tf32, fp32 accumulate in TMEM; falls back to
+                            DCG_PREC_FP32 kernels for shapes the tensor path cannot take */
+    DCG_PREC_3XTF32 = 1, /* error-compensated split, fp32-level accuracy (opt-in) */
+    DCG_PREC_FP32 = 2    /* CUDA-core fp32 with the reference CPU's summation order,
+                            unfused multiply/add: bit-comparable with src/cpu/ops.hxx */
+};
+
+/* Geometry of one strided convolution y = conv2d(x, k).  The same descriptor
+ * drives the forward, input-gradient and kernel-gradient entry points; the
+ * transposed convolution and its gradients reuse them with roles swapped,
+ * exactly as src/gpu/conv2d.cu:167-307 does. */
+typedef struct dcg_conv_desc {
+    int n, h, w, c;         /* x  [n, h, w, c]             */
+    int kh, kw, o;          /* k  [kh, kw, c, o]           */
+    int ho, wo;             /* y  [n, ho, wo, o]           */
+    int stride_h, stride_w;
+    int pad_top, pad_left;  /* taps outside x contribute nothing (src/cpu/ops.hxx:236-243) */
+} dcg_conv_desc;
+
+/* Work fused behind the accumulator of dcg_conv2d_fwd / dcg_conv2d_dx, applied
+ * per output element v with output-channel index ch, in this order:
+ *   raw_out[i] = v           if raw_out   (the bare convolution result)
+ *   v += bias[ch]            if bias      (mvrow_add,   src/gpu/matmul.cu:27-38)
+ *   pre_act[i] = v           if pre_act   (the z tensor backward needs)
+ *   v = act(v)               if act       (src/gpu/relu.cu, sigmoid.cu)
+ *   v *= act'(gate[i])       if gate      (leaky/relu grad take the pre-activation,
+ *                                          tanh grad takes the tanh OUTPUT:
+ *                                          src/gpu/relu.cu:50-66, sigmoid.cu:42-50)
+ *   out[i] = v
+ * A NULL dcg_epilogue* means "store the accumulator". */
+typedef struct dcg_epilogue {
+    float* raw_out;
+    const float* bias;
+    float* pre_act;
+    int act;          /* dcg_act */
+    float alpha;      /* leaky slope for act */
+    const float* gate;
+    int gate_act;     /* dcg_act whose derivative gates the result */
+    float gate_alpha; /* leaky slope for gate_act */
+} dcg_epilogue;
+
+/* ---- convolutions -------------------------------------------------------- */
+
+/* Scratch bytes the three conv entry points need for `desc` at `precision`
+ * (kind: 0 = fwd, 1 = dx, 2 = dk).  0 when none is needed. */
+size_t dcg_conv_workspace_bytes(const dcg_conv_desc* desc, int kind, int precision);
+
+/* y = conv2d(x, k) [+ epilogue].
+ * Replaces gpu::kernel_conv2d (src/gpu/conv2d.cu:13-62) and, with dy as x,
+ * gpu::kernel_conv2d_transpose_input_grad (src/gpu/conv2d.cu:214-259). */
+int dcg_conv2d_fwd(const dcg_conv_desc* desc, const float* x, const float* k, float* y,
+                   const dcg_epilogue* ep, int precision,
+                   void* workspace, size_t workspace_bytes, dcg_stream_t stream);
+
+/* dx = d conv2d / d x given dy [+ epilogue]; dx has desc's x shape.
+ * Replaces gpu::kernel_conv2d_input_grad (src/gpu/conv2d.cu:70-117) and, with
+ * the layer input as dy, gpu::kernel_conv2d_transpose (src/gpu/conv2d.cu:167-212). */
+int dcg_conv2d_dx(const dcg_conv_desc* desc, const float* dy, const float* k, float* dx,
+                  const dcg_epilogue* ep, int precision,
+                  void* workspace, size_t workspace_bytes, dcg_stream_t stream);
+
+/* dk = d conv2d / d k given x and dy; dk has desc's k shape.
+ * Replaces gpu::kernel_conv2d_kernel_grad (src/gpu/conv2d.cu:119-165) and, with
+ * (dy, x) swapped, gpu::kernel_conv2d_transpose_kernel_grad (src/gpu/conv2d.cu:264-307). */
+int dcg_conv2d_dk(const dcg_conv_desc* desc, const float* x, const float* dy, float* dk,
+                  int precision, void* workspace, size_t workspace_bytes, dcg_stream_t stream);
+
+/* ---- memory-bound operators ---------------------------------------------- */
+
+/* z = a + bias[col] and/or act(z) over a row-major [rows, cols] matrix: either
+ * output pointer may be NULL.  Replaces gpu::kernel_mat_rvect_add
+ * (src/gpu/matmul.cu:106-119) chained with an activation node. */
+int dcg_bias_act(const float* a, const float* bias, float* z_out, float* act_out,
+                 size_t rows, size_t cols, int act, float alpha, dcg_stream_t stream);
+
+/* out = act(a).  Replaces gpu::kernel_relu / relu_leaky / tanh / sigmoid
+ * (src/gpu/relu.cu:88-109, src/gpu/sigmoid.cu:124-165). */
+int dcg_act_fwd(const float* a, float* out, size_t n, int act, float alpha, dcg_stream_t stream);
+
+/* out = dout * act'(gate).  gate is the pre-activation for LEAKY/RELU and the
+ * activation OUTPUT for TANH/SIGMOID.  Replaces gpu::kernel_leaky_relu_grad,
+ * relu_grad, tanh_grad, sigmoid_grad (src/gpu/relu.cu:50-66, sigmoid.cu:31-50). */
+int dcg_act_grad(const float* gate, const float* dout, float* out, size_t n,
+                 int act, float alpha, dcg_stream_t stream);
+
+/* out[c] = sum_r a[r, c]: the conv/dense bias gradient.
+ * Replaces gpu::kernel_mat_sum_cols (src/gpu/sum.cu:111-151,238-243).
+ * workspace: dcg_colsum_workspace_bytes(rows, cols) bytes (may be 0). */
+size_t dcg_colsum_workspace_bytes(size_t rows, size_t cols);
+int dcg_colsum(const float* a, float* out, size_t rows, size_t cols,
+               void* workspace, size_t workspace_bytes, dcg_stream_t stream);
+
+/* out[r] = sum_c a[r, c].  Replaces gpu::kernel_mat_sum_rows (src/gpu/sum.cu:66-109). */
+int dcg_rowsum(const float* a, float* out, size_t rows, size_t cols, dcg_stream_t stream);
+
+/* out = a + b.  Replaces gpu::kernel_add (src/gpu/sum.cu:206-214,251-257). */
+int dcg_add(const float* a, const float* b, float* out, size_t n, dcg_stream_t stream);
+
+/* out += coeff[0] * dv, coeff a DEVICE scalar.
+ * Replaces gpu::kernel_update (src/gpu/update.cu:13-21,58-63). */
+int dcg_update(const float* dv, float* out, const float* coeff, size_t n, dcg_stream_t stream);
+
+/* Dense layers on row-major matrices (src/gpu/matmul.cu:11-86):
+ *   dcg_matmul   out[m,p] = a[m,n] b[n,p] (+ bias[p] if bias)   mat_mat_mul / mat_mul_add
+ *   dcg_matmul_tn out[m,p] = a[n,m]^T b[n,p]                    tmat_mat_mul  (dW = x^T dy)
+ *   dcg_matmul_nt out[m,p] = a[m,n] b[p,n]^T                    mat_tmat_mul  (dx = dy W^T) */
+int dcg_matmul(const float* a, const float* b, const float* bias, float* out,
+               size_t m, size_t n, size_t p, dcg_stream_t stream);
+int dcg_matmul_tn(const float* a, const float* b, float* out,
+                  size_t m, size_t n, size_t p, dcg_stream_t stream);
+int dcg_matmul_nt(const float* a, const float* b, float* out,
+                  size_t m, size_t n, size_t p, dcg_stream_t stream);
+
+/* out[0] = mean_i( max(x,0) - x*y + log(1+exp(-|x|)) ).
+ * Replaces gpu::kernel_sigmoid_cross_entropy (src/gpu/sigmoid.cu:52-100,167-172). */
+int dcg_sigmoid_xent(const float* y, const float* logits, float* out, size_t n, dcg_stream_t stream);
+/* out = (sigmoid(logits) - y) / n.  Replaces src/gpu/sigmoid.cu:102-111,174-181. */
+int dcg_sigmoid_xent_grad(const float* y, const float* logits, float* out, size_t n,
+                          dcg_stream_t stream);
+
+/* Operators the MNIST example needs to keep working (src/gpu/sum.cu, softmax.cu). */
+int dcg_mse(const float* y, const float* y_hat, float* out, size_t rows, size_t cols,
+            dcg_stream_t stream);
+int dcg_mse_grad(const float* y, const float* y_hat, float* out, size_t n, dcg_stream_t stream);
+int dcg_softmax(const float* a, float* out, size_t rows, size_t cols, dcg_stream_t stream);
+int dcg_log_softmax(const float* a, float* out, size_t rows, size_t cols, dcg_stream_t stream);
+int dcg_softmax_xent(const float* y, const float* logits, float* out, size_t rows, size_t cols,
+                     dcg_stream_t stream);
+int dcg_softmax_xent_grad(const float* y, const float* logits, float* out, size_t rows,
+                          size_t cols, dcg_stream_t stream);
+/* out[0] = number of rows whose first arg-max agrees (bit-exact integer count).
+ * Replaces gpu::kernel_argmax_acc (src/gpu/sum.cu:153-204). */
+int dcg_argmax_acc(const float* y, const float* y_hat, float* out, size_t rows, size_t cols,
+                   dcg_stream_t stream);
+
+/* ---- Adam ---------------------------------------------------------------- */
+
+/* One variable of a fused multi-tensor Adam step. */
+typedef struct dcg_adam_tensor {
+    float* p;        /* parameter, updated in place */
+    const float* g;  /* gradient */
+    const float* g2; /* optional second gradient path, added to g (NULL if none) */
+    float* m;        /* first moment, updated in place */
+    float* v;        /* second moment, updated in place */
+    size_t n;        /* element count */
+} dcg_adam_tensor;
+
+/* The reference's step size: t += 1; lr*sqrt(1-beta2^t)/(1-beta1^t)
+ * (src/gpu/update.cu:80-96).  `t` is a HOST float, as rt::Node::out2 of the
+ * adam_update node is (src/ops/adam-update.cu:45-48). */
+float dcg_adam_lr_t(float* t_host, float lr, float beta1, float beta2);
+
+/* For every tensor:  g' = grad_scale*(g [+ g2]);  m = b1*m + (1-b1)*g';
+ * v = b2*v + (1-b2)*g'*g';  p = p - lr_t*m/(sqrt(v)+eps).
+ * One launch replaces the moment_update / moment_update2 / adam_update triple
+ * of every variable (src/gpu/update.cu:23-54,65-96).  `tensors` is a HOST array. */
+int dcg_adam_multi(const dcg_adam_tensor* tensors, int count,
+                   float lr_t, float beta1, float beta2, float eps, float grad_scale,
+                   dcg_stream_t stream);
+
+/* ---- node-level backend: the drop-in boundary ---------------------------- */
+
+/* The operand record of one runtime instruction: field for field what the
+ * reference's kernels read from rt::Node (src/runtime/node.hh:215-243).  `type`
+ * uses the rt::Node::OP_* numbering (src/runtime/node.hh:16-54). */
+typedef struct dcg_node {
+    int type;
+    const float* in1;
+    const float* in2;
+    const float* in3;
+    float* out1;
+    float* out2; /* adam_update: HOST pointer to the step counter t */
+    float cons1, cons2, cons3, cons4;
+    size_t len1, len2, len3;
+    int intconst[2];
+    int intconst2[2];
+    int sizes1[4];
+    int sizes2[4];
+    int sizes3[4];
+    int int_cons1, int_cons2;
+    float alpha_leaky;
+    unsigned flags; /* DCG_NODE_* bits; 0 when translated from an rt::Node */
+} dcg_node;
+
+#define DCG_NODE_OUT_DEAD 1u /* out1 is read by nobody but the next fusable node: a fused
+                                kernel may skip storing it */
+
+#define DCG_OP_MAT_MAT_MUL 0
+#define DCG_OP_MAT_RVECT_ADD 1
+#define DCG_OP_SIGMOID 2
+#define DCG_OP_MSE 3
+#define DCG_OP_SOFTMAX 4
+#define DCG_OP_LOG_SOFTMAX 5
+#define DCG_OP_SOFTMAX_CROSS_ENTROPY 6
+#define DCG_OP_CONV2D 7
+#define DCG_OP_RELU 8
+#define DCG_OP_RELU_LEAKY 9
+#define DCG_OP_TANH 10
+#define DCG_OP_MSE_GRAD 11
+#define DCG_OP_SIGMOID_GRAD 12
+#define DCG_OP_MAT_MUL_ADD 13
+#define DCG_OP_TMAT_MAT_MUL 14
+#define DCG_OP_MAT_TMAT_MUL 15
+#define DCG_OP_MAT_SUM_ROWS 16
+#define DCG_OP_MAT_SUM_COLS 17
+#define DCG_OP_SOFTMAX_CROSS_ENTROPY_GRAD 18
+#define DCG_OP_RELU_GRAD 19
+#define DCG_OP_CONV2D_BIAS_ADD 20
+#define DCG_OP_UPDATE 21
+#define DCG_OP_SIGMOID_CROSS_ENTROPY 22
+#define DCG_OP_SIGMOID_CROSS_ENTROPY_GRAD 23
+#define DCG_OP_CONV2D_INPUT_GRAD 24
+#define DCG_OP_CONV2D_KERNEL_GRAD 25
+#define DCG_OP_ARGMAX_ACC 26
+#define DCG_OP_MOMENT_UPDATE 27
+#define DCG_OP_MOMENT_UPDATE2 28
+#define DCG_OP_ADAM_UPDATE 29
+#define DCG_OP_LEAKY_RELU_GRAD 30
+#define DCG_OP_CONV2D_BIAS_ADD_GRAD 31
+#define DCG_OP_TANH_GRAD 32
+#define DCG_OP_CONV2D_TRANSPOSE 33
+#define DCG_OP_CONV2D_TRANSPOSE_INPUT_GRAD 34
+#define DCG_OP_CONV2D_TRANSPOSE_KERNEL_GRAD 35
+#define DCG_OP_ADD 36
+#define DCG_OP_COUNT 37
+
+/* Execution context of the node-level backend: stream, precision, scratch. */
+typedef struct dcg_context dcg_context;
+
+/* workspace may be NULL with workspace_bytes 0: the context then owns a scratch
+ * buffer it grows on demand with cudaMalloc (what src/gpu/conv2d_gemm.hh does on
+ * every call); a caller-provided buffer is never reallocated. */
+int dcg_context_create(dcg_context** out, int precision, void* workspace, size_t workspace_bytes,
+                       dcg_stream_t stream);
+void dcg_context_destroy(dcg_context* ctx);
+int dcg_context_set_precision(dcg_context* ctx, int precision);
+/* Number of kernels launched through this context so far. */
+uint64_t dcg_context_launch_count(const dcg_context* ctx);
+
+/* Executes one node: the function gpu::kernels_list[node->type] stands for
+ * (src/gpu/kernels.cu:20-64).  Asynchronous on the context's stream. */
+int dcg_run_node(dcg_context* ctx, const dcg_node* node);
+
+/* Executes nodes in order, the body of gpu::run (src/gpu/runner.cu:10-18)
+ * without its per-node device synchronisation.  With fuse != 0 adjacent nodes
+ * are combined: conv -> bias add -> activation into the conv epilogue,
+ * input-gradient -> activation-gradient likewise, and every
+ * moment_update / moment_update2 / adam_update triple of the list into one
+ * multi-tensor launch.  Results are identical to unfused execution except for
+ * buffers flagged DCG_NODE_OUT_DEAD. */
+int dcg_run_nodes(dcg_context* ctx, const dcg_node* nodes, int count, int fuse);
+
+/* ---- diagnostics --------------------------------------------------------- */
+const char* dcg_last_error(void);
+/* Library version and the architecture the kernels were built for ("sm_100a"). */
+const char* dcg_build_info(void);
+/* Kernels launched by this library since it was loaded (all contexts, all threads). */
+uint64_t dcg_launches_total(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DCGAN_B200_H */

@@ -241,6 +241,7 @@ class Port(_Base):
 
     def conv2d_input_grad(self, dy, k, stride, in_hw):
         dy, k = _f32(dy), _f32(k)
+        in_hw = (int(in_hw[0]), int(in_hw[1]))
         N, Ho, Wo, O = dy.shape
         KH, KW, C, O2 = k.shape
         assert O == O2
@@ -251,6 +252,7 @@ class Port(_Base):
 
     def conv2d_kernel_grad(self, dy, x, stride, pad_hw):
         dy, x = _f32(dy), _f32(x)
+        pad_hw = (int(pad_hw[0]), int(pad_hw[1]))
         N, Ho, Wo, O = dy.shape
         N2, H, W, C = x.shape
         assert N == N2

@@ -1,0 +1,184 @@
+"""GPU parity of the three convolution entry points (through the C ABI) against the CPU oracle.
+
+DCG_PREC_FP32 keeps the reference CPU's summation order with unfused multiply/add and must
+reproduce the oracle bit for bit.  DCG_PREC_TF32 (tcgen05, fp32 accumulate) must stay within
+1e-2 * max|ref| per output tensor - the tolerance stated for the TF32 tensor-core path.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import seeded
+
+pytestmark = pytest.mark.gpu
+
+TF32_TOL = 1e-2  # max abs error <= TF32_TOL * max|ref|
+
+# N, H, W, C, K, O, stride.  Small / ragged shapes the reference's unit tests use, odd sizes,
+# channel counts below and above one 32-wide K chunk, and DCGAN layer shapes at batch 2.
+SHAPES = [
+    (2, 4, 4, 2, 2, 2, 2), (2, 3, 5, 3, 3, 2, 2), (1, 7, 9, 3, 5, 4, 2), (2, 6, 6, 2, 3, 3, 1),
+    (3, 3, 5, 1, 2, 3, 1), (2, 9, 9, 5, 5, 2, 2), (1, 1, 1, 1, 1, 1, 1),
+    (2, 8, 8, 4, 5, 8, 2), (2, 16, 16, 32, 5, 64, 2), (2, 12, 20, 36, 5, 40, 2),
+    (2, 64, 64, 3, 5, 64, 2), (2, 32, 32, 64, 5, 128, 2), (2, 16, 16, 128, 5, 256, 2),
+    (2, 8, 8, 256, 5, 512, 2),
+]
+
+
+def _check(got, ref, prec, pkg, what):
+    got = got.cpu().numpy()
+    assert got.shape == ref.shape, (what, got.shape, ref.shape)
+    if prec == pkg.PREC_FP32:
+        assert np.array_equal(got, ref), "%s: fp32 path differs from the oracle, max err %g" % (
+            what, np.abs(got - ref).max())
+    else:
+        lim = TF32_TOL * max(np.abs(ref).max(), 1e-30)
+        err = np.abs(got - ref).max()
+        assert err <= lim, "%s: max err %g > %g" % (what, err, lim)
+
+
+@pytest.mark.parametrize("prec_name", ["fp32", "tf32"])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_conv_fwd_dx_dk(pkg, dev, orc, shape, prec_name):
+    F = pkg.functional
+    prec = pkg.PREC_FP32 if prec_name == "fp32" else pkg.PREC_TF32
+    N, H, W, C, K, O, s = shape
+    x = seeded((N, H, W, C), 234)
+    k = seeded((K, K, C, O), 235) * np.float32(0.1)
+    pad = (oracle.same_pad(H, K, s), oracle.same_pad(W, K, s))
+    y_ref = orc.conv2d(x, k, (s, s))
+    dy = seeded(y_ref.shape, 236)
+    xd, kd, dyd = (torch.from_numpy(a).to(dev) for a in (x, k, dy))
+    y = F.conv2d_fwd(xd, kd, (s, s), precision=prec)
+    dx = F.conv2d_dx(dyd, kd, (H, W), (s, s), precision=prec)
+    dk = F.conv2d_dk(xd, dyd, (K, K), (s, s), precision=prec)
+    torch.cuda.synchronize()
+    _check(y, y_ref, prec, pkg, "fwd")
+    _check(dx, orc.conv2d_input_grad(dy, k, s, (H, W)), prec, pkg, "dx")
+    _check(dk, orc.conv2d_kernel_grad(dy, x, s, pad), prec, pkg, "dk")
+
+
+@pytest.mark.parametrize("prec_name", ["fp32", "tf32"])
+def test_golden_reference_cases(pkg, dev, golden, prec_name):
+    """The reference's own unit-test tensors (tests/test_conv2d*.cu) through the C ABI."""
+    F = pkg.functional
+    prec = pkg.PREC_FP32 if prec_name == "fp32" else pkg.PREC_TF32
+    for case in ("conv2d", "conv2d_padding"):
+        x, k = (torch.from_numpy(golden[case + "/" + n]).to(dev) for n in ("x", "k"))
+        _check(F.conv2d_fwd(x, k, precision=prec), golden[case + "/y"], prec, pkg, case)
+    for case in ("conv2d_grad", "conv2d_padding_grad"):
+        x, k, dy = (torch.from_numpy(golden[case + "/" + n]).to(dev) for n in ("x", "k", "dy_hat"))
+        _check(F.conv2d_dx(dy, k, x.shape[1:3], precision=prec), golden[case + "/dx"], prec, pkg, case + " dx")
+        _check(F.conv2d_dk(x, dy, k.shape[:2], precision=prec), golden[case + "/dk"], prec, pkg, case + " dk")
+    # conv2d_transpose = dx of the mirrored conv; its gradients = fwd / dk with roles swapped
+    c = "conv2d_transpose_grad"
+    x, k, dy = (torch.from_numpy(golden[c + "/" + n]).to(dev) for n in ("x", "k", "dy_hat"))
+    _check(F.conv2d_dx(x, k, (8, 8), pad=(0, 0), precision=prec), golden[c + "/y_hat"], prec, pkg, "convT fwd")
+    _check(F.conv2d_fwd(dy, k, pad=(0, 0), precision=prec), golden[c + "/dx"], prec, pkg, "convT dx")
+    _check(F.conv2d_dk(dy, x, (2, 2), pad=(0, 0), precision=prec), golden[c + "/dk"], prec, pkg, "convT dk")
+
+
+@pytest.mark.parametrize("prec_name", ["fp32", "tf32"])
+@pytest.mark.parametrize("shape", [(2, 9, 9, 5, 5, 6, 2), (2, 16, 16, 32, 5, 64, 2)])
+def test_fused_epilogues(pkg, dev, orc, shape, prec_name):
+    F = pkg.functional
+    prec = pkg.PREC_FP32 if prec_name == "fp32" else pkg.PREC_TF32
+    N, H, W, C, K, O, s = shape
+    x = seeded((N, H, W, C), 301)
+    k = seeded((K, K, C, O), 302) * np.float32(0.1)
+    b = seeded((O,), 303)
+    raw_ref = orc.conv2d(x, k, (s, s))
+    z_ref = orc.mvrow_add(raw_ref, b)
+    xd, kd, bd = (torch.from_numpy(a).to(dev) for a in (x, k, b))
+    for act, fn in ((pkg.ACT_LEAKY, lambda a: orc.vect_relu_leaky(a, 0.2)), (pkg.ACT_RELU, orc.vect_relu),
+                    (pkg.ACT_TANH, orc.vect_tanh), (pkg.ACT_SIGMOID, orc.vect_sigmoid), (pkg.ACT_NONE, lambda a: a)):
+        raw = torch.empty(raw_ref.shape, device=dev)
+        z = torch.empty(raw_ref.shape, device=dev)
+        ep = F.make_epilogue(bias=bd, act=act, alpha=0.2, pre_act=z, raw_out=raw)
+        y = F.conv2d_fwd(xd, kd, (s, s), epilogue=ep, precision=prec)
+        torch.cuda.synchronize()
+        _check(raw, raw_ref, prec, pkg, "raw")
+        _check(z, z_ref, prec, pkg, "pre_act")
+        a_ref = fn(z_ref)
+        if prec == pkg.PREC_FP32 and act in (pkg.ACT_TANH, pkg.ACT_SIGMOID):
+            # device expf is not glibc's: a few ulp on the exponential
+            np.testing.assert_allclose(y.cpu().numpy(), a_ref, rtol=0, atol=2e-6)
+        else:
+            _check(y, a_ref, prec, pkg, "act %d" % act)
+
+    # input gradient gated by the derivative of the previous layer's activation
+    dy = seeded(raw_ref.shape, 304)
+    zprev = seeded((N, H, W, C), 305)
+    dyd, zd = torch.from_numpy(dy).to(dev), torch.from_numpy(zprev).to(dev)
+    dx_ref = orc.conv2d_input_grad(dy, k, s, (H, W))
+    for gact, fn in ((pkg.ACT_LEAKY, lambda g, d: orc.leaky_relu_grad(g, d, 0.2)), (pkg.ACT_RELU, orc.relu_grad),
+                     (pkg.ACT_TANH, orc.tanh_grad)):
+        raw = torch.empty(dx_ref.shape, device=dev)
+        ep = F.make_epilogue(gate=zd, gate_act=gact, gate_alpha=0.2, raw_out=raw)
+        dx = F.conv2d_dx(dyd, kd, (H, W), (s, s), epilogue=ep, precision=prec)
+        torch.cuda.synchronize()
+        _check(raw, dx_ref, prec, pkg, "dx raw")
+        ref_g = fn(zprev, dx_ref)
+        if prec == pkg.PREC_FP32:
+            assert np.array_equal(dx.cpu().numpy(), ref_g)
+        else:
+            _check(dx, ref_g, prec, pkg, "gated dx")
+
+
+def test_transposed_conv_roles(pkg, dev, orc):
+    """Generator layer [2,4,4,64] -> [2,8,8,32] (5x5, stride 2, SAME): forward is the dx entry
+    point, its input gradient the fwd entry point, its kernel gradient dk with roles swapped."""
+    F = pkg.functional
+    x = seeded((2, 4, 4, 64), 401)
+    k = seeded((5, 5, 32, 64), 402) * np.float32(0.05)   # [kh, kw, Cout, Cin]
+    dy = seeded((2, 8, 8, 32), 403)
+    xd, kd, dyd = (torch.from_numpy(a).to(dev) for a in (x, k, dy))
+    for prec in (pkg.PREC_FP32, pkg.PREC_TF32):
+        y = F.conv2d_dx(xd, kd, (8, 8), precision=prec)
+        dx = F.conv2d_fwd(dyd, kd, precision=prec)
+        dk = F.conv2d_dk(dyd, xd, (5, 5), precision=prec)
+        torch.cuda.synchronize()
+        _check(y, orc.conv2d_transpose(x, k, (2, 8, 8, 32), 2), prec, pkg, "convT")
+        _check(dx, orc.conv2d_transpose_input_grad(dy, k, 2, (4, 4)), prec, pkg, "convT dx")
+        _check(dk, orc.conv2d_transpose_kernel_grad(dy, x, 2, (5, 5)), prec, pkg, "convT dk")
+
+
+@pytest.mark.parametrize("layer", [(64, 32, 32, 64, 128), (64, 16, 16, 128, 256), (64, 8, 8, 256, 512),
+                                   (64, 64, 64, 3, 64)])
+def test_full_batch_layers_tf32_vs_fp32_path(pkg, dev, layer):
+    """Batch-64 DCGAN layers: too slow for the scalar oracle, so the tensor path is compared with
+    the fp32 CUDA-core path (itself bit-exact with the oracle at small sizes), and the three
+    operators are tied together by the adjoint identity <conv(x,k),dy> = <x,dx> = <k,dk>."""
+    F = pkg.functional
+    N, H, W, C, O = layer
+    g = torch.Generator(device="cpu").manual_seed(5)
+    x = (torch.rand((N, H, W, C), generator=g) * 2 - 1).to(dev)
+    k = (torch.randn((5, 5, C, O), generator=g) * 0.02).to(dev)
+    dy = (torch.rand((N, H // 2, W // 2, O), generator=g) * 2 - 1).to(dev)
+    outs = {}
+    for prec in (pkg.PREC_FP32, pkg.PREC_TF32):
+        outs[prec] = (F.conv2d_fwd(x, k, precision=prec), F.conv2d_dx(dy, k, (H, W), precision=prec),
+                      F.conv2d_dk(x, dy, (5, 5), precision=prec))
+    torch.cuda.synchronize()
+    for name, a, b in zip(("fwd", "dx", "dk"), outs[pkg.PREC_FP32], outs[pkg.PREC_TF32]):
+        lim = TF32_TOL * a.abs().max().item()
+        assert (a - b).abs().max().item() <= lim, name
+    y, dx, dk = (t.double() for t in outs[pkg.PREC_TF32])
+    lhs = (y * dy.double()).sum().item()
+    assert abs(lhs - (dx * x.double()).sum().item()) <= 2e-3 * abs(lhs) + 1e-3
+    assert abs(lhs - (dk * k.double()).sum().item()) <= 2e-3 * abs(lhs) + 1e-3
+
+
+def test_deterministic(pkg, dev):
+    """Two runs of every operator give identical bits (fixed-order split-K reduction)."""
+    F = pkg.functional
+    g = torch.Generator(device="cpu").manual_seed(9)
+    x = (torch.rand((8, 16, 16, 128), generator=g) * 2 - 1).to(dev)
+    k = (torch.randn((5, 5, 128, 256), generator=g) * 0.02).to(dev)
+    dy = (torch.rand((8, 8, 8, 256), generator=g) * 2 - 1).to(dev)
+    a = (F.conv2d_fwd(x, k), F.conv2d_dx(dy, k, (16, 16)), F.conv2d_dk(x, dy, (5, 5)))
+    b = (F.conv2d_fwd(x, k), F.conv2d_dx(dy, k, (16, 16)), F.conv2d_dk(x, dy, (5, 5)))
+    torch.cuda.synchronize()
+    for u, v in zip(a, b):
+        assert torch.equal(u, v)
