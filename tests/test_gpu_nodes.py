@@ -59,7 +59,7 @@ def test_golden_graphs_through_nodes(pkg, dev, golden):
     ctx.close()
 
 
-def _layer_nodes(N, bufs, dead=False):
+def _layer_nodes(N, bufs):
     """One discriminator layer forward and backward, lowered like dcgan/main.cu:123-168 + autodiff:
     conv2d -> mat_rvect_add -> relu_leaky ; leaky_relu_grad -> (mat_sum_cols, kernel grad, input grad
     -> leaky_relu_grad of the layer below)."""
@@ -74,8 +74,6 @@ def _layer_nodes(N, bufs, dead=False):
         N.op_mat_rvect_add(b["conv"], b["bias"], b["z"], rows, o),
         N.op_relu_leaky(b["z"], b["a"], rows * o, 0.2),
     ]
-    if dead:
-        fwd[0].flags = pkg_flags_dead
     bwd = [
         N.op_leaky_relu_grad(b["z"], b["da"], b["dz"], 0.2, rows * o),
         N.op_mat_sum_cols(b["dz"], b["db"], rows, o),
@@ -84,9 +82,6 @@ def _layer_nodes(N, bufs, dead=False):
         N.op_leaky_relu_grad(b["zprev"], b["dx"], b["dzprev"], 0.2, b["x"].numel()),
     ]
     return fwd, bwd
-
-
-pkg_flags_dead = 1
 
 
 @pytest.mark.parametrize("prec_name", ["fp32", "tf32"])
@@ -174,8 +169,9 @@ def test_adam_triples_fuse_into_one_launch(pkg, dev, orc):
             gs = [_t(seeded((n,), 930 + 10 * step + i), dev) for i, n in enumerate(sizes)]
             nodes = []
             for p, g, m, v, t in zip(ps, gs, ms, vs, ts):
-                nodes += [N.op_moment_update(m, g, b1, 1 - b1, p.numel()),
-                          N.op_moment_update2(v, g, b2, 1 - b2, p.numel()),
+                # 1 - beta is formed in fp32, as AdamOptimizer::minimize does with its dbl_t members
+                nodes += [N.op_moment_update(m, g, b1, float(np.float32(1) - np.float32(b1)), p.numel()),
+                          N.op_moment_update2(v, g, b2, float(np.float32(1) - np.float32(b2)), p.numel()),
                           N.op_adam_update(p, t, m, v, lr, b1, b2, eps, p.numel())]
             before = ctx.launch_count()
             ctx.run(nodes, fuse=fuse)
