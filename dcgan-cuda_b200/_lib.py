@@ -97,6 +97,7 @@ SIGNATURES = {
     "dcg_context_launch_count": (ctypes.c_uint64, [_P]),
     "dcg_run_node": (c_int, [_P, ctypes.POINTER(Node)]),
     "dcg_run_nodes": (c_int, [_P, ctypes.POINTER(Node), c_int, c_int]),
+    "dcg_device_status": (c_int, []),
     "dcg_last_error": (ctypes.c_char_p, []),
     "dcg_build_info": (ctypes.c_char_p, []),
     "dcg_launches_total": (ctypes.c_uint64, []),

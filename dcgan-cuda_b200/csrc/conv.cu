@@ -23,6 +23,15 @@ int conv_check_desc(const dcg_conv_desc* d, const char* who)
     return DCG_OK;
 }
 
+// The tensor path moves tiles with TMA and 128-bit epilogue accesses: every tensor it touches
+// must start on a 16-byte boundary.
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static bool epilogue_aligned(const EpilogueArgs& e)
+{
+    return aligned16(e.raw_out) && aligned16(e.bias) && aligned16(e.pre_act) && aligned16(e.gate);
+}
+
 static int check_precision(int precision, const char* who)
 {
     DCG_CHECK_ARG(precision == DCG_PREC_TF32 || precision == DCG_PREC_3XTF32 ||
@@ -54,7 +63,8 @@ extern "C" int dcg_conv2d_fwd(const dcg_conv_desc* desc, const float* x, const f
     if ((st = check_precision(precision, "dcg_conv2d_fwd"))) return st;
     DCG_CHECK_ARG(x && k && y, "dcg_conv2d_fwd: null tensor pointer");
     const EpilogueArgs e = make_epilogue(ep);
-    if (precision != DCG_PREC_FP32 && conv_tc_supported(*desc, kConvFwd))
+    if (precision != DCG_PREC_FP32 && conv_tc_supported(*desc, kConvFwd) && aligned16(x) && aligned16(k) &&
+        aligned16(y) && epilogue_aligned(e))
         return conv_tc_fwd(*desc, x, k, y, e, workspace, workspace_bytes, as_stream(stream));
     return conv_fwd_generic(*desc, x, k, y, e, as_stream(stream));
 }
@@ -68,7 +78,8 @@ extern "C" int dcg_conv2d_dx(const dcg_conv_desc* desc, const float* dy, const f
     if ((st = check_precision(precision, "dcg_conv2d_dx"))) return st;
     DCG_CHECK_ARG(dy && k && dx, "dcg_conv2d_dx: null tensor pointer");
     const EpilogueArgs e = make_epilogue(ep);
-    if (precision != DCG_PREC_FP32 && conv_tc_supported(*desc, kConvDx))
+    if (precision != DCG_PREC_FP32 && conv_tc_supported(*desc, kConvDx) && aligned16(dy) && aligned16(k) &&
+        aligned16(dx) && epilogue_aligned(e))
         return conv_tc_dx(*desc, dy, k, dx, e, workspace, workspace_bytes, as_stream(stream));
     return conv_dx_generic(*desc, dy, k, dx, e, as_stream(stream));
 }
@@ -81,7 +92,8 @@ extern "C" int dcg_conv2d_dk(const dcg_conv_desc* desc, const float* x, const fl
     if (st) return st;
     if ((st = check_precision(precision, "dcg_conv2d_dk"))) return st;
     DCG_CHECK_ARG(x && dy && dk, "dcg_conv2d_dk: null tensor pointer");
-    if (precision != DCG_PREC_FP32 && conv_tc_supported(*desc, kConvDk))
+    if (precision != DCG_PREC_FP32 && conv_tc_supported(*desc, kConvDk) && aligned16(x) && aligned16(dy) &&
+        aligned16(dk))
         return conv_tc_dk(*desc, x, dy, dk, workspace, workspace_bytes, as_stream(stream));
     return conv_dk_generic(*desc, x, dy, dk, as_stream(stream));
 }

@@ -1,10 +1,845 @@
-// placeholder until the tcgen05 kernels land
+// tcgen05 implicit-GEMM convolution kernels (TF32 operands, fp32 accumulation in TMEM).
+//
+// One kernel template covers the three operators; each is a GEMM D[M x N] += A[M x K] B[K x N]
+// whose operand tiles are fetched straight from the NHWC / HWIO tensors by TMA - no im2col
+// buffer, no zero-inserted gradient, no weight repacking ever exists in memory:
+//
+//   FWD  y[pix, o]      = sum_{tap, c} x[pix*s + tap - pad, c] * k[tap, c, o]
+//        A: x through a 4-D tiled map with traversal stride s, box (32 c, TW, TH, TN) -> 128 output
+//           pixels x 32 channels, K-major; taps that fall outside x are zero-filled by TMA, which is
+//           the reference's "skip out-of-range taps" (src/cpu/ops.hxx:236-243).
+//        B: k as [tap][c][o], o contiguous -> MN-major tile (32 c x BN o).
+//   DX   dx[pix, c]     = sum_{tap, o} dy[(pix + pad - tap)/s, o] * k[tap, c, o]
+//        split by output parity class (pix mod s): inside a class the taps with matching parity
+//        read a dense, stride-1 window of dy, so none of the 4x multiplications by inserted zeros
+//        of the reference's formulation (src/gpu/conv2d_gemm.hh:396-412) is ever issued.
+//        A: dy, box (32 o, TW, TH, TN), K-major.  B: k rows c, 32 o contiguous, K-major.
+//   DK   dk[tap, c, o]  = sum_{pix} x[pix*s + tap - pad, c] * dy[pix, o]
+//        reduction over pixels; both operands have the reduction index outermost in memory, so
+//        both tiles are MN-major (32 pixels x 128 channels / BN channels), 5-D maps.
+//
+// CTA = 192 threads: warp 0 issues TMA, warp 1 owns TMEM and issues tcgen05.mma, warps 2-5 drain the
+// accumulator (tcgen05.ld) through the fused epilogue (raw / bias / pre-activation / activation /
+// activation-gradient gate) into HBM.  A ring of smem stages (A 16 KB + B BN*128 B, 128-byte
+// swizzle) is handed over with mbarriers: TMA complete_tx -> MMA, tcgen05.commit -> TMA.
+// Split-K partitions write fp32 partials to scratch; a second kernel adds them in split order
+// (deterministic) and applies the epilogue.
+//
+// Every wait is bounded: a barrier that does not complete within ~1 s makes the waiting role
+// record an error code in a device status word and leave; TMEM is always released.
+#include <cuda.h>
+
+#include <cstdlib>
+#include <mutex>
+
 #include "common.cuh"
 #include "conv.cuh"
+
 namespace dcg {
-bool conv_tc_supported(const dcg_conv_desc&, int) { return false; }
-size_t conv_tc_workspace(const dcg_conv_desc&, int) { return 0; }
-int conv_tc_fwd(const dcg_conv_desc&, const float*, const float*, float*, const EpilogueArgs&, void*, size_t, cudaStream_t) { return fail(DCG_ERR_UNSUPPORTED, "tensor path not built"); }
-int conv_tc_dx(const dcg_conv_desc&, const float*, const float*, float*, const EpilogueArgs&, void*, size_t, cudaStream_t) { return fail(DCG_ERR_UNSUPPORTED, "tensor path not built"); }
-int conv_tc_dk(const dcg_conv_desc&, const float*, const float*, float*, void*, size_t, cudaStream_t) { return fail(DCG_ERR_UNSUPPORTED, "tensor path not built"); }
+namespace {
+
+constexpr int BM = 128;                 // accumulator rows (TMEM lanes)
+constexpr int BK = 32;                  // K elements per pipeline stage (one 128-byte swizzle row)
+constexpr int A_STAGE_BYTES = BM * BK * 4;
+constexpr int kThreads = 192;
+constexpr int kMaxSmem = 227 * 1024;
+constexpr long long kWaitCycles = 2000000000LL;  // ~1 s at 2 GHz
+
+enum Mode { MODE_FWD = 0, MODE_DX = 1, MODE_DK = 2 };
+
+// Error word: [0] code (0 = ok), [1] blockIdx, [2] role, [3] stage.  Read by dcg_device_status().
+__device__ int g_tc_status[4];
+
+struct Params {
+    int N, H, W, C, KH, KW, O, Ho, Wo, sh, sw, pt, pl;
+    int TW, TH, TN;               // pixel-tile extents (FWD/DX: the 128 rows; DK: the 32-pixel K step)
+    int tiles_w, tiles_h, tiles_n;  // pixel tiles along each axis
+    int m_tiles;                  // DK: 128-row tiles along the M channel axis
+    int n_tiles;                  // BN-column tiles along the N channel axis
+    int bn;                       // accumulator columns, multiple of 16, <= 256
+    int splits;                   // K partitions
+    int kchunks;                  // 32-wide chunks along the contracted channel axis (FWD: C, DX: O)
+    int swap;                     // DK: M axis is o (A from dy, B from x)
+    int stages;                   // pipeline depth
+    int direct;                   // 1: epilogue + final store, 0: raw partial to scratch
+    float* out;                   // final tensor (direct) or scratch base
+    unsigned long long out_elems; // elements of the output tensor (scratch stride per split)
+    EpilogueArgs ep;
+};
+
+// ---- PTX wrappers ----------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
+{
+    return (uint32_t)__cvta_generic_to_shared(p);
 }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  Returns false (after recording the failure) if the phase never completes.
+__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int role, int stage)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (clock64() - t0 > kWaitCycles) break;
+    }
+    if (atomicCAS(&g_tc_status[0], 0, 1) == 0) {
+        g_tc_status[1] = blockIdx.x;
+        g_tc_status[2] = role;
+        g_tc_status[3] = stage;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3, int c4)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                                 uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t* r)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t* r)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+
+// Shared-memory operand descriptor (tcgen05): start address, leading / stride byte offsets in
+// 16-byte units, version 1, swizzle layout.  Layout 2 = 128-byte swizzle of 16-byte chunks (what
+// K-major tiles use); layout 1 = 128-byte swizzle of 32-byte chunks, the only swizzled layout the
+// tensor core accepts for MN-major 32-bit (TF32) operands.
+constexpr uint32_t kLayoutSw128 = 2, kLayoutSw128Base32 = 1;
+
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                   uint32_t layout)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version
+    d |= (uint64_t)layout << 61;
+    return d;
+}
+
+// Instruction descriptor: fp32 accumulator, TF32 operands, operand majors, N and M.
+__device__ __forceinline__ uint32_t make_idesc(int a_mn_major, int b_mn_major, int n, int m)
+{
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)a_mn_major << 15) |
+           ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// ---- the kernel ---------------------------------------------------------------------------------
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ Params p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int b_stage_bytes = p.bn * BK * 4;
+    const uint32_t a_base = smem_base;
+    const uint32_t b_base = a_base + (uint32_t)p.stages * A_STAGE_BYTES;
+    const uint32_t bar_base = b_base + (uint32_t)p.stages * b_stage_bytes;
+    // barriers: full[stages], empty[stages], tmem_full; then the TMEM base address word
+    const uint32_t full_bar = bar_base;
+    const uint32_t empty_bar = bar_base + 8u * p.stages;
+    const uint32_t tmem_full_bar = bar_base + 16u * p.stages;
+    const uint32_t tmem_slot = tmem_full_bar + 8u;
+    uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // ---- decode this CTA's work item -------------------------------------------------------------
+    // blockIdx.x = ((group * m_count + m) * n_tiles + n) * splits + split, where group is the parity
+    // class (DX), the kernel tap (DK) or absent (FWD), and m a pixel tile (FWD/DX) or channel tile (DK).
+    int rem = blockIdx.x;
+    const int split = rem % p.splits; rem /= p.splits;
+    const int n_tile = rem % p.n_tiles; rem /= p.n_tiles;
+    int m_count;
+    if (MODE == MODE_DK) m_count = p.m_tiles;
+    else m_count = p.tiles_w * p.tiles_h * p.tiles_n;
+    const int m_tile = rem % m_count;
+    const int group = rem / m_count;
+
+    // pixel-tile origin (FWD/DX)
+    int j0 = 0, i0 = 0, n0 = 0;
+    if (MODE != MODE_DK) {
+        j0 = (m_tile % p.tiles_w) * p.TW;
+        i0 = ((m_tile / p.tiles_w) % p.tiles_h) * p.TH;
+        n0 = (m_tile / (p.tiles_w * p.tiles_h)) * p.TN;
+    }
+    // DX: parity class and its taps; DK: the kernel tap
+    int ph = 0, pw = 0, rh = 0, rw = 0, eh = 0, ew = 0, taps_h = 1, taps_w = 1, tap_di = 0, tap_dj = 0;
+    if (MODE == MODE_DX) {
+        ph = group / p.sw; pw = group % p.sw;
+        rh = (ph + p.pt) % p.sh; rw = (pw + p.pl) % p.sw;
+        eh = (ph + p.pt) / p.sh; ew = (pw + p.pl) / p.sw;
+        taps_h = rh < p.KH ? (p.KH - rh + p.sh - 1) / p.sh : 0;
+        taps_w = rw < p.KW ? (p.KW - rw + p.sw - 1) / p.sw : 0;
+    } else if (MODE == MODE_DK) {
+        tap_di = group / p.KW; tap_dj = group % p.KW;
+    }
+    // K-stage range of this split
+    int total_stages;
+    if (MODE == MODE_FWD) total_stages = p.KH * p.KW * p.kchunks;
+    else if (MODE == MODE_DX) total_stages = taps_h * taps_w * p.kchunks;
+    else total_stages = p.tiles_w * p.tiles_h * p.tiles_n;
+    const int q0 = (int)((long long)total_stages * split / p.splits);
+    const int q1 = (int)((long long)total_stages * (split + 1) / p.splits);
+    const int nq = q1 - q0;
+
+    // ---- one-time setup ----------------------------------------------------------------------------
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(full_bar + 8u * s, 1);
+            mbar_init(empty_bar + 8u * s, 1);
+        }
+        mbar_init(tmem_full_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    }
+    int tmem_cols = 32;
+    while (tmem_cols < p.bn) tmem_cols <<= 1;
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        // ===== TMA producer =====
+        if (lane == 0) {
+            const uint32_t tx_bytes = (uint32_t)(A_STAGE_BYTES + b_stage_bytes);
+            for (int it = 0; it < nq; ++it) {
+                const int s = it % p.stages;
+                const uint32_t phase = (uint32_t)(it / p.stages) & 1u;
+                if (!mbar_wait(empty_bar + 8u * s, phase ^ 1u, 0, it)) break;
+                const uint32_t fb = full_bar + 8u * s;
+                mbar_expect_tx(fb, tx_bytes);
+                const uint32_t a_dst = a_base + (uint32_t)s * A_STAGE_BYTES;
+                const uint32_t b_dst = b_base + (uint32_t)s * b_stage_bytes;
+                const int q = q0 + it;
+                if (MODE == MODE_FWD) {
+                    const int tap = q / p.kchunks, cc = q % p.kchunks;
+                    const int di = tap / p.KW, dj = tap % p.KW;
+                    tma_load_4d(a_dst, &map_a, fb, cc * BK, p.sw * j0 + dj - p.pl, p.sh * i0 + di - p.pt, n0);
+                    tma_load_4d(b_dst, &map_b, fb, 0, cc * BK, tap, n_tile * (p.bn / 32));
+                } else if (MODE == MODE_DX) {
+                    const int t = q / p.kchunks, oc = q % p.kchunks;
+                    const int th = t / taps_w, tw = t % taps_w;
+                    const int di = rh + p.sh * th, dj = rw + p.sw * tw;
+                    tma_load_4d(a_dst, &map_a, fb, oc * BK, j0 + ew - tw, i0 + eh - th, n0);
+                    tma_load_4d(b_dst, &map_b, fb, oc * BK, n_tile * p.bn, dj, di);
+                } else {
+                    const int pj = (q % p.tiles_w) * p.TW;
+                    const int pi = ((q / p.tiles_w) % p.tiles_h) * p.TH;
+                    const int pn = (q / (p.tiles_w * p.tiles_h)) * p.TN;
+                    const int xw = p.sw * pj + tap_dj - p.pl, xh = p.sh * pi + tap_di - p.pt;
+                    if (!p.swap) {   // A: x (rows c), B: dy (cols o)
+                        tma_load_5d(a_dst, &map_a, fb, 0, xw, xh, pn, m_tile * (BM / 32));
+                        tma_load_5d(b_dst, &map_b, fb, 0, pj, pi, pn, n_tile * (p.bn / 32));
+                    } else {         // A: dy (rows o), B: x (cols c)
+                        tma_load_5d(a_dst, &map_a, fb, 0, pj, pi, pn, m_tile * (BM / 32));
+                        tma_load_5d(b_dst, &map_b, fb, 0, xw, xh, pn, n_tile * (p.bn / 32));
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ===== MMA issuer =====
+        if (lane == 0) {
+            const int a_mn = (MODE == MODE_DK) ? 1 : 0;
+            const int b_mn = (MODE == MODE_DX) ? 0 : 1;
+            const uint32_t idesc = make_idesc(a_mn, b_mn, p.bn, BM);
+            // K-major tile: rows of 128 B, 8-row groups 1024 B apart (stride offset); one MMA (K = 8)
+            // consumes 32 B of each row.
+            // MN-major tile: [32-channel chunk][k row][128 B]: chunks 4096 B apart (leading offset), the
+            // 32-byte-chunk swizzle repeats every 4 k rows, so 4-row groups are 512 B apart (stride
+            // offset); one MMA consumes 8 k rows = 1024 B.
+            const uint32_t a_lbo = a_mn ? 4096u : 16u, b_lbo = b_mn ? 4096u : 16u;
+            const uint32_t a_sbo = a_mn ? 512u : 1024u, b_sbo = b_mn ? 512u : 1024u;
+            const uint32_t a_lay = a_mn ? kLayoutSw128Base32 : kLayoutSw128;
+            const uint32_t b_lay = b_mn ? kLayoutSw128Base32 : kLayoutSw128;
+            const uint32_t a_step = a_mn ? 1024u : 32u, b_step = b_mn ? 1024u : 32u;
+            bool ok = true;
+            for (int it = 0; it < nq && ok; ++it) {
+                const int s = it % p.stages;
+                const uint32_t phase = (uint32_t)(it / p.stages) & 1u;
+                ok = mbar_wait(full_bar + 8u * s, phase, 1, it);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = a_base + (uint32_t)s * A_STAGE_BYTES;
+                const uint32_t b_addr = b_base + (uint32_t)s * b_stage_bytes;
+#pragma unroll
+                for (int kk = 0; kk < BK / 8; ++kk) {
+                    const uint64_t adesc = make_smem_desc(a_addr + kk * a_step, a_lbo, a_sbo, a_lay);
+                    const uint64_t bdesc = make_smem_desc(b_addr + kk * b_step, b_lbo, b_sbo, b_lay);
+                    tcgen05_mma_tf32(tmem_d, adesc, bdesc, idesc, (it > 0 || kk > 0) ? 1u : 0u);
+                }
+                tcgen05_commit(empty_bar + 8u * s);  // frees the stage once these MMAs have read it
+            }
+            tcgen05_commit(tmem_full_bar);           // accumulator complete (or abandoned)
+        }
+    } else {
+        // ===== epilogue: warps 2..5, TMEM lane quadrant = warp % 4 =====
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        bool ok = mbar_wait(tmem_full_bar, 0, 2, 0);
+        ok = __all_sync(0xffffffffu, ok);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+        // where does this accumulator row go?
+        bool row_valid = false;
+        unsigned long long row_off = 0;   // element offset of column 0 of this row
+        long long col_stride = 1;         // element stride between accumulator columns
+        int ncols_valid = 0;              // valid columns in this N tile
+        int ch0 = n_tile * p.bn;          // channel index of column 0 (bias axis) unless DK
+        if (MODE == MODE_FWD) {
+            const int tw = row % p.TW, th = (row / p.TW) % p.TH, tn = row / (p.TW * p.TH);
+            const int n = n0 + tn, i = i0 + th, j = j0 + tw;
+            row_valid = n < p.N && i < p.Ho && j < p.Wo;
+            row_off = (((unsigned long long)n * p.Ho + i) * p.Wo + j) * p.O + ch0;
+            ncols_valid = min(p.bn, p.O - ch0);
+        } else if (MODE == MODE_DX) {
+            const int tw = row % p.TW, th = (row / p.TW) % p.TH, tn = row / (p.TW * p.TH);
+            const int n = n0 + tn, h = p.sh * (i0 + th) + ph, w = p.sw * (j0 + tw) + pw;
+            row_valid = n < p.N && h < p.H && w < p.W;
+            row_off = (((unsigned long long)n * p.H + h) * p.W + w) * p.C + ch0;
+            ncols_valid = min(p.bn, p.C - ch0);
+        } else {
+            const unsigned long long tap_off = (unsigned long long)group * p.C * p.O;
+            if (!p.swap) {   // rows c, columns o
+                const int c = m_tile * BM + row;
+                row_valid = c < p.C;
+                row_off = tap_off + (unsigned long long)c * p.O + ch0;
+                ncols_valid = min(p.bn, p.O - ch0);
+            } else {         // rows o, columns c
+                const int o = m_tile * BM + row;
+                row_valid = o < p.O;
+                row_off = tap_off + (unsigned long long)ch0 * p.O + o;
+                col_stride = p.O;
+                ncols_valid = min(p.bn, p.C - ch0);
+            }
+        }
+        if (!ok || nq <= 0) row_valid = false;   // nothing trustworthy to store
+        float* dst = p.direct ? p.out : p.out + (unsigned long long)split * p.out_elems;
+        const bool vec_ok = col_stride == 1 && (row_off & 3ull) == 0 && (ncols_valid & 3) == 0;
+
+        for (int c0 = 0; c0 < p.bn; c0 += 32) {
+            uint32_t r[32];
+            const uint32_t taddr = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0;
+            if (p.bn - c0 >= 32) {
+                tmem_ld_32x32b_x32(taddr, r);
+            } else {
+                tmem_ld_32x32b_x16(taddr, r);
+#pragma unroll
+                for (int q = 16; q < 32; ++q) r[q] = 0u;
+            }
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (!row_valid) continue;
+            if (p.direct) {
+#pragma unroll
+                for (int q = 0; q < 32; q += 4) {
+                    const int col = c0 + q;
+                    if (col >= ncols_valid) break;
+                    const unsigned long long idx = row_off + (unsigned long long)col * col_stride;
+                    if (vec_ok) {
+                        float4 v = make_float4(__uint_as_float(r[q]), __uint_as_float(r[q + 1]),
+                                               __uint_as_float(r[q + 2]), __uint_as_float(r[q + 3]));
+                        const EpilogueArgs& e = p.ep;
+                        if (e.raw_out) *reinterpret_cast<float4*>(e.raw_out + idx) = v;
+                        if (e.bias) {
+                            const float4 b = __ldg(reinterpret_cast<const float4*>(e.bias + ch0 + col));
+                            v.x = __fadd_rn(v.x, b.x); v.y = __fadd_rn(v.y, b.y);
+                            v.z = __fadd_rn(v.z, b.z); v.w = __fadd_rn(v.w, b.w);
+                        }
+                        if (e.pre_act) *reinterpret_cast<float4*>(e.pre_act + idx) = v;
+                        if (e.act != DCG_ACT_NONE) {
+                            v.x = act_apply(v.x, e.act, e.alpha); v.y = act_apply(v.y, e.act, e.alpha);
+                            v.z = act_apply(v.z, e.act, e.alpha); v.w = act_apply(v.w, e.act, e.alpha);
+                        }
+                        if (e.gate) {
+                            const float4 g = __ldg(reinterpret_cast<const float4*>(e.gate + idx));
+                            v.x = act_grad_apply(g.x, v.x, e.gate_act, e.gate_alpha);
+                            v.y = act_grad_apply(g.y, v.y, e.gate_act, e.gate_alpha);
+                            v.z = act_grad_apply(g.z, v.z, e.gate_act, e.gate_alpha);
+                            v.w = act_grad_apply(g.w, v.w, e.gate_act, e.gate_alpha);
+                        }
+                        *reinterpret_cast<float4*>(dst + idx) = v;
+                    } else {
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            if (col + u >= ncols_valid) break;
+                            const unsigned long long id = idx + (unsigned long long)u * col_stride;
+                            // the epilogue chain only applies to FWD/DX, whose columns are contiguous
+                            dst[id] = (MODE == MODE_DK) ? __uint_as_float(r[q + u])
+                                                        : epilogue_apply(p.ep, __uint_as_float(r[q + u]), id, ch0 + col + u);
+                        }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < 32; q += 4) {
+                    const int col = c0 + q;
+                    if (col >= ncols_valid) break;
+                    const unsigned long long idx = row_off + (unsigned long long)col * col_stride;
+                    if (vec_ok) {
+                        *reinterpret_cast<float4*>(dst + idx) =
+                            make_float4(__uint_as_float(r[q]), __uint_as_float(r[q + 1]),
+                                        __uint_as_float(r[q + 2]), __uint_as_float(r[q + 3]));
+                    } else {
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            if (col + u < ncols_valid)
+                                dst[idx + (unsigned long long)u * col_stride] = __uint_as_float(r[q + u]);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- teardown: everyone is done with TMEM before warp 1 releases it --------------------------
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
+    }
+}
+
+// ---- split-K finish: sum partials in split order, then the epilogue -----------------------------
+__global__ void __launch_bounds__(256)
+splitk_finish_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                     unsigned long long n, int splits, int channels, const EpilogueArgs ep)
+{
+    const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+    const bool plain = !ep.raw_out && !ep.bias && !ep.pre_act && ep.act == DCG_ACT_NONE && !ep.gate;
+    if ((n & 3ull) == 0 && (channels & 3) == 0) {
+        const unsigned long long n4 = n >> 2;
+        for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+            float4 acc = __ldg(reinterpret_cast<const float4*>(partial) + i);
+            for (int s = 1; s < splits; ++s) {
+                const float4 v = __ldg(reinterpret_cast<const float4*>(partial + (unsigned long long)s * n) + i);
+                acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y);
+                acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+            }
+            if (!plain) {
+                const unsigned long long e0 = i << 2;
+                const int ch = (int)(e0 % (unsigned long long)channels);
+                acc.x = epilogue_apply(ep, acc.x, e0, ch);
+                acc.y = epilogue_apply(ep, acc.y, e0 + 1, ch + 1);
+                acc.z = epilogue_apply(ep, acc.z, e0 + 2, ch + 2);
+                acc.w = epilogue_apply(ep, acc.w, e0 + 3, ch + 3);
+            }
+            reinterpret_cast<float4*>(out)[i] = acc;
+        }
+    } else {
+        for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+            float acc = __ldg(partial + i);
+            for (int s = 1; s < splits; ++s) acc = __fadd_rn(acc, __ldg(partial + (unsigned long long)s * n + i));
+            out[i] = plain ? acc : epilogue_apply(ep, acc, i, (int)(i % (unsigned long long)channels));
+        }
+    }
+}
+
+// ---- host side: tensor maps ---------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    return fn;
+}
+
+// dims/strides innermost first; strides[i] is the byte stride of dimension i+1.
+int encode_map(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims, bool mn_major,
+               const cuuint64_t* strides, const cuuint32_t* box, const cuuint32_t* estrides)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(DCG_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void*>(base), dims,
+                          strides, box, estrides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        return fail(DCG_ERR_CUDA,
+                    "cuTensorMapEncodeTiled failed (%d): rank %d dims [%llu,%llu,%llu,%llu,%llu] box [%u,%u,%u,%u,%u]",
+                    (int)r, rank, (unsigned long long)dims[0], (unsigned long long)dims[1],
+                    (unsigned long long)(rank > 2 ? dims[2] : 0), (unsigned long long)(rank > 3 ? dims[3] : 0),
+                    (unsigned long long)(rank > 4 ? dims[4] : 0), box[0], box[1], rank > 2 ? box[2] : 0,
+                    rank > 3 ? box[3] : 0, rank > 4 ? box[4] : 0);
+    }
+    return DCG_OK;
+}
+
+// Activation [N, Hh, Ww, Cc] as a 4-D map (c, w, h, n) with a (32, tw, th, tn)-element box and
+// traversal strides (1, sw, sh, 1).
+int map_act_4d(CUtensorMap* map, const float* base, int N, int Hh, int Ww, int Cc, int tw, int th, int tn,
+               int sw, int sh)
+{
+    const cuuint64_t dims[4] = {(cuuint64_t)Cc, (cuuint64_t)Ww, (cuuint64_t)Hh, (cuuint64_t)N};
+    const cuuint64_t strides[3] = {(cuuint64_t)Cc * 4, (cuuint64_t)Ww * Cc * 4, (cuuint64_t)Hh * Ww * Cc * 4};
+    const cuuint32_t box[4] = {32, (cuuint32_t)(tw * sw), (cuuint32_t)(th * sh), (cuuint32_t)tn};
+    const cuuint32_t es[4] = {1, (cuuint32_t)sw, (cuuint32_t)sh, 1};
+    return encode_map(map, base, 4, dims, false, strides, box, es);
+}
+
+// Activation [N, Hh, Ww, Cc] as a 5-D map (c%32, w, h, n, c/32): box (32, tw, th, tn, chunks) lands in
+// shared memory as [chunk][pixel][32 channels], the MN-major operand layout.
+int map_act_5d(CUtensorMap* map, const float* base, int N, int Hh, int Ww, int Cc, int tw, int th, int tn,
+               int sw, int sh, int chunks)
+{
+    const cuuint64_t dims[5] = {32, (cuuint64_t)Ww, (cuuint64_t)Hh, (cuuint64_t)N, (cuuint64_t)(Cc / 32)};
+    const cuuint64_t strides[4] = {(cuuint64_t)Cc * 4, (cuuint64_t)Ww * Cc * 4, (cuuint64_t)Hh * Ww * Cc * 4, 128};
+    const cuuint32_t box[5] = {32, (cuuint32_t)(tw * sw), (cuuint32_t)(th * sh), (cuuint32_t)tn, (cuuint32_t)chunks};
+    const cuuint32_t es[5] = {1, (cuuint32_t)sw, (cuuint32_t)sh, 1, 1};
+    return encode_map(map, base, 5, dims, true, strides, box, es);
+}
+
+int pow2_ceil(int v)
+{
+    int r = 1;
+    while (r < v) r <<= 1;
+    return r;
+}
+
+// 128 (or `total`) pixels as a (tw, th, tn) box: w first, then h, then images.
+void pixel_tile(int total, int Wd, int Hd, int& tw, int& th, int& tn)
+{
+    tw = pow2_ceil(Wd); if (tw > total) tw = total;
+    th = pow2_ceil(Hd); if (th > total / tw) th = total / tw;
+    tn = total / (tw * th);
+}
+
+struct Plan {
+    Params p;
+    int grid;
+    size_t smem;
+    size_t ws_bytes;   // scratch for split-K partials (0 when splits == 1)
+};
+
+// DCG_TC_SPLITS / DCG_TC_STAGES (environment, read once) pin the K partitioning and the pipeline
+// depth for experiments; unset or 0 leaves the heuristics below in charge.
+int env_int(const char* name)
+{
+    const char* v = getenv(name);
+    return v ? atoi(v) : 0;
+}
+
+int choose_splits(int tiles, int min_stages_per_tile)
+{
+    static const int forced = env_int("DCG_TC_SPLITS");
+    if (forced > 0) return forced <= min_stages_per_tile ? forced : (min_stages_per_tile > 0 ? min_stages_per_tile : 1);
+    const int sms = sm_count();
+    if (tiles >= sms) return 1;
+    int s = (2 * sms) / tiles;                       // aim at ~2 CTAs per SM
+    const int cap = min_stages_per_tile / 4;         // keep at least 4 K stages per CTA
+    if (s > cap) s = cap;
+    if (s > 16) s = 16;
+    return s < 1 ? 1 : s;
+}
+
+void finish_plan(Plan& pl)
+{
+    Params& p = pl.p;
+    const int b_stage = p.bn * BK * 4;
+    const int per_stage = A_STAGE_BYTES + b_stage;
+    // two CTAs per SM when the grid has more CTAs than SMs, else one deep pipeline
+    const int budget = (pl.grid > sm_count()) ? (kMaxSmem / 2 - 2048) : (kMaxSmem - 2048);
+    int stages = budget / per_stage;
+    if (stages > 8) stages = 8;
+    static const int forced_stages = env_int("DCG_TC_STAGES");
+    if (forced_stages > 0 && forced_stages < stages) stages = forced_stages;
+    if (stages < 2) stages = 2;
+    p.stages = stages;
+    pl.smem = (size_t)stages * per_stage + 1024 /*alignment slack*/ + 16 * stages + 32;
+    pl.ws_bytes = p.splits > 1 ? (size_t)p.splits * p.out_elems * sizeof(float) : 0;
+    p.direct = p.splits == 1 ? 1 : 0;
+}
+
+void base_params(Params& p, const dcg_conv_desc& d)
+{
+    p = Params{};
+    p.N = d.n; p.H = d.h; p.W = d.w; p.C = d.c; p.KH = d.kh; p.KW = d.kw; p.O = d.o;
+    p.Ho = d.ho; p.Wo = d.wo; p.sh = d.stride_h; p.sw = d.stride_w; p.pt = d.pad_top; p.pl = d.pad_left;
+    p.m_tiles = 1; p.n_tiles = 1; p.splits = 1; p.kchunks = 1;
+}
+
+bool plan_fwd(const dcg_conv_desc& d, Plan& pl)
+{
+    if (d.c % 4 != 0 || d.o % 32 != 0 || d.stride_h > 8 || d.stride_w > 8) return false;
+    Params& p = pl.p;
+    base_params(p, d);
+    pixel_tile(BM, d.wo, d.ho, p.TW, p.TH, p.TN);
+    if (p.TW * d.stride_w > 256 || p.TH * d.stride_h > 256) return false;
+    p.tiles_w = (d.wo + p.TW - 1) / p.TW; p.tiles_h = (d.ho + p.TH - 1) / p.TH; p.tiles_n = (d.n + p.TN - 1) / p.TN;
+    p.bn = d.o >= 128 ? 128 : d.o;
+    p.n_tiles = (d.o + p.bn - 1) / p.bn;
+    p.kchunks = (d.c + BK - 1) / BK;
+    const int tiles = p.tiles_w * p.tiles_h * p.tiles_n * p.n_tiles;
+    p.splits = choose_splits(tiles, d.kh * d.kw * p.kchunks);
+    p.out_elems = (unsigned long long)d.n * d.ho * d.wo * d.o;
+    pl.grid = tiles * p.splits;
+    finish_plan(pl);
+    return true;
+}
+
+bool plan_dx(const dcg_conv_desc& d, Plan& pl)
+{
+    if (d.o % 4 != 0 || d.stride_h > 8 || d.stride_w > 8) return false;
+    if (d.stride_h > d.kh || d.stride_w > d.kw) return false;   // some parity class would have no tap
+    Params& p = pl.p;
+    base_params(p, d);
+    const int ha = (d.h + d.stride_h - 1) / d.stride_h, wa = (d.w + d.stride_w - 1) / d.stride_w;
+    pixel_tile(BM, wa, ha, p.TW, p.TH, p.TN);
+    p.tiles_w = (wa + p.TW - 1) / p.TW; p.tiles_h = (ha + p.TH - 1) / p.TH; p.tiles_n = (d.n + p.TN - 1) / p.TN;
+    int bn = (d.c + 15) / 16 * 16;
+    if (bn > 128) bn = 128;
+    p.bn = bn;
+    p.n_tiles = (d.c + p.bn - 1) / p.bn;
+    p.kchunks = (d.o + BK - 1) / BK;
+    const int classes = d.stride_h * d.stride_w;
+    const int tiles = classes * p.tiles_w * p.tiles_h * p.tiles_n * p.n_tiles;
+    const int min_taps = (d.kh / d.stride_h) * (d.kw / d.stride_w);
+    p.splits = choose_splits(tiles, (min_taps < 1 ? 1 : min_taps) * p.kchunks);
+    p.out_elems = (unsigned long long)d.n * d.h * d.w * d.c;
+    pl.grid = tiles * p.splits;
+    finish_plan(pl);
+    return true;
+}
+
+bool plan_dk(const dcg_conv_desc& d, Plan& pl)
+{
+    if (d.c % 32 != 0 || d.o % 32 != 0 || d.stride_h > 8 || d.stride_w > 8) return false;
+    Params& p = pl.p;
+    base_params(p, d);
+    pixel_tile(BK, d.wo, d.ho, p.TW, p.TH, p.TN);   // 32 output pixels per K stage
+    if (p.TW * d.stride_w > 256 || p.TH * d.stride_h > 256) return false;
+    p.tiles_w = (d.wo + p.TW - 1) / p.TW; p.tiles_h = (d.ho + p.TH - 1) / p.TH; p.tiles_n = (d.n + p.TN - 1) / p.TN;
+    // the wider channel axis becomes M (128 accumulator rows), the other N
+    p.swap = d.o > d.c ? 1 : 0;
+    const int m_ch = p.swap ? d.o : d.c, n_ch = p.swap ? d.c : d.o;
+    p.m_tiles = (m_ch + BM - 1) / BM;
+    p.bn = n_ch >= 128 ? 128 : n_ch;
+    p.n_tiles = (n_ch + p.bn - 1) / p.bn;
+    const int tiles = d.kh * d.kw * p.m_tiles * p.n_tiles;
+    p.splits = choose_splits(tiles, p.tiles_w * p.tiles_h * p.tiles_n);
+    p.out_elems = (unsigned long long)d.kh * d.kw * d.c * d.o;
+    pl.grid = tiles * p.splits;
+    finish_plan(pl);
+    return true;
+}
+
+bool make_plan(const dcg_conv_desc& d, int kind, Plan& pl)
+{
+    switch (kind) {
+    case kConvFwd: return plan_fwd(d, pl);
+    case kConvDx: return plan_dx(d, pl);
+    case kConvDk: return plan_dk(d, pl);
+    default: return false;
+    }
+}
+
+template <int MODE>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, Plan& pl, float* out, const EpilogueArgs& ep,
+           int channels, void* ws, size_t ws_bytes, cudaStream_t stream)
+{
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(conv_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    });
+    if (attr_err != cudaSuccess)
+        return fail(DCG_ERR_CUDA, "cudaFuncSetAttribute(conv_tc_kernel): %s", cudaGetErrorString(attr_err));
+    Params& p = pl.p;
+    if (p.splits > 1) {
+        if (!ws || ws_bytes < pl.ws_bytes)
+            return fail(DCG_ERR_WORKSPACE, "conv (tensor path): workspace %zu < %zu bytes", ws_bytes, pl.ws_bytes);
+        p.out = static_cast<float*>(ws);
+        p.ep = EpilogueArgs{};
+    } else {
+        p.out = out;
+        p.ep = ep;
+    }
+    conv_tc_kernel<MODE><<<pl.grid, kThreads, pl.smem, stream>>>(ma, mb, p);
+    DCG_LAUNCH_CHECK("conv_tc_kernel");
+    if (p.splits > 1) {
+        const unsigned long long n = p.out_elems;
+        unsigned long long blocks = (n / 4 + 255) / 256;
+        const unsigned long long cap = (unsigned long long)sm_count() * 8;
+        if (blocks > cap) blocks = cap;
+        if (blocks < 1) blocks = 1;
+        splitk_finish_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const float*>(ws), out, n, p.splits,
+                                                                   channels, ep);
+        DCG_LAUNCH_CHECK("splitk_finish_kernel");
+    }
+    return DCG_OK;
+}
+
+}  // namespace
+
+bool conv_tc_supported(const dcg_conv_desc& d, int kind)
+{
+    Plan pl;
+    return make_plan(d, kind, pl);
+}
+
+size_t conv_tc_workspace(const dcg_conv_desc& d, int kind)
+{
+    Plan pl;
+    if (!make_plan(d, kind, pl)) return 0;
+    return pl.ws_bytes;
+}
+
+int conv_tc_fwd(const dcg_conv_desc& d, const float* x, const float* k, float* y, const EpilogueArgs& ep,
+                void* ws, size_t ws_bytes, cudaStream_t stream)
+{
+    Plan pl;
+    if (!plan_fwd(d, pl)) return fail(DCG_ERR_UNSUPPORTED, "conv fwd: shape not supported by the tensor path");
+    const Params& p = pl.p;
+    CUtensorMap ma, mb;
+    int st = map_act_4d(&ma, x, d.n, d.h, d.w, d.c, p.TW, p.TH, p.TN, d.stride_w, d.stride_h);
+    if (st) return st;
+    // k [tap][c][o] as (o%32, c, tap, o/32), box (32, 32, 1, bn/32)
+    const cuuint64_t dims[4] = {32, (cuuint64_t)d.c, (cuuint64_t)(d.kh * d.kw), (cuuint64_t)(d.o / 32)};
+    const cuuint64_t strides[3] = {(cuuint64_t)d.o * 4, (cuuint64_t)d.c * d.o * 4, 128};
+    const cuuint32_t box[4] = {32, 32, 1, (cuuint32_t)(p.bn / 32)};
+    const cuuint32_t es[4] = {1, 1, 1, 1};
+    if ((st = encode_map(&mb, k, 4, dims, true, strides, box, es))) return st;
+    return launch<MODE_FWD>(ma, mb, pl, y, ep, d.o, ws, ws_bytes, stream);
+}
+
+int conv_tc_dx(const dcg_conv_desc& d, const float* dy, const float* k, float* dx, const EpilogueArgs& ep,
+               void* ws, size_t ws_bytes, cudaStream_t stream)
+{
+    Plan pl;
+    if (!plan_dx(d, pl)) return fail(DCG_ERR_UNSUPPORTED, "conv dx: shape not supported by the tensor path");
+    const Params& p = pl.p;
+    CUtensorMap ma, mb;
+    int st = map_act_4d(&ma, dy, d.n, d.ho, d.wo, d.o, p.TW, p.TH, p.TN, 1, 1);
+    if (st) return st;
+    // k [kh][kw][c][o] as (o, c, kw, kh), box (32 o, bn c, 1, 1)
+    const cuuint64_t dims[4] = {(cuuint64_t)d.o, (cuuint64_t)d.c, (cuuint64_t)d.kw, (cuuint64_t)d.kh};
+    const cuuint64_t strides[3] = {(cuuint64_t)d.o * 4, (cuuint64_t)d.c * d.o * 4, (cuuint64_t)d.kw * d.c * d.o * 4};
+    const cuuint32_t box[4] = {32, (cuuint32_t)p.bn, 1, 1};
+    const cuuint32_t es[4] = {1, 1, 1, 1};
+    if ((st = encode_map(&mb, k, 4, dims, false, strides, box, es))) return st;
+    return launch<MODE_DX>(ma, mb, pl, dx, ep, d.c, ws, ws_bytes, stream);
+}
+
+int conv_tc_dk(const dcg_conv_desc& d, const float* x, const float* dy, float* dk, void* ws, size_t ws_bytes,
+               cudaStream_t stream)
+{
+    Plan pl;
+    if (!plan_dk(d, pl)) return fail(DCG_ERR_UNSUPPORTED, "conv dk: shape not supported by the tensor path");
+    const Params& p = pl.p;
+    CUtensorMap mx, mdy;
+    const int x_chunks = p.swap ? p.bn / 32 : BM / 32, dy_chunks = p.swap ? BM / 32 : p.bn / 32;
+    int st = map_act_5d(&mx, x, d.n, d.h, d.w, d.c, p.TW, p.TH, p.TN, d.stride_w, d.stride_h, x_chunks);
+    if (st) return st;
+    if ((st = map_act_5d(&mdy, dy, d.n, d.ho, d.wo, d.o, p.TW, p.TH, p.TN, 1, 1, dy_chunks))) return st;
+    const EpilogueArgs none{};
+    if (p.swap) return launch<MODE_DK>(mdy, mx, pl, dk, none, d.o, ws, ws_bytes, stream);
+    return launch<MODE_DK>(mx, mdy, pl, dk, none, d.o, ws, ws_bytes, stream);
+}
+
+// Reads (and clears) the device status word of the tensor-path kernels.  Synchronises the device.
+int conv_tc_device_status(int* detail /* [4] */)
+{
+    int h[4] = {0, 0, 0, 0};
+    DCG_CUDA(cudaDeviceSynchronize());
+    DCG_CUDA(cudaMemcpyFromSymbol(h, g_tc_status, sizeof(h)));
+    if (detail) for (int i = 0; i < 4; ++i) detail[i] = h[i];
+    if (h[0] != 0) {
+        const int zero[4] = {0, 0, 0, 0};
+        DCG_CUDA(cudaMemcpyToSymbol(g_tc_status, zero, sizeof(zero)));
+        return fail(DCG_ERR_DEVICE, "tensor-path kernel gave up waiting: code %d block %d role %d stage %d",
+                    h[0], h[1], h[2], h[3]);
+    }
+    return DCG_OK;
+}
+
+}  // namespace dcg
+
+extern "C" int dcg_device_status(void) { return dcg::conv_tc_device_status(nullptr); }

@@ -299,6 +299,10 @@ int dcg_run_node(dcg_context* ctx, const dcg_node* node);
 int dcg_run_nodes(dcg_context* ctx, const dcg_node* nodes, int count, int fuse);
 
 /* ---- diagnostics --------------------------------------------------------- */
+/* Synchronises the device, then reads and clears the status word the tensor-path
+ * kernels write when one of their bounded waits (mbarrier, ~1 s) runs out.
+ * Returns DCG_OK or DCG_ERR_DEVICE (dcg_last_error() names block, role, stage). */
+int dcg_device_status(void);
 const char* dcg_last_error(void);
 /* Library version and the architecture the kernels were built for ("sm_100a"). */
 const char* dcg_build_info(void);
