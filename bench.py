@@ -1,0 +1,395 @@
+#!/usr/bin/env python
+"""Benchmark of the DCGAN training iteration on the B200 convolution / Adam hot path.
+
+    python bench.py --gpus N --steps K --warmup W            # this repository's CUDA path
+    python bench.py --impl reference --gpus N --steps K ...  # the reference's CPU code, host cores
+    python bench.py --sweep                                   # per-layer conv roofline sweep
+
+A step is one training iteration exactly as dcgan/main.cu:378-391 runs it - one discriminator
+update and two generator updates, each recomputing its forward passes - at batch 64 per GPU
+(weak scaling: N GPUs train 64*N images per step; gradients are averaged with one all-reduce
+per update).  Inputs are synthetic with the data's shapes and ranges: images ~ U(-1,1)
+[64,64,64,3], z ~ U(-1,1) [64,100], weights ~ N(0,0.02), seeded.
+
+One JSON line is printed by rank 0:
+  value      images/s over all GPUs, device-timed (CUDA events, max over ranks), inputs resident in HBM
+  e2e        the same through Trainer.step_host: pinned host -> device copies of the step's inputs and
+             a device -> host read of both losses inside the timed region
+  roofline   the tensor-path convolution kernel: algorithmic FLOPs / event-timed duration of its
+             launches inside profiled steps, against the TF32 peak (half the measured dense bf16 peak)
+  cpu_baseline  the reference's CPU code (oracle/_ref) on a bounded, FLOP-weighted sample of the same
+             iteration at batch 1, one thread
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+BATCH = 64
+METRIC = "dcgan_train_images_per_s"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        p["_source"] = "measured"
+        return p
+    except (OSError, ValueError):
+        p = dict(FALLBACK_PEAKS)
+        p["_source"] = "fallback"
+        return p
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=fd, stderr=subprocess.DEVNULL)
+            os.close(fd)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        try:
+            with open(self.path) as f:
+                for line in f:
+                    parts = [p.strip() for p in line.split(",")]
+                    if len(parts) < 9:
+                        continue
+                    try:
+                        sm.append(float(parts[1]))
+                        mx.append(float(parts[2]))
+                    except ValueError:
+                        continue
+                    for name, val in zip(names, parts[5:9]):
+                        if val.lower().startswith("active"):
+                            reasons.add(name)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def synthetic_batches(rank, count):
+    """`count` host batches of (images, z) ~ U(-1,1), pinned, seeded per rank (234 + rank)."""
+    import torch
+    g = torch.Generator().manual_seed(234 + rank)
+    out = []
+    for _ in range(count):
+        x = (torch.rand((BATCH, 64, 64, 3), generator=g) * 2 - 1).pin_memory()
+        z = (torch.rand((BATCH, 100), generator=g) * 2 - 1).pin_memory()
+        out.append((x, z))
+    return out
+
+
+class CpuSampler:
+    """The reference's CPU code on the batch-1 training iteration, advanced in bounded slices.
+
+    advance(budget_s) runs the iteration's operator sequence from where the previous slice stopped
+    for about budget_s seconds (it stops at a convolution boundary; finished iterations restart),
+    and extrapolates images/s from the algorithmic convolution FLOPs done in the slice."""
+
+    def __init__(self):
+        import numpy as np
+        import oracle
+        from oracle import dcgan_model as M
+        self.M = M
+        self.be, self.kind = oracle.reference(), "reference"
+        if self.be is None:
+            self.be, self.kind = oracle.port(), "port"
+        rng = np.random.default_rng(234)
+        self.st = M.init_state(rng, 1)
+        self.x = rng.uniform(-1, 1, (1, 64, 64, 3)).astype(np.float32)
+        self.z = rng.uniform(-1, 1, (1, 100)).astype(np.float32)
+        self.gen = None
+
+    def advance(self, budget_s):
+        M = self.M
+        flops, ops = 0.0, 0
+        t0 = time.perf_counter()
+        while time.perf_counter() - t0 < budget_s:
+            if self.gen is None:
+                self.gen = M.train_iteration(self.be, self.st, self.x, self.z)
+            try:
+                _, f = next(self.gen)
+                flops += f
+                ops += 1
+            except StopIteration:
+                self.gen = None
+        elapsed = time.perf_counter() - t0
+        per_image = M.iteration_flops(1)
+        return {"value": (flops / per_image) / elapsed, "seconds": elapsed, "ops": ops, "kind": self.kind,
+                "fraction_of_iteration": flops / per_image}
+
+
+def run_reference(args, rank):
+    """--impl reference: the reference's own CPU implementation of the iteration, host cores."""
+    if rank != 0:
+        return
+    per_step = max(0.5, min(20.0, 150.0 / max(1, args.steps + args.warmup)))
+    sampler = CpuSampler()
+    for _ in range(args.warmup):
+        sampler.advance(per_step)
+    fracs, secs = [], []
+    kind = sampler.kind
+    for _ in range(args.steps):
+        r = sampler.advance(per_step)
+        fracs.append(r["fraction_of_iteration"])
+        secs.append(r["seconds"])
+    value = sum(fracs) / sum(secs) if secs else 0.0   # images per second over the whole timed run
+    sample = ("per step ~%.1f s of the batch-1 iteration's convolution sequence (src/cpu/ops.hxx compiled "
+              "-O2), images/s extrapolated by algorithmic FLOPs" % per_step)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * statistics.mean(secs) if secs else None,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "configs[2]: full DCGAN training iteration (1 D update + 2 G updates), "
+                               "batch 64 per GPU; CPU arm runs a bounded batch-1 sample", "global_batch": BATCH},
+        "cpu_baseline": {"value": value, "unit": "images/s", "cores": 1, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def profile_steps(pkg, trainer, steps):
+    """Event-timed launch groups of `steps` iterations: rows of (name, calls, ms, flops)."""
+    lib, L = pkg.lib, pkg._lib
+    ctx = lib.dcg_trainer_context(trainer._h)
+    L.check(lib.dcg_context_profile_begin(ctx))
+    for _ in range(steps):
+        trainer.step()
+    rows = (L.ProfileRow * 256)()
+    n = ctypes.c_int()
+    L.check(lib.dcg_context_profile_end(ctx, rows, 256, ctypes.byref(n)))
+    out = []
+    for i in range(min(n.value, 256)):
+        r = rows[i]
+        out.append({"name": r.name.decode(), "calls": int(r.calls), "ms": r.ms, "flops": r.flops})
+    return out
+
+
+def run_ours(args, rank, local_rank, world):
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda:%d" % local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    assert world == args.gpus, "launch with torchrun --nproc-per-node equal to --gpus"
+
+    precision = {"tf32": pkg.PREC_TF32, "fp32": pkg.PREC_FP32}[args.precision]
+    trainer = pkg.Trainer(batch=BATCH, precision=precision, fuse=True, seed=234, world=world)
+    batches = synthetic_batches(rank, 4)
+    trainer.x.copy_(batches[0][0])
+    trainer.z.copy_(batches[0][1])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing -------------------------------------------------------------
+    for _ in range(args.warmup):
+        trainer.step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = pkg.launches_total()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        trainer.step()
+    e1.record()
+    barrier()
+    launches = pkg.launches_total() - launches0
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    pkg._lib.check(pkg.lib.dcg_device_status())
+    ms_per_step = ms_total / args.steps
+    value = world * BATCH / (ms_per_step * 1e-3)
+
+    # ---- end to end: host inputs in, losses out, every step -------------------------------------
+    for i in range(min(3, args.warmup)):
+        trainer.step_host(*batches[i % len(batches)])
+    barrier()
+    t0 = time.perf_counter()
+    losses = None
+    for i in range(args.steps):
+        losses = trainer.step_host(*batches[i % len(batches)])
+    torch.cuda.synchronize()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    barrier()
+    clocks = sampler.stop()
+    e2e_value = world * BATCH * args.steps / e2e_s
+
+    # ---- per-kernel view of the step (event-timed launch groups) --------------------------------
+    peaks = read_peaks()
+    rows = profile_steps(pkg, trainer, 3)
+    torch.cuda.synchronize()
+    total_ms = sum(r["ms"] for r in rows) or 1.0
+    conv = [r for r in rows if r["name"].startswith("conv_") and r["flops"] > 0]
+    conv_ms = sum(r["ms"] for r in conv)
+    conv_flops = sum(r["flops"] for r in conv)
+    tf32_peak = peaks["bf16_tflops"] / 2.0
+    achieved = conv_flops / (conv_ms * 1e-3) / 1e12 if conv_ms > 0 else 0.0
+    roofline = {
+        "kernel": "conv_tc_kernel (tcgen05 implicit-GEMM conv: fwd, dx, dk launch groups of the step)",
+        "bound": "tensor", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
+        "frac": achieved / tf32_peak if tf32_peak else None,
+        "peak_source": "%s: dense bf16 %.1f TFLOP/s / 2 for TF32" % (peaks["_source"], peaks["bf16_tflops"]),
+        "share_of_step": conv_ms / total_ms, "traffic": None,
+    }
+    kernels = sorted(rows, key=lambda r: -r["ms"])[:14]
+    kernel_table = [{"name": r["name"], "calls_per_step": r["calls"] / 3.0, "us_per_call": 1e3 * r["ms"] / r["calls"],
+                     "share": r["ms"] / total_ms,
+                     "tflops": (r["flops"] / (r["ms"] * 1e-3) / 1e12) if r["flops"] > 0 and r["ms"] > 0 else None}
+                    for r in kernels]
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        r = CpuSampler().advance(args.cpu_seconds)
+        cpu = {"value": r["value"], "unit": "images/s", "cores": 1, "kind": r["kind"],
+               "sample": "%.1f s (%d convolution calls, %.2f of one iteration) of the batch-1 training iteration, "
+                         "images/s extrapolated by algorithmic FLOPs" % (r["seconds"], r["ops"],
+                                                                        r["fraction_of_iteration"])}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "tf32" if args.precision == "tf32" else "f32", "data": "synthetic",
+            "config": {"workload": "configs[2]: full DCGAN training iteration (1 D update + 2 G updates, forwards "
+                                   "recomputed per update as dcgan/main.cu:378-391), batch 64 per GPU",
+                       "global_batch": BATCH * world, "parallelism": "dp%d" % world,
+                       "l2": "no flush: every step streams through the trainer's %.0f MB arena of activations, "
+                             "gradients and Adam state, several times the 126 MB L2" % (trainer.arena_bytes() / 2 ** 20),
+                       "adam": "lr 2e-4 beta1 0.5 beta2 0.999 eps 1e-8"},
+            "steps_per_s": 1e3 / ms_per_step,
+            "conv_tflops": achieved,
+            "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": trainer.h2d_bytes_per_step,
+                    "d2h_bytes_per_step": trainer.d2h_bytes_per_step, "losses_last": losses},
+            "gpu_launches": launches,
+            "gpu_launches_per_step": launches / args.steps,
+            "roofline": roofline,
+            "kernels": kernel_table,
+            "cpu_baseline": cpu,
+            "clocks": clocks,
+        }
+        print(json.dumps(line))
+    trainer.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_sweep(args):
+    """Config 4: the eight DCGAN conv shapes x {fwd, dx, dk} x batch, isolated, L2 flushed."""
+    import torch
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    F = pkg.functional
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    peaks = read_peaks()
+    tf32_peak = peaks["bf16_tflops"] / 2.0
+    flush = torch.empty(256 * 2 ** 20 // 4, device=dev)
+    rows = []
+    for B in args.sweep_batches:
+        for name, H, C, O in (("D0/G3", 64, 3, 64), ("D1/G2", 32, 64, 128), ("D2/G1", 16, 128, 256),
+                              ("D3/G0", 8, 256, 512)):
+            x = torch.rand(B, H, H, C, device=dev) * 2 - 1
+            k = torch.randn(5, 5, C, O, device=dev) * 0.02
+            dy = torch.rand(B, H // 2, H // 2, O, device=dev) * 2 - 1
+            y, dx, dk = torch.empty_like(dy), torch.empty_like(x), torch.empty_like(k)
+            flops = 2.0 * B * (H // 2) ** 2 * 25 * C * O
+            ops = (("fwd", lambda: F.conv2d_fwd(x, k, out=y)), ("dx", lambda: F.conv2d_dx(dy, k, (H, H), out=dx)),
+                   ("dk", lambda: F.conv2d_dk(x, dy, (5, 5), out=dk)))
+            for op, fn in ops:
+                for _ in range(3):
+                    fn()
+                times = []
+                for _ in range(args.sweep_iters):
+                    flush.zero_()
+                    s, t = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    s.record()
+                    fn()
+                    t.record()
+                    torch.cuda.synchronize()
+                    times.append(s.elapsed_time(t))
+                med = statistics.median(times)
+                tflops = flops / (med * 1e-3) / 1e12
+                rows.append({"layer": name, "op": op, "batch": B, "us": med * 1e3, "tflops": tflops,
+                             "frac_tf32_peak": tflops / tf32_peak})
+    pkg._lib.check(pkg.lib.dcg_device_status())
+    print(json.dumps({"sweep": rows, "tf32_peak_tflops": tf32_peak, "peak_source": peaks["_source"],
+                      "timing": "median of %d, CUDA events, 256 MB L2 flush before each" % args.sweep_iters}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--precision", choices=["tf32", "fp32"], default="tf32")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=20.0)
+    ap.add_argument("--sweep", action="store_true")
+    ap.add_argument("--sweep-batches", type=int, nargs="+", default=[64, 256, 1024])
+    ap.add_argument("--sweep-iters", type=int, default=30)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.sweep:
+        return run_sweep(args)
+    if args.impl == "reference":
+        return run_reference(args, rank)
+    run_ours(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

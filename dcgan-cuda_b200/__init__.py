@@ -21,3 +21,4 @@ def build_info():
 def launches_total():
     """Kernels launched by the library since it was loaded."""
     return int(lib.dcg_launches_total())
+from .trainer import Trainer  # noqa: E402,F401

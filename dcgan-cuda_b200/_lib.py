@@ -62,6 +62,17 @@ class Node(ctypes.Structure):
                 ("flags", ctypes.c_uint)]
 
 
+class ProfileRow(ctypes.Structure):
+    _fields_ = [("name", ctypes.c_char * 96), ("calls", ctypes.c_uint64), ("ms", ctypes.c_double),
+                ("flops", ctypes.c_double)]
+
+
+class TrainerConfig(ctypes.Structure):
+    _fields_ = [("batch", c_int), ("world", c_int), ("precision", c_int), ("fuse", c_int),
+                ("g_leaky", c_int), ("lr", c_float), ("beta1", c_float), ("beta2", c_float),
+                ("eps", c_float), ("seed", ctypes.c_uint64)]
+
+
 # Every exported symbol of include/dcgan_b200.h: name -> (restype, argtypes)
 _P = c_void_p
 SIGNATURES = {
@@ -97,6 +108,20 @@ SIGNATURES = {
     "dcg_context_launch_count": (ctypes.c_uint64, [_P]),
     "dcg_run_node": (c_int, [_P, ctypes.POINTER(Node)]),
     "dcg_run_nodes": (c_int, [_P, ctypes.POINTER(Node), c_int, c_int]),
+    "dcg_trainer_create": (c_int, [ctypes.POINTER(_P), ctypes.POINTER(TrainerConfig), _P]),
+    "dcg_trainer_destroy": (None, [_P]),
+    "dcg_trainer_tensor": (c_int, [_P, ctypes.c_char_p, ctypes.POINTER(_P), ctypes.POINTER(c_size_t)]),
+    "dcg_trainer_generate": (c_int, [_P]),
+    "dcg_trainer_d_backward": (c_int, [_P]),
+    "dcg_trainer_d_apply": (c_int, [_P, c_float]),
+    "dcg_trainer_g_backward": (c_int, [_P]),
+    "dcg_trainer_g_apply": (c_int, [_P, c_float]),
+    "dcg_trainer_step": (c_int, [_P]),
+    "dcg_trainer_context": (_P, [_P]),
+    "dcg_context_profile_begin": (c_int, [_P]),
+    "dcg_context_profile_end": (c_int, [_P, ctypes.POINTER(ProfileRow), c_int, ctypes.POINTER(c_int)]),
+    "dcg_trainer_step_launches": (ctypes.c_uint64, [_P]),
+    "dcg_trainer_arena_bytes": (c_size_t, [_P]),
     "dcg_device_status": (c_int, []),
     "dcg_last_error": (ctypes.c_char_p, []),
     "dcg_build_info": (ctypes.c_char_p, []),

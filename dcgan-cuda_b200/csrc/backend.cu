@@ -6,11 +6,21 @@
 // dcg_run_nodes that loop - minus the per-node device synchronisation, plus
 // optional fusion of adjacent nodes.  Operand decoding follows the reference
 // handlers field for field, including which size array each handler reads.
+#include <cstring>
+#include <string>
 #include <vector>
 
 #include "adam.cuh"
+#include "backend.cuh"
 #include "common.cuh"
 #include "conv.cuh"
+
+// One timed launch group of a profiled run: CUDA events on the context's stream around it.
+struct ProfRec {
+    std::string name;
+    double flops;
+    cudaEvent_t e0, e1;
+};
 
 struct dcg_context {
     cudaStream_t stream = nullptr;
@@ -19,10 +29,44 @@ struct dcg_context {
     size_t ws_bytes = 0;
     bool owns_ws = false;
     uint64_t launches_base = 0;
+    bool profiling = false;
+    std::vector<ProfRec> recs;
 };
 
 namespace dcg {
+
+// Times everything enqueued on the context's stream during its lifetime when profiling is on.
+ProfScope::ProfScope(dcg_context* c, const char* name, double flops) : ctx(c), active(c && c->profiling)
+{
+    if (!active) return;
+    ProfRec r;
+    r.name = name;
+    r.flops = flops;
+    if (cudaEventCreate(&r.e0) != cudaSuccess || cudaEventCreate(&r.e1) != cudaSuccess) { active = false; return; }
+    cudaEventRecord(r.e0, ctx->stream);
+    ctx->recs.push_back(r);
+}
+
+ProfScope::~ProfScope()
+{
+    if (active) cudaEventRecord(ctx->recs.back().e1, ctx->stream);
+}
+
 namespace {
+
+const char* node_type_name(int type)
+{
+    static const char* names[DCG_OP_COUNT] = {
+        "mat_mat_mul", "mat_rvect_add", "sigmoid", "mse", "softmax", "log_softmax", "softmax_cross_entropy",
+        "conv2d", "relu", "relu_leaky", "tanh", "mse_grad", "sigmoid_grad", "mat_mul_add", "tmat_mat_mul",
+        "mat_tmat_mul", "mat_sum_rows", "mat_sum_cols", "softmax_cross_entropy_grad", "relu_grad",
+        "conv2d_bias_add", "update", "sigmoid_cross_entropy", "sigmoid_cross_entropy_grad",
+        "conv2d_input_grad", "conv2d_kernel_grad", "argmax_acc", "moment_update", "moment_update2",
+        "adam_update", "leaky_relu_grad", "conv2d_bias_add_grad", "tanh_grad", "conv2d_transpose",
+        "conv2d_transpose_input_grad", "conv2d_transpose_kernel_grad", "add"};
+    return (type >= 0 && type < DCG_OP_COUNT) ? names[type] : "unknown";
+}
+
 
 // Makes sure the context has `bytes` of scratch.  A context that owns its
 // scratch grows it (cudaFree synchronises, so kernels still reading the old
@@ -137,6 +181,14 @@ int run_conv(dcg_context* ctx, const ConvCall& cc, const dcg_epilogue* ep)
     const size_t need = dcg_conv_workspace_bytes(&cc.d, cc.kind, ctx->precision);
     int st = ensure_workspace(ctx, need);
     if (st) return st;
+    char name[96];
+    if (ctx->profiling) {
+        static const char* kinds[3] = {"conv_fwd", "conv_dx", "conv_dk"};
+        snprintf(name, sizeof(name), "%s x[%d,%d,%d,%d] k[%d,%d,%d,%d]", kinds[cc.kind], cc.d.n, cc.d.h, cc.d.w,
+                 cc.d.c, cc.d.kh, cc.d.kw, cc.d.c, cc.d.o);
+    }
+    // algorithmic work of any of the three operators: 2 * B*Ho*Wo * KH*KW * Cin * Cout
+    ProfScope scope(ctx, name, 2.0 * cc.d.n * cc.d.ho * cc.d.wo * cc.d.kh * cc.d.kw * (double)cc.d.c * cc.d.o);
     switch (cc.kind) {
     case kConvFwd:
         return dcg_conv2d_fwd(&cc.d, cc.a, cc.b, cc.out, ep, ctx->precision, ctx->ws, ctx->ws_bytes, ctx->stream);
@@ -312,6 +364,9 @@ extern "C" int dcg_run_node(dcg_context* ctx, const dcg_node* nd)
 {
     DCG_CHECK_ARG(ctx && nd, "dcg_run_node: null argument");
     dcg_stream_t s = ctx->stream;
+    const bool is_conv = is_conv_with_epilogue(nd->type) || nd->type == DCG_OP_CONV2D_KERNEL_GRAD ||
+                         nd->type == DCG_OP_CONV2D_TRANSPOSE_KERNEL_GRAD;
+    ProfScope scope(is_conv ? nullptr : ctx, node_type_name(nd->type), 0.0);  // convolutions time themselves
     switch (nd->type) {
     case DCG_OP_MAT_MAT_MUL:  // src/gpu/matmul.cu:90-104
         return dcg_matmul(nd->in1, nd->in2, nullptr, nd->out1, nd->len1, nd->len2, nd->len3, s);
@@ -446,8 +501,12 @@ extern "C" int dcg_run_nodes(dcg_context* ctx, const dcg_node* nodes, int count,
                 for (size_t r = 0; r < q; ++r) seen |= counters[r] == counters[q];
                 if (!seen) lr_t = dcg_adam_lr_t(counters[q], first.lr, first.beta1, first.beta2);
             }
-            int st = adam_multi_launch(batch.data(), (int)batch.size(), lr_t, first.a1, first.b1,
+            int st;
+            {
+                ProfScope scope(ctx, "adam_multi", 0.0);
+                st = adam_multi_launch(batch.data(), (int)batch.size(), lr_t, first.a1, first.b1,
                                        first.a2, first.b2, first.eps, 1.f, ctx->stream);
+            }
             if (st) return st;
             i = j;
             continue;
@@ -456,5 +515,45 @@ extern "C" int dcg_run_nodes(dcg_context* ctx, const dcg_node* nodes, int count,
         if (st) return st;
         ++i;
     }
+    return DCG_OK;
+}
+
+// ---- profiling mode ---------------------------------------------------------------------------
+extern "C" int dcg_context_profile_begin(dcg_context* ctx)
+{
+    DCG_CHECK_ARG(ctx, "dcg_context_profile_begin: null context");
+    for (ProfRec& r : ctx->recs) { cudaEventDestroy(r.e0); cudaEventDestroy(r.e1); }
+    ctx->recs.clear();
+    ctx->profiling = true;
+    return DCG_OK;
+}
+
+extern "C" int dcg_context_profile_end(dcg_context* ctx, dcg_profile_row* rows, int max_rows, int* n_rows)
+{
+    DCG_CHECK_ARG(ctx && n_rows && (rows || max_rows == 0), "dcg_context_profile_end: bad arguments");
+    ctx->profiling = false;
+    DCG_CUDA(cudaStreamSynchronize(ctx->stream));
+    std::vector<dcg_profile_row> agg;
+    for (ProfRec& r : ctx->recs) {
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, r.e0, r.e1);
+        cudaEventDestroy(r.e0);
+        cudaEventDestroy(r.e1);
+        size_t k = 0;
+        for (; k < agg.size(); ++k)
+            if (r.name == agg[k].name) break;
+        if (k == agg.size()) {
+            dcg_profile_row row;
+            std::memset(&row, 0, sizeof(row));
+            snprintf(row.name, sizeof(row.name), "%s", r.name.c_str());
+            agg.push_back(row);
+        }
+        agg[k].calls += 1;
+        agg[k].ms += ms;
+        agg[k].flops += r.flops;
+    }
+    ctx->recs.clear();
+    *n_rows = (int)agg.size();
+    for (int i = 0; i < (int)agg.size() && i < max_rows; ++i) rows[i] = agg[i];
     return DCG_OK;
 }

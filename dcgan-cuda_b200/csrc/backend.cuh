@@ -1,0 +1,19 @@
+// Internal interface of the node backend's profiling mode (see backend.cu).
+#pragma once
+#include "dcgan_b200.h"
+
+namespace dcg {
+
+// RAII timer: when the context is profiling, records a CUDA event on the context's stream at
+// construction and another at destruction, and files the pair under `name` with `flops` of
+// algorithmic work.  A no-op otherwise.
+struct ProfScope {
+    ProfScope(dcg_context* ctx, const char* name, double flops);
+    ~ProfScope();
+    ProfScope(const ProfScope&) = delete;
+    ProfScope& operator=(const ProfScope&) = delete;
+    dcg_context* ctx;
+    bool active;
+};
+
+}  // namespace dcg

@@ -1,0 +1,564 @@
+// DCGAN training step as node lists: the host-side counterpart of dcgan/main.cu.
+//
+// The reference builds the generator / discriminator with its ops graph, lets autodiff add the
+// gradient ops and AdamOptimizer::minimize the update ops (dcgan/main.cu:271-332), then every
+// iteration runs graph.run({d_opti, d_loss}) once and graph.run({g_opti, g_loss}) twice
+// (dcgan/main.cu:378-391).  Each run lowers to a flat list of rt::Node instructions.  This file
+// writes those lists down directly for the fixed DCGAN topology - same instructions, same
+// operands, same recomputation of the forward passes in every run - and executes them through the
+// node backend (dcg_run_nodes) with fusion on.  All device memory comes from one arena allocated
+// at creation; parameters and gradients of each network are contiguous so a data-parallel caller
+// can average a network's gradients with a single all-reduce between *_backward and *_apply.
+#include <cmath>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "adam.cuh"
+#include "backend.cuh"
+#include "common.cuh"
+
+namespace {
+
+constexpr int kZ = 100;       // dcgan/main.cu:34
+constexpr int kImg = 64;
+constexpr int kLayers = 4;
+const int kGChan[kLayers + 1] = {512, 256, 128, 64, 3};   // generator feature maps 4x4 -> 64x64
+const int kDChan[kLayers + 1] = {3, 64, 128, 256, 512};   // discriminator feature maps 64x64 -> 4x4
+
+struct Tensor {
+    float* p = nullptr;
+    size_t n = 0;
+};
+
+// xorshift generator of the reference (src/utils/xorshift.cu:11-34) with Box-Muller on top: a
+// seeded stand-in for the reference's clock-seeded std::normal_distribution initialiser
+// (src/api/normal-initializer.cu:6-9).
+struct Rng {
+    uint64_t s[4];
+    explicit Rng(uint64_t x) { s[0] = 1000 * x; s[1] = 2000 * x; s[2] = 3000 * x; s[3] = 4000 * x; }
+    uint64_t next_u64()
+    {
+        uint64_t t = s[0] ^ (s[0] << 11);
+        s[0] = s[1]; s[1] = s[2]; s[2] = s[3];
+        s[3] = s[3] ^ (s[3] >> 19) ^ t ^ (t >> 8);
+        return s[3];
+    }
+    float next_f32() { return (float)next_u64() / (float)0xFFFFFFFFFFFFFFFFull; }
+    float normal(float sd)
+    {
+        float u1 = next_f32(), u2 = next_f32();
+        if (u1 < 1e-12f) u1 = 1e-12f;
+        return sd * std::sqrt(-2.f * std::log(u1)) * std::cos(6.28318530718f * u2);
+    }
+};
+
+}  // namespace
+
+struct dcg_trainer {
+    dcg_trainer_config cfg;
+    cudaStream_t stream = nullptr;
+    dcg_context* ctx = nullptr;
+    uint8_t* arena = nullptr;
+    size_t arena_bytes = 0, arena_used = 0;
+
+    // parameters / gradients / Adam moments: index 0..9 = (k0,b0,...,k3,b3,dense w,dense b)
+    Tensor g_param[10], g_grad[10], g_m[10], g_v[10];
+    Tensor d_param[10], d_grad[10], d_grad2[10], d_m[10], d_v[10];
+    Tensor g_params_all, g_grads_all, d_params_all, d_grads_all;
+    float g_t = 0.f, d_t = 0.f;   // Adam step counters (host, as rt::Node::out2 of adam_update)
+
+    // inputs, constants, losses
+    Tensor x, z, ones, zeros, d_loss, d1_loss, d2_loss, g_loss;
+    // generator activations
+    Tensor g0z, g0a, gc[kLayers], gz[kLayers], ga[kLayers], g_out;
+    // discriminator activations for the fake (0) and real (1) pass
+    Tensor dc[2][kLayers], dz[2][kLayers], da[2][kLayers], logits[2];
+    // backward scratch
+    Tensor dlogits[2], dda[kLayers + 1], ddz[kLayers], dg_out, dgz[kLayers], dga[kLayers], dg0a, dg0z;
+
+    std::vector<dcg_node> d_nodes, g_nodes, gen_nodes;
+    uint64_t last_step_launches = 0;
+};
+
+namespace {
+
+using dcg::fail;
+
+// Bump allocator over the arena, 256-byte aligned.  A dry pass only measures.
+struct Alloc {
+    dcg_trainer* t;
+    bool dry;
+    size_t off = 0;
+    Tensor get(size_t n)
+    {
+        Tensor r;
+        r.n = n;
+        off = dcg::align_up(off, 256);
+        if (!dry) r.p = reinterpret_cast<float*>(t->arena + off);
+        off += n * sizeof(float);
+        return r;
+    }
+};
+
+// Lays every tensor out in the arena.  Called twice: dry (sizes only) and for real.
+void layout(dcg_trainer* t, Alloc& a)
+{
+    const int B = t->cfg.batch;
+    auto pack = [&](Tensor* dst, const size_t* sizes, Tensor& all) {
+        const size_t start = dcg::align_up(a.off, 256);
+        for (int i = 0; i < 10; ++i) dst[i] = a.get(sizes[i]);
+        all.n = (a.off - start) / sizeof(float);
+        all.p = a.dry ? nullptr : reinterpret_cast<float*>(t->arena + start);
+    };
+    size_t gs[10], ds[10];
+    for (int i = 0; i < kLayers; ++i) {
+        gs[2 * i] = (size_t)25 * kGChan[i + 1] * kGChan[i];  // [5,5,Cout,Cin]
+        gs[2 * i + 1] = kGChan[i + 1];
+        ds[2 * i] = (size_t)25 * kDChan[i] * kDChan[i + 1];  // [5,5,Cin,Cout]
+        ds[2 * i + 1] = kDChan[i + 1];
+    }
+    gs[8] = (size_t)kZ * 8192; gs[9] = 8192;
+    ds[8] = 8192; ds[9] = 1;
+    Tensor dummy;
+    pack(t->g_param, gs, t->g_params_all);
+    pack(t->g_grad, gs, t->g_grads_all);
+    pack(t->g_m, gs, dummy);
+    pack(t->g_v, gs, dummy);
+    pack(t->d_param, ds, t->d_params_all);
+    pack(t->d_grad, ds, t->d_grads_all);
+    pack(t->d_grad2, ds, dummy);
+    pack(t->d_m, ds, dummy);
+    pack(t->d_v, ds, dummy);
+
+    t->x = a.get((size_t)B * kImg * kImg * 3);
+    t->z = a.get((size_t)B * kZ);
+    t->ones = a.get(B); t->zeros = a.get(B);
+    t->d_loss = a.get(1); t->d1_loss = a.get(1); t->d2_loss = a.get(1); t->g_loss = a.get(1);
+    t->g0z = a.get((size_t)B * 8192); t->g0a = a.get((size_t)B * 8192);
+    for (int i = 0; i < kLayers; ++i) {
+        const int hw = 8 << i;
+        const size_t n = (size_t)B * hw * hw * kGChan[i + 1];
+        t->gc[i] = a.get(n); t->gz[i] = a.get(n);
+        if (i < kLayers - 1) t->ga[i] = a.get(n);
+        t->dgz[i] = a.get(n); t->dga[i] = a.get(n);
+    }
+    t->g_out = a.get((size_t)B * kImg * kImg * 3);
+    t->dg_out = a.get((size_t)B * kImg * kImg * 3);
+    t->dg0a = a.get((size_t)B * 8192); t->dg0z = a.get((size_t)B * 8192);
+    for (int pss = 0; pss < 2; ++pss) {
+        for (int i = 0; i < kLayers; ++i) {
+            const int hw = 32 >> i;
+            const size_t n = (size_t)B * hw * hw * kDChan[i + 1];
+            t->dc[pss][i] = a.get(n); t->dz[pss][i] = a.get(n); t->da[pss][i] = a.get(n);
+        }
+        t->logits[pss] = a.get(B);
+        t->dlogits[pss] = a.get(B);
+    }
+    for (int i = 0; i < kLayers; ++i) {
+        const int hw = 32 >> i;
+        t->ddz[i] = a.get((size_t)B * hw * hw * kDChan[i + 1]);
+        t->dda[i + 1] = a.get((size_t)B * hw * hw * kDChan[i + 1]);
+    }
+}
+
+// ---- node construction: field packing as in src/runtime/node.cu ----------------------------------
+dcg_node node(int type)
+{
+    dcg_node n;
+    std::memset(&n, 0, sizeof(n));
+    n.type = type;
+    return n;
+}
+
+void set4(int* dst, int a, int b, int c, int d) { dst[0] = a; dst[1] = b; dst[2] = c; dst[3] = d; }
+
+dcg_node n_mat_mul_add(const float* x, const float* w, const float* b, float* out, size_t m, size_t n, size_t p)
+{
+    dcg_node nd = node(DCG_OP_MAT_MUL_ADD);
+    nd.in1 = x; nd.in2 = w; nd.in3 = b; nd.out1 = out; nd.len1 = m; nd.len2 = n; nd.len3 = p;
+    return nd;
+}
+
+dcg_node n_unary(int type, const float* in, float* out, size_t len, float alpha = 0.f)
+{
+    dcg_node nd = node(type);
+    nd.in1 = in; nd.out1 = out; nd.len1 = len; nd.alpha_leaky = alpha;
+    return nd;
+}
+
+dcg_node n_binary(int type, const float* a, const float* b, float* out, size_t len, float cons1 = 0.f)
+{
+    dcg_node nd = node(type);
+    nd.in1 = a; nd.in2 = b; nd.out1 = out; nd.len1 = len; nd.cons1 = cons1;
+    return nd;
+}
+
+dcg_node n_rows_cols(int type, const float* a, const float* b, float* out, size_t rows, size_t cols)
+{
+    dcg_node nd = node(type);
+    nd.in1 = a; nd.in2 = b; nd.out1 = out; nd.len1 = rows; nd.len2 = cols;
+    return nd;
+}
+
+dcg_node n_mat3(int type, const float* a, const float* b, float* out, size_t l1, size_t l2, size_t l3)
+{
+    dcg_node nd = node(type);
+    nd.in1 = a; nd.in2 = b; nd.out1 = out; nd.len1 = l1; nd.len2 = l2; nd.len3 = l3;
+    return nd;
+}
+
+// conv2d [B,h,h,c] -> [B,h/2,h/2,o], 5x5, stride 2, SAME (total pad 3): src/ops/conv2d.cu:44-77
+dcg_node n_conv2d(const float* x, const float* k, float* y, int B, int h, int c, int o)
+{
+    dcg_node nd = node(DCG_OP_CONV2D);
+    nd.in1 = x; nd.in2 = k; nd.out1 = y;
+    nd.intconst[0] = nd.intconst[1] = 2;
+    nd.int_cons1 = nd.int_cons2 = 3;
+    set4(nd.sizes1, B, h, h, c);
+    set4(nd.sizes2, 5, 5, c, o);
+    return nd;
+}
+
+dcg_node n_conv2d_input_grad(const float* dy, const float* k, float* dx, int B, int h, int c, int o)
+{
+    dcg_node nd = node(DCG_OP_CONV2D_INPUT_GRAD);
+    nd.in1 = dy; nd.in2 = k; nd.out1 = dx;
+    nd.intconst[0] = nd.intconst[1] = 2;
+    nd.intconst2[0] = nd.intconst2[1] = h;
+    set4(nd.sizes1, B, h / 2, h / 2, o);
+    set4(nd.sizes2, 5, 5, c, o);
+    return nd;
+}
+
+dcg_node n_conv2d_kernel_grad(const float* dy, const float* x, float* dk, int B, int h, int c, int o)
+{
+    dcg_node nd = node(DCG_OP_CONV2D_KERNEL_GRAD);
+    nd.in1 = dy; nd.in2 = x; nd.out1 = dk;
+    nd.intconst[0] = nd.intconst[1] = 2;
+    nd.intconst2[0] = nd.intconst2[1] = 3;
+    set4(nd.sizes1, B, h / 2, h / 2, o);
+    set4(nd.sizes2, B, h, h, c);
+    return nd;
+}
+
+// conv2d_transpose [B,h,h,cin] -> [B,2h,2h,cout], kernel [5,5,cout,cin]: src/ops/conv2d-transpose.cu:31-52
+dcg_node n_conv2d_transpose(const float* x, const float* k, float* y, int B, int h, int cin, int cout)
+{
+    dcg_node nd = node(DCG_OP_CONV2D_TRANSPOSE);
+    nd.in1 = x; nd.in2 = k; nd.out1 = y;
+    nd.intconst[0] = nd.intconst[1] = 2;
+    set4(nd.sizes1, B, 2 * h, 2 * h, cout);
+    set4(nd.sizes2, B, h, h, cin);
+    set4(nd.sizes3, 5, 5, cout, cin);
+    return nd;
+}
+
+dcg_node n_conv2d_transpose_input_grad(const float* dy, const float* k, float* dx, int B, int h, int cin, int cout)
+{
+    dcg_node nd = node(DCG_OP_CONV2D_TRANSPOSE_INPUT_GRAD);
+    nd.in1 = dy; nd.in2 = k; nd.out1 = dx;
+    nd.intconst[0] = nd.intconst[1] = 2;
+    nd.intconst2[0] = nd.intconst2[1] = h;
+    set4(nd.sizes1, B, 2 * h, 2 * h, cout);
+    set4(nd.sizes2, 5, 5, cout, cin);
+    return nd;
+}
+
+dcg_node n_conv2d_transpose_kernel_grad(const float* dy, const float* x, float* dk, int B, int h, int cin, int cout)
+{
+    dcg_node nd = node(DCG_OP_CONV2D_TRANSPOSE_KERNEL_GRAD);
+    nd.in1 = dy; nd.in2 = x; nd.out1 = dk;
+    nd.intconst[0] = nd.intconst[1] = 2;
+    set4(nd.sizes1, B, 2 * h, 2 * h, cout);
+    set4(nd.sizes2, B, h, h, cin);
+    set4(nd.sizes3, 5, 5, cout, cin);
+    return nd;
+}
+
+dcg_node dead(dcg_node n)
+{
+    n.flags |= DCG_NODE_OUT_DEAD;
+    return n;
+}
+
+// Generator forward: dcgan/main.cu:89-120 and :288 (tanh on the last layer's pre-activation).
+void build_generator(dcg_trainer* t, std::vector<dcg_node>& L)
+{
+    const int B = t->cfg.batch;
+    const int act = t->cfg.g_leaky ? DCG_OP_RELU_LEAKY : DCG_OP_RELU;
+    L.push_back(n_mat_mul_add(t->z.p, t->g_param[8].p, t->g_param[9].p, t->g0z.p, B, kZ, 8192));
+    L.push_back(n_unary(act, t->g0z.p, t->g0a.p, (size_t)B * 8192, 0.2f));
+    const float* in = t->g0a.p;   // reshape to [B,4,4,512] is an alias (src/ops/reshape.cu:20-44)
+    for (int i = 0; i < kLayers; ++i) {
+        const int h = 4 << i, hw = 2 * h;
+        const size_t rows = (size_t)B * hw * hw;
+        L.push_back(dead(n_conv2d_transpose(in, t->g_param[2 * i].p, t->gc[i].p, B, h, kGChan[i], kGChan[i + 1])));
+        L.push_back(n_rows_cols(DCG_OP_MAT_RVECT_ADD, t->gc[i].p, t->g_param[2 * i + 1].p, t->gz[i].p, rows, kGChan[i + 1]));
+        if (i < kLayers - 1) {
+            L.push_back(n_unary(act, t->gz[i].p, t->ga[i].p, rows * kGChan[i + 1], 0.2f));
+            in = t->ga[i].p;
+        } else {
+            L.push_back(n_unary(DCG_OP_TANH, t->gz[i].p, t->g_out.p, rows * 3));
+        }
+    }
+}
+
+// Discriminator forward on `img` into pass `ps` buffers: dcgan/main.cu:123-249.
+void build_discriminator(dcg_trainer* t, std::vector<dcg_node>& L, const float* img, int ps)
+{
+    const int B = t->cfg.batch;
+    const float* in = img;
+    for (int i = 0; i < kLayers; ++i) {
+        const int h = 64 >> i, ho = h / 2;
+        const size_t rows = (size_t)B * ho * ho;
+        L.push_back(dead(n_conv2d(in, t->d_param[2 * i].p, t->dc[ps][i].p, B, h, kDChan[i], kDChan[i + 1])));
+        L.push_back(n_rows_cols(DCG_OP_MAT_RVECT_ADD, t->dc[ps][i].p, t->d_param[2 * i + 1].p, t->dz[ps][i].p, rows, kDChan[i + 1]));
+        L.push_back(n_unary(DCG_OP_RELU_LEAKY, t->dz[ps][i].p, t->da[ps][i].p, rows * kDChan[i + 1], 0.2f));
+        in = t->da[ps][i].p;
+    }
+    L.push_back(n_mat_mul_add(in, t->d_param[8].p, t->d_param[9].p, t->logits[ps].p, B, 8192, 1));
+}
+
+// Backward through the discriminator for pass `ps`, starting from dlogits[ps].
+// grads != nullptr: weight gradients into grads[0..9]; to_image: also the gradient w.r.t. the input.
+void build_discriminator_backward(dcg_trainer* t, std::vector<dcg_node>& L, const float* img, int ps,
+                                  Tensor* grads, bool to_image)
+{
+    const int B = t->cfg.batch;
+    if (grads) {
+        L.push_back(n_mat3(DCG_OP_TMAT_MAT_MUL, t->da[ps][3].p, t->dlogits[ps].p, grads[8].p, 8192, B, 1));
+        L.push_back(n_rows_cols(DCG_OP_MAT_SUM_COLS, t->dlogits[ps].p, nullptr, grads[9].p, B, 1));
+    }
+    L.push_back(n_mat3(DCG_OP_MAT_TMAT_MUL, t->dlogits[ps].p, t->d_param[8].p, t->dda[4].p, B, 1, 8192));
+    for (int i = kLayers - 1; i >= 0; --i) {
+        const int h = 64 >> i, ho = h / 2;
+        const size_t rows = (size_t)B * ho * ho;
+        const float* in = i == 0 ? img : t->da[ps][i - 1].p;
+        // dda[i+1] is produced by the layer above; its leaky gradient is this layer's dz
+        L.push_back(n_binary(DCG_OP_LEAKY_RELU_GRAD, t->dz[ps][i].p, t->dda[i + 1].p, t->ddz[i].p, rows * kDChan[i + 1], 0.2f));
+        if (grads) {
+            L.push_back(n_rows_cols(DCG_OP_MAT_SUM_COLS, t->ddz[i].p, nullptr, grads[2 * i + 1].p, rows, kDChan[i + 1]));
+            L.push_back(n_conv2d_kernel_grad(t->ddz[i].p, in, grads[2 * i].p, B, h, kDChan[i], kDChan[i + 1]));
+        }
+        // the input gradient is only ever read by the activation gradient that follows it
+        if (i > 0)
+            L.push_back(dead(n_conv2d_input_grad(t->ddz[i].p, t->d_param[2 * i].p, t->dda[i].p, B, h, kDChan[i], kDChan[i + 1])));
+        else if (to_image)
+            L.push_back(dead(n_conv2d_input_grad(t->ddz[i].p, t->d_param[2 * i].p, t->dg_out.p, B, h, kDChan[i], kDChan[i + 1])));
+    }
+}
+
+void build_lists(dcg_trainer* t)
+{
+    const int B = t->cfg.batch;
+    // ---- generate: G forward only ----
+    build_generator(t, t->gen_nodes);
+
+    // ---- D run: graph.run({d_opti, d_loss}) ----
+    std::vector<dcg_node>& D = t->d_nodes;
+    build_generator(t, D);
+    build_discriminator(t, D, t->g_out.p, 0);
+    build_discriminator(t, D, t->x.p, 1);
+    D.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY, t->zeros.p, t->logits[0].p, t->d1_loss.p, B));
+    D.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY, t->ones.p, t->logits[1].p, t->d2_loss.p, B));
+    D.push_back(n_binary(DCG_OP_ADD, t->d1_loss.p, t->d2_loss.p, t->d_loss.p, 1));
+    D.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY_GRAD, t->zeros.p, t->logits[0].p, t->dlogits[0].p, B));
+    D.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY_GRAD, t->ones.p, t->logits[1].p, t->dlogits[1].p, B));
+    build_discriminator_backward(t, D, t->g_out.p, 0, t->d_grad, false);
+    build_discriminator_backward(t, D, t->x.p, 1, t->d_grad2, false);
+
+    // ---- G run: graph.run({g_opti, g_loss}) ----
+    std::vector<dcg_node>& G = t->g_nodes;
+    build_generator(t, G);
+    build_discriminator(t, G, t->g_out.p, 0);
+    G.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY, t->ones.p, t->logits[0].p, t->g_loss.p, B));
+    G.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY_GRAD, t->ones.p, t->logits[0].p, t->dlogits[0].p, B));
+    build_discriminator_backward(t, G, t->g_out.p, 0, nullptr, true);
+    // through tanh and the generator (src/ops/vect-tanh.cu:41: the gradient takes the tanh OUTPUT)
+    G.push_back(n_binary(DCG_OP_TANH_GRAD, t->g_out.p, t->dg_out.p, t->dgz[3].p, (size_t)B * 64 * 64 * 3));
+    const int gact_grad = t->cfg.g_leaky ? DCG_OP_LEAKY_RELU_GRAD : DCG_OP_RELU_GRAD;
+    for (int i = kLayers - 1; i >= 0; --i) {
+        const int h = 4 << i, hw = 2 * h;
+        const size_t rows = (size_t)B * hw * hw;
+        const float* in = i == 0 ? t->g0a.p : t->ga[i - 1].p;
+        G.push_back(n_rows_cols(DCG_OP_MAT_SUM_COLS, t->dgz[i].p, nullptr, t->g_grad[2 * i + 1].p, rows, kGChan[i + 1]));
+        G.push_back(n_conv2d_transpose_kernel_grad(t->dgz[i].p, in, t->g_grad[2 * i].p, B, h, kGChan[i], kGChan[i + 1]));
+        float* dprev_a = i == 0 ? t->dg0a.p : t->dga[i - 1].p;
+        G.push_back(dead(n_conv2d_transpose_input_grad(t->dgz[i].p, t->g_param[2 * i].p, dprev_a, B, h, kGChan[i], kGChan[i + 1])));
+        const float* zprev = i == 0 ? t->g0z.p : t->gz[i - 1].p;
+        float* dprev_z = i == 0 ? t->dg0z.p : t->dgz[i - 1].p;
+        const size_t nprev = i == 0 ? (size_t)B * 8192 : (size_t)B * h * h * kGChan[i];
+        G.push_back(n_binary(gact_grad, zprev, dprev_a, dprev_z, nprev, 0.2f));
+    }
+    G.push_back(n_mat3(DCG_OP_TMAT_MAT_MUL, t->z.p, t->dg0z.p, t->g_grad[8].p, kZ, B, 8192));
+    G.push_back(n_rows_cols(DCG_OP_MAT_SUM_COLS, t->dg0z.p, nullptr, t->g_grad[9].p, B, 8192));
+}
+
+int run_list(dcg_trainer* t, const std::vector<dcg_node>& L)
+{
+    return dcg_run_nodes(t->ctx, L.data(), (int)L.size(), t->cfg.fuse);
+}
+
+int apply_adam(dcg_trainer* t, Tensor* param, Tensor* grad, Tensor* grad2, Tensor* m, Tensor* v, float* step,
+               float grad_scale)
+{
+    dcg_adam_tensor ts[10];
+    for (int i = 0; i < 10; ++i) {
+        ts[i].p = param[i].p; ts[i].g = grad[i].p; ts[i].g2 = grad2 ? grad2[i].p : nullptr;
+        ts[i].m = m[i].p; ts[i].v = v[i].p; ts[i].n = param[i].n;
+    }
+    const float lr_t = dcg_adam_lr_t(step, t->cfg.lr, t->cfg.beta1, t->cfg.beta2);
+    dcg::ProfScope scope(t->ctx, "adam_multi", 0.0);
+    return dcg_adam_multi(ts, 10, lr_t, t->cfg.beta1, t->cfg.beta2, t->cfg.eps, grad_scale, t->stream);
+}
+
+}  // namespace
+
+extern "C" int dcg_trainer_create(dcg_trainer** out, const dcg_trainer_config* cfg, dcg_stream_t stream)
+{
+    DCG_CHECK_ARG(out && cfg, "dcg_trainer_create: null argument");
+    DCG_CHECK_ARG(cfg->batch > 0 && cfg->batch <= 4096, "dcg_trainer_create: bad batch %d", cfg->batch);
+    dcg_trainer* t = new dcg_trainer();
+    t->cfg = *cfg;
+    t->stream = dcg::as_stream(stream);
+    Alloc dry{t, true};
+    layout(t, dry);
+    t->arena_bytes = dcg::align_up(dry.off, 256) + 256;
+    if (cudaMalloc(&t->arena, t->arena_bytes) != cudaSuccess) {
+        const size_t want = t->arena_bytes;
+        delete t;
+        return fail(DCG_ERR_CUDA, "dcg_trainer_create: cudaMalloc of %zu bytes failed", want);
+    }
+    cudaMemsetAsync(t->arena, 0, t->arena_bytes, t->stream);
+    Alloc real{t, false};
+    layout(t, real);
+    t->arena_used = real.off;
+    int st = dcg_context_create(&t->ctx, cfg->precision, nullptr, 0, stream);
+    if (st) { cudaFree(t->arena); delete t; return st; }
+
+    // weights ~ N(0, 0.02), biases 0 (dcgan/main.cu:60-63, 148-151); labels
+    Rng rng(cfg->seed ? cfg->seed : 234);
+    auto fill_normal = [&](Tensor& w) {
+        std::vector<float> h(w.n);
+        for (size_t i = 0; i < w.n; ++i) h[i] = rng.normal(0.02f);
+        cudaMemcpyAsync(w.p, h.data(), w.n * sizeof(float), cudaMemcpyHostToDevice, t->stream);
+        cudaStreamSynchronize(t->stream);
+    };
+    for (int i = 0; i < 10; i += 2) { fill_normal(t->g_param[i]); fill_normal(t->d_param[i]); }
+    std::vector<float> one(cfg->batch, 1.f);
+    cudaMemcpyAsync(t->ones.p, one.data(), one.size() * sizeof(float), cudaMemcpyHostToDevice, t->stream);
+    cudaStreamSynchronize(t->stream);
+    build_lists(t);
+    if (cudaGetLastError() != cudaSuccess) {
+        dcg_trainer_destroy(t);
+        return fail(DCG_ERR_CUDA, "dcg_trainer_create: initialisation copies failed");
+    }
+    *out = t;
+    return DCG_OK;
+}
+
+extern "C" void dcg_trainer_destroy(dcg_trainer* t)
+{
+    if (!t) return;
+    if (t->ctx) dcg_context_destroy(t->ctx);
+    if (t->arena) cudaFree(t->arena);
+    delete t;
+}
+
+extern "C" int dcg_trainer_generate(dcg_trainer* t)
+{
+    DCG_CHECK_ARG(t, "dcg_trainer_generate: null trainer");
+    return run_list(t, t->gen_nodes);
+}
+
+extern "C" int dcg_trainer_d_backward(dcg_trainer* t)
+{
+    DCG_CHECK_ARG(t, "dcg_trainer_d_backward: null trainer");
+    int st = run_list(t, t->d_nodes);
+    if (st) return st;
+    if (t->cfg.world > 1) {
+        // sum the two gradient paths now (the Add op of src/ops/graph.cu:302-309) so that one
+        // all-reduce of the gradient arena averages the final gradients
+        for (int i = 0; i < 10; ++i)
+            if ((st = dcg_add(t->d_grad[i].p, t->d_grad2[i].p, t->d_grad[i].p, t->d_grad[i].n, t->stream))) return st;
+    }
+    return DCG_OK;
+}
+
+extern "C" int dcg_trainer_d_apply(dcg_trainer* t, float grad_scale)
+{
+    DCG_CHECK_ARG(t, "dcg_trainer_d_apply: null trainer");
+    return apply_adam(t, t->d_param, t->d_grad, t->cfg.world > 1 ? nullptr : t->d_grad2, t->d_m, t->d_v, &t->d_t,
+                      grad_scale);
+}
+
+extern "C" int dcg_trainer_g_backward(dcg_trainer* t)
+{
+    DCG_CHECK_ARG(t, "dcg_trainer_g_backward: null trainer");
+    return run_list(t, t->g_nodes);
+}
+
+extern "C" int dcg_trainer_g_apply(dcg_trainer* t, float grad_scale)
+{
+    DCG_CHECK_ARG(t, "dcg_trainer_g_apply: null trainer");
+    return apply_adam(t, t->g_param, t->g_grad, nullptr, t->g_m, t->g_v, &t->g_t, grad_scale);
+}
+
+extern "C" int dcg_trainer_step(dcg_trainer* t)
+{
+    DCG_CHECK_ARG(t, "dcg_trainer_step: null trainer");
+    DCG_CHECK_ARG(t->cfg.world <= 1, "dcg_trainer_step: data-parallel callers drive the phases themselves");
+    const uint64_t before = dcg_launches_total();
+    int st;
+    if ((st = dcg_trainer_d_backward(t))) return st;
+    if ((st = dcg_trainer_d_apply(t, 1.f))) return st;
+    for (int rep = 0; rep < 2; ++rep) {
+        if ((st = dcg_trainer_g_backward(t))) return st;
+        if ((st = dcg_trainer_g_apply(t, 1.f))) return st;
+    }
+    t->last_step_launches = dcg_launches_total() - before;
+    return DCG_OK;
+}
+
+extern "C" int dcg_trainer_tensor(dcg_trainer* t, const char* name, float** ptr, size_t* count)
+{
+    DCG_CHECK_ARG(t && name && ptr && count, "dcg_trainer_tensor: null argument");
+    const std::string s(name);
+    Tensor r;
+    auto indexed = [&](const char* prefix, Tensor* arr, int n) -> bool {
+        const size_t len = std::strlen(prefix);
+        if (s.compare(0, len, prefix) != 0 || s.size() != len + 1) return false;
+        const int i = s[len] - '0';
+        if (i < 0 || i >= n) return false;
+        r = arr[i];
+        return true;
+    };
+    if (s == "x") r = t->x;
+    else if (s == "z") r = t->z;
+    else if (s == "g_out") r = t->g_out;
+    else if (s == "d_loss") r = t->d_loss;
+    else if (s == "g_loss") r = t->g_loss;
+    else if (s == "d_params") r = t->d_params_all;
+    else if (s == "g_params") r = t->g_params_all;
+    else if (s == "d_grads") r = t->d_grads_all;
+    else if (s == "g_grads") r = t->g_grads_all;
+    else if (s == "logits_fake") r = t->logits[0];
+    else if (s == "logits_real") r = t->logits[1];
+    else if (indexed("d_param", t->d_param, 10) || indexed("g_param", t->g_param, 10) ||
+             indexed("d_grad", t->d_grad, 10) || indexed("g_grad", t->g_grad, 10) ||
+             indexed("d_gradb", t->d_grad2, 10) || indexed("d_m", t->d_m, 10) || indexed("d_v", t->d_v, 10) ||
+             indexed("g_m", t->g_m, 10) || indexed("g_v", t->g_v, 10)) {
+    } else {
+        return fail(DCG_ERR_INVALID, "dcg_trainer_tensor: unknown tensor '%s'", name);
+    }
+    *ptr = r.p;
+    *count = r.n;
+    return DCG_OK;
+}
+
+extern "C" dcg_context* dcg_trainer_context(dcg_trainer* t) { return t ? t->ctx : nullptr; }
+
+extern "C" uint64_t dcg_trainer_step_launches(const dcg_trainer* t) { return t ? t->last_step_launches : 0; }
+
+extern "C" size_t dcg_trainer_arena_bytes(const dcg_trainer* t) { return t ? t->arena_bytes : 0; }

@@ -1,0 +1,115 @@
+"""DCGAN training step driver: thin Python over dcg_trainer (csrc/trainer.cu).
+
+The C++ trainer owns the model (one device arena) and executes the node lists of
+one training iteration.  This wrapper adds what lives above the C ABI:
+
+* zero-copy torch views of the trainer's device tensors (inputs, losses,
+  parameter and gradient arenas);
+* the end-to-end step with HOST inputs: pinned host -> device copies of the real
+  images and the noise, the iteration, a device -> host read of the two losses;
+* data-parallel training: one process per GPU, each on its own 64-image shard;
+  between *_backward and *_apply the gradient arena of the network being updated
+  is summed over ranks with one torch.distributed all_reduce (NCCL on GPUs), and
+  Adam divides by the world size.  Replicas start from the same seed and apply
+  identical updates, so parameters stay identical on every rank.
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import TrainerConfig, check, lib
+
+
+class _CudaView:
+    """Minimal __cuda_array_interface__ carrier so torch can wrap a raw device pointer."""
+
+    def __init__(self, ptr, n):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+class Trainer:
+    def __init__(self, batch=64, precision=_lib.PREC_TF32, fuse=True, g_leaky=False, lr=2e-4, beta1=0.5,
+                 beta2=0.999, eps=1e-8, seed=234, world=1, device=None, process_group=None):
+        self.device = torch.device(device if device is not None else "cuda:%d" % torch.cuda.current_device())
+        torch.cuda.set_device(self.device)
+        self.batch, self.world, self.group = batch, world, process_group
+        self.cfg = TrainerConfig(batch, world, precision, 1 if fuse else 0, 1 if g_leaky else 0, lr, beta1,
+                                 beta2, eps, seed)
+        self._h = ctypes.c_void_p()
+        self.stream = torch.cuda.current_stream(self.device)
+        check(lib.dcg_trainer_create(ctypes.byref(self._h), ctypes.byref(self.cfg), self.stream.cuda_stream))
+        self._views = {}
+        self.x = self.tensor("x").view(batch, 64, 64, 3)
+        self.z = self.tensor("z").view(batch, 100)
+        self.g_out = self.tensor("g_out").view(batch, 64, 64, 3)
+        self.d_loss, self.g_loss = self.tensor("d_loss"), self.tensor("g_loss")
+        self.d_grads, self.g_grads = self.tensor("d_grads"), self.tensor("g_grads")
+        # pinned staging for the end-to-end step
+        self._hx = torch.empty((batch, 64, 64, 3), dtype=torch.float32).pin_memory()
+        self._hz = torch.empty((batch, 100), dtype=torch.float32).pin_memory()
+        self._hloss = torch.empty((2,), dtype=torch.float32).pin_memory()
+
+    # ---- device tensors ------------------------------------------------------
+    def tensor(self, name):
+        """Zero-copy torch view (1-D, fp32) of a trainer tensor; see dcg_trainer_tensor for names."""
+        if name not in self._views:
+            ptr, n = ctypes.c_void_p(), ctypes.c_size_t()
+            check(lib.dcg_trainer_tensor(self._h, name.encode(), ctypes.byref(ptr), ctypes.byref(n)))
+            self._views[name] = torch.as_tensor(_CudaView(ptr.value, n.value), device=self.device)
+        return self._views[name]
+
+    def arena_bytes(self):
+        return int(lib.dcg_trainer_arena_bytes(self._h))
+
+    # ---- phases ----------------------------------------------------------------
+    def generate(self):
+        check(lib.dcg_trainer_generate(self._h))
+        return self.g_out
+
+    def _allreduce(self, grads):
+        if self.world > 1:
+            torch.distributed.all_reduce(grads, group=self.group)
+
+    def step(self):
+        """One training iteration on inputs already resident in self.x / self.z."""
+        scale = 1.0 / self.world
+        check(lib.dcg_trainer_d_backward(self._h))
+        self._allreduce(self.d_grads)
+        check(lib.dcg_trainer_d_apply(self._h, scale))
+        for _ in range(2):
+            check(lib.dcg_trainer_g_backward(self._h))
+            self._allreduce(self.g_grads)
+            check(lib.dcg_trainer_g_apply(self._h, scale))
+
+    def step_host(self, x_host, z_host):
+        """End-to-end iteration: x_host [B,64,64,3] and z_host [B,100] are HOST arrays (numpy or
+        CPU torch); returns (d_loss, g_loss) as Python floats read back from the device."""
+        self._hx.copy_(torch.as_tensor(x_host).reshape(self._hx.shape))
+        self._hz.copy_(torch.as_tensor(z_host).reshape(self._hz.shape))
+        self.x.copy_(self._hx, non_blocking=True)
+        self.z.copy_(self._hz, non_blocking=True)
+        self.step()
+        self._hloss[0:1].copy_(self.d_loss, non_blocking=True)
+        self._hloss[1:2].copy_(self.g_loss, non_blocking=True)
+        self.stream.synchronize()
+        return float(self._hloss[0]), float(self._hloss[1])
+
+    h2d_bytes_per_step = property(lambda self: self.batch * (64 * 64 * 3 + 100) * 4)
+    d2h_bytes_per_step = property(lambda self: 8)
+
+    def launches_per_step(self):
+        return int(lib.dcg_trainer_step_launches(self._h))
+
+    def close(self):
+        if self._h:
+            self._views.clear()
+            lib.dcg_trainer_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

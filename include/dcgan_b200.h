@@ -285,6 +285,21 @@ int dcg_context_set_precision(dcg_context* ctx, int precision);
 /* Number of kernels launched through this context so far. */
 uint64_t dcg_context_launch_count(const dcg_context* ctx);
 
+/* Profiling mode: the counterpart of the reference's Graph::debug_set timing printout
+ * (src/ops/graph.cu:153-221), per launch group instead of per run.  Between begin and end every
+ * group the context launches (a fused convolution, a single node, a multi-tensor Adam) is
+ * bracketed by CUDA events on the context's stream.  end synchronises the stream and returns one
+ * row per distinct group name: calls, summed device milliseconds, summed algorithmic FLOPs
+ * (2*B*Ho*Wo*KH*KW*Cin*Cout for the convolutions, 0 for the memory-bound groups). */
+typedef struct dcg_profile_row {
+    char name[96];
+    uint64_t calls;
+    double ms;
+    double flops;
+} dcg_profile_row;
+int dcg_context_profile_begin(dcg_context* ctx);
+int dcg_context_profile_end(dcg_context* ctx, dcg_profile_row* rows, int max_rows, int* n_rows);
+
 /* Executes one node: the function gpu::kernels_list[node->type] stands for
  * (src/gpu/kernels.cu:20-64).  Asynchronous on the context's stream. */
 int dcg_run_node(dcg_context* ctx, const dcg_node* node);
@@ -297,6 +312,52 @@ int dcg_run_node(dcg_context* ctx, const dcg_node* node);
  * multi-tensor launch.  Results are identical to unfused execution except for
  * buffers flagged DCG_NODE_OUT_DEAD. */
 int dcg_run_nodes(dcg_context* ctx, const dcg_node* nodes, int count, int fuse);
+
+/* ---- DCGAN training step: the caller of the hot path ----------------------
+ * Host-side counterpart of dcgan/main.cu:271-410: the generator / discriminator
+ * of that file lowered to node lists (forward, autodiff gradients) and executed
+ * through dcg_run_nodes, followed by the fused Adam update.  One training
+ * iteration is one discriminator update and two generator updates, each
+ * recomputing its forward passes, as dcgan/main.cu:378-391 does. */
+typedef struct dcg_trainer dcg_trainer;
+
+typedef struct dcg_trainer_config {
+    int batch;           /* images per step on this GPU (dcgan/main.cu:33: 64) */
+    int world;           /* data-parallel ranks; > 1 makes d_backward sum the two gradient paths
+                            so one all-reduce of "d_grads" averages the final gradients */
+    int precision;       /* dcg_precision of the convolutions */
+    int fuse;            /* node fusion on/off (dcg_run_nodes) */
+    int g_leaky;         /* generator activation: 0 = relu (dcgan/main.cu:69,97), 1 = leaky-relu(0.2) */
+    float lr, beta1, beta2, eps; /* Adam (dcgan/main.cu:35-36, src/api/adam-optimizer.hh:11-14) */
+    uint64_t seed;       /* weights ~ N(0, 0.02) from the xorshift generator, biases 0 */
+} dcg_trainer_config;
+
+/* Allocates one device arena (parameters, Adam state, gradients, activations) and builds the
+ * node lists.  The only allocating entry point besides dcg_context_create. */
+int dcg_trainer_create(dcg_trainer** out, const dcg_trainer_config* cfg, dcg_stream_t stream);
+void dcg_trainer_destroy(dcg_trainer* t);
+/* Device tensors by name: "x" [B,64,64,3] real images and "z" [B,100] noise (inputs the caller
+ * fills), "g_out", "d_loss", "g_loss", "logits_fake", "logits_real", the contiguous per-network
+ * arenas "d_params", "g_params", "d_grads", "g_grads", and single variables "d_param0".."d_param9",
+ * "g_param0".., "d_grad0".., "d_gradb0".. (second path), "g_grad0".., "d_m0", "d_v0", "g_m0", "g_v0"..
+ * Variable order: (kernel, bias) of conv layers 0..3, then dense weight, dense bias. */
+int dcg_trainer_tensor(dcg_trainer* t, const char* name, float** ptr, size_t* count);
+/* Generator forward only (z -> g_out): dcgan/main.cu:252-269. */
+int dcg_trainer_generate(dcg_trainer* t);
+/* graph.run({d_opti, d_loss}) minus the update: G forward, D on fake and real, d_loss, D gradients. */
+int dcg_trainer_d_backward(dcg_trainer* t);
+/* Adam on the discriminator with gradients scaled by grad_scale (1/world after an all-reduce). */
+int dcg_trainer_d_apply(dcg_trainer* t, float grad_scale);
+/* graph.run({g_opti, g_loss}) minus the update: G forward, D on fake, g_loss, G gradients. */
+int dcg_trainer_g_backward(dcg_trainer* t);
+int dcg_trainer_g_apply(dcg_trainer* t, float grad_scale);
+/* One whole iteration on a single GPU: d_backward, d_apply, then twice g_backward, g_apply. */
+int dcg_trainer_step(dcg_trainer* t);
+/* The trainer's execution context (for dcg_context_profile_begin / _end around its phases). */
+dcg_context* dcg_trainer_context(dcg_trainer* t);
+/* Kernels launched by the last dcg_trainer_step. */
+uint64_t dcg_trainer_step_launches(const dcg_trainer* t);
+size_t dcg_trainer_arena_bytes(const dcg_trainer* t);
 
 /* ---- diagnostics --------------------------------------------------------- */
 /* Synchronises the device, then reads and clears the status word the tensor-path

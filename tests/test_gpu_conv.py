@@ -165,9 +165,13 @@ def test_full_batch_layers_tf32_vs_fp32_path(pkg, dev, layer):
         lim = TF32_TOL * a.abs().max().item()
         assert (a - b).abs().max().item() <= lim, name
     y, dx, dk = (t.double() for t in outs[pkg.PREC_TF32])
-    lhs = (y * dy.double()).sum().item()
-    assert abs(lhs - (dx * x.double()).sum().item()) <= 2e-3 * abs(lhs) + 1e-3
-    assert abs(lhs - (dk * k.double()).sum().item()) <= 2e-3 * abs(lhs) + 1e-3
+    terms = y * dy.double()
+    lhs = terms.sum().item()
+    # the inner product is a sum of ~1e6 signed terms that largely cancel; TF32 rounding (~5e-4 per
+    # term, random sign) perturbs it by about 5e-4 * sqrt(sum of squared terms)
+    tol = 5e-3 * terms.pow(2).sum().sqrt().item() + 1e-3
+    assert abs(lhs - (dx * x.double()).sum().item()) <= tol
+    assert abs(lhs - (dk * k.double()).sum().item()) <= tol
 
 
 def test_deterministic(pkg, dev):

@@ -1,0 +1,119 @@
+"""The DCGAN training step (dcg_trainer, node lists + fusion) against the CPU restatement of
+dcgan/main.cu built from oracle operators, on identical parameters and inputs."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oracle import dcgan_model as M
+
+pytestmark = pytest.mark.gpu
+
+
+def _load_state(tr, st):
+    for i in range(10):
+        tr.tensor("g_param%d" % i).copy_(torch.from_numpy(st["g"][i].reshape(-1)))
+        tr.tensor("d_param%d" % i).copy_(torch.from_numpy(st["d"][i].reshape(-1)))
+
+
+def _maxrel(got, ref):
+    return float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+@pytest.mark.parametrize("prec_name,tol", [("fp32", 2e-5), ("tf32", 1e-2)])
+@pytest.mark.parametrize("fuse", [False, True])
+def test_gradients_match_cpu_model(pkg, dev, orc, prec_name, tol, fuse):
+    """Every weight gradient of the D run and the G run, per layer, within tol * max|ref|
+    (fp32 path: summation-order noise only; TF32 tensor path: the stated 1e-2)."""
+    B = 2
+    rng = np.random.default_rng(3)
+    st = M.init_state(rng, B)
+    for i in (1, 3, 5, 7, 9):   # non-zero biases make the bias path visible
+        st["g"][i] = (rng.standard_normal(st["g"][i].shape) * 0.05).astype(np.float32)
+        st["d"][i] = (rng.standard_normal(st["d"][i].shape) * 0.05).astype(np.float32)
+    x = rng.uniform(-1, 1, (B, 64, 64, 3)).astype(np.float32)
+    z = rng.uniform(-1, 1, (B, 100)).astype(np.float32)
+    prec = pkg.PREC_FP32 if prec_name == "fp32" else pkg.PREC_TF32
+    tr = pkg.Trainer(batch=B, precision=prec, fuse=fuse)
+    _load_state(tr, st)
+    tr.x.copy_(torch.from_numpy(x))
+    tr.z.copy_(torch.from_numpy(z))
+
+    d_loss, gf, gr = M.run(M.d_gradients(orc, st, x, z))
+    pkg._lib.check(pkg.lib.dcg_trainer_d_backward(tr._h))
+    torch.cuda.synchronize()
+    assert pkg.lib.dcg_device_status() == 0
+    assert abs(tr.d_loss.item() - float(d_loss)) <= tol * abs(float(d_loss)) + 1e-6
+    for i in range(10):
+        assert _maxrel(tr.tensor("d_grad%d" % i).cpu().numpy(), gf[i].reshape(-1)) <= tol, ("fake", i)
+        assert _maxrel(tr.tensor("d_gradb%d" % i).cpu().numpy(), gr[i].reshape(-1)) <= tol, ("real", i)
+
+    g_loss, gg = M.run(M.g_gradients(orc, st, z))
+    pkg._lib.check(pkg.lib.dcg_trainer_g_backward(tr._h))
+    torch.cuda.synchronize()
+    assert pkg.lib.dcg_device_status() == 0
+    assert abs(tr.g_loss.item() - float(g_loss)) <= tol * abs(float(g_loss)) + 1e-6
+    for i in range(10):
+        assert _maxrel(tr.tensor("g_grad%d" % i).cpu().numpy(), gg[i].reshape(-1)) <= tol, ("gen", i)
+    tr.close()
+
+
+def test_iteration_matches_cpu_model(pkg, dev, orc):
+    """Two whole iterations (D update + 2 G updates each) on the fp32 path: parameters after the
+    Adam updates follow the CPU model (Adam itself is bit-exact; the gradients carry reduction-order
+    noise, so parameters are compared to a few 1e-6)."""
+    B = 2
+    rng = np.random.default_rng(5)
+    st = M.init_state(rng, B)
+    tr = pkg.Trainer(batch=B, precision=pkg.PREC_FP32, fuse=True)
+    _load_state(tr, st)
+    for it in range(2):
+        x = rng.uniform(-1, 1, (B, 64, 64, 3)).astype(np.float32)
+        z = rng.uniform(-1, 1, (B, 100)).astype(np.float32)
+        d_ref, g_ref = M.run(M.train_iteration(orc, st, x, z))
+        d_got, g_got = tr.step_host(x, z)
+        assert abs(d_got - float(d_ref)) < 1e-4 and abs(g_got - float(g_ref)) < 1e-4
+    for i in range(10):
+        for net in ("g", "d"):
+            got = tr.tensor("%s_param%d" % (net, i)).cpu().numpy()
+            ref = st[net][i].reshape(-1)
+            # Adam's first steps move each weight by ~lr whatever the gradient's size, so a sign flip
+            # of a near-zero gradient shows up as 2*lr: bound the difference by a few lr
+            assert np.abs(got - ref).max() <= 3 * 2e-4 + 1e-6, (net, i)
+            assert np.mean(np.abs(got - ref) > 1e-5) < 0.02, (net, i)
+    tr.close()
+
+
+def test_fused_and_unfused_steps_are_identical(pkg, dev):
+    B = 4
+    g = torch.Generator().manual_seed(1)
+    x = torch.rand((B, 64, 64, 3), generator=g) * 2 - 1
+    z = torch.rand((B, 100), generator=g) * 2 - 1
+    params = {}
+    for fuse in (False, True):
+        tr = pkg.Trainer(batch=B, precision=pkg.PREC_TF32, fuse=fuse, seed=77)
+        before = pkg.launches_total()
+        losses = tr.step_host(x.numpy(), z.numpy())
+        launches = pkg.launches_total() - before
+        params[fuse] = (torch.cat([tr.tensor("d_params"), tr.tensor("g_params")]).cpu(), losses, launches)
+        tr.close()
+    assert torch.equal(params[False][0], params[True][0])
+    assert params[False][1] == params[True][1]
+    assert params[True][2] < params[False][2]
+
+
+def test_generate_matches_cpu_model(pkg, dev, orc):
+    """Config 0 of the benchmark set: generator forward, leaky-relu(0.2) between layers, tanh out."""
+    B = 2
+    rng = np.random.default_rng(9)
+    st = M.init_state(rng, B)
+    z = rng.uniform(-1, 1, (B, 100)).astype(np.float32)
+    ref, _ = M.run(M.generator_forward(orc, st["g"], z, g_leaky=True))
+    for prec, tol in ((pkg.PREC_FP32, 1e-5), (pkg.PREC_TF32, 1e-2)):
+        tr = pkg.Trainer(batch=B, precision=prec, g_leaky=True)
+        _load_state(tr, st)
+        tr.z.copy_(torch.from_numpy(z))
+        out = tr.generate()
+        torch.cuda.synchronize()
+        assert _maxrel(out.cpu().numpy(), ref) <= tol
+        tr.close()
