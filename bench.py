@@ -339,6 +339,8 @@ def run_sweep(args):
     for B in args.sweep_batches:
         for name, H, C, O in (("D0/G3", 64, 3, 64), ("D1/G2", 32, 64, 128), ("D2/G1", 16, 128, 256),
                               ("D3/G0", 8, 256, 512)):
+            if args.sweep_layers and name.split("/")[0] not in args.sweep_layers:
+                continue
             x = torch.rand(B, H, H, C, device=dev) * 2 - 1
             k = torch.randn(5, 5, C, O, device=dev) * 0.02
             dy = torch.rand(B, H // 2, H // 2, O, device=dev) * 2 - 1
@@ -347,6 +349,8 @@ def run_sweep(args):
             ops = (("fwd", lambda: F.conv2d_fwd(x, k, out=y)), ("dx", lambda: F.conv2d_dx(dy, k, (H, H), out=dx)),
                    ("dk", lambda: F.conv2d_dk(x, dy, (5, 5), out=dk)))
             for op, fn in ops:
+                if args.sweep_ops and op not in args.sweep_ops:
+                    continue
                 for _ in range(3):
                     fn()
                 times = []
@@ -379,6 +383,8 @@ def main():
     ap.add_argument("--sweep", action="store_true")
     ap.add_argument("--sweep-batches", type=int, nargs="+", default=[64, 256, 1024])
     ap.add_argument("--sweep-iters", type=int, default=30)
+    ap.add_argument("--sweep-layers", nargs="*", default=None, help="subset of D0 D1 D2 D3")
+    ap.add_argument("--sweep-ops", nargs="*", default=None, help="subset of fwd dx dk")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))

@@ -60,6 +60,7 @@ struct Params {
     int splits;                   // K partitions
     int kchunks;                  // 32-wide chunks along the contracted channel axis (FWD: C, DX: O)
     int swap;                     // DK: M axis is o (A from dy, B from x)
+    int narrow;                   // FWD/DK with <= 4 input channels: x is read through the window map
     int stages;                   // pipeline depth
     int direct;                   // 1: epilogue + final store, 0: raw partial to scratch
     float* out;                   // final tensor (direct) or scratch base
@@ -243,11 +244,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         taps_h = rh < p.KH ? (p.KH - rh + p.sh - 1) / p.sh : 0;
         taps_w = rw < p.KW ? (p.KW - rw + p.sw - 1) / p.sw : 0;
     } else if (MODE == MODE_DK) {
-        tap_di = group / p.KW; tap_dj = group % p.KW;
+        if (p.narrow) { tap_di = group; tap_dj = 0; }   // one group per kernel row, all columns at once
+        else { tap_di = group / p.KW; tap_dj = group % p.KW; }
     }
     // K-stage range of this split
     int total_stages;
-    if (MODE == MODE_FWD) total_stages = p.KH * p.KW * p.kchunks;
+    if (MODE == MODE_FWD) total_stages = p.narrow ? p.KH : p.KH * p.KW * p.kchunks;
     else if (MODE == MODE_DX) total_stages = taps_h * taps_w * p.kchunks;
     else total_stages = p.tiles_w * p.tiles_h * p.tiles_n;
     const int q0 = (int)((long long)total_stages * split / p.splits);
@@ -289,7 +291,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint32_t a_dst = a_base + (uint32_t)s * A_STAGE_BYTES;
                 const uint32_t b_dst = b_base + (uint32_t)s * b_stage_bytes;
                 const int q = q0 + it;
-                if (MODE == MODE_FWD) {
+                if (MODE == MODE_FWD && p.narrow) {
+                    // stage q = kernel row q: 128 output pixels x the 32-float window (8 pixels x 4
+                    // channels) that starts at padded column s*j of padded row s*i + q
+                    tma_load_5d(a_dst, &map_a, fb, 0, j0, i0, n0, q);
+                    tma_load_4d(b_dst, &map_b, fb, 0, 0, q, n_tile * (p.bn / 32));
+                } else if (MODE == MODE_FWD) {
                     const int tap = q / p.kchunks, cc = q % p.kchunks;
                     const int di = tap / p.KW, dj = tap % p.KW;
                     tma_load_4d(a_dst, &map_a, fb, cc * BK, p.sw * j0 + dj - p.pl, p.sh * i0 + di - p.pt, n0);
@@ -305,7 +312,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const int pi = ((q / p.tiles_w) % p.tiles_h) * p.TH;
                     const int pn = (q / (p.tiles_w * p.tiles_h)) * p.TN;
                     const int xw = p.sw * pj + tap_dj - p.pl, xh = p.sh * pi + tap_di - p.pt;
-                    if (!p.swap) {   // A: x (rows c), B: dy (cols o)
+                    if (p.narrow) {  // A: dy (rows o), B: the 32-float windows of 32 output pixels, row tap_di
+                        tma_load_5d(a_dst, &map_a, fb, 0, pj, pi, pn, m_tile * (BM / 32));
+                        tma_load_5d(b_dst, &map_b, fb, 0, pj, pi, pn, tap_di);
+                    } else if (!p.swap) {   // A: x (rows c), B: dy (cols o)
                         tma_load_5d(a_dst, &map_a, fb, 0, xw, xh, pn, m_tile * (BM / 32));
                         tma_load_5d(b_dst, &map_b, fb, 0, pj, pi, pn, n_tile * (p.bn / 32));
                     } else {         // A: dy (rows o), B: x (cols c)
@@ -378,7 +388,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             ncols_valid = min(p.bn, p.C - ch0);
         } else {
             const unsigned long long tap_off = (unsigned long long)group * p.C * p.O;
-            if (!p.swap) {   // rows c, columns o
+            if (p.narrow) {  // rows o, columns = window slots (kernel column dj = slot / 4, channel = slot % 4)
+                const int o = m_tile * BM + row;
+                row_valid = o < p.O;
+                row_off = (unsigned long long)group * p.KW * p.C * p.O + o;   // group = kernel row
+                col_stride = p.O;        // never used as such: narrow_off() maps slots to dk
+                ncols_valid = 4 * p.KW;
+            } else if (!p.swap) {   // rows c, columns o
                 const int c = m_tile * BM + row;
                 row_valid = c < p.C;
                 row_off = tap_off + (unsigned long long)c * p.O + ch0;
@@ -440,7 +456,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
                             if (col + u >= ncols_valid) break;
-                            const unsigned long long id = idx + (unsigned long long)u * col_stride;
+                            unsigned long long id = idx + (unsigned long long)u * col_stride;
+                            if (MODE == MODE_DK && p.narrow) {
+                                if (u >= p.C) break;   // slot = 4*dj + channel, channels beyond C are padding
+                                id = row_off + (unsigned long long)((col >> 2) * p.C + u) * p.O;
+                            }
                             // the epilogue chain only applies to FWD/DX, whose columns are contiguous
                             dst[id] = (MODE == MODE_DK) ? __uint_as_float(r[q + u])
                                                         : epilogue_apply(p.ep, __uint_as_float(r[q + u]), id, ch0 + col + u);
@@ -459,9 +479,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                         __uint_as_float(r[q + 2]), __uint_as_float(r[q + 3]));
                     } else {
 #pragma unroll
-                        for (int u = 0; u < 4; ++u)
-                            if (col + u < ncols_valid)
-                                dst[idx + (unsigned long long)u * col_stride] = __uint_as_float(r[q + u]);
+                        for (int u = 0; u < 4; ++u) {
+                            if (col + u >= ncols_valid) break;
+                            unsigned long long id = idx + (unsigned long long)u * col_stride;
+                            if (MODE == MODE_DK && p.narrow) {
+                                if (u >= p.C) break;
+                                id = row_off + (unsigned long long)((col >> 2) * p.C + u) * p.O;
+                            }
+                            dst[id] = __uint_as_float(r[q + u]);
+                        }
                     }
                 }
             }
@@ -509,6 +535,48 @@ splitk_finish_kernel(const float* __restrict__ partial, float* __restrict__ out,
             for (int s = 1; s < splits; ++s) acc = __fadd_rn(acc, __ldg(partial + (unsigned long long)s * n + i));
             out[i] = plain ? acc : epilogue_apply(ep, acc, i, (int)(i % (unsigned long long)channels));
         }
+    }
+}
+
+// ---- narrow-channel layers (<= 4 input channels: the RGB end of both networks) -------------------
+// A 3-channel NHWC pixel is 12 bytes, which TMA cannot address (16-byte granularity), and a K of
+// 3 per tap would waste the tensor core.  Such an input is first copied into a zero-bordered
+// 4-channel image xp[n][h + pad_top][w + pad_left][4]; in that image the five taps of one kernel
+// row that output pixel (i, j) needs are 32 CONTIGUOUS floats (8 pixels x 4 channels, the last 3
+// pixels unused) starting at xp[n][s*i + di][s*j][0].  A tensor map whose pixel stride (s*16 bytes)
+// is smaller than its 128-byte inner extent hands these overlapping windows to TMA directly, so a
+// whole kernel row becomes one K = 32 step: FWD contracts it against the row's weights repacked as
+// k4[di][4*dj + c][o]; DK contracts the window against dy over pixels and scatters the 32 slots
+// back to dk[di][dj][c][o].
+__global__ void __launch_bounds__(256)
+repack_narrow_kernel(const float* __restrict__ x, float4* __restrict__ xp, int N, int H, int W, int C,
+                     int Hp, int Wp, int pt, int pl)
+{
+    const size_t total = (size_t)N * Hp * Wp;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int wp = (int)(i % Wp);
+        const int hp = (int)((i / Wp) % Hp);
+        const int n = (int)(i / ((size_t)Wp * Hp));
+        const int h = hp - pt, w = wp - pl;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (h >= 0 && h < H && w >= 0 && w < W) {
+            const float* src = x + (((size_t)n * H + h) * W + w) * C;
+            for (int c = 0; c < C; ++c) v[c] = __ldg(src + c);
+        }
+        xp[i] = make_float4(v[0], v[1], v[2], v[3]);
+    }
+}
+
+// k [KH][KW][C][O] -> k4 [KH][32][O], row 4*dj + c; rows of unused slots are zero.
+__global__ void __launch_bounds__(256)
+repack_k4_kernel(const float* __restrict__ k, float* __restrict__ k4, int KH, int KW, int C, int O)
+{
+    const int total = KH * 32 * O;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int o = i % O, slot = (i / O) % 32, di = i / (O * 32);
+        const int dj = slot >> 2, c = slot & 3;
+        k4[i] = (dj < KW && c < C) ? __ldg(k + (((size_t)di * KW + dj) * C + c) * O + o) : 0.f;
     }
 }
 
@@ -596,7 +664,12 @@ struct Plan {
     Params p;
     int grid;
     size_t smem;
-    size_t ws_bytes;   // scratch for split-K partials (0 when splits == 1)
+    // scratch layout: [split-K partials][padded 4-channel input xp][repacked weights k4], each
+    // part 256-byte aligned; the last two only exist for narrow-channel layers
+    size_t partial_bytes = 0, xp_bytes = 0, k4_bytes = 0, ws_bytes = 0;
+    int Hp = 0, Wp = 0;   // padded input extent of a narrow-channel layer
+    size_t xp_off() const { return align_up(partial_bytes, 256); }
+    size_t k4_off() const { return xp_off() + align_up(xp_bytes, 256); }
 };
 
 // DCG_TC_SPLITS / DCG_TC_STAGES (environment, read once) pin the K partitioning and the pipeline
@@ -616,7 +689,7 @@ int choose_splits(int tiles, int min_stages_per_tile)
     int s = (2 * sms) / tiles;                       // aim at ~2 CTAs per SM
     const int cap = min_stages_per_tile / 4;         // keep at least 4 K stages per CTA
     if (s > cap) s = cap;
-    if (s > 16) s = 16;
+    if (s > 32) s = 32;
     return s < 1 ? 1 : s;
 }
 
@@ -634,8 +707,26 @@ void finish_plan(Plan& pl)
     if (stages < 2) stages = 2;
     p.stages = stages;
     pl.smem = (size_t)stages * per_stage + 1024 /*alignment slack*/ + 16 * stages + 32;
-    pl.ws_bytes = p.splits > 1 ? (size_t)p.splits * p.out_elems * sizeof(float) : 0;
+    pl.partial_bytes = p.splits > 1 ? (size_t)p.splits * p.out_elems * sizeof(float) : 0;
+    pl.ws_bytes = pl.partial_bytes;
+    if (pl.xp_bytes || pl.k4_bytes) pl.ws_bytes = pl.k4_off() + align_up(pl.k4_bytes, 256);
     p.direct = p.splits == 1 ? 1 : 0;
+}
+
+// Padded-image geometry of a narrow-channel layer: rows s*i + di and columns s*j .. s*j + 7 of xp
+// must exist for every output pixel and kernel row.
+void narrow_geometry(const dcg_conv_desc& d, Plan& pl)
+{
+    pl.Hp = d.stride_h * (d.ho - 1) + d.kh;
+    pl.Wp = (d.stride_w * (d.wo - 1) + 8 + 3) / 4 * 4;
+    if (pl.Hp < d.h + d.pad_top) pl.Hp = d.h + d.pad_top;
+    if (pl.Wp < d.w + d.pad_left) pl.Wp = (d.w + d.pad_left + 3) / 4 * 4;
+    pl.xp_bytes = (size_t)d.n * pl.Hp * pl.Wp * 16;
+}
+
+bool narrow_ok(const dcg_conv_desc& d)
+{
+    return d.c <= 4 && d.kw <= 8 && d.o % 32 == 0 && d.stride_h <= 8 && d.stride_w <= 8;
 }
 
 void base_params(Params& p, const dcg_conv_desc& d)
@@ -648,7 +739,8 @@ void base_params(Params& p, const dcg_conv_desc& d)
 
 bool plan_fwd(const dcg_conv_desc& d, Plan& pl)
 {
-    if (d.c % 4 != 0 || d.o % 32 != 0 || d.stride_h > 8 || d.stride_w > 8) return false;
+    const bool narrow = narrow_ok(d);
+    if (!narrow && (d.c % 4 != 0 || d.o % 32 != 0 || d.stride_h > 8 || d.stride_w > 8)) return false;
     Params& p = pl.p;
     base_params(p, d);
     pixel_tile(BM, d.wo, d.ho, p.TW, p.TH, p.TN);
@@ -658,7 +750,13 @@ bool plan_fwd(const dcg_conv_desc& d, Plan& pl)
     p.n_tiles = (d.o + p.bn - 1) / p.bn;
     p.kchunks = (d.c + BK - 1) / BK;
     const int tiles = p.tiles_w * p.tiles_h * p.tiles_n * p.n_tiles;
-    p.splits = choose_splits(tiles, d.kh * d.kw * p.kchunks);
+    if (narrow) {
+        p.narrow = 1;
+        p.kchunks = 1;
+        narrow_geometry(d, pl);
+        pl.k4_bytes = (size_t)d.kh * 32 * d.o * sizeof(float);
+    }
+    p.splits = choose_splits(tiles, narrow ? d.kh : d.kh * d.kw * p.kchunks);
     p.out_elems = (unsigned long long)d.n * d.ho * d.wo * d.o;
     pl.grid = tiles * p.splits;
     finish_plan(pl);
@@ -691,12 +789,28 @@ bool plan_dx(const dcg_conv_desc& d, Plan& pl)
 
 bool plan_dk(const dcg_conv_desc& d, Plan& pl)
 {
-    if (d.c % 32 != 0 || d.o % 32 != 0 || d.stride_h > 8 || d.stride_w > 8) return false;
+    const bool narrow = narrow_ok(d);
+    if (!narrow && (d.c % 32 != 0 || d.o % 32 != 0 || d.stride_h > 8 || d.stride_w > 8)) return false;
     Params& p = pl.p;
     base_params(p, d);
     pixel_tile(BK, d.wo, d.ho, p.TW, p.TH, p.TN);   // 32 output pixels per K stage
     if (p.TW * d.stride_w > 256 || p.TH * d.stride_h > 256) return false;
     p.tiles_w = (d.wo + p.TW - 1) / p.TW; p.tiles_h = (d.ho + p.TH - 1) / p.TH; p.tiles_n = (d.n + p.TN - 1) / p.TN;
+    if (narrow) {
+        // rows = output channels (from dy), columns = the 32 window slots, one group per kernel row
+        p.narrow = 1;
+        p.swap = 1;
+        p.m_tiles = (d.o + BM - 1) / BM;
+        p.bn = 32;
+        p.n_tiles = 1;
+        narrow_geometry(d, pl);
+        const int tiles = d.kh * p.m_tiles;
+        p.splits = choose_splits(tiles, p.tiles_w * p.tiles_h * p.tiles_n);
+        p.out_elems = (unsigned long long)d.kh * d.kw * d.c * d.o;
+        pl.grid = tiles * p.splits;
+        finish_plan(pl);
+        return true;
+    }
     // the wider channel axis becomes M (128 accumulator rows), the other N
     p.swap = d.o > d.c ? 1 : 0;
     const int m_ch = p.swap ? d.o : d.c, n_ch = p.swap ? d.c : d.o;
@@ -757,6 +871,46 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, Plan& pl, float* out, c
     return DCG_OK;
 }
 
+// Narrow-channel layers: builds the padded 4-channel image (and, for FWD, the repacked weights) in
+// the caller's scratch and returns their addresses.
+int narrow_prepare(const dcg_conv_desc& d, const Plan& pl, const float* x, const float* k, void* ws, size_t ws_bytes,
+                   cudaStream_t stream, float** xp_out, float** k4_out)
+{
+    if (!ws || ws_bytes < pl.ws_bytes)
+        return fail(DCG_ERR_WORKSPACE, "conv (tensor path, narrow input): workspace %zu < %zu bytes", ws_bytes, pl.ws_bytes);
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    float* xp = reinterpret_cast<float*>(base + pl.xp_off());
+    const size_t pixels = (size_t)d.n * pl.Hp * pl.Wp;
+    size_t blocks = (pixels + 255) / 256;
+    const size_t cap = (size_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    repack_narrow_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, reinterpret_cast<float4*>(xp), d.n, d.h, d.w, d.c,
+                                                                pl.Hp, pl.Wp, d.pad_top, d.pad_left);
+    DCG_LAUNCH_CHECK("repack_narrow_kernel");
+    *xp_out = xp;
+    if (k4_out) {
+        float* k4 = reinterpret_cast<float*>(base + pl.k4_off());
+        const int total = d.kh * 32 * d.o;
+        repack_k4_kernel<<<(total + 255) / 256, 256, 0, stream>>>(k, k4, d.kh, d.kw, d.c, d.o);
+        DCG_LAUNCH_CHECK("repack_k4_kernel");
+        *k4_out = k4;
+    }
+    return DCG_OK;
+}
+
+// The overlapping-window view of xp [n][Hp][Wp][4]: (32 floats, j, i, n, kernel row) where output
+// pixel (i, j) and kernel row r address xp[n][s*i + r][s*j][0].  Box (32, tw, th, tn, 1).
+int map_window(CUtensorMap* map, const float* xp, const dcg_conv_desc& d, const Plan& pl, int tw, int th, int tn,
+               bool mn_major)
+{
+    const cuuint64_t row = (cuuint64_t)pl.Wp * 16;
+    const cuuint64_t dims[5] = {32, (cuuint64_t)d.wo, (cuuint64_t)d.ho, (cuuint64_t)d.n, (cuuint64_t)d.kh};
+    const cuuint64_t strides[4] = {(cuuint64_t)d.stride_w * 16, (cuuint64_t)d.stride_h * row, (cuuint64_t)pl.Hp * row, row};
+    const cuuint32_t box[5] = {32, (cuuint32_t)tw, (cuuint32_t)th, (cuuint32_t)tn, 1};
+    const cuuint32_t es[5] = {1, 1, 1, 1, 1};
+    return encode_map(map, xp, 5, dims, mn_major, strides, box, es);
+}
+
 }  // namespace
 
 bool conv_tc_supported(const dcg_conv_desc& d, int kind)
@@ -779,7 +933,20 @@ int conv_tc_fwd(const dcg_conv_desc& d, const float* x, const float* k, float* y
     if (!plan_fwd(d, pl)) return fail(DCG_ERR_UNSUPPORTED, "conv fwd: shape not supported by the tensor path");
     const Params& p = pl.p;
     CUtensorMap ma, mb;
-    int st = map_act_4d(&ma, x, d.n, d.h, d.w, d.c, p.TW, p.TH, p.TN, d.stride_w, d.stride_h);
+    int st;
+    if (p.narrow) {
+        float *xp, *k4;
+        if ((st = narrow_prepare(d, pl, x, k, ws, ws_bytes, stream, &xp, &k4))) return st;
+        if ((st = map_window(&ma, xp, d, pl, p.TW, p.TH, p.TN, false))) return st;
+        // k4 [kh][slot][o] as (o%32, slot, kh, o/32), box (32, 32, 1, bn/32)
+        const cuuint64_t dims[4] = {32, 32, (cuuint64_t)d.kh, (cuuint64_t)(d.o / 32)};
+        const cuuint64_t strides[3] = {(cuuint64_t)d.o * 4, (cuuint64_t)32 * d.o * 4, 128};
+        const cuuint32_t box[4] = {32, 32, 1, (cuuint32_t)(p.bn / 32)};
+        const cuuint32_t es[4] = {1, 1, 1, 1};
+        if ((st = encode_map(&mb, k4, 4, dims, true, strides, box, es))) return st;
+        return launch<MODE_FWD>(ma, mb, pl, y, ep, d.o, ws, ws_bytes, stream);
+    }
+    st = map_act_4d(&ma, x, d.n, d.h, d.w, d.c, p.TW, p.TH, p.TN, d.stride_w, d.stride_h);
     if (st) return st;
     // k [tap][c][o] as (o%32, c, tap, o/32), box (32, 32, 1, bn/32)
     const cuuint64_t dims[4] = {32, (cuuint64_t)d.c, (cuuint64_t)(d.kh * d.kw), (cuuint64_t)(d.o / 32)};
@@ -815,8 +982,17 @@ int conv_tc_dk(const dcg_conv_desc& d, const float* x, const float* dy, float* d
     if (!plan_dk(d, pl)) return fail(DCG_ERR_UNSUPPORTED, "conv dk: shape not supported by the tensor path");
     const Params& p = pl.p;
     CUtensorMap mx, mdy;
+    const EpilogueArgs no_epilogue{};
+    int st;
+    if (p.narrow) {
+        float* xp;
+        if ((st = narrow_prepare(d, pl, x, nullptr, ws, ws_bytes, stream, &xp, nullptr))) return st;
+        if ((st = map_window(&mx, xp, d, pl, p.TW, p.TH, p.TN, true))) return st;
+        if ((st = map_act_5d(&mdy, dy, d.n, d.ho, d.wo, d.o, p.TW, p.TH, p.TN, 1, 1, BM / 32))) return st;
+        return launch<MODE_DK>(mdy, mx, pl, dk, no_epilogue, d.o, ws, ws_bytes, stream);
+    }
     const int x_chunks = p.swap ? p.bn / 32 : BM / 32, dy_chunks = p.swap ? BM / 32 : p.bn / 32;
-    int st = map_act_5d(&mx, x, d.n, d.h, d.w, d.c, p.TW, p.TH, p.TN, d.stride_w, d.stride_h, x_chunks);
+    st = map_act_5d(&mx, x, d.n, d.h, d.w, d.c, p.TW, p.TH, p.TN, d.stride_w, d.stride_h, x_chunks);
     if (st) return st;
     if ((st = map_act_5d(&mdy, dy, d.n, d.ho, d.wo, d.o, p.TW, p.TH, p.TN, 1, 1, dy_chunks))) return st;
     const EpilogueArgs none{};

@@ -117,13 +117,19 @@ def test_fused_equals_unfused_and_oracle(pkg, dev, orc, prec_name):
         assert np.array_equal(results[False][name], results[True][name]), name
     assert launches[True] < launches[False]
 
+    # Each operator is checked against the oracle applied to the inputs the GPU gave it: on the TF32
+    # path a pre-activation within rounding distance of zero may land on the other side of the
+    # leaky-relu kink, which changes downstream values by a finite step and is not an error.
+    got = results[True]
+    exact = prec == pkg.PREC_FP32
     conv = orc.conv2d(x, k, (2, 2))
-    z = orc.mvrow_add(conv, bias)
-    dz = orc.leaky_relu_grad(z, da, 0.2)
-    dx = orc.conv2d_input_grad(dz, k, 2, (16, 16))
-    ref = {"conv": conv, "z": z, "a": orc.vect_relu_leaky(z, 0.2), "dz": dz,
-           "dk": orc.conv2d_kernel_grad(dz, x, 2, (3, 3)), "dx": dx,
-           "dzprev": orc.leaky_relu_grad(zprev, dx, 0.2)}
+    z = orc.mvrow_add(conv if exact else got["conv"], bias)
+    dz = orc.leaky_relu_grad(z if exact else got["z"], da, 0.2)
+    dz_in = dz if exact else got["dz"]
+    dx = orc.conv2d_input_grad(dz_in, k, 2, (16, 16))
+    ref = {"conv": conv, "z": z, "a": orc.vect_relu_leaky(z if exact else got["z"], 0.2), "dz": dz,
+           "dk": orc.conv2d_kernel_grad(dz_in, x, 2, (3, 3)), "dx": dx,
+           "dzprev": orc.leaky_relu_grad(zprev, dx if exact else got["dx"], 0.2)}
     for name, r in ref.items():
         got = results[True][name]
         if prec == pkg.PREC_FP32:

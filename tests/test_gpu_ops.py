@@ -105,7 +105,8 @@ def test_argmax_first_max_wins_and_is_exact(pkg, dev, orc):
     a = np.round(seeded((rows, cols), 520) * 3).astype(np.float32)  # many ties
     b = np.round(seeded((rows, cols), 521) * 3).astype(np.float32)
     acc = torch.empty((1,), device=dev)
-    pkg._lib.check(pkg.lib.dcg_argmax_acc(_t(a, dev).data_ptr(), _t(b, dev).data_ptr(), acc.data_ptr(), rows, cols, _s()))
+    ad, bd = _t(a, dev), _t(b, dev)
+    pkg._lib.check(pkg.lib.dcg_argmax_acc(ad.data_ptr(), bd.data_ptr(), acc.data_ptr(), rows, cols, _s()))
     assert acc.item() == float(orc.argmax_acc(a, b))
 
 
