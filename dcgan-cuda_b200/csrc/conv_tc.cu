@@ -50,6 +50,15 @@ enum Mode { MODE_FWD = 0, MODE_DX = 1, MODE_DK = 2 };
 // Error word: [0] code (0 = ok), [1] blockIdx, [2] role, [3] stage.  Read by dcg_device_status().
 __device__ int g_tc_status[4];
 
+// Timeline of CTA 0 for tuning (DCG_TC_DEBUG bit 4): SM clock stamps of [0..1023] TMA issue of
+// stage i, [1024..2047] stage i seen full by the MMA thread, [2048..3071] MMAs of stage i issued,
+// [3072] kernel entry, [3073] setup done, [3074] accumulator ready, [3075] epilogue stores done.
+__device__ long long g_tc_trace[3080];
+#define TC_TRACE(slot)                                                         \
+    do {                                                                       \
+        if ((p.debug & 4) && blockIdx.x == 0 && (slot) < 3080) g_tc_trace[(slot)] = clock64(); \
+    } while (0)
+
 struct Params {
     int N, H, W, C, KH, KW, O, Ho, Wo, sh, sw, pt, pl;
     int TW, TH, TN;               // pixel-tile extents (FWD/DX: the 128 rows; DK: the 32-pixel K step)
@@ -61,6 +70,7 @@ struct Params {
     int kchunks;                  // 32-wide chunks along the contracted channel axis (FWD: C, DX: O)
     int swap;                     // DK: M axis is o (A from dy, B from x)
     int narrow;                   // FWD/DK with <= 4 input channels: x is read through the window map
+    int debug;                    // timing experiments (DCG_TC_DEBUG): 1 = no MMA, 2 = no TMA; results are garbage
     int stages;                   // pipeline depth
     int direct;                   // 1: epilogue + final store, 0: raw partial to scratch
     float* out;                   // final tensor (direct) or scratch base
@@ -202,6 +212,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                const __grid_constant__ Params p)
 {
     extern __shared__ uint8_t smem_raw[];
+    if (threadIdx.x == 64) TC_TRACE(3072);
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int b_stage_bytes = p.bn * BK * 4;
     const uint32_t a_base = smem_base;
@@ -277,52 +288,78 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = *tmem_slot_ptr;
+    if (threadIdx.x == 64) TC_TRACE(3073);
 
     if (warp == 0) {
         // ===== TMA producer =====
+        // One thread issues every load.  All position bookkeeping is incremental: an integer division
+        // costs this lone thread ~100 cycles, and the loop has to turn around in well under the 256
+        // cycles the tensor core needs per stage.
         if (lane == 0) {
             const uint32_t tx_bytes = (uint32_t)(A_STAGE_BYTES + b_stage_bytes);
+            int s = 0;
+            uint32_t phase = 0;
+            // counters of stage q0: FWD (chunk, tap, di, dj); DX (chunk, -, th, tw); DK (-, tile_n, tile_h, tile_w)
+            int chunk = 0, tap = 0, di = 0, dj = 0;
+            if (MODE == MODE_FWD && !p.narrow) {
+                tap = q0 / p.kchunks; chunk = q0 % p.kchunks; di = tap / p.KW; dj = tap % p.KW;
+            } else if (MODE == MODE_DX) {
+                const int t = q0 / p.kchunks;
+                chunk = q0 % p.kchunks; di = t / taps_w; dj = t % taps_w;
+            } else if (MODE == MODE_DK) {
+                dj = q0 % p.tiles_w; di = (q0 / p.tiles_w) % p.tiles_h; tap = q0 / (p.tiles_w * p.tiles_h);
+            }
+            const int wrap_dj = (MODE == MODE_FWD) ? p.KW : taps_w;
             for (int it = 0; it < nq; ++it) {
-                const int s = it % p.stages;
-                const uint32_t phase = (uint32_t)(it / p.stages) & 1u;
                 if (!mbar_wait(empty_bar + 8u * s, phase ^ 1u, 0, it)) break;
                 const uint32_t fb = full_bar + 8u * s;
-                mbar_expect_tx(fb, tx_bytes);
-                const uint32_t a_dst = a_base + (uint32_t)s * A_STAGE_BYTES;
-                const uint32_t b_dst = b_base + (uint32_t)s * b_stage_bytes;
-                const int q = q0 + it;
-                if (MODE == MODE_FWD && p.narrow) {
-                    // stage q = kernel row q: 128 output pixels x the 32-float window (8 pixels x 4
-                    // channels) that starts at padded column s*j of padded row s*i + q
-                    tma_load_5d(a_dst, &map_a, fb, 0, j0, i0, n0, q);
-                    tma_load_4d(b_dst, &map_b, fb, 0, 0, q, n_tile * (p.bn / 32));
-                } else if (MODE == MODE_FWD) {
-                    const int tap = q / p.kchunks, cc = q % p.kchunks;
-                    const int di = tap / p.KW, dj = tap % p.KW;
-                    tma_load_4d(a_dst, &map_a, fb, cc * BK, p.sw * j0 + dj - p.pl, p.sh * i0 + di - p.pt, n0);
-                    tma_load_4d(b_dst, &map_b, fb, 0, cc * BK, tap, n_tile * (p.bn / 32));
-                } else if (MODE == MODE_DX) {
-                    const int t = q / p.kchunks, oc = q % p.kchunks;
-                    const int th = t / taps_w, tw = t % taps_w;
-                    const int di = rh + p.sh * th, dj = rw + p.sw * tw;
-                    tma_load_4d(a_dst, &map_a, fb, oc * BK, j0 + ew - tw, i0 + eh - th, n0);
-                    tma_load_4d(b_dst, &map_b, fb, oc * BK, n_tile * p.bn, dj, di);
+                TC_TRACE(it);
+                if (p.debug & 2) {   // timing experiment: no loads, the stage is declared full at once
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(fb) : "memory");
                 } else {
-                    const int pj = (q % p.tiles_w) * p.TW;
-                    const int pi = ((q / p.tiles_w) % p.tiles_h) * p.TH;
-                    const int pn = (q / (p.tiles_w * p.tiles_h)) * p.TN;
-                    const int xw = p.sw * pj + tap_dj - p.pl, xh = p.sh * pi + tap_di - p.pt;
-                    if (p.narrow) {  // A: dy (rows o), B: the 32-float windows of 32 output pixels, row tap_di
-                        tma_load_5d(a_dst, &map_a, fb, 0, pj, pi, pn, m_tile * (BM / 32));
-                        tma_load_5d(b_dst, &map_b, fb, 0, pj, pi, pn, tap_di);
-                    } else if (!p.swap) {   // A: x (rows c), B: dy (cols o)
-                        tma_load_5d(a_dst, &map_a, fb, 0, xw, xh, pn, m_tile * (BM / 32));
-                        tma_load_5d(b_dst, &map_b, fb, 0, pj, pi, pn, n_tile * (p.bn / 32));
-                    } else {         // A: dy (rows o), B: x (cols c)
-                        tma_load_5d(a_dst, &map_a, fb, 0, pj, pi, pn, m_tile * (BM / 32));
-                        tma_load_5d(b_dst, &map_b, fb, 0, xw, xh, pn, n_tile * (p.bn / 32));
+                    mbar_expect_tx(fb, tx_bytes);
+                    const uint32_t a_dst = a_base + (uint32_t)s * A_STAGE_BYTES;
+                    const uint32_t b_dst = b_base + (uint32_t)s * b_stage_bytes;
+                    if (MODE == MODE_FWD && p.narrow) {
+                        // stage = kernel row: 128 output pixels x the 32-float window (8 pixels x 4
+                        // channels) that starts at padded column s*j of padded row s*i + row
+                        const int q = q0 + it;
+                        tma_load_5d(a_dst, &map_a, fb, 0, j0, i0, n0, q);
+                        tma_load_4d(b_dst, &map_b, fb, 0, 0, q, n_tile * (p.bn / 32));
+                    } else if (MODE == MODE_FWD) {
+                        if (it < 128) TC_TRACE(256 + it);
+                        tma_load_4d(a_dst, &map_a, fb, chunk * BK, p.sw * j0 + dj - p.pl, p.sh * i0 + di - p.pt, n0);
+                        if (it < 128) TC_TRACE(512 + it);
+                        tma_load_4d(b_dst, &map_b, fb, 0, chunk * BK, tap, n_tile * (p.bn / 32));
+                        if (it < 128) TC_TRACE(768 + it);
+                    } else if (MODE == MODE_DX) {
+                        // (di, dj) count the taps of this parity class: kernel tap (rh + sh*di, rw + sw*dj)
+                        tma_load_4d(a_dst, &map_a, fb, chunk * BK, j0 + ew - dj, i0 + eh - di, n0);
+                        tma_load_4d(b_dst, &map_b, fb, chunk * BK, n_tile * p.bn, rw + p.sw * dj, rh + p.sh * di);
+                    } else {
+                        // (tap, di, dj) count the 32-pixel tiles along (n, h, w)
+                        const int pj = dj * p.TW, pi = di * p.TH, pn = tap * p.TN;
+                        const int xw = p.sw * pj + tap_dj - p.pl, xh = p.sh * pi + tap_di - p.pt;
+                        if (p.narrow) {  // A: dy (rows o), B: the 32-float windows of 32 output pixels, row tap_di
+                            tma_load_5d(a_dst, &map_a, fb, 0, pj, pi, pn, m_tile * (BM / 32));
+                            tma_load_5d(b_dst, &map_b, fb, 0, pj, pi, pn, tap_di);
+                        } else if (!p.swap) {   // A: x (rows c), B: dy (cols o)
+                            tma_load_5d(a_dst, &map_a, fb, 0, xw, xh, pn, m_tile * (BM / 32));
+                            tma_load_5d(b_dst, &map_b, fb, 0, pj, pi, pn, n_tile * (p.bn / 32));
+                        } else {         // A: dy (rows o), B: x (cols c)
+                            tma_load_5d(a_dst, &map_a, fb, 0, pj, pi, pn, m_tile * (BM / 32));
+                            tma_load_5d(b_dst, &map_b, fb, 0, xw, xh, pn, n_tile * (p.bn / 32));
+                        }
                     }
                 }
+                // advance to the next stage
+                if (MODE == MODE_DK) {
+                    if (++dj == p.tiles_w) { dj = 0; if (++di == p.tiles_h) { di = 0; ++tap; } }
+                } else if (++chunk == p.kchunks) {
+                    chunk = 0; ++tap;
+                    if (++dj == wrap_dj) { dj = 0; ++di; }
+                }
+                if (++s == p.stages) { s = 0; phase ^= 1u; }
             }
         }
     } else if (warp == 1) {
@@ -341,22 +378,29 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t a_lay = a_mn ? kLayoutSw128Base32 : kLayoutSw128;
             const uint32_t b_lay = b_mn ? kLayoutSw128Base32 : kLayoutSw128;
             const uint32_t a_step = a_mn ? 1024u : 32u, b_step = b_mn ? 1024u : 32u;
-            bool ok = true;
-            for (int it = 0; it < nq && ok; ++it) {
-                const int s = it % p.stages;
-                const uint32_t phase = (uint32_t)(it / p.stages) & 1u;
-                ok = mbar_wait(full_bar + 8u * s, phase, 1, it);
-                if (!ok) break;
+            // descriptors of stage 0; a stage further on only changes the 14-bit start-address field
+            const uint64_t adesc0 = make_smem_desc(a_base, a_lbo, a_sbo, a_lay);
+            const uint64_t bdesc0 = make_smem_desc(b_base, b_lbo, b_sbo, b_lay);
+            const uint32_t a_stage16 = A_STAGE_BYTES >> 4, b_stage16 = (uint32_t)b_stage_bytes >> 4;
+            int s = 0;
+            uint32_t phase = 0;
+            for (int it = 0; it < nq; ++it) {
+                if (!mbar_wait(full_bar + 8u * s, phase, 1, it)) break;
+                TC_TRACE(1024 + it);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = a_base + (uint32_t)s * A_STAGE_BYTES;
-                const uint32_t b_addr = b_base + (uint32_t)s * b_stage_bytes;
+                if (p.debug & 1) {   // timing experiment: no MMA, the stage is released at once
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_bar + 8u * s) : "memory");
+                } else {
+                    const uint64_t adesc = adesc0 + (uint64_t)(s * a_stage16);
+                    const uint64_t bdesc = bdesc0 + (uint64_t)(s * b_stage16);
 #pragma unroll
-                for (int kk = 0; kk < BK / 8; ++kk) {
-                    const uint64_t adesc = make_smem_desc(a_addr + kk * a_step, a_lbo, a_sbo, a_lay);
-                    const uint64_t bdesc = make_smem_desc(b_addr + kk * b_step, b_lbo, b_sbo, b_lay);
-                    tcgen05_mma_tf32(tmem_d, adesc, bdesc, idesc, (it > 0 || kk > 0) ? 1u : 0u);
+                    for (int kk = 0; kk < BK / 8; ++kk)
+                        tcgen05_mma_tf32(tmem_d, adesc + (uint64_t)(kk * (a_step >> 4)), bdesc + (uint64_t)(kk * (b_step >> 4)),
+                                         idesc, (it > 0 || kk > 0) ? 1u : 0u);
+                    tcgen05_commit(empty_bar + 8u * s);  // frees the stage once these MMAs have read it
                 }
-                tcgen05_commit(empty_bar + 8u * s);  // frees the stage once these MMAs have read it
+                TC_TRACE(2048 + it);
+                if (++s == p.stages) { s = 0; phase ^= 1u; }
             }
             tcgen05_commit(tmem_full_bar);           // accumulator complete (or abandoned)
         }
@@ -367,6 +411,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bool ok = mbar_wait(tmem_full_bar, 0, 2, 0);
         ok = __all_sync(0xffffffffu, ok);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (threadIdx.x == 64) TC_TRACE(3074);
 
         // where does this accumulator row go?
         bool row_valid = false;
@@ -409,29 +454,50 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         if (!ok || nq <= 0) row_valid = false;   // nothing trustworthy to store
         float* dst = p.direct ? p.out : p.out + (unsigned long long)split * p.out_elems;
-        const bool vec_ok = col_stride == 1 && (row_off & 3ull) == 0 && (ncols_valid & 3) == 0;
-
-        for (int c0 = 0; c0 < p.bn; c0 += 32) {
-            uint32_t r[32];
-            const uint32_t taddr = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0;
-            if (p.bn - c0 >= 32) {
-                tmem_ld_32x32b_x32(taddr, r);
-            } else {
-                tmem_ld_32x32b_x16(taddr, r);
+        // Row-contiguous outputs whose channel count is a multiple of 4 go through shared memory:
+        // with one accumulator row per thread a direct 128-bit store instruction would scatter its 32
+        // lanes over 32 different cache lines, so each 32-column slab is first parked in a padded
+        // staging buffer (the pipeline stages are free by now) and then written out with every
+        // store instruction covering four whole 128-byte row segments.  The fused epilogue runs in
+        // that second, coalesced phase.  Column-strided outputs (DK with the roles swapped, the
+        // narrow-channel DK) are already coalesced across lanes and keep the per-row scalar path.
+        const int ch_total = (MODE == MODE_DX) ? p.C : p.O;
+        const bool staged = col_stride == 1 && (ch_total & 3) == 0 && (ncols_valid & 3) == 0;
+        if (staged) {
+            constexpr int kPitch = 36;   // floats per staged row: 32 + 4 keeps 128-bit accesses conflict-free
+            float* stg = reinterpret_cast<float*>(smem_raw + (a_base - smem_u32(smem_raw)));
+            long long* s_rowoff = reinterpret_cast<long long*>(stg + 2 * BM * kPitch);
+            const int tid_e = threadIdx.x - 64;
+            s_rowoff[row] = row_valid ? (long long)row_off : -1;
+            int pass = 0;
+            for (int c0 = 0; c0 < p.bn; c0 += 32, ++pass) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0;
+                if (p.bn - c0 >= 32) {
+                    tmem_ld_32x32b_x32(taddr, r);
+                } else {
+                    tmem_ld_32x32b_x16(taddr, r);
 #pragma unroll
-                for (int q = 16; q < 32; ++q) r[q] = 0u;
-            }
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (!row_valid) continue;
-            if (p.direct) {
+                    for (int q = 16; q < 32; ++q) r[q] = 0u;
+                }
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                float* buf = stg + (pass & 1) * (BM * kPitch);
+                float4* mine = reinterpret_cast<float4*>(buf + row * kPitch);
 #pragma unroll
-                for (int q = 0; q < 32; q += 4) {
-                    const int col = c0 + q;
-                    if (col >= ncols_valid) break;
-                    const unsigned long long idx = row_off + (unsigned long long)col * col_stride;
-                    if (vec_ok) {
-                        float4 v = make_float4(__uint_as_float(r[q]), __uint_as_float(r[q + 1]),
-                                               __uint_as_float(r[q + 2]), __uint_as_float(r[q + 3]));
+                for (int q = 0; q < 8; ++q)
+                    mine[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                          __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps only
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int f = tid_e + 128 * k;
+                    const int rr = f >> 3, c4 = (f & 7) << 2;
+                    const int col = c0 + c4;
+                    const long long ro = s_rowoff[rr];
+                    if (ro < 0 || col >= ncols_valid) continue;
+                    float4 v = *reinterpret_cast<const float4*>(buf + rr * kPitch + c4);
+                    const unsigned long long idx = (unsigned long long)ro + (unsigned long long)col;
+                    if (p.direct) {
                         const EpilogueArgs& e = p.ep;
                         if (e.raw_out) *reinterpret_cast<float4*>(e.raw_out + idx) = v;
                         if (e.bias) {
@@ -451,49 +517,42 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             v.z = act_grad_apply(g.z, v.z, e.gate_act, e.gate_alpha);
                             v.w = act_grad_apply(g.w, v.w, e.gate_act, e.gate_alpha);
                         }
-                        *reinterpret_cast<float4*>(dst + idx) = v;
-                    } else {
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            if (col + u >= ncols_valid) break;
-                            unsigned long long id = idx + (unsigned long long)u * col_stride;
-                            if (MODE == MODE_DK && p.narrow) {
-                                if (u >= p.C) break;   // slot = 4*dj + channel, channels beyond C are padding
-                                id = row_off + (unsigned long long)((col >> 2) * p.C + u) * p.O;
-                            }
-                            // the epilogue chain only applies to FWD/DX, whose columns are contiguous
-                            dst[id] = (MODE == MODE_DK) ? __uint_as_float(r[q + u])
-                                                        : epilogue_apply(p.ep, __uint_as_float(r[q + u]), id, ch0 + col + u);
-                        }
                     }
+                    *reinterpret_cast<float4*>(dst + idx) = v;
                 }
-            } else {
+            }
+        } else {
+            for (int c0 = 0; c0 < p.bn; c0 += 32) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0;
+                if (p.bn - c0 >= 32) {
+                    tmem_ld_32x32b_x32(taddr, r);
+                } else {
+                    tmem_ld_32x32b_x16(taddr, r);
 #pragma unroll
-                for (int q = 0; q < 32; q += 4) {
+                    for (int q = 16; q < 32; ++q) r[q] = 0u;
+                }
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (!row_valid) continue;
+#pragma unroll
+                for (int q = 0; q < 32; ++q) {
                     const int col = c0 + q;
                     if (col >= ncols_valid) break;
-                    const unsigned long long idx = row_off + (unsigned long long)col * col_stride;
-                    if (vec_ok) {
-                        *reinterpret_cast<float4*>(dst + idx) =
-                            make_float4(__uint_as_float(r[q]), __uint_as_float(r[q + 1]),
-                                        __uint_as_float(r[q + 2]), __uint_as_float(r[q + 3]));
-                    } else {
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            if (col + u >= ncols_valid) break;
-                            unsigned long long id = idx + (unsigned long long)u * col_stride;
-                            if (MODE == MODE_DK && p.narrow) {
-                                if (u >= p.C) break;
-                                id = row_off + (unsigned long long)((col >> 2) * p.C + u) * p.O;
-                            }
-                            dst[id] = __uint_as_float(r[q + u]);
-                        }
+                    unsigned long long id = row_off + (unsigned long long)col * col_stride;
+                    if (MODE == MODE_DK && p.narrow) {
+                        if ((col & 3) >= p.C) continue;   // slot = 4*dj + channel, channels beyond C are padding
+                        id = row_off + (unsigned long long)((col >> 2) * p.C + (col & 3)) * p.O;
                     }
+                    // the epilogue chain only exists for FWD/DX; DK and split-K partials store raw sums
+                    dst[id] = (MODE == MODE_DK || !p.direct)
+                                  ? __uint_as_float(r[q])
+                                  : epilogue_apply(p.ep, __uint_as_float(r[q]), id, ch0 + col);
                 }
             }
         }
     }
 
+    if (threadIdx.x == 64) TC_TRACE(3075);
     // ---- teardown: everyone is done with TMEM before warp 1 releases it --------------------------
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -705,7 +764,11 @@ void finish_plan(Plan& pl)
     static const int forced_stages = env_int("DCG_TC_STAGES");
     if (forced_stages > 0 && forced_stages < stages) stages = forced_stages;
     if (stages < 2) stages = 2;
+    // the epilogue parks two 128 x 36-float slabs and 128 row offsets in the (by then idle) stage ring
+    while ((size_t)stages * per_stage < 2 * BM * 36 * 4 + BM * 8) ++stages;
     p.stages = stages;
+    static const int debug = env_int("DCG_TC_DEBUG");
+    p.debug = debug;
     pl.smem = (size_t)stages * per_stage + 1024 /*alignment slack*/ + 16 * stages + 32;
     pl.partial_bytes = p.splits > 1 ? (size_t)p.splits * p.out_elems * sizeof(float) : 0;
     pl.ws_bytes = pl.partial_bytes;
@@ -1019,3 +1082,11 @@ int conv_tc_device_status(int* detail /* [4] */)
 }  // namespace dcg
 
 extern "C" int dcg_device_status(void) { return dcg::conv_tc_device_status(nullptr); }
+
+// Tuning aid, not part of the public header: copies the timeline recorded by CTA 0 of the last
+// tensor-path launch (DCG_TC_DEBUG bit 4) to `out` (3080 values).  Synchronises the device.
+extern "C" int dcg_debug_trace(long long* out)
+{
+    if (cudaDeviceSynchronize() != cudaSuccess) return DCG_ERR_CUDA;
+    return cudaMemcpyFromSymbol(out, dcg::g_tc_trace, sizeof(long long) * 3080) == cudaSuccess ? DCG_OK : DCG_ERR_CUDA;
+}
