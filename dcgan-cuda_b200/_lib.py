@@ -85,6 +85,8 @@ SIGNATURES = {
     "dcg_act_grad": (c_int, [_P, _P, _P, c_size_t, c_int, c_float, _P]),
     "dcg_colsum_workspace_bytes": (c_size_t, [c_size_t, c_size_t]),
     "dcg_colsum": (c_int, [_P, _P, c_size_t, c_size_t, _P, c_size_t, _P]),
+    "dcg_colsum_noalloc_max_bytes": (c_size_t, []),
+    "dcg_colsum_noalloc": (c_int, [_P, _P, c_size_t, c_size_t, _P]),
     "dcg_rowsum": (c_int, [_P, _P, c_size_t, c_size_t, _P]),
     "dcg_add": (c_int, [_P, _P, _P, c_size_t, _P]),
     "dcg_update": (c_int, [_P, _P, _P, c_size_t, _P]),

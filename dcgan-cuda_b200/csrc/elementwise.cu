@@ -4,6 +4,8 @@
 // All of them are HBM-bound streaming kernels: 128-bit loads and stores where
 // the pointers and sizes allow it, grid-stride loops, grids sized as a multiple
 // of the SM count.  Reductions use a fixed tree so results are deterministic.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace dcg {
@@ -437,6 +439,7 @@ extern "C" size_t dcg_colsum_workspace_bytes(size_t rows, size_t cols)
     // Sized for the larger of the vector / scalar plans (pointer alignment is unknown here).
     const ColsumPlan a = colsum_plan(rows, cols, true), b = colsum_plan(rows, cols, false);
     const unsigned slabs = a.slabs > b.slabs ? a.slabs : b.slabs;
+    if (slabs <= 1) return 0;   // a single slab writes the result directly
     return (size_t)slabs * cols * sizeof(float);
 }
 
@@ -562,4 +565,52 @@ extern "C" int dcg_argmax_acc(const float* y, const float* y_hat, float* out, si
     argmax_acc_kernel<<<1, 512, 0, as_stream(stream)>>>(y, y_hat, out, rows, cols);
     DCG_LAUNCH_CHECK("argmax_acc_kernel");
     return DCG_OK;
+}
+
+// ---- column sums with built-in scratch ---------------------------------------------------------
+// Some callers have device memory for their operands and nothing else, and are not in a position
+// to call cudaMalloc: the reference's runtime is the case in point - a node handler has the
+// signature void(rt::Node*) (src/gpu/kernels.hh:8), the node carries operand pointers only, and
+// the loop that calls it (src/gpu/runner.cu:10-18) may run where allocating is off the table
+// (a memory budget fixed at start-up, a latency-critical loop that must not enter the driver's
+// allocator).  For them the two-stage column sum can use a scratch area that is part of the
+// library image: it exists on every GPU the library is loaded on, from load to exit, and costs
+// kColsumStaticBytes of device memory there whether or not this entry point is ever called.
+constexpr size_t kColsumStaticBytes = (size_t)256 << 10;   // 256 KiB: 65536 partial sums
+static __device__ __align__(256) unsigned char g_colsum_static[kColsumStaticBytes];
+
+// Device address of g_colsum_static per device ordinal.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel could use: the address is looked up once per
+// device with cudaGetSymbolAddress while that device is current.
+static void* g_colsum_static_ptr[64];
+static std::mutex g_colsum_static_mutex;
+
+extern "C" size_t dcg_colsum_noalloc_max_bytes(void) { return kColsumStaticBytes; }
+
+extern "C" int dcg_colsum_noalloc(const float* a, float* out, size_t rows, size_t cols, dcg_stream_t stream)
+{
+    DCG_CHECK_ARG(a && out, "dcg_colsum_noalloc: null pointer");
+    DCG_CHECK_ARG(cols > 0 && cols <= 0x7fffffffu && rows > 0, "dcg_colsum_noalloc: bad shape %zu x %zu", rows, cols);
+    const size_t need = dcg_colsum_workspace_bytes(rows, cols);
+    if (need > kColsumStaticBytes)
+        return fail(DCG_ERR_WORKSPACE,
+                    "dcg_colsum_noalloc: a %zu x %zu column sum needs %zu bytes of scratch, the built-in area holds %zu; "
+                    "use dcg_colsum with caller-provided scratch",
+                    rows, cols, need, kColsumStaticBytes);
+    int dev = 0;
+    DCG_CUDA(cudaGetDevice(&dev));
+    DCG_CHECK_ARG(dev >= 0 && dev < 64, "dcg_colsum_noalloc: device ordinal %d out of range", dev);
+    void* scratch;
+    {
+        std::lock_guard<std::mutex> lock(g_colsum_static_mutex);
+        if (!g_colsum_static_ptr[dev]) {
+            void* p = nullptr;
+            DCG_CUDA(cudaGetSymbolAddress(&p, g_colsum_static));
+            g_colsum_static_ptr[dev] = p;
+        }
+        scratch = g_colsum_static_ptr[dev];
+    }
+    // Stage 1 overwrites every partial sum stage 2 reads, so nothing in the area has to be
+    // cleared between calls even though it keeps the previous call's contents.
+    return dcg_colsum(a, out, rows, cols, scratch, kColsumStaticBytes, stream);
 }

@@ -138,6 +138,20 @@ size_t dcg_colsum_workspace_bytes(size_t rows, size_t cols);
 int dcg_colsum(const float* a, float* out, size_t rows, size_t cols,
                void* workspace, size_t workspace_bytes, dcg_stream_t stream);
 
+/* The same column sum for callers that cannot allocate device memory and have none to spare for
+ * scratch - for instance a backend plugged in behind a handler that is given operand pointers only
+ * and runs under a memory budget fixed at start-up, or inside a loop that must stay out of the
+ * driver's allocator.  This entry point has no counterpart in the reference.
+ * The scratch is a 256 KiB array built into the library image (dcg_colsum_noalloc_max_bytes()); every
+ * GPU the library is loaded on holds it until the process exits.  A shape whose partial sums do not
+ * fit (dcg_colsum_workspace_bytes(rows, cols) larger than that) is refused with DCG_ERR_WORKSPACE.
+ * No cudaMalloc, cudaFree or other allocating call is made.  The first call on a device looks up
+ * the array's device address (one cudaGetSymbolAddress); make that first call before any stream
+ * capture.  All calls on a device share the one array: two calls whose kernels can overlap on the
+ * GPU (different streams, no ordering between them) race on it and corrupt each other's result. */
+size_t dcg_colsum_noalloc_max_bytes(void);
+int dcg_colsum_noalloc(const float* a, float* out, size_t rows, size_t cols, dcg_stream_t stream);
+
 /* out[r] = sum_c a[r, c].  Replaces gpu::kernel_mat_sum_rows (src/gpu/sum.cu:66-109). */
 int dcg_rowsum(const float* a, float* out, size_t rows, size_t cols, dcg_stream_t stream);
 
