@@ -211,6 +211,9 @@ def run_ours(args, rank, local_rank, world):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda:%d" % local_rank)
     if world > 1:
+        # NCCL_DEBUG=VERSION makes NCCL print its version banner on stdout, next to the JSON line
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=dev)
     assert world == args.gpus, "launch with torchrun --nproc-per-node equal to --gpus"
 

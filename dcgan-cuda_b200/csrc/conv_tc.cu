@@ -105,10 +105,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 
-// Bounded wait.  Returns false (after recording the failure) if the phase never completes.
-__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int role, int stage)
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
 {
-    if (mbar_try_wait(bar, parity)) return true;
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// Bounded wait, slow path.  Returns false (after recording the failure) if the phase never completes.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int role, int stage)
+{
     const long long t0 = clock64();
     for (;;) {
 #pragma unroll 1
@@ -122,6 +132,33 @@ __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int role, 
         g_tc_status[3] = stage;
     }
     return false;
+}
+
+// Bounded wait: a non-blocking probe first (the common case in a running pipeline), then the
+// suspending, time-limited loop.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int role, int stage)
+{
+    if (mbar_test_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, role, stage);
+}
+
+// Warp-uniform form for loops that a whole warp walks in lockstep (one elected lane issues): the
+// vote makes the outcome uniform by construction, which keeps the loop state in uniform registers.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int role, int stage)
+{
+    if (__all_sync(0xffffffffu, mbar_test_wait(bar, parity))) return true;
+    return __all_sync(0xffffffffu, mbar_wait_slow(bar, parity, role, stage));
+}
+
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
 }
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
@@ -225,7 +262,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t tmem_slot = tmem_full_bar + 8u;
     uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
 
     // ---- decode this CTA's work item -------------------------------------------------------------
     // blockIdx.x = ((group * m_count + m) * n_tiles + n) * splits + split, where group is the parity
@@ -295,7 +332,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // One thread issues every load.  All position bookkeeping is incremental: an integer division
         // costs this lone thread ~100 cycles, and the loop has to turn around in well under the 256
         // cycles the tensor core needs per stage.
-        if (lane == 0) {
+        {
             const uint32_t tx_bytes = (uint32_t)(A_STAGE_BYTES + b_stage_bytes);
             int s = 0;
             uint32_t phase = 0;
@@ -311,8 +348,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             const int wrap_dj = (MODE == MODE_FWD) ? p.KW : taps_w;
             for (int it = 0; it < nq; ++it) {
-                if (!mbar_wait(empty_bar + 8u * s, phase ^ 1u, 0, it)) break;
+                if (!mbar_wait_warp(empty_bar + 8u * s, phase ^ 1u, 0, it)) break;
                 const uint32_t fb = full_bar + 8u * s;
+                if (elect_one()) {
                 TC_TRACE(it);
                 if (p.debug & 2) {   // timing experiment: no loads, the stage is declared full at once
                     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(fb) : "memory");
@@ -352,6 +390,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         }
                     }
                 }
+                }
                 // advance to the next stage
                 if (MODE == MODE_DK) {
                     if (++dj == p.tiles_w) { dj = 0; if (++di == p.tiles_h) { di = 0; ++tap; } }
@@ -364,7 +403,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     } else if (warp == 1) {
         // ===== MMA issuer =====
-        if (lane == 0) {
+        {
             const int a_mn = (MODE == MODE_DK) ? 1 : 0;
             const int b_mn = (MODE == MODE_DX) ? 0 : 1;
             const uint32_t idesc = make_idesc(a_mn, b_mn, p.bn, BM);
@@ -385,9 +424,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int s = 0;
             uint32_t phase = 0;
             for (int it = 0; it < nq; ++it) {
-                if (!mbar_wait(full_bar + 8u * s, phase, 1, it)) break;
-                TC_TRACE(1024 + it);
+                if (!mbar_wait_warp(full_bar + 8u * s, phase, 1, it)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (elect_one()) {
+                TC_TRACE(1024 + it);
                 if (p.debug & 1) {   // timing experiment: no MMA, the stage is released at once
                     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_bar + 8u * s) : "memory");
                 } else {
@@ -400,20 +440,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tcgen05_commit(empty_bar + 8u * s);  // frees the stage once these MMAs have read it
                 }
                 TC_TRACE(2048 + it);
+                }
                 if (++s == p.stages) { s = 0; phase ^= 1u; }
             }
-            tcgen05_commit(tmem_full_bar);           // accumulator complete (or abandoned)
+            if (elect_one()) tcgen05_commit(tmem_full_bar);   // accumulator complete (or abandoned)
         }
     } else {
         // ===== epilogue: warps 2..5, TMEM lane quadrant = warp % 4 =====
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
-        bool ok = mbar_wait(tmem_full_bar, 0, 2, 0);
-        ok = __all_sync(0xffffffffu, ok);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (threadIdx.x == 64) TC_TRACE(3074);
-
-        // where does this accumulator row go?
+        // where does this accumulator row go?  (worked out while the main loop is still running)
         bool row_valid = false;
         unsigned long long row_off = 0;   // element offset of column 0 of this row
         long long col_stride = 1;         // element stride between accumulator columns
@@ -452,6 +488,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 ncols_valid = min(p.bn, p.C - ch0);
             }
         }
+        bool ok = mbar_wait(tmem_full_bar, 0, 2, 0);
+        ok = __all_sync(0xffffffffu, ok);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (threadIdx.x == 64) TC_TRACE(3074);
         if (!ok || nq <= 0) row_valid = false;   // nothing trustworthy to store
         float* dst = p.direct ? p.out : p.out + (unsigned long long)split * p.out_elems;
         // Row-contiguous outputs whose channel count is a multiple of 4 go through shared memory:
@@ -469,6 +509,21 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             long long* s_rowoff = reinterpret_cast<long long*>(stg + 2 * BM * kPitch);
             const int tid_e = threadIdx.x - 64;
             s_rowoff[row] = row_valid ? (long long)row_off : -1;
+            asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps only
+            // Store phase geometry, fixed for the whole tile: thread t writes the 16-byte column quad
+            // cq of rows r0, r0+16, ..., r0+112 - every store instruction covers four whole
+            // 128-byte row segments.  With one warp per scheduler nothing hides instruction latency,
+            // so everything that does not depend on the slab is worked out once, here.
+            const int cq = (tid_e & 7) << 2;
+            const int r0 = tid_e >> 3;
+            long long off[8];             // element offset of (row, cq), < 0: row outside the tensor
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const long long ro = s_rowoff[r0 + 16 * k];
+                off[k] = ro < 0 ? -1 : ro + cq;
+            }
+            const EpilogueArgs& e = p.ep;
+            const bool fused = p.direct && (e.raw_out || e.bias || e.pre_act || e.gate || e.act != DCG_ACT_NONE);
             int pass = 0;
             for (int c0 = 0; c0 < p.bn; c0 += 32, ++pass) {
                 uint32_t r[32];
@@ -481,45 +536,74 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     for (int q = 16; q < 32; ++q) r[q] = 0u;
                 }
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (threadIdx.x == 64) TC_TRACE(3000 + pass * 4 + 0);
                 float* buf = stg + (pass & 1) * (BM * kPitch);
                 float4* mine = reinterpret_cast<float4*>(buf + row * kPitch);
 #pragma unroll
                 for (int q = 0; q < 8; ++q)
                     mine[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
                                           __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-                asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps only
+                if (threadIdx.x == 64) TC_TRACE(3000 + pass * 4 + 1);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) TC_TRACE(3000 + pass * 4 + 2);
+                const bool col_ok = c0 + cq < ncols_valid;
+                float4 vv[8];
+                const float* src = buf + r0 * kPitch + cq;
 #pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const int f = tid_e + 128 * k;
-                    const int rr = f >> 3, c4 = (f & 7) << 2;
-                    const int col = c0 + c4;
-                    const long long ro = s_rowoff[rr];
-                    if (ro < 0 || col >= ncols_valid) continue;
-                    float4 v = *reinterpret_cast<const float4*>(buf + rr * kPitch + c4);
-                    const unsigned long long idx = (unsigned long long)ro + (unsigned long long)col;
-                    if (p.direct) {
-                        const EpilogueArgs& e = p.ep;
-                        if (e.raw_out) *reinterpret_cast<float4*>(e.raw_out + idx) = v;
-                        if (e.bias) {
-                            const float4 b = __ldg(reinterpret_cast<const float4*>(e.bias + ch0 + col));
-                            v.x = __fadd_rn(v.x, b.x); v.y = __fadd_rn(v.y, b.y);
-                            v.z = __fadd_rn(v.z, b.z); v.w = __fadd_rn(v.w, b.w);
-                        }
-                        if (e.pre_act) *reinterpret_cast<float4*>(e.pre_act + idx) = v;
-                        if (e.act != DCG_ACT_NONE) {
-                            v.x = act_apply(v.x, e.act, e.alpha); v.y = act_apply(v.y, e.act, e.alpha);
-                            v.z = act_apply(v.z, e.act, e.alpha); v.w = act_apply(v.w, e.act, e.alpha);
-                        }
-                        if (e.gate) {
-                            const float4 g = __ldg(reinterpret_cast<const float4*>(e.gate + idx));
-                            v.x = act_grad_apply(g.x, v.x, e.gate_act, e.gate_alpha);
-                            v.y = act_grad_apply(g.y, v.y, e.gate_act, e.gate_alpha);
-                            v.z = act_grad_apply(g.z, v.z, e.gate_act, e.gate_alpha);
-                            v.w = act_grad_apply(g.w, v.w, e.gate_act, e.gate_alpha);
+                for (int k = 0; k < 8; ++k) vv[k] = *reinterpret_cast<const float4*>(src + 16 * k * kPitch);
+                if (!col_ok) continue;
+                float* dcol = dst + c0;
+                if (fused) {
+                    // each optional step of the chain runs over all eight quads at once, so its
+                    // test is paid once per slab and the loads of a step are in flight together
+                    if (e.raw_out) {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            if (off[k] >= 0) *reinterpret_cast<float4*>(e.raw_out + c0 + off[k]) = vv[k];
+                    }
+                    if (e.bias) {
+                        const float4 b = __ldg(reinterpret_cast<const float4*>(e.bias + ch0 + c0 + cq));
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            vv[k].x = __fadd_rn(vv[k].x, b.x); vv[k].y = __fadd_rn(vv[k].y, b.y);
+                            vv[k].z = __fadd_rn(vv[k].z, b.z); vv[k].w = __fadd_rn(vv[k].w, b.w);
                         }
                     }
-                    *reinterpret_cast<float4*>(dst + idx) = v;
+                    if (e.pre_act) {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            if (off[k] >= 0) *reinterpret_cast<float4*>(e.pre_act + c0 + off[k]) = vv[k];
+                    }
+                    if (e.act != DCG_ACT_NONE) {
+                        const int act = e.act;
+                        const float alpha = e.alpha;
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            vv[k].x = act_apply(vv[k].x, act, alpha); vv[k].y = act_apply(vv[k].y, act, alpha);
+                            vv[k].z = act_apply(vv[k].z, act, alpha); vv[k].w = act_apply(vv[k].w, act, alpha);
+                        }
+                    }
+                    if (e.gate) {
+                        float4 gg[8];
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)
+                            gg[k] = off[k] >= 0 ? __ldg(reinterpret_cast<const float4*>(e.gate + c0 + off[k]))
+                                                : make_float4(0.f, 0.f, 0.f, 0.f);
+                        const int gact = e.gate_act;
+                        const float galpha = e.gate_alpha;
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            vv[k].x = act_grad_apply(gg[k].x, vv[k].x, gact, galpha);
+                            vv[k].y = act_grad_apply(gg[k].y, vv[k].y, gact, galpha);
+                            vv[k].z = act_grad_apply(gg[k].z, vv[k].z, gact, galpha);
+                            vv[k].w = act_grad_apply(gg[k].w, vv[k].w, gact, galpha);
+                        }
+                    }
                 }
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    if (off[k] >= 0) *reinterpret_cast<float4*>(dcol + off[k]) = vv[k];
+                if (threadIdx.x == 64) TC_TRACE(3000 + pass * 4 + 3);
             }
         } else {
             for (int c0 = 0; c0 < p.bn; c0 += 32) {
