@@ -22,8 +22,10 @@
 // accumulator (tcgen05.ld) through the fused epilogue (raw / bias / pre-activation / activation /
 // activation-gradient gate) into HBM.  A ring of smem stages (A 16 KB + B BN*128 B, 128-byte
 // swizzle) is handed over with mbarriers: TMA complete_tx -> MMA, tcgen05.commit -> TMA.
-// Split-K partitions write fp32 partials to scratch; a second kernel adds them in split order
-// (deterministic) and applies the epilogue.
+// The K partitions of one tile form a thread-block cluster: each writes its fp32 partial tile to
+// scratch (L2-resident), the cluster meets at a hardware barrier, and every CTA then adds the
+// partials of its share of the tile in partition order (deterministic) and finishes it, fused
+// epilogue included - one launch per convolution, no reduction kernel.
 //
 // Every wait is bounded: a barrier that does not complete within ~1 s makes the waiting role
 // record an error code in a device status word and leave; TMEM is always released.
@@ -43,6 +45,10 @@ constexpr int BK = 32;                  // K elements per pipeline stage (one 12
 constexpr int A_STAGE_BYTES = BM * BK * 4;
 constexpr int kThreads = 192;
 constexpr int kMaxSmem = 227 * 1024;
+constexpr int kMaxCluster = 8;          // portable thread-block cluster size: the cap on K partitions
+// Floats of shared memory the epilogue's transposition buffer takes for a 128 x bn tile (quads at a
+// pitch of BM + 1 sixteen-byte units); the row-offset table follows it.
+__host__ __device__ constexpr int kRedFloats(int bn) { return (bn / 4) * (BM + 1) * 4; }
 constexpr long long kWaitCycles = 2000000000LL;  // ~1 s at 2 GHz
 
 enum Mode { MODE_FWD = 0, MODE_DX = 1, MODE_DK = 2 };
@@ -66,15 +72,15 @@ struct Params {
     int m_tiles;                  // DK: 128-row tiles along the M channel axis
     int n_tiles;                  // BN-column tiles along the N channel axis
     int bn;                       // accumulator columns, multiple of 16, <= 256
-    int splits;                   // K partitions
+    int splits;                   // K partitions = CTAs per cluster (<= 8)
     int kchunks;                  // 32-wide chunks along the contracted channel axis (FWD: C, DX: O)
     int swap;                     // DK: M axis is o (A from dy, B from x)
     int narrow;                   // FWD/DK with <= 4 input channels: x is read through the window map
+    int ext_finish;               // the K partitions only write partials; a second kernel adds them (narrow DK)
     int debug;                    // timing experiments (DCG_TC_DEBUG): 1 = no MMA, 2 = no TMA; results are garbage
     int stages;                   // pipeline depth
-    int direct;                   // 1: epilogue + final store, 0: raw partial to scratch
-    float* out;                   // final tensor (direct) or scratch base
-    unsigned long long out_elems; // elements of the output tensor (scratch stride per split)
+    float* out;                   // the output tensor
+    float* scratch;               // splits > 1: partial tiles, [CTA][128 x bn], quad- or column-major
     EpilogueArgs ep;
 };
 
@@ -161,6 +167,14 @@ __device__ __forceinline__ bool elect_one()
     return pred != 0;
 }
 
+// ---- thread-block cluster barrier -----------------------------------------------------------------
+// The barrier is a hardware one (no time limit can be attached); every thread of every CTA of the
+// cluster reaches both of its uses on every path, error paths included.
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                             int c0, int c1, int c2, int c3)
 {
@@ -244,7 +258,7 @@ __device__ __forceinline__ uint32_t make_idesc(int a_mn_major, int b_mn_major, i
 
 // ---- the kernel ---------------------------------------------------------------------------------
 template <int MODE>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ Params p)
 {
@@ -292,7 +306,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         taps_h = rh < p.KH ? (p.KH - rh + p.sh - 1) / p.sh : 0;
         taps_w = rw < p.KW ? (p.KW - rw + p.sw - 1) / p.sw : 0;
     } else if (MODE == MODE_DK) {
-        if (p.narrow) { tap_di = group; tap_dj = 0; }   // one group per kernel row, all columns at once
+        if (p.narrow) { tap_di = 0; tap_dj = 0; }   // one tile holds every tap: 32 window slots per kernel row
         else { tap_di = group / p.KW; tap_dj = group % p.KW; }
     }
     // K-stage range of this split
@@ -326,6 +340,21 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = *tmem_slot_ptr;
     if (threadIdx.x == 64) TC_TRACE(3073);
+
+    // ---- epilogue geometry (uniform over the CTA) ---------------------------------------------------
+    const int ch0 = n_tile * p.bn;    // channel index of accumulator column 0 (bias axis) unless DK
+    int ncols_valid;                  // valid columns in this N tile
+    long long col_stride = 1;         // element stride between accumulator columns in the output
+    if (MODE == MODE_FWD) ncols_valid = min(p.bn, p.O - ch0);
+    else if (MODE == MODE_DX) ncols_valid = min(p.bn, p.C - ch0);
+    else if (p.narrow) { ncols_valid = 32 * p.KH; col_stride = p.O; }
+    else if (!p.swap) ncols_valid = min(p.bn, p.O - ch0);
+    else { ncols_valid = min(p.bn, p.C - ch0); col_stride = p.O; }
+    // Row-contiguous outputs whose channel count allows 16-byte stores take the vector path.
+    const int ch_total = (MODE == MODE_DX) ? p.C : p.O;
+    const bool vec = col_stride == 1 && (ch_total & 3) == 0 && (ncols_valid & 3) == 0;
+    float* red = reinterpret_cast<float*>(smem_raw + (a_base - smem_u32(smem_raw)));
+    long long* s_rowoff = reinterpret_cast<long long*>(red + kRedFloats(p.bn));
 
     if (warp == 0) {
         // ===== TMA producer =====
@@ -378,9 +407,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         // (tap, di, dj) count the 32-pixel tiles along (n, h, w)
                         const int pj = dj * p.TW, pi = di * p.TH, pn = tap * p.TN;
                         const int xw = p.sw * pj + tap_dj - p.pl, xh = p.sh * pi + tap_di - p.pt;
-                        if (p.narrow) {  // A: dy (rows o), B: the 32-float windows of 32 output pixels, row tap_di
+                        if (p.narrow) {  // A: dy (rows o), B: the KH 32-float windows of 32 output pixels
                             tma_load_5d(a_dst, &map_a, fb, 0, pj, pi, pn, m_tile * (BM / 32));
-                            tma_load_5d(b_dst, &map_b, fb, 0, pj, pi, pn, tap_di);
+                            tma_load_5d(b_dst, &map_b, fb, 0, pj, pi, pn, 0);   // box covers all KH kernel rows
                         } else if (!p.swap) {   // A: x (rows c), B: dy (cols o)
                             tma_load_5d(a_dst, &map_a, fb, 0, xw, xh, pn, m_tile * (BM / 32));
                             tma_load_5d(b_dst, &map_b, fb, 0, pj, pi, pn, n_tile * (p.bn / 32));
@@ -446,46 +475,36 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (elect_one()) tcgen05_commit(tmem_full_bar);   // accumulator complete (or abandoned)
         }
     } else {
-        // ===== epilogue: warps 2..5, TMEM lane quadrant = warp % 4 =====
+        // ===== epilogue, part 1 (warps 2..5; TMEM lane quadrant = warp % 4; thread = accumulator row) =====
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
         // where does this accumulator row go?  (worked out while the main loop is still running)
         bool row_valid = false;
         unsigned long long row_off = 0;   // element offset of column 0 of this row
-        long long col_stride = 1;         // element stride between accumulator columns
-        int ncols_valid = 0;              // valid columns in this N tile
-        int ch0 = n_tile * p.bn;          // channel index of column 0 (bias axis) unless DK
         if (MODE == MODE_FWD) {
             const int tw = row % p.TW, th = (row / p.TW) % p.TH, tn = row / (p.TW * p.TH);
             const int n = n0 + tn, i = i0 + th, j = j0 + tw;
             row_valid = n < p.N && i < p.Ho && j < p.Wo;
             row_off = (((unsigned long long)n * p.Ho + i) * p.Wo + j) * p.O + ch0;
-            ncols_valid = min(p.bn, p.O - ch0);
         } else if (MODE == MODE_DX) {
             const int tw = row % p.TW, th = (row / p.TW) % p.TH, tn = row / (p.TW * p.TH);
             const int n = n0 + tn, h = p.sh * (i0 + th) + ph, w = p.sw * (j0 + tw) + pw;
             row_valid = n < p.N && h < p.H && w < p.W;
             row_off = (((unsigned long long)n * p.H + h) * p.W + w) * p.C + ch0;
-            ncols_valid = min(p.bn, p.C - ch0);
         } else {
             const unsigned long long tap_off = (unsigned long long)group * p.C * p.O;
-            if (p.narrow) {  // rows o, columns = window slots (kernel column dj = slot / 4, channel = slot % 4)
+            if (p.narrow) {  // rows o, columns = 32 * kernel row + window slot (kernel column dj = slot / 4, channel = slot % 4)
                 const int o = m_tile * BM + row;
                 row_valid = o < p.O;
-                row_off = (unsigned long long)group * p.KW * p.C * p.O + o;   // group = kernel row
-                col_stride = p.O;        // never used as such: narrow_off() maps slots to dk
-                ncols_valid = 4 * p.KW;
+                row_off = o;
             } else if (!p.swap) {   // rows c, columns o
                 const int c = m_tile * BM + row;
                 row_valid = c < p.C;
                 row_off = tap_off + (unsigned long long)c * p.O + ch0;
-                ncols_valid = min(p.bn, p.O - ch0);
             } else {         // rows o, columns c
                 const int o = m_tile * BM + row;
                 row_valid = o < p.O;
                 row_off = tap_off + (unsigned long long)ch0 * p.O + o;
-                col_stride = p.O;
-                ncols_valid = min(p.bn, p.C - ch0);
             }
         }
         bool ok = mbar_wait(tmem_full_bar, 0, 2, 0);
@@ -493,145 +512,202 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (threadIdx.x == 64) TC_TRACE(3074);
         if (!ok || nq <= 0) row_valid = false;   // nothing trustworthy to store
-        float* dst = p.direct ? p.out : p.out + (unsigned long long)split * p.out_elems;
-        // Row-contiguous outputs whose channel count is a multiple of 4 go through shared memory:
-        // with one accumulator row per thread a direct 128-bit store instruction would scatter its 32
-        // lanes over 32 different cache lines, so each 32-column slab is first parked in a padded
-        // staging buffer (the pipeline stages are free by now) and then written out with every
-        // store instruction covering four whole 128-byte row segments.  The fused epilogue runs in
-        // that second, coalesced phase.  Column-strided outputs (DK with the roles swapped, the
-        // narrow-channel DK) are already coalesced across lanes and keep the per-row scalar path.
-        const int ch_total = (MODE == MODE_DX) ? p.C : p.O;
-        const bool staged = col_stride == 1 && (ch_total & 3) == 0 && (ncols_valid & 3) == 0;
-        if (staged) {
-            constexpr int kPitch = 36;   // floats per staged row: 32 + 4 keeps 128-bit accesses conflict-free
-            float* stg = reinterpret_cast<float*>(smem_raw + (a_base - smem_u32(smem_raw)));
-            long long* s_rowoff = reinterpret_cast<long long*>(stg + 2 * BM * kPitch);
-            const int tid_e = threadIdx.x - 64;
-            s_rowoff[row] = row_valid ? (long long)row_off : -1;
-            asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps only
-            // Store phase geometry, fixed for the whole tile: thread t writes the 16-byte column quad
-            // cq of rows r0, r0+16, ..., r0+112 - every store instruction covers four whole
-            // 128-byte row segments.  With one warp per scheduler nothing hides instruction latency,
-            // so everything that does not depend on the slab is worked out once, here.
-            const int cq = (tid_e & 7) << 2;
-            const int r0 = tid_e >> 3;
-            long long off[8];             // element offset of (row, cq), < 0: row outside the tensor
+        // The pipeline stages are idle from here on (every MMA that read them has completed).
+        s_rowoff[row] = row_valid ? (long long)row_off : -1;
+    }
+
+    // ===== the K partitions of a tile meet =====
+    // The S partitions of one tile form a thread-block cluster, which guarantees that they run at the
+    // same time and gives them a hardware barrier.  Each partition writes its partial accumulator
+    // to scratch (it stays in L2), the cluster meets, and partition j then finishes a 1/S share of
+    // the tile: it adds the S partials in partition order - so the result does not depend on timing -
+    // applies the fused chain and writes the final tensor.  (Handing the partials over through
+    // distributed shared memory instead was measured at under 10 bytes per clock and SM.)
+    // Partials are stored quad-major, [CTA][16-byte column quad][row]: lanes are consecutive rows, so
+    // both the partial stores and the loads of the second phase move 512 contiguous bytes per warp.
+    // Without partitions the same layout in shared memory (quad pitch QS) is the transposition buffer
+    // between "thread = row" (TMEM) and "warp = row segment" (coalesced global stores).
+    const int S = p.splits, part = split;
+    const bool multi = S > 1;
+    const bool finish_here = !p.ext_finish;   // else: partials only, a second kernel adds them
+    const int qpr = p.bn >> 2;                // vector path: 16-byte column quads per row,
+    const int QPO = (qpr + S - 1) / S;        //   quads per share
+    const int QS = BM + 1;                    // shared-memory quad pitch in 16-byte units (odd: lanes = quads hit distinct banks)
+    const int CL = (p.bn + S - 1) / S;        // scalar path: columns per share
+    float* my_scratch = p.scratch + (size_t)blockIdx.x * BM * p.bn;
+    const float* tile_scratch = p.scratch + (size_t)(blockIdx.x - part) * BM * p.bn;
+    if (threadIdx.x == 64) TC_TRACE(3000);
+    if (warp >= 2) {
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        for (int c0 = 0; c0 < p.bn; c0 += 32) {
+            uint32_t r[32];
+            const uint32_t taddr = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0;
+            const bool full = p.bn - c0 >= 32;   // bn is a multiple of 16: the last slab has 32 or 16 columns
+            if (full) tmem_ld_32x32b_x32(taddr, r);
+            else tmem_ld_32x32b_x16(taddr, r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (vec) {
+                if (multi) {
+                    float4* d4 = reinterpret_cast<float4*>(my_scratch) + (size_t)(c0 >> 2) * BM + row;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const long long ro = s_rowoff[r0 + 16 * k];
-                off[k] = ro < 0 ? -1 : ro + cq;
-            }
-            const EpilogueArgs& e = p.ep;
-            const bool fused = p.direct && (e.raw_out || e.bias || e.pre_act || e.gate || e.act != DCG_ACT_NONE);
-            int pass = 0;
-            for (int c0 = 0; c0 < p.bn; c0 += 32, ++pass) {
-                uint32_t r[32];
-                const uint32_t taddr = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0;
-                if (p.bn - c0 >= 32) {
-                    tmem_ld_32x32b_x32(taddr, r);
+                    for (int q = 0; q < 8; ++q)
+                        if (q < 4 || full)
+                            __stcg(d4 + q * BM, make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                            __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3])));
                 } else {
-                    tmem_ld_32x32b_x16(taddr, r);
+                    float4* d4 = reinterpret_cast<float4*>(red) + (c0 >> 2) * QS + row;
 #pragma unroll
-                    for (int q = 16; q < 32; ++q) r[q] = 0u;
+                    for (int q = 0; q < 8; ++q)
+                        if (q < 4 || full)
+                            d4[q * QS] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                     __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
                 }
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (threadIdx.x == 64) TC_TRACE(3000 + pass * 4 + 0);
-                float* buf = stg + (pass & 1) * (BM * kPitch);
-                float4* mine = reinterpret_cast<float4*>(buf + row * kPitch);
+            } else {
+                // column-major [column][row], in scratch or in shared memory
+                float* d1 = (multi ? my_scratch : red) + (size_t)c0 * BM + row;
 #pragma unroll
-                for (int q = 0; q < 8; ++q)
-                    mine[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                          __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-                if (threadIdx.x == 64) TC_TRACE(3000 + pass * 4 + 1);
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (threadIdx.x == 64) TC_TRACE(3000 + pass * 4 + 2);
-                const bool col_ok = c0 + cq < ncols_valid;
-                float4 vv[8];
-                const float* src = buf + r0 * kPitch + cq;
+                for (int q = 0; q < 32; ++q)
+                    if (q < 16 || full) d1[q * BM] = __uint_as_float(r[q]);
+            }
+        }
+        if (multi) __threadfence();   // the partial is visible device-wide before this CTA arrives
+    }
+    if (threadIdx.x == 64) TC_TRACE(3001);
+    __syncwarp();
+    if (multi && finish_here) cluster_sync_all();
+    else if (warp >= 2) asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (threadIdx.x == 64) TC_TRACE(3002);
+
+    if (warp >= 2 && finish_here) {
+        // ===== this partition's share: sum in partition order, fused chain, stores =====
+        const int tid_e = threadIdx.x - 64;
+        const EpilogueArgs& e = p.ep;
+        if (vec) {
+            const bool fused = e.raw_out || e.bias || e.pre_act || e.gate || e.act != DCG_ACT_NONE;
+            // multi: thread = row, items = the quads of this share.  single: item = (row, quad) with
+            // consecutive lanes on consecutive quads, so a warp stores whole 128-byte row segments.
+            const int Qm = min(QPO, qpr - part * QPO);
+            const int per_thread = multi ? Qm : qpr;             // items per thread (128 * qpr items / 128 threads)
+            const int step_r = 128 / qpr, step_q = 128 % qpr;    // single: how (row, quad) moves when the item index grows by 128
+            int rr = tid_e / qpr, q = tid_e % qpr;
+            const long long my_ro = s_rowoff[tid_e];
+            const float4* red4 = reinterpret_cast<const float4*>(red);
+            const float4* ts4 = reinterpret_cast<const float4*>(tile_scratch);
+            for (int base = 0; base < per_thread; base += 4) {
+                float4 acc[4];
+                long long goff[4];
+                int cq[4];
+                if (multi) {
+                    const float4* src[4];
 #pragma unroll
-                for (int k = 0; k < 8; ++k) vv[k] = *reinterpret_cast<const float4*>(src + 16 * k * kPitch);
-                if (!col_ok) continue;
-                float* dcol = dst + c0;
+                    for (int u = 0; u < 4; ++u) {
+                        const bool in = base + u < per_thread;
+                        const int qd = part * QPO + (in ? base + u : 0);
+                        cq[u] = qd << 2;
+                        goff[u] = (!in || my_ro < 0 || cq[u] >= ncols_valid) ? -1 : my_ro + cq[u];
+                        src[u] = ts4 + (size_t)qd * BM + tid_e;
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) acc[u] = __ldcg(src[u]);
+                    for (int sidx = 1; sidx < S; ++sidx) {
+                        float4 v[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) v[u] = __ldcg(src[u] + (size_t)sidx * BM * qpr);
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            acc[u].x = __fadd_rn(acc[u].x, v[u].x); acc[u].y = __fadd_rn(acc[u].y, v[u].y);
+                            acc[u].z = __fadd_rn(acc[u].z, v[u].z); acc[u].w = __fadd_rn(acc[u].w, v[u].w);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const bool in = base + u < per_thread;
+                        cq[u] = q << 2;
+                        const long long ro = in ? s_rowoff[rr] : -1;
+                        goff[u] = (ro < 0 || cq[u] >= ncols_valid) ? -1 : ro + cq[u];
+                        acc[u] = red4[in ? q * QS + rr : 0];
+                        rr += step_r; q += step_q;
+                        if (q >= qpr) { q -= qpr; ++rr; }
+                    }
+                }
                 if (fused) {
-                    // each optional step of the chain runs over all eight quads at once, so its
-                    // test is paid once per slab and the loads of a step are in flight together
+                    // each optional step of the chain runs over the four items at once, so its
+                    // test is paid once and the loads of a step are in flight together
                     if (e.raw_out) {
 #pragma unroll
-                        for (int k = 0; k < 8; ++k)
-                            if (off[k] >= 0) *reinterpret_cast<float4*>(e.raw_out + c0 + off[k]) = vv[k];
+                        for (int u = 0; u < 4; ++u)
+                            if (goff[u] >= 0) *reinterpret_cast<float4*>(e.raw_out + goff[u]) = acc[u];
                     }
                     if (e.bias) {
-                        const float4 b = __ldg(reinterpret_cast<const float4*>(e.bias + ch0 + c0 + cq));
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-                            vv[k].x = __fadd_rn(vv[k].x, b.x); vv[k].y = __fadd_rn(vv[k].y, b.y);
-                            vv[k].z = __fadd_rn(vv[k].z, b.z); vv[k].w = __fadd_rn(vv[k].w, b.w);
+                        for (int u = 0; u < 4; ++u) {
+                            const float4 bv = __ldg(reinterpret_cast<const float4*>(e.bias + ch0 + cq[u]));
+                            acc[u].x = __fadd_rn(acc[u].x, bv.x); acc[u].y = __fadd_rn(acc[u].y, bv.y);
+                            acc[u].z = __fadd_rn(acc[u].z, bv.z); acc[u].w = __fadd_rn(acc[u].w, bv.w);
                         }
                     }
                     if (e.pre_act) {
 #pragma unroll
-                        for (int k = 0; k < 8; ++k)
-                            if (off[k] >= 0) *reinterpret_cast<float4*>(e.pre_act + c0 + off[k]) = vv[k];
+                        for (int u = 0; u < 4; ++u)
+                            if (goff[u] >= 0) *reinterpret_cast<float4*>(e.pre_act + goff[u]) = acc[u];
                     }
                     if (e.act != DCG_ACT_NONE) {
                         const int act = e.act;
                         const float alpha = e.alpha;
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-                            vv[k].x = act_apply(vv[k].x, act, alpha); vv[k].y = act_apply(vv[k].y, act, alpha);
-                            vv[k].z = act_apply(vv[k].z, act, alpha); vv[k].w = act_apply(vv[k].w, act, alpha);
+                        for (int u = 0; u < 4; ++u) {
+                            acc[u].x = act_apply(acc[u].x, act, alpha); acc[u].y = act_apply(acc[u].y, act, alpha);
+                            acc[u].z = act_apply(acc[u].z, act, alpha); acc[u].w = act_apply(acc[u].w, act, alpha);
                         }
                     }
                     if (e.gate) {
-                        float4 gg[8];
+                        float4 gg[4];
 #pragma unroll
-                        for (int k = 0; k < 8; ++k)
-                            gg[k] = off[k] >= 0 ? __ldg(reinterpret_cast<const float4*>(e.gate + c0 + off[k]))
-                                                : make_float4(0.f, 0.f, 0.f, 0.f);
+                        for (int u = 0; u < 4; ++u)
+                            gg[u] = goff[u] >= 0 ? __ldg(reinterpret_cast<const float4*>(e.gate + goff[u]))
+                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
                         const int gact = e.gate_act;
                         const float galpha = e.gate_alpha;
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-                            vv[k].x = act_grad_apply(gg[k].x, vv[k].x, gact, galpha);
-                            vv[k].y = act_grad_apply(gg[k].y, vv[k].y, gact, galpha);
-                            vv[k].z = act_grad_apply(gg[k].z, vv[k].z, gact, galpha);
-                            vv[k].w = act_grad_apply(gg[k].w, vv[k].w, gact, galpha);
+                        for (int u = 0; u < 4; ++u) {
+                            acc[u].x = act_grad_apply(gg[u].x, acc[u].x, gact, galpha);
+                            acc[u].y = act_grad_apply(gg[u].y, acc[u].y, gact, galpha);
+                            acc[u].z = act_grad_apply(gg[u].z, acc[u].z, gact, galpha);
+                            acc[u].w = act_grad_apply(gg[u].w, acc[u].w, gact, galpha);
                         }
                     }
                 }
 #pragma unroll
-                for (int k = 0; k < 8; ++k)
-                    if (off[k] >= 0) *reinterpret_cast<float4*>(dcol + off[k]) = vv[k];
-                if (threadIdx.x == 64) TC_TRACE(3000 + pass * 4 + 3);
+                for (int u = 0; u < 4; ++u)
+                    if (goff[u] >= 0) *reinterpret_cast<float4*>(p.out + goff[u]) = acc[u];
             }
         } else {
-            for (int c0 = 0; c0 < p.bn; c0 += 32) {
-                uint32_t r[32];
-                const uint32_t taddr = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0;
-                if (p.bn - c0 >= 32) {
-                    tmem_ld_32x32b_x32(taddr, r);
+            // thread = row; share = every S-th column.  Used where consecutive ROWS are adjacent in
+            // memory (DK with the channel roles swapped, narrow-channel DK) and for channel counts
+            // that rule out 16-byte stores.
+            const long long ro = s_rowoff[tid_e];
+            for (int cl = 0; cl < CL; ++cl) {
+                const int col = cl * S + part;
+                if (col >= ncols_valid) break;
+                float acc;
+                if (multi) {
+                    const float* src = tile_scratch + (size_t)col * BM + tid_e;
+                    acc = __ldcg(src);
+                    for (int sidx = 1; sidx < S; ++sidx) acc = __fadd_rn(acc, __ldcg(src + (size_t)sidx * BM * p.bn));
                 } else {
-                    tmem_ld_32x32b_x16(taddr, r);
-#pragma unroll
-                    for (int q = 16; q < 32; ++q) r[q] = 0u;
+                    acc = red[col * BM + tid_e];
                 }
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (!row_valid) continue;
-#pragma unroll
-                for (int q = 0; q < 32; ++q) {
-                    const int col = c0 + q;
-                    if (col >= ncols_valid) break;
-                    unsigned long long id = row_off + (unsigned long long)col * col_stride;
-                    if (MODE == MODE_DK && p.narrow) {
-                        if ((col & 3) >= p.C) continue;   // slot = 4*dj + channel, channels beyond C are padding
-                        id = row_off + (unsigned long long)((col >> 2) * p.C + (col & 3)) * p.O;
-                    }
-                    // the epilogue chain only exists for FWD/DX; DK and split-K partials store raw sums
-                    dst[id] = (MODE == MODE_DK || !p.direct)
-                                  ? __uint_as_float(r[q])
-                                  : epilogue_apply(p.ep, __uint_as_float(r[q]), id, ch0 + col);
+                if (ro < 0) continue;
+                unsigned long long id = (unsigned long long)ro + (unsigned long long)col * col_stride;
+                if (MODE == MODE_DK && p.narrow) {
+                    const int di = col >> 5, dj = (col & 31) >> 2, c = col & 3;   // slot = 4*dj + channel
+                    if (dj >= p.KW || c >= p.C) continue;                          // padding slots
+                    id = (unsigned long long)ro + (unsigned long long)((di * p.KW + dj) * p.C + c) * p.O;
                 }
+                // the fused chain only exists for FWD/DX; DK stores raw sums
+                p.out[id] = (MODE == MODE_DK) ? acc : epilogue_apply(e, acc, id, ch0 + col);
             }
         }
     }
@@ -646,38 +722,32 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
-// ---- split-K finish: sum partials in split order, then the epilogue -----------------------------
+// ---- narrow-channel DK: add the partitions' partial tiles in partition order ----------------------
+// partial[s][col][row] (col = 32 * kernel row + window slot, row = output channel); one thread per
+// (col, row), consecutive threads on consecutive rows: loads and stores are coalesced.
 __global__ void __launch_bounds__(256)
-splitk_finish_kernel(const float* __restrict__ partial, float* __restrict__ out,
-                     unsigned long long n, int splits, int channels, const EpilogueArgs ep)
+dk_narrow_finish_kernel(const float* __restrict__ partial, float* __restrict__ dk, int parts, int bn,
+                        int KH, int KW, int C, int O, int m_tiles)
 {
-    const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
-    const bool plain = !ep.raw_out && !ep.bias && !ep.pre_act && ep.act == DCG_ACT_NONE && !ep.gate;
-    if ((n & 3ull) == 0 && (channels & 3) == 0) {
-        const unsigned long long n4 = n >> 2;
-        for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
-            float4 acc = __ldg(reinterpret_cast<const float4*>(partial) + i);
-            for (int s = 1; s < splits; ++s) {
-                const float4 v = __ldg(reinterpret_cast<const float4*>(partial + (unsigned long long)s * n) + i);
-                acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y);
-                acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
-            }
-            if (!plain) {
-                const unsigned long long e0 = i << 2;
-                const int ch = (int)(e0 % (unsigned long long)channels);
-                acc.x = epilogue_apply(ep, acc.x, e0, ch);
-                acc.y = epilogue_apply(ep, acc.y, e0 + 1, ch + 1);
-                acc.z = epilogue_apply(ep, acc.z, e0 + 2, ch + 2);
-                acc.w = epilogue_apply(ep, acc.w, e0 + 3, ch + 3);
-            }
-            reinterpret_cast<float4*>(out)[i] = acc;
+    const int total = m_tiles * bn * BM;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int row = i % BM, col = (i / BM) % bn, mt = i / (BM * bn);
+        const int o = mt * BM + row;
+        const int di = col >> 5, dj = (col & 31) >> 2, c = col & 3;
+        if (o >= O || di >= KH || dj >= KW || c >= C) continue;
+        const float* src = partial + ((size_t)mt * parts * bn + col) * BM + row;
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;   // four loads in flight; added below in partition order
+        float acc = __ldcg(src);
+        int sidx = 1;
+        for (; sidx + 4 <= parts; sidx += 4) {
+            a0 = __ldcg(src + (size_t)sidx * bn * BM);
+            a1 = __ldcg(src + (size_t)(sidx + 1) * bn * BM);
+            a2 = __ldcg(src + (size_t)(sidx + 2) * bn * BM);
+            a3 = __ldcg(src + (size_t)(sidx + 3) * bn * BM);
+            acc = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(acc, a0), a1), a2), a3);
         }
-    } else {
-        for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-            float acc = __ldg(partial + i);
-            for (int s = 1; s < splits; ++s) acc = __fadd_rn(acc, __ldg(partial + (unsigned long long)s * n + i));
-            out[i] = plain ? acc : epilogue_apply(ep, acc, i, (int)(i % (unsigned long long)channels));
-        }
+        for (; sidx < parts; ++sidx) acc = __fadd_rn(acc, __ldcg(src + (size_t)sidx * bn * BM));
+        dk[((size_t)(di * KW + dj) * C + c) * O + o] = acc;
     }
 }
 
@@ -720,6 +790,50 @@ repack_k4_kernel(const float* __restrict__ k, float* __restrict__ k4, int KH, in
         const int o = i % O, slot = (i / O) % 32, di = i / (O * 32);
         const int dj = slot >> 2, c = slot & 3;
         k4[i] = (dj < KW && c < C) ? __ldg(k + (((size_t)di * KW + dj) * C + c) * O + o) : 0.f;
+    }
+}
+
+// ---- input gradient of a narrow-channel layer (<= 4 input channels) -------------------------------
+// With C <= 4 the implicit GEMM of DX has N = C: every 128 x 32 tile of dy would be fetched for a
+// sliver of tensor work, once per tap.  Instead dy is read ONCE by a plain GEMM against all taps,
+//   ycol[pixel of dy][tap * C + c] = sum_o dy[pixel, o] * k[tap, c, o]      (N = KH*KW*C, padded to 32s)
+// - the FWD kernel on a 1x1 "convolution" with the weights transposed to k2[o][tap * C + c] - and a
+// gather ("col2im") then adds, for every input pixel, the <= ceil(KH/s)*ceil(KW/s) products that
+// land on it and applies the fused chain.
+__global__ void __launch_bounds__(256)
+repack_k2_kernel(const float* __restrict__ k, float* __restrict__ k2, int J, int Jp, int O)
+{
+    const int total = O * Jp;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int j = i % Jp, o = i / Jp;
+        k2[i] = j < J ? __ldg(k + (size_t)j * O + o) : 0.f;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+col2im_kernel(const float* __restrict__ ycol, float* __restrict__ out, int N, int H, int W, int C, int Ho, int Wo,
+              int KH, int KW, int sh, int sw, int pt, int pl, int Jp, const EpilogueArgs ep)
+{
+    const size_t total = (size_t)N * H * W * C;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const int c = (int)(idx % C);
+        const int w = (int)((idx / C) % W);
+        const int h = (int)((idx / ((size_t)C * W)) % H);
+        const int n = (int)(idx / ((size_t)C * W * H));
+        float acc = 0.f;
+        for (int di = (h + pt) % sh; di < KH; di += sh) {      // taps whose row parity matches
+            const int i = (h + pt - di) / sh;
+            if (h + pt - di < 0) break;
+            if (i >= Ho) continue;
+            for (int dj = (w + pl) % sw; dj < KW; dj += sw) {
+                const int j = (w + pl - dj) / sw;
+                if (w + pl - dj < 0) break;
+                if (j >= Wo) continue;
+                acc = __fadd_rn(acc, __ldg(ycol + (((size_t)n * Ho + i) * Wo + j) * Jp + (di * KW + dj) * C + c));
+            }
+        }
+        out[idx] = epilogue_apply(ep, acc, idx, c);
     }
 }
 
@@ -807,10 +921,16 @@ struct Plan {
     Params p;
     int grid;
     size_t smem;
-    // scratch layout: [split-K partials][padded 4-channel input xp][repacked weights k4], each
-    // part 256-byte aligned; the last two only exist for narrow-channel layers
+    // scratch layout: [partial tiles of the K partitions][padded 4-channel input xp][repacked weights
+    // k4], each part 256-byte aligned; the last two only exist for narrow-channel layers
     size_t partial_bytes = 0, xp_bytes = 0, k4_bytes = 0, ws_bytes = 0;
     int Hp = 0, Wp = 0;   // padded input extent of a narrow-channel layer
+    // DX of a narrow-channel layer (GEMM + gather): p describes the 1x1 FWD problem; the transposed
+    // weights k2 and the GEMM result ycol follow the partial tiles in the scratch area
+    int Jp = 0;
+    size_t k2_bytes = 0, ycol_bytes = 0;
+    size_t k2_off() const { return align_up(partial_bytes, 256); }
+    size_t ycol_off() const { return k2_off() + align_up(k2_bytes, 256); }
     size_t xp_off() const { return align_up(partial_bytes, 256); }
     size_t k4_off() const { return xp_off() + align_up(xp_bytes, 256); }
 };
@@ -826,13 +946,16 @@ int env_int(const char* name)
 int choose_splits(int tiles, int min_stages_per_tile)
 {
     static const int forced = env_int("DCG_TC_SPLITS");
-    if (forced > 0) return forced <= min_stages_per_tile ? forced : (min_stages_per_tile > 0 ? min_stages_per_tile : 1);
+    if (forced > 0) {
+        int f = forced <= min_stages_per_tile ? forced : (min_stages_per_tile > 0 ? min_stages_per_tile : 1);
+        return f > kMaxCluster ? kMaxCluster : f;
+    }
     const int sms = sm_count();
     if (tiles >= sms) return 1;
     int s = (2 * sms) / tiles;                       // aim at ~2 CTAs per SM
     const int cap = min_stages_per_tile / 4;         // keep at least 4 K stages per CTA
     if (s > cap) s = cap;
-    if (s > 32) s = 32;
+    if (s > kMaxCluster) s = kMaxCluster;
     return s < 1 ? 1 : s;
 }
 
@@ -848,16 +971,16 @@ void finish_plan(Plan& pl)
     static const int forced_stages = env_int("DCG_TC_STAGES");
     if (forced_stages > 0 && forced_stages < stages) stages = forced_stages;
     if (stages < 2) stages = 2;
-    // the epilogue parks two 128 x 36-float slabs and 128 row offsets in the (by then idle) stage ring
-    while ((size_t)stages * per_stage < 2 * BM * 36 * 4 + BM * 8) ++stages;
+    // the epilogue parks the 128 x bn tile (padded rows) and 128 row offsets in the (by then idle) stage ring
+    while ((size_t)stages * per_stage < (size_t)kRedFloats(p.bn) * 4 + BM * 8) ++stages;
     p.stages = stages;
     static const int debug = env_int("DCG_TC_DEBUG");
     p.debug = debug;
     pl.smem = (size_t)stages * per_stage + 1024 /*alignment slack*/ + 16 * stages + 32;
-    pl.partial_bytes = p.splits > 1 ? (size_t)p.splits * p.out_elems * sizeof(float) : 0;
+    pl.partial_bytes = p.splits > 1 ? (size_t)pl.grid * BM * p.bn * sizeof(float) : 0;
     pl.ws_bytes = pl.partial_bytes;
     if (pl.xp_bytes || pl.k4_bytes) pl.ws_bytes = pl.k4_off() + align_up(pl.k4_bytes, 256);
-    p.direct = p.splits == 1 ? 1 : 0;
+    if (pl.ycol_bytes) pl.ws_bytes = pl.ycol_off() + align_up(pl.ycol_bytes, 256);
 }
 
 // Padded-image geometry of a narrow-channel layer: rows s*i + di and columns s*j .. s*j + 7 of xp
@@ -904,14 +1027,32 @@ bool plan_fwd(const dcg_conv_desc& d, Plan& pl)
         pl.k4_bytes = (size_t)d.kh * 32 * d.o * sizeof(float);
     }
     p.splits = choose_splits(tiles, narrow ? d.kh : d.kh * d.kw * p.kchunks);
-    p.out_elems = (unsigned long long)d.n * d.ho * d.wo * d.o;
     pl.grid = tiles * p.splits;
     finish_plan(pl);
     return true;
 }
 
+// The 1x1 FWD problem behind the DX of a narrow-channel layer: dy [n, ho, wo, o] times k2 [o][Jp].
+dcg_conv_desc dx_gemm_desc(const dcg_conv_desc& d, int Jp)
+{
+    dcg_conv_desc g{};
+    g.n = d.n; g.h = d.ho; g.w = d.wo; g.c = d.o; g.kh = 1; g.kw = 1; g.o = Jp; g.ho = d.ho; g.wo = d.wo;
+    g.stride_h = 1; g.stride_w = 1; g.pad_top = 0; g.pad_left = 0;
+    return g;
+}
+
+bool plan_fwd(const dcg_conv_desc& d, Plan& pl);
+
 bool plan_dx(const dcg_conv_desc& d, Plan& pl)
 {
+    if (d.c <= 4 && d.o % 32 == 0 && d.stride_h <= d.kh && d.stride_w <= d.kw) {
+        const int Jp = (d.kh * d.kw * d.c + 31) / 32 * 32;
+        pl.Jp = Jp;
+        pl.k2_bytes = (size_t)d.o * Jp * sizeof(float);
+        pl.ycol_bytes = (size_t)d.n * d.ho * d.wo * Jp * sizeof(float);
+        if (plan_fwd(dx_gemm_desc(d, Jp), pl)) return true;
+        pl = Plan{};
+    }
     if (d.o % 4 != 0 || d.stride_h > 8 || d.stride_w > 8) return false;
     if (d.stride_h > d.kh || d.stride_w > d.kw) return false;   // some parity class would have no tap
     Params& p = pl.p;
@@ -928,7 +1069,6 @@ bool plan_dx(const dcg_conv_desc& d, Plan& pl)
     const int tiles = classes * p.tiles_w * p.tiles_h * p.tiles_n * p.n_tiles;
     const int min_taps = (d.kh / d.stride_h) * (d.kw / d.stride_w);
     p.splits = choose_splits(tiles, (min_taps < 1 ? 1 : min_taps) * p.kchunks);
-    p.out_elems = (unsigned long long)d.n * d.h * d.w * d.c;
     pl.grid = tiles * p.splits;
     finish_plan(pl);
     return true;
@@ -944,29 +1084,35 @@ bool plan_dk(const dcg_conv_desc& d, Plan& pl)
     if (p.TW * d.stride_w > 256 || p.TH * d.stride_h > 256) return false;
     p.tiles_w = (d.wo + p.TW - 1) / p.TW; p.tiles_h = (d.ho + p.TH - 1) / p.TH; p.tiles_n = (d.n + p.TN - 1) / p.TN;
     if (narrow) {
-        // rows = output channels (from dy), columns = the 32 window slots, one group per kernel row
+        // rows = output channels (from dy), columns = 32 window slots per kernel row: one tile holds
+        // all of dk, so dy is read exactly once; the parallelism comes from partitioning the pixels
+        // over about as many CTAs as there are SMs, whose partial tiles a second kernel adds up
+        if (d.kh * 32 > 256) return false;
         p.narrow = 1;
         p.swap = 1;
         p.m_tiles = (d.o + BM - 1) / BM;
-        p.bn = 32;
+        p.bn = 32 * d.kh;
         p.n_tiles = 1;
         narrow_geometry(d, pl);
-        const int tiles = d.kh * p.m_tiles;
-        p.splits = choose_splits(tiles, p.tiles_w * p.tiles_h * p.tiles_n);
-        p.out_elems = (unsigned long long)d.kh * d.kw * d.c * d.o;
-        pl.grid = tiles * p.splits;
+        const int k_stages = p.tiles_w * p.tiles_h * p.tiles_n;
+        int parts = sm_count() / p.m_tiles;
+        if (parts > k_stages / 4) parts = k_stages / 4;   // at least 4 K stages per CTA
+        if (parts < 1) parts = 1;
+        p.splits = parts;
+        p.ext_finish = parts > 1 ? 1 : 0;
+        pl.grid = p.m_tiles * p.splits;
         finish_plan(pl);
         return true;
     }
-    // the wider channel axis becomes M (128 accumulator rows), the other N
-    p.swap = d.o > d.c ? 1 : 0;
+    // M (128 accumulator rows) is the input-channel axis - dk rows are then contiguous along the
+    // accumulator columns - unless that would leave the M tile part empty and o can fill it
+    p.swap = (d.c < BM && d.o > d.c) ? 1 : 0;
     const int m_ch = p.swap ? d.o : d.c, n_ch = p.swap ? d.c : d.o;
     p.m_tiles = (m_ch + BM - 1) / BM;
     p.bn = n_ch >= 128 ? 128 : n_ch;
     p.n_tiles = (n_ch + p.bn - 1) / p.bn;
     const int tiles = d.kh * d.kw * p.m_tiles * p.n_tiles;
     p.splits = choose_splits(tiles, p.tiles_w * p.tiles_h * p.tiles_n);
-    p.out_elems = (unsigned long long)d.kh * d.kw * d.c * d.o;
     pl.grid = tiles * p.splits;
     finish_plan(pl);
     return true;
@@ -994,26 +1140,35 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, Plan& pl, float* out, c
     if (attr_err != cudaSuccess)
         return fail(DCG_ERR_CUDA, "cudaFuncSetAttribute(conv_tc_kernel): %s", cudaGetErrorString(attr_err));
     Params& p = pl.p;
+    p.out = out;
+    p.ep = ep;
+    p.scratch = nullptr;
     if (p.splits > 1) {
         if (!ws || ws_bytes < pl.ws_bytes)
             return fail(DCG_ERR_WORKSPACE, "conv (tensor path): workspace %zu < %zu bytes", ws_bytes, pl.ws_bytes);
-        p.out = static_cast<float*>(ws);
-        p.ep = EpilogueArgs{};
-    } else {
-        p.out = out;
-        p.ep = ep;
+        p.scratch = static_cast<float*>(ws);
     }
-    conv_tc_kernel<MODE><<<pl.grid, kThreads, pl.smem, stream>>>(ma, mb, p);
-    DCG_LAUNCH_CHECK("conv_tc_kernel");
-    if (p.splits > 1) {
-        const unsigned long long n = p.out_elems;
-        unsigned long long blocks = (n / 4 + 255) / 256;
-        const unsigned long long cap = (unsigned long long)sm_count() * 8;
-        if (blocks > cap) blocks = cap;
-        if (blocks < 1) blocks = 1;
-        splitk_finish_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const float*>(ws), out, n, p.splits,
-                                                                   channels, ep);
-        DCG_LAUNCH_CHECK("splitk_finish_kernel");
+    (void)channels;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)pl.grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = pl.smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)p.splits;   // blockIdx.x = tile * splits + split: one cluster per tile
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (p.splits > 1 && !p.ext_finish) ? 1 : 0;
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE>, ma, mb, p);
+    if (err != cudaSuccess) return fail(DCG_ERR_CUDA, "conv_tc_kernel launch: %s", cudaGetErrorString(err));
+    count_launch();
+    if (p.ext_finish) {
+        const int total = p.m_tiles * p.bn * BM;
+        dk_narrow_finish_kernel<<<(total + 255) / 256, 256, 0, stream>>>(p.scratch, out, p.splits, p.bn, p.KH, p.KW,
+                                                                         p.C, p.O, p.m_tiles);
+        DCG_LAUNCH_CHECK("dk_narrow_finish_kernel");
     }
     return DCG_OK;
 }
@@ -1046,14 +1201,14 @@ int narrow_prepare(const dcg_conv_desc& d, const Plan& pl, const float* x, const
 }
 
 // The overlapping-window view of xp [n][Hp][Wp][4]: (32 floats, j, i, n, kernel row) where output
-// pixel (i, j) and kernel row r address xp[n][s*i + r][s*j][0].  Box (32, tw, th, tn, 1).
+// pixel (i, j) and kernel row r address xp[n][s*i + r][s*j][0].  Box (32, tw, th, tn, rows).
 int map_window(CUtensorMap* map, const float* xp, const dcg_conv_desc& d, const Plan& pl, int tw, int th, int tn,
-               bool mn_major)
+               bool mn_major, int rows)
 {
     const cuuint64_t row = (cuuint64_t)pl.Wp * 16;
     const cuuint64_t dims[5] = {32, (cuuint64_t)d.wo, (cuuint64_t)d.ho, (cuuint64_t)d.n, (cuuint64_t)d.kh};
     const cuuint64_t strides[4] = {(cuuint64_t)d.stride_w * 16, (cuuint64_t)d.stride_h * row, (cuuint64_t)pl.Hp * row, row};
-    const cuuint32_t box[5] = {32, (cuuint32_t)tw, (cuuint32_t)th, (cuuint32_t)tn, 1};
+    const cuuint32_t box[5] = {32, (cuuint32_t)tw, (cuuint32_t)th, (cuuint32_t)tn, (cuuint32_t)rows};
     const cuuint32_t es[5] = {1, 1, 1, 1, 1};
     return encode_map(map, xp, 5, dims, mn_major, strides, box, es);
 }
@@ -1084,7 +1239,7 @@ int conv_tc_fwd(const dcg_conv_desc& d, const float* x, const float* k, float* y
     if (p.narrow) {
         float *xp, *k4;
         if ((st = narrow_prepare(d, pl, x, k, ws, ws_bytes, stream, &xp, &k4))) return st;
-        if ((st = map_window(&ma, xp, d, pl, p.TW, p.TH, p.TN, false))) return st;
+        if ((st = map_window(&ma, xp, d, pl, p.TW, p.TH, p.TN, false, 1))) return st;
         // k4 [kh][slot][o] as (o%32, slot, kh, o/32), box (32, 32, 1, bn/32)
         const cuuint64_t dims[4] = {32, 32, (cuuint64_t)d.kh, (cuuint64_t)(d.o / 32)};
         const cuuint64_t strides[3] = {(cuuint64_t)d.o * 4, (cuuint64_t)32 * d.o * 4, 128};
@@ -1113,6 +1268,32 @@ int conv_tc_dx(const dcg_conv_desc& d, const float* dy, const float* k, float* d
     CUtensorMap ma, mb;
     int st = map_act_4d(&ma, dy, d.n, d.ho, d.wo, d.o, p.TW, p.TH, p.TN, 1, 1);
     if (st) return st;
+    if (pl.ycol_bytes) {   // narrow-channel layer: GEMM over all taps, then gather
+        if (!ws || ws_bytes < pl.ws_bytes)
+            return fail(DCG_ERR_WORKSPACE, "conv dx (tensor path, narrow input): workspace %zu < %zu bytes", ws_bytes, pl.ws_bytes);
+        uint8_t* base = static_cast<uint8_t*>(ws);
+        float* k2 = reinterpret_cast<float*>(base + pl.k2_off());
+        float* ycol = reinterpret_cast<float*>(base + pl.ycol_off());
+        const int J = d.kh * d.kw * d.c, Jp = pl.Jp;
+        repack_k2_kernel<<<(d.o * Jp + 255) / 256, 256, 0, stream>>>(k, k2, J, Jp, d.o);
+        DCG_LAUNCH_CHECK("repack_k2_kernel");
+        // k2 [o][Jp] as (j%32, o, 1, j/32), box (32, 32, 1, bn/32): the FWD kernel's weight view with one tap
+        const cuuint64_t dims[4] = {32, (cuuint64_t)d.o, 1, (cuuint64_t)(Jp / 32)};
+        const cuuint64_t strides[3] = {(cuuint64_t)Jp * 4, (cuuint64_t)d.o * Jp * 4, 128};
+        const cuuint32_t box[4] = {32, 32, 1, (cuuint32_t)(p.bn / 32)};
+        const cuuint32_t es[4] = {1, 1, 1, 1};
+        if ((st = encode_map(&mb, k2, 4, dims, true, strides, box, es))) return st;
+        const EpilogueArgs none{};
+        if ((st = launch<MODE_FWD>(ma, mb, pl, ycol, none, Jp, ws, ws_bytes, stream))) return st;
+        const size_t total = (size_t)d.n * d.h * d.w * d.c;
+        size_t blocks = (total + 255) / 256;
+        const size_t cap = (size_t)sm_count() * 16;
+        if (blocks > cap) blocks = cap;
+        col2im_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ycol, dx, d.n, d.h, d.w, d.c, d.ho, d.wo, d.kh, d.kw,
+                                                            d.stride_h, d.stride_w, d.pad_top, d.pad_left, Jp, ep);
+        DCG_LAUNCH_CHECK("col2im_kernel");
+        return DCG_OK;
+    }
     // k [kh][kw][c][o] as (o, c, kw, kh), box (32 o, bn c, 1, 1)
     const cuuint64_t dims[4] = {(cuuint64_t)d.o, (cuuint64_t)d.c, (cuuint64_t)d.kw, (cuuint64_t)d.kh};
     const cuuint64_t strides[3] = {(cuuint64_t)d.o * 4, (cuuint64_t)d.c * d.o * 4, (cuuint64_t)d.kw * d.c * d.o * 4};
@@ -1134,7 +1315,7 @@ int conv_tc_dk(const dcg_conv_desc& d, const float* x, const float* dy, float* d
     if (p.narrow) {
         float* xp;
         if ((st = narrow_prepare(d, pl, x, nullptr, ws, ws_bytes, stream, &xp, nullptr))) return st;
-        if ((st = map_window(&mx, xp, d, pl, p.TW, p.TH, p.TN, true))) return st;
+        if ((st = map_window(&mx, xp, d, pl, p.TW, p.TH, p.TN, true, d.kh))) return st;
         if ((st = map_act_5d(&mdy, dy, d.n, d.ho, d.wo, d.o, p.TW, p.TH, p.TN, 1, 1, BM / 32))) return st;
         return launch<MODE_DK>(mdy, mx, pl, dk, no_epilogue, d.o, ws, ws_bytes, stream);
     }

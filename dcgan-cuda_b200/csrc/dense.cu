@@ -4,8 +4,10 @@
 // These are small and HBM/latency bound (the largest operand is 3.3 MB), so they
 // stay on CUDA cores: a shared-memory tiled kernel that accumulates each output
 // over k in ascending order with unfused multiply/add - bit-identical to the
-// reference CPU loops (src/cpu/ops.hxx:56-105,375-390) - plus a warp-per-output
-// kernel for the "few outputs, long reduction" head (64 x 8192 x 1).
+// reference CPU loops (src/cpu/ops.hxx:56-105,375-390) - plus three shape
+// specialists for the DCGAN layers: short reduction / wide output (100 -> 8192 and
+// its weight gradient), few outputs / long reduction (8192 -> 1), and tall output
+// from a transposed operand (the head's weight gradient).
 #include "common.cuh"
 
 namespace dcg {
@@ -84,22 +86,129 @@ gemm_tiled_kernel(const float* __restrict__ a, const float* __restrict__ b,
     }
 }
 
-// One warp per output element, for m*p small and n long: out = A[m,n] B[n,p] (+bias).
+// One block per output element, for m*p small and n long: out = A[m,n] B[n,p] (+bias).
+// Thread t adds elements t, t+256, ... in ascending order; the 256 thread sums are then added
+// in a fixed tree, so the result is independent of scheduling.
 __global__ void __launch_bounds__(TPB)
-gemm_warp_per_output_kernel(const float* __restrict__ a, const float* __restrict__ b,
-                            const float* __restrict__ bias, float* __restrict__ out,
-                            size_t m, size_t n, size_t p)
+gemm_long_k_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                   const float* __restrict__ bias, float* __restrict__ out,
+                   size_t m, size_t n, size_t p)
 {
-    const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (warp >= m * p) return;
-    const size_t r = warp / p, c = warp % p;
+    __shared__ float part[TPB];
+    const size_t o = blockIdx.x;
+    const size_t r = o / p, c = o % p;
+    const float* ar = a + r * n;
     float s = 0.f;
-    for (size_t k = lane; k < n; k += 32) s = fmaf(__ldg(a + r * n + k), __ldg(b + k * p + c), s);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (lane == 0) out[warp] = bias ? s + __ldg(bias + c) : s;
+    size_t k = threadIdx.x;
+    for (; k + 3 * TPB < n; k += 4 * TPB) {
+        const float a0 = __ldg(ar + k), a1 = __ldg(ar + k + TPB), a2 = __ldg(ar + k + 2 * TPB), a3 = __ldg(ar + k + 3 * TPB);
+        const float b0 = __ldg(b + k * p + c), b1 = __ldg(b + (k + TPB) * p + c);
+        const float b2 = __ldg(b + (k + 2 * TPB) * p + c), b3 = __ldg(b + (k + 3 * TPB) * p + c);
+        s = fmaf(a0, b0, s); s = fmaf(a1, b1, s); s = fmaf(a2, b2, s); s = fmaf(a3, b3, s);
+    }
+    for (; k < n; k += TPB) s = fmaf(__ldg(ar + k), __ldg(b + k * p + c), s);
+    part[threadIdx.x] = s;
+    __syncthreads();
+    for (int h = TPB / 2; h > 0; h >>= 1) {
+        if ((int)threadIdx.x < h) part[threadIdx.x] += part[threadIdx.x + h];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out[o] = bias ? part[0] + __ldg(bias + c) : part[0];
 }
+
+// Short reduction, wide output (the generator's projection and its weight gradient):
+// out[m,p] = A[m,n] B[n,p] (+bias) with n <= 256 and B row-major.  A block owns 128 columns and
+// RB rows: the RB x n slab of A sits in shared memory, every thread walks one column of B
+// (coalesced across the block) and keeps RB accumulators.  k ascends, multiply and add stay
+// unfused: the same rounding sequence as the reference loops (src/cpu/ops.hxx:56-105).
+constexpr int RB = 16;
+template <bool TA>
+__global__ void __launch_bounds__(128)
+gemm_wide_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                 const float* __restrict__ bias, float* __restrict__ out,
+                 size_t m, size_t n, size_t p)
+{
+    __shared__ __align__(16) float As[256 * RB];   // [k][RB]
+    const size_t row0 = (size_t)blockIdx.y * RB;
+    for (int e = threadIdx.x; e < (int)n * RB; e += 128) {
+        int kk, rr;
+        if (TA) { rr = e % RB; kk = e / RB; } else { kk = e % (int)n; rr = e / (int)n; }
+        const size_t r = row0 + rr;
+        As[kk * RB + rr] = r < m ? load_elem<TA>(a, r, (size_t)kk, m, n) : 0.f;
+    }
+    __syncthreads();
+    const size_t c = (size_t)blockIdx.x * 128 + threadIdx.x;
+    if (c >= p) return;
+    float acc[RB];
+#pragma unroll
+    for (int i = 0; i < RB; ++i) acc[i] = 0.f;
+    const float* bc = b + c;
+    int k = 0;
+    for (; k + 4 <= (int)n; k += 4) {
+        float bv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) bv[u] = __ldg(bc + (size_t)(k + u) * p);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float4* ak = reinterpret_cast<const float4*>(As + (k + u) * RB);
+#pragma unroll
+            for (int q = 0; q < RB / 4; ++q) {
+                const float4 av = ak[q];
+                acc[4 * q + 0] = __fadd_rn(acc[4 * q + 0], __fmul_rn(av.x, bv[u]));
+                acc[4 * q + 1] = __fadd_rn(acc[4 * q + 1], __fmul_rn(av.y, bv[u]));
+                acc[4 * q + 2] = __fadd_rn(acc[4 * q + 2], __fmul_rn(av.z, bv[u]));
+                acc[4 * q + 3] = __fadd_rn(acc[4 * q + 3], __fmul_rn(av.w, bv[u]));
+            }
+        }
+    }
+    for (; k < (int)n; ++k) {
+        const float bv = __ldg(bc + (size_t)k * p);
+#pragma unroll
+        for (int i = 0; i < RB; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(As[k * RB + i], bv));
+    }
+    const float bb = bias ? __ldg(bias + c) : 0.f;
+#pragma unroll
+    for (int i = 0; i < RB; ++i) {
+        const size_t r = row0 + i;
+        if (r < m) out[r * p + c] = bias ? __fadd_rn(acc[i], bb) : acc[i];
+    }
+}
+
+// Tall output with a handful of columns from a transposed left operand (the discriminator head's
+// weight gradient, x^T dy): out[r,c] = sum_k A^T[k,r] B[k,c]; one thread per output, loads
+// coalesced along r, k ascending, unfused.
+__global__ void __launch_bounds__(TPB)
+gemm_tall_tn_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
+                    size_t m, size_t n, size_t p)
+{
+    const size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (o >= m * p) return;
+    const size_t c = o / m, r = o % m;   // r fastest across threads: coalesced reads of A^T
+    float s = 0.f;
+    size_t k = 0;
+    for (; k + 4 <= n; k += 4) {
+        const float a0 = __ldg(a + k * m + r), a1 = __ldg(a + (k + 1) * m + r);
+        const float a2 = __ldg(a + (k + 2) * m + r), a3 = __ldg(a + (k + 3) * m + r);
+        s = __fadd_rn(s, __fmul_rn(a0, __ldg(b + k * p + c)));
+        s = __fadd_rn(s, __fmul_rn(a1, __ldg(b + (k + 1) * p + c)));
+        s = __fadd_rn(s, __fmul_rn(a2, __ldg(b + (k + 2) * p + c)));
+        s = __fadd_rn(s, __fmul_rn(a3, __ldg(b + (k + 3) * p + c)));
+    }
+    for (; k < n; ++k) s = __fadd_rn(s, __fmul_rn(__ldg(a + k * m + r), __ldg(b + k * p + c)));
+    out[r * p + c] = s;
+}
+
+template <bool TA>
+int launch_wide(const float* a, const float* b, const float* bias, float* out, size_t m, size_t n,
+                size_t p, cudaStream_t stream)
+{
+    const dim3 grid((unsigned)((p + 127) / 128), (unsigned)((m + RB - 1) / RB));
+    gemm_wide_kernel<TA><<<grid, 128, 0, stream>>>(a, b, bias, out, m, n, p);
+    DCG_LAUNCH_CHECK("gemm_wide_kernel");
+    return DCG_OK;
+}
+
+inline bool wide_shape(size_t m, size_t n, size_t p) { return n <= 256 && p >= 512 && m <= 65535u * RB; }
 
 template <bool TA, bool TB>
 int launch_tiled(const float* a, const float* b, const float* bias, float* out, size_t m, size_t n,
@@ -121,11 +230,11 @@ extern "C" int dcg_matmul(const float* a, const float* b, const float* bias, flo
 {
     DCG_CHECK_ARG(a && b && out && m > 0 && n > 0 && p > 0, "dcg_matmul: bad arguments");
     if (m * p <= 4096 && n >= 1024) {
-        const size_t blocks = (m * p * 32 + TPB - 1) / TPB;
-        gemm_warp_per_output_kernel<<<(unsigned)blocks, TPB, 0, as_stream(stream)>>>(a, b, bias, out, m, n, p);
-        DCG_LAUNCH_CHECK("gemm_warp_per_output_kernel");
+        gemm_long_k_kernel<<<(unsigned)(m * p), TPB, 0, as_stream(stream)>>>(a, b, bias, out, m, n, p);
+        DCG_LAUNCH_CHECK("gemm_long_k_kernel");
         return DCG_OK;
     }
+    if (wide_shape(m, n, p)) return launch_wide<false>(a, b, bias, out, m, n, p, as_stream(stream));
     return launch_tiled<false, false>(a, b, bias, out, m, n, p, as_stream(stream), "gemm_tiled_kernel<nn>");
 }
 
@@ -133,6 +242,12 @@ extern "C" int dcg_matmul_tn(const float* a, const float* b, float* out, size_t 
                              size_t p, dcg_stream_t stream)
 {
     DCG_CHECK_ARG(a && b && out && m > 0 && n > 0 && p > 0, "dcg_matmul_tn: bad arguments");
+    if (wide_shape(m, n, p)) return launch_wide<true>(a, b, nullptr, out, m, n, p, as_stream(stream));
+    if (p <= 8 && m >= 1024) {
+        gemm_tall_tn_kernel<<<(unsigned)((m * p + TPB - 1) / TPB), TPB, 0, as_stream(stream)>>>(a, b, out, m, n, p);
+        DCG_LAUNCH_CHECK("gemm_tall_tn_kernel");
+        return DCG_OK;
+    }
     return launch_tiled<true, false>(a, b, nullptr, out, m, n, p, as_stream(stream), "gemm_tiled_kernel<tn>");
 }
 

@@ -166,14 +166,36 @@ colsum_partial_kernel(const float* __restrict__ a, float* __restrict__ partial,
     }
 }
 
-__global__ void colsum_final_kernel(const float* __restrict__ partial, float* __restrict__ out,
-                                    unsigned slabs, unsigned cols)
+// Stage 2: block = 32 columns x 8 slab lanes.  Lane ty adds slabs ty, ty+8, ... (four loads in
+// flight at a time), then the eight lane sums are added in lane order: the result does not depend
+// on the launch shape of anything else.
+__global__ void __launch_bounds__(256)
+colsum_final_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                    unsigned slabs, unsigned cols)
 {
-    const unsigned c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= cols) return;
+    __shared__ float part[8][33];
+    const unsigned tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const unsigned c = blockIdx.x * 32 + tx;
     float s = 0.f;
-    for (unsigned k = 0; k < slabs; ++k) s += partial[(size_t)k * cols + c];
-    out[c] = s;
+    if (c < cols) {
+        unsigned k = ty;
+        for (; k + 24 < slabs; k += 32) {
+            const float v0 = __ldg(partial + (size_t)k * cols + c);
+            const float v1 = __ldg(partial + (size_t)(k + 8) * cols + c);
+            const float v2 = __ldg(partial + (size_t)(k + 16) * cols + c);
+            const float v3 = __ldg(partial + (size_t)(k + 24) * cols + c);
+            s += v0; s += v1; s += v2; s += v3;
+        }
+        for (; k < slabs; k += 8) s += __ldg(partial + (size_t)k * cols + c);
+    }
+    part[ty][tx] = s;
+    __syncthreads();
+    if (ty == 0 && c < cols) {
+        float t = part[0][tx];
+#pragma unroll
+        for (int q = 1; q < 8; ++q) t += part[q][tx];
+        out[c] = t;
+    }
 }
 
 // ---- row sums: one warp per row -----------------------------------------------
@@ -468,7 +490,7 @@ extern "C" int dcg_colsum(const float* a, float* out, size_t rows, size_t cols, 
             a, partial, rows, (unsigned)cols, p.rows_per_slab, p.tx_count);
     DCG_LAUNCH_CHECK("colsum_partial_kernel");
     if (p.slabs > 1) {
-        colsum_final_kernel<<<(unsigned)((cols + 127) / 128), 128, 0, as_stream(stream)>>>(
+        colsum_final_kernel<<<(unsigned)((cols + 31) / 32), 256, 0, as_stream(stream)>>>(
             partial, out, p.slabs, (unsigned)cols);
         DCG_LAUNCH_CHECK("colsum_final_kernel");
     }
