@@ -65,6 +65,21 @@ __device__ long long g_tc_trace[3080];
         if ((p.debug & 4) && blockIdx.x == 0 && (slot) < 3080) g_tc_trace[(slot)] = clock64(); \
     } while (0)
 
+// Per-CTA timeline for tuning (DCG_TC_DEBUG bit 8): global-timer stamps (ns) of thread 64 of the first
+// 1024 CTAs at [0] kernel entry, [1] setup done, [2] accumulator ready, [3] tile handed over,
+// [4] partitions met, [5] end; [6] = SM id.
+__device__ unsigned long long g_tc_cta_trace[1024][8];
+__device__ __forceinline__ unsigned long long global_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define TC_CTA_TRACE(slot)                                                                         \
+    do {                                                                                           \
+        if ((p.debug & 8) && threadIdx.x == 64 && blockIdx.x < 1024) g_tc_cta_trace[blockIdx.x][(slot)] = global_ns(); \
+    } while (0)
+
 struct Params {
     int N, H, W, C, KH, KW, O, Ho, Wo, sh, sw, pt, pl;
     int TW, TH, TN;               // pixel-tile extents (FWD/DX: the 128 rows; DK: the 32-pixel K step)
@@ -77,6 +92,8 @@ struct Params {
     int swap;                     // DK: M axis is o (A from dy, B from x)
     int narrow;                   // FWD/DK with <= 4 input channels: x is read through the window map
     int ext_finish;               // the K partitions only write partials; a second kernel adds them (narrow DK)
+    int planes;                   // FWD: 16-byte column quad q of output pixel r goes to out[(q * pixels + r) * 4]
+    unsigned long long plane_stride;  // planes: elements between two quads' planes (4 * pixels)
     int debug;                    // timing experiments (DCG_TC_DEBUG): 1 = no MMA, 2 = no TMA; results are garbage
     int stages;                   // pipeline depth
     float* out;                   // the output tensor
@@ -264,6 +281,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 {
     extern __shared__ uint8_t smem_raw[];
     if (threadIdx.x == 64) TC_TRACE(3072);
+    TC_CTA_TRACE(0);
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int b_stage_bytes = p.bn * BK * 4;
     const uint32_t a_base = smem_base;
@@ -339,7 +357,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = *tmem_slot_ptr;
+    // Programmatic dependent launch: everything above (barriers, TMEM, descriptor prefetch) may run
+    // while the previous kernel of the stream is still draining; from here on its results are needed.
+    // The next kernel's CTAs may in turn be set up as soon as every CTA of this grid has got here.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == 64) TC_TRACE(3073);
+    TC_CTA_TRACE(1);
+    if ((p.debug & 8) && threadIdx.x == 64 && blockIdx.x < 1024) {
+        unsigned smid;
+        asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+        g_tc_cta_trace[blockIdx.x][6] = smid;
+    }
 
     // ---- epilogue geometry (uniform over the CTA) ---------------------------------------------------
     const int ch0 = n_tile * p.bn;    // channel index of accumulator column 0 (bias axis) unless DK
@@ -486,6 +515,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int n = n0 + tn, i = i0 + th, j = j0 + tw;
             row_valid = n < p.N && i < p.Ho && j < p.Wo;
             row_off = (((unsigned long long)n * p.Ho + i) * p.Wo + j) * p.O + ch0;
+            if (p.planes) row_off = (((unsigned long long)n * p.Ho + i) * p.Wo + j) * 4ull;
         } else if (MODE == MODE_DX) {
             const int tw = row % p.TW, th = (row / p.TW) % p.TH, tn = row / (p.TW * p.TH);
             const int n = n0 + tn, h = p.sh * (i0 + th) + ph, w = p.sw * (j0 + tw) + pw;
@@ -511,6 +541,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         ok = __all_sync(0xffffffffu, ok);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (threadIdx.x == 64) TC_TRACE(3074);
+        TC_CTA_TRACE(2);
         if (!ok || nq <= 0) row_valid = false;   // nothing trustworthy to store
         // The pipeline stages are idle from here on (every MMA that read them has completed).
         s_rowoff[row] = row_valid ? (long long)row_off : -1;
@@ -574,10 +605,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (multi) __threadfence();   // the partial is visible device-wide before this CTA arrives
     }
     if (threadIdx.x == 64) TC_TRACE(3001);
+    TC_CTA_TRACE(3);
     __syncwarp();
     if (multi && finish_here) cluster_sync_all();
     else if (warp >= 2) asm volatile("bar.sync 1, 128;" ::: "memory");
     if (threadIdx.x == 64) TC_TRACE(3002);
+    TC_CTA_TRACE(4);
 
     if (warp >= 2 && finish_here) {
         // ===== this partition's share: sum in partition order, fused chain, stores =====
@@ -588,7 +621,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // multi: thread = row, items = the quads of this share.  single: item = (row, quad) with
             // consecutive lanes on consecutive quads, so a warp stores whole 128-byte row segments.
             const int Qm = min(QPO, qpr - part * QPO);
+            const bool by_row = multi || p.planes;               // thread = row (else: lanes walk the quads of a row)
             const int per_thread = multi ? Qm : qpr;             // items per thread (128 * qpr items / 128 threads)
+            const int quad0 = ch0 >> 2;                          // planes: global index of this tile's first quad
             const int step_r = 128 / qpr, step_q = 128 % qpr;    // single: how (row, quad) moves when the item index grows by 128
             int rr = tid_e / qpr, q = tid_e % qpr;
             const long long my_ro = s_rowoff[tid_e];
@@ -598,18 +633,20 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 float4 acc[4];
                 long long goff[4];
                 int cq[4];
-                if (multi) {
+                if (by_row) {
                     const float4* src[4];
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
                         const bool in = base + u < per_thread;
                         const int qd = part * QPO + (in ? base + u : 0);
                         cq[u] = qd << 2;
-                        goff[u] = (!in || my_ro < 0 || cq[u] >= ncols_valid) ? -1 : my_ro + cq[u];
-                        src[u] = ts4 + (size_t)qd * BM + tid_e;
+                        goff[u] = (!in || my_ro < 0 || cq[u] >= ncols_valid) ? -1
+                                  : p.planes ? my_ro + (long long)((unsigned long long)(quad0 + qd) * p.plane_stride)
+                                             : my_ro + cq[u];
+                        src[u] = (multi ? ts4 + (size_t)qd * BM : red4 + qd * QS) + tid_e;
                     }
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) acc[u] = __ldcg(src[u]);
+                    for (int u = 0; u < 4; ++u) acc[u] = multi ? __ldcg(src[u]) : *src[u];
                     for (int sidx = 1; sidx < S; ++sidx) {
                         float4 v[4];
 #pragma unroll
@@ -713,6 +750,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 
     if (threadIdx.x == 64) TC_TRACE(3075);
+    TC_CTA_TRACE(5);
     // ---- teardown: everyone is done with TMEM before warp 1 releases it --------------------------
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -722,32 +760,34 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
-// ---- narrow-channel DK: add the partitions' partial tiles in partition order ----------------------
-// partial[s][col][row] (col = 32 * kernel row + window slot, row = output channel); one thread per
-// (col, row), consecutive threads on consecutive rows: loads and stores are coalesced.
+// ---- narrow-channel DK: add the partitions' partial tiles -----------------------------------------
+// partial[m tile][partition][col][row] (col = 32 * kernel row + window slot, row = output channel).
+// Block = 32 rows x 8 lanes of one column: lane l adds partitions l, l+8, ... (all loads in
+// flight), the eight lane sums are then added in lane order - a fixed order for a given partition
+// count, so the result does not depend on timing.  blockIdx.x = column, blockIdx.y = 32-row group.
 __global__ void __launch_bounds__(256)
 dk_narrow_finish_kernel(const float* __restrict__ partial, float* __restrict__ dk, int parts, int bn,
-                        int KH, int KW, int C, int O, int m_tiles)
+                        int KH, int KW, int C, int O)
 {
-    const int total = m_tiles * bn * BM;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-        const int row = i % BM, col = (i / BM) % bn, mt = i / (BM * bn);
-        const int o = mt * BM + row;
-        const int di = col >> 5, dj = (col & 31) >> 2, c = col & 3;
-        if (o >= O || di >= KH || dj >= KW || c >= C) continue;
+    __shared__ float lane_sum[8][32];
+    const int col = blockIdx.x;
+    const int di = col >> 5, dj = (col & 31) >> 2, c = col & 3;
+    if (di >= KH || dj >= KW || c >= C) return;   // padding slot (uniform over the block)
+    const int r = threadIdx.x & 31, l = threadIdx.x >> 5;
+    const int o = blockIdx.y * 32 + r;
+    const int mt = o / BM, row = o % BM;
+    float acc = 0.f;
+    if (o < O) {
         const float* src = partial + ((size_t)mt * parts * bn + col) * BM + row;
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;   // four loads in flight; added below in partition order
-        float acc = __ldcg(src);
-        int sidx = 1;
-        for (; sidx + 4 <= parts; sidx += 4) {
-            a0 = __ldcg(src + (size_t)sidx * bn * BM);
-            a1 = __ldcg(src + (size_t)(sidx + 1) * bn * BM);
-            a2 = __ldcg(src + (size_t)(sidx + 2) * bn * BM);
-            a3 = __ldcg(src + (size_t)(sidx + 3) * bn * BM);
-            acc = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(acc, a0), a1), a2), a3);
-        }
-        for (; sidx < parts; ++sidx) acc = __fadd_rn(acc, __ldcg(src + (size_t)sidx * bn * BM));
-        dk[((size_t)(di * KW + dj) * C + c) * O + o] = acc;
+        for (int sidx = l; sidx < parts; sidx += 8) acc = __fadd_rn(acc, __ldcg(src + (size_t)sidx * bn * BM));
+    }
+    lane_sum[l][r] = acc;
+    __syncthreads();
+    if (l == 0 && o < O) {
+        float t = lane_sum[0][r];
+#pragma unroll
+        for (int q = 1; q < 8; ++q) t = __fadd_rn(t, lane_sum[q][r]);
+        dk[((size_t)(di * KW + dj) * C + c) * O + o] = t;
     }
 }
 
@@ -796,44 +836,52 @@ repack_k4_kernel(const float* __restrict__ k, float* __restrict__ k4, int KH, in
 // ---- input gradient of a narrow-channel layer (<= 4 input channels) -------------------------------
 // With C <= 4 the implicit GEMM of DX has N = C: every 128 x 32 tile of dy would be fetched for a
 // sliver of tensor work, once per tap.  Instead dy is read ONCE by a plain GEMM against all taps,
-//   ycol[pixel of dy][tap * C + c] = sum_o dy[pixel, o] * k[tap, c, o]      (N = KH*KW*C, padded to 32s)
-// - the FWD kernel on a 1x1 "convolution" with the weights transposed to k2[o][tap * C + c] - and a
+//   ycol[tap][pixel of dy][c] = sum_o dy[pixel, o] * k[tap, c, o]      (N = 4 * KH*KW, padded to 32s)
+// - the FWD kernel on a 1x1 "convolution" with the weights transposed to k2[o][4 * tap + c] - and a
 // gather ("col2im") then adds, for every input pixel, the <= ceil(KH/s)*ceil(KW/s) products that
 // land on it and applies the fused chain.
 __global__ void __launch_bounds__(256)
-repack_k2_kernel(const float* __restrict__ k, float* __restrict__ k2, int J, int Jp, int O)
+repack_k2_kernel(const float* __restrict__ k, float* __restrict__ k2, int taps, int C, int Jp, int O)
 {
     const int total = O * Jp;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
         const int j = i % Jp, o = i / Jp;
-        k2[i] = j < J ? __ldg(k + (size_t)j * O + o) : 0.f;
+        const int tap = j >> 2, c = j & 3;   // four columns per tap, channels beyond C are zero
+        k2[i] = (tap < taps && c < C) ? __ldg(k + ((size_t)tap * C + c) * O + o) : 0.f;
     }
 }
 
+// ycol is stored tap-major, [tap][pixel of dy][4 channels]: the threads of a warp walk adjacent
+// pixels, so their 16-byte reads of one tap's plane are contiguous.  One thread per output pixel.
 __global__ void __launch_bounds__(256)
-col2im_kernel(const float* __restrict__ ycol, float* __restrict__ out, int N, int H, int W, int C, int Ho, int Wo,
-              int KH, int KW, int sh, int sw, int pt, int pl, int Jp, const EpilogueArgs ep)
+col2im_kernel(const float4* __restrict__ ycol, float* __restrict__ out, int N, int H, int W, int C, int Ho, int Wo,
+              int KH, int KW, int sh, int sw, int pt, int pl, const EpilogueArgs ep)
 {
-    const size_t total = (size_t)N * H * W * C;
+    const size_t total = (size_t)N * H * W;
+    const size_t pixels = (size_t)N * Ho * Wo;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
-        const int c = (int)(idx % C);
-        const int w = (int)((idx / C) % W);
-        const int h = (int)((idx / ((size_t)C * W)) % H);
-        const int n = (int)(idx / ((size_t)C * W * H));
-        float acc = 0.f;
+    for (size_t pix = (size_t)blockIdx.x * blockDim.x + threadIdx.x; pix < total; pix += stride) {
+        const int w = (int)(pix % W);
+        const int h = (int)((pix / W) % H);
+        const int n = (int)(pix / ((size_t)W * H));
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
         for (int di = (h + pt) % sh; di < KH; di += sh) {      // taps whose row parity matches
-            const int i = (h + pt - di) / sh;
             if (h + pt - di < 0) break;
+            const int i = (h + pt - di) / sh;
             if (i >= Ho) continue;
             for (int dj = (w + pl) % sw; dj < KW; dj += sw) {
-                const int j = (w + pl - dj) / sw;
                 if (w + pl - dj < 0) break;
+                const int j = (w + pl - dj) / sw;
                 if (j >= Wo) continue;
-                acc = __fadd_rn(acc, __ldg(ycol + (((size_t)n * Ho + i) * Wo + j) * Jp + (di * KW + dj) * C + c));
+                const float4 v = __ldg(ycol + (size_t)(di * KW + dj) * pixels + ((size_t)n * Ho + i) * Wo + j);
+                acc[0] = __fadd_rn(acc[0], v.x); acc[1] = __fadd_rn(acc[1], v.y);
+                acc[2] = __fadd_rn(acc[2], v.z); acc[3] = __fadd_rn(acc[3], v.w);
             }
         }
-        out[idx] = epilogue_apply(ep, acc, idx, c);
+        for (int c = 0; c < C; ++c) {
+            const size_t idx = pix * C + c;
+            out[idx] = epilogue_apply(ep, acc[c], idx, c);
+        }
     }
 }
 
@@ -1046,11 +1094,15 @@ bool plan_fwd(const dcg_conv_desc& d, Plan& pl);
 bool plan_dx(const dcg_conv_desc& d, Plan& pl)
 {
     if (d.c <= 4 && d.o % 32 == 0 && d.stride_h <= d.kh && d.stride_w <= d.kw) {
-        const int Jp = (d.kh * d.kw * d.c + 31) / 32 * 32;
+        const int Jp = (d.kh * d.kw * 4 + 31) / 32 * 32;   // four columns per tap
         pl.Jp = Jp;
         pl.k2_bytes = (size_t)d.o * Jp * sizeof(float);
         pl.ycol_bytes = (size_t)d.n * d.ho * d.wo * Jp * sizeof(float);
-        if (plan_fwd(dx_gemm_desc(d, Jp), pl)) return true;
+        if (plan_fwd(dx_gemm_desc(d, Jp), pl)) {
+            pl.p.planes = 1;
+            pl.p.plane_stride = (unsigned long long)d.n * d.ho * d.wo * 4ull;
+            return true;
+        }
         pl = Plan{};
     }
     if (d.o % 4 != 0 || d.stride_h > 8 || d.stride_w > 8) return false;
@@ -1154,20 +1206,29 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, Plan& pl, float* out, c
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = pl.smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = (unsigned)p.splits;   // blockIdx.x = tile * splits + split: one cluster per tile
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    static const int no_pdl = env_int("DCG_TC_NO_PDL");
+    if (!no_pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (p.splits > 1 && !p.ext_finish) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = (unsigned)p.splits;   // blockIdx.x = tile * splits + split: one cluster per tile
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = (p.splits > 1 && !p.ext_finish) ? 1 : 0;
+    cfg.numAttrs = na;
     const cudaError_t err = cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE>, ma, mb, p);
     if (err != cudaSuccess) return fail(DCG_ERR_CUDA, "conv_tc_kernel launch: %s", cudaGetErrorString(err));
     count_launch();
     if (p.ext_finish) {
-        const int total = p.m_tiles * p.bn * BM;
-        dk_narrow_finish_kernel<<<(total + 255) / 256, 256, 0, stream>>>(p.scratch, out, p.splits, p.bn, p.KH, p.KW,
-                                                                         p.C, p.O, p.m_tiles);
+        const dim3 fgrid((unsigned)p.bn, (unsigned)((p.O + 31) / 32));
+        dk_narrow_finish_kernel<<<fgrid, 256, 0, stream>>>(p.scratch, out, p.splits, p.bn, p.KH, p.KW, p.C, p.O);
         DCG_LAUNCH_CHECK("dk_narrow_finish_kernel");
     }
     return DCG_OK;
@@ -1274,8 +1335,8 @@ int conv_tc_dx(const dcg_conv_desc& d, const float* dy, const float* k, float* d
         uint8_t* base = static_cast<uint8_t*>(ws);
         float* k2 = reinterpret_cast<float*>(base + pl.k2_off());
         float* ycol = reinterpret_cast<float*>(base + pl.ycol_off());
-        const int J = d.kh * d.kw * d.c, Jp = pl.Jp;
-        repack_k2_kernel<<<(d.o * Jp + 255) / 256, 256, 0, stream>>>(k, k2, J, Jp, d.o);
+        const int Jp = pl.Jp;
+        repack_k2_kernel<<<(d.o * Jp + 255) / 256, 256, 0, stream>>>(k, k2, d.kh * d.kw, d.c, Jp, d.o);
         DCG_LAUNCH_CHECK("repack_k2_kernel");
         // k2 [o][Jp] as (j%32, o, 1, j/32), box (32, 32, 1, bn/32): the FWD kernel's weight view with one tap
         const cuuint64_t dims[4] = {32, (cuuint64_t)d.o, 1, (cuuint64_t)(Jp / 32)};
@@ -1285,12 +1346,13 @@ int conv_tc_dx(const dcg_conv_desc& d, const float* dy, const float* k, float* d
         if ((st = encode_map(&mb, k2, 4, dims, true, strides, box, es))) return st;
         const EpilogueArgs none{};
         if ((st = launch<MODE_FWD>(ma, mb, pl, ycol, none, Jp, ws, ws_bytes, stream))) return st;
-        const size_t total = (size_t)d.n * d.h * d.w * d.c;
+        const size_t total = (size_t)d.n * d.h * d.w;
         size_t blocks = (total + 255) / 256;
         const size_t cap = (size_t)sm_count() * 16;
         if (blocks > cap) blocks = cap;
-        col2im_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ycol, dx, d.n, d.h, d.w, d.c, d.ho, d.wo, d.kh, d.kw,
-                                                            d.stride_h, d.stride_w, d.pad_top, d.pad_left, Jp, ep);
+        col2im_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const float4*>(ycol), dx, d.n, d.h, d.w, d.c,
+                                                            d.ho, d.wo, d.kh, d.kw, d.stride_h, d.stride_w, d.pad_top,
+                                                            d.pad_left, ep);
         DCG_LAUNCH_CHECK("col2im_kernel");
         return DCG_OK;
     }
@@ -1350,6 +1412,12 @@ extern "C" int dcg_device_status(void) { return dcg::conv_tc_device_status(nullp
 
 // Tuning aid, not part of the public header: copies the timeline recorded by CTA 0 of the last
 // tensor-path launch (DCG_TC_DEBUG bit 4) to `out` (3080 values).  Synchronises the device.
+extern "C" int dcg_debug_cta_trace(unsigned long long* out /* [1024][8] */)
+{
+    if (cudaDeviceSynchronize() != cudaSuccess) return DCG_ERR_CUDA;
+    return cudaMemcpyFromSymbol(out, dcg::g_tc_cta_trace, sizeof(unsigned long long) * 1024 * 8) == cudaSuccess ? DCG_OK : DCG_ERR_CUDA;
+}
+
 extern "C" int dcg_debug_trace(long long* out)
 {
     if (cudaDeviceSynchronize() != cudaSuccess) return DCG_ERR_CUDA;

@@ -144,6 +144,25 @@ gemm_wide_kernel(const float* __restrict__ a, const float* __restrict__ b,
     for (int i = 0; i < RB; ++i) acc[i] = 0.f;
     const float* bc = b + c;
     int k = 0;
+    // sixteen loads of B in flight per thread: the kernel is latency-bound otherwise (one warp walks
+    // a column of B with nothing else to overlap the memory round trips)
+    for (; k + 16 <= (int)n; k += 16) {
+        float bv[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) bv[u] = __ldg(bc + (size_t)(k + u) * p);
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+            const float4* ak = reinterpret_cast<const float4*>(As + (k + u) * RB);
+#pragma unroll
+            for (int q = 0; q < RB / 4; ++q) {
+                const float4 av = ak[q];
+                acc[4 * q + 0] = __fadd_rn(acc[4 * q + 0], __fmul_rn(av.x, bv[u]));
+                acc[4 * q + 1] = __fadd_rn(acc[4 * q + 1], __fmul_rn(av.y, bv[u]));
+                acc[4 * q + 2] = __fadd_rn(acc[4 * q + 2], __fmul_rn(av.z, bv[u]));
+                acc[4 * q + 3] = __fadd_rn(acc[4 * q + 3], __fmul_rn(av.w, bv[u]));
+            }
+        }
+    }
     for (; k + 4 <= (int)n; k += 4) {
         float bv[4];
 #pragma unroll
@@ -186,13 +205,12 @@ gemm_tall_tn_kernel(const float* __restrict__ a, const float* __restrict__ b, fl
     const size_t c = o / m, r = o % m;   // r fastest across threads: coalesced reads of A^T
     float s = 0.f;
     size_t k = 0;
-    for (; k + 4 <= n; k += 4) {
-        const float a0 = __ldg(a + k * m + r), a1 = __ldg(a + (k + 1) * m + r);
-        const float a2 = __ldg(a + (k + 2) * m + r), a3 = __ldg(a + (k + 3) * m + r);
-        s = __fadd_rn(s, __fmul_rn(a0, __ldg(b + k * p + c)));
-        s = __fadd_rn(s, __fmul_rn(a1, __ldg(b + (k + 1) * p + c)));
-        s = __fadd_rn(s, __fmul_rn(a2, __ldg(b + (k + 2) * p + c)));
-        s = __fadd_rn(s, __fmul_rn(a3, __ldg(b + (k + 3) * p + c)));
+    for (; k + 16 <= n; k += 16) {
+        float av[16], bw[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) { av[u] = __ldg(a + (k + u) * m + r); bw[u] = __ldg(b + (k + u) * p + c); }
+#pragma unroll
+        for (int u = 0; u < 16; ++u) s = __fadd_rn(s, __fmul_rn(av[u], bw[u]));
     }
     for (; k < n; ++k) s = __fadd_rn(s, __fmul_rn(__ldg(a + k * m + r), __ldg(b + k * p + c)));
     out[r * p + c] = s;
@@ -244,7 +262,7 @@ extern "C" int dcg_matmul_tn(const float* a, const float* b, float* out, size_t 
     DCG_CHECK_ARG(a && b && out && m > 0 && n > 0 && p > 0, "dcg_matmul_tn: bad arguments");
     if (wide_shape(m, n, p)) return launch_wide<true>(a, b, nullptr, out, m, n, p, as_stream(stream));
     if (p <= 8 && m >= 1024) {
-        gemm_tall_tn_kernel<<<(unsigned)((m * p + TPB - 1) / TPB), TPB, 0, as_stream(stream)>>>(a, b, out, m, n, p);
+        gemm_tall_tn_kernel<<<(unsigned)((m * p + 63) / 64), 64, 0, as_stream(stream)>>>(a, b, out, m, n, p);
         DCG_LAUNCH_CHECK("gemm_tall_tn_kernel");
         return DCG_OK;
     }

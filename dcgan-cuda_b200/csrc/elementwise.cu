@@ -6,6 +6,8 @@
 // of the SM count.  Reductions use a fixed tree so results are deterministic.
 #include <mutex>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace dcg {
@@ -117,13 +119,20 @@ update_kernel(const float* __restrict__ dv, float* __restrict__ out,
 }
 
 // ---- column sums (bias gradient) ---------------------------------------------
-// Stage 1: block (tx over column groups, ty over rows) reduces a slab of rows
-// into partial[slab][cols]; stage 2 sums the slabs in order.  VEC: a column
-// group is one float4.
+// Block (tx over column groups, ty over rows) reduces a slab of rows into
+// partial[slab][cols].  VEC: a column group is one float4.  The slabs of one column tile are
+// then added by whichever of its blocks finishes last (a ticket per column tile tells it so):
+// lane l adds slabs l, l+L, ... and the lane sums are added in lane order, so the result depends
+// on the launch shape only, never on which block came last.  `tickets` == nullptr leaves the
+// slabs to colsum_final_kernel.
+constexpr int kTicketSets = 64, kTicketTiles = 64;
+__device__ unsigned g_colsum_tickets[kTicketSets][kTicketTiles];   // zero at load, reset by the last block
+
 template <bool VEC>
 __global__ void __launch_bounds__(kThreads)
 colsum_partial_kernel(const float* __restrict__ a, float* __restrict__ partial,
-                      size_t rows, unsigned cols, unsigned rows_per_slab, int tx_count)
+                      size_t rows, unsigned cols, unsigned rows_per_slab, int tx_count,
+                      float* __restrict__ out, unsigned* __restrict__ tickets)
 {
     extern __shared__ float smem[];  // [ty_count][tx_count * (VEC ? 4 : 1)]
     const int ty_count = blockDim.x / tx_count;
@@ -163,6 +172,63 @@ colsum_partial_kernel(const float* __restrict__ a, float* __restrict__ partial,
         float* dst = partial + (size_t)blockIdx.y * cols + (size_t)group * W;
 #pragma unroll
         for (int q = 0; q < W; ++q) dst[q] = mine[q];
+    }
+    if (tickets == nullptr) return;
+    // ---- the last block of this column tile adds the slabs ----
+    __shared__ unsigned s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned t = atomicAdd(tickets + blockIdx.x, 1u);
+        s_last = (t == gridDim.y - 1) ? 1u : 0u;
+        if (s_last) tickets[blockIdx.x] = 0u;   // ready for the next launch that uses this set
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // thread = (column group, slab lane): lane l adds slabs l, l+L, ... through four independent
+    // accumulators (four loads in flight), combined in a fixed order
+    const int lanes = blockDim.x / tx_count;     // >= 8
+    const int g = threadIdx.x % tx_count, l = threadIdx.x / tx_count;
+    const unsigned grp = blockIdx.x * tx_count + g;
+    float4 t[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) t[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (grp < groups) {
+        unsigned k = l;
+        for (; k + 3 * lanes < gridDim.y; k += 4 * lanes) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float* src = partial + (size_t)(k + u * lanes) * cols + (size_t)grp * W;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (VEC) v = __ldcg(reinterpret_cast<const float4*>(src));
+                else v.x = __ldcg(src);
+                t[u].x += v.x; t[u].y += v.y; t[u].z += v.z; t[u].w += v.w;
+            }
+        }
+        for (; k < gridDim.y; k += lanes) {
+            const float* src = partial + (size_t)k * cols + (size_t)grp * W;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (VEC) v = __ldcg(reinterpret_cast<const float4*>(src));
+            else v.x = __ldcg(src);
+            t[0].x += v.x; t[0].y += v.y; t[0].z += v.z; t[0].w += v.w;
+        }
+    }
+    float4 s4;
+    s4.x = (t[0].x + t[1].x) + (t[2].x + t[3].x); s4.y = (t[0].y + t[1].y) + (t[2].y + t[3].y);
+    s4.z = (t[0].z + t[1].z) + (t[2].z + t[3].z); s4.w = (t[0].w + t[1].w) + (t[2].w + t[3].w);
+    __syncthreads();                             // smem is reused: [lane][group][W]
+    float* slot = smem + ((size_t)l * tx_count + g) * W;
+    slot[0] = s4.x;
+    if (VEC) { slot[1] = s4.y; slot[2] = s4.z; slot[3] = s4.w; }
+    __syncthreads();
+    if (l == 0 && grp < groups) {
+#pragma unroll
+        for (int q = 0; q < W; ++q) {
+            float r = smem[(size_t)g * W + q];
+            for (int j = 1; j < lanes; ++j) r += smem[((size_t)j * tx_count + g) * W + q];
+            out[(size_t)grp * W + q] = r;
+        }
     }
 }
 
@@ -482,14 +548,23 @@ extern "C" int dcg_colsum(const float* a, float* out, size_t rows, size_t cols, 
     }
     const dim3 grid(p.grid_x, p.slabs);
     const size_t smem = (size_t)kThreads * (p.vec ? 4 : 1) * sizeof(float);
+    // One launch when the column tiles fit a ticket set: consecutive launches rotate through the
+    // sets, so up to kTicketSets column sums may be in flight on different streams at once.
+    unsigned* tickets = nullptr;
+    if (p.slabs > 1 && p.grid_x <= (unsigned)kTicketTiles) {
+        static std::atomic<unsigned> seq{0};
+        void* base = nullptr;
+        DCG_CUDA(cudaGetSymbolAddress(&base, g_colsum_tickets));
+        tickets = static_cast<unsigned*>(base) + (size_t)(seq.fetch_add(1) % kTicketSets) * kTicketTiles;
+    }
     if (p.vec)
         colsum_partial_kernel<true><<<grid, kThreads, smem, as_stream(stream)>>>(
-            a, partial, rows, (unsigned)cols, p.rows_per_slab, p.tx_count);
+            a, partial, rows, (unsigned)cols, p.rows_per_slab, p.tx_count, out, tickets);
     else
         colsum_partial_kernel<false><<<grid, kThreads, smem, as_stream(stream)>>>(
-            a, partial, rows, (unsigned)cols, p.rows_per_slab, p.tx_count);
+            a, partial, rows, (unsigned)cols, p.rows_per_slab, p.tx_count, out, tickets);
     DCG_LAUNCH_CHECK("colsum_partial_kernel");
-    if (p.slabs > 1) {
+    if (p.slabs > 1 && !tickets) {
         colsum_final_kernel<<<(unsigned)((cols + 31) / 32), 256, 0, as_stream(stream)>>>(
             partial, out, p.slabs, (unsigned)cols);
         DCG_LAUNCH_CHECK("colsum_final_kernel");
