@@ -44,6 +44,7 @@ __device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, 
 __global__ void __launch_bounds__(kAdamThreads)
 adam_multi_kernel(const __grid_constant__ AdamBatch batch, const AdamCoeffs c)
 {
+    pdl_enter();
     // which tensor does this block belong to?
     int t = 0;
     while (t + 1 < batch.count && blockIdx.x >= batch.block_begin[t + 1]) ++t;
@@ -109,6 +110,7 @@ __global__ void __launch_bounds__(kAdamThreads)
 moment_kernel(const float* __restrict__ dv, float* __restrict__ out, float a, float b, size_t n,
               int squared)
 {
+    pdl_enter();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         const float g = __ldg(dv + i);
@@ -121,6 +123,7 @@ __global__ void __launch_bounds__(kAdamThreads)
 adam_apply_kernel(const float* __restrict__ m, const float* __restrict__ v, float* __restrict__ out,
                   float lr_t, float eps, size_t n)
 {
+    pdl_enter();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
         out[i] = __fsub_rn(out[i], __fdiv_rn(__fmul_rn(lr_t, __ldg(m + i)),
@@ -141,7 +144,7 @@ int moment_update_launch(const float* dv, float* out, float a, float b, size_t n
 {
     DCG_CHECK_ARG(dv && out, "moment_update: null pointer");
     if (n == 0) return DCG_OK;
-    moment_kernel<<<flat_grid(n), kAdamThreads, 0, stream>>>(dv, out, a, b, n, squared ? 1 : 0);
+    launch_pdl(moment_kernel, flat_grid(n), kAdamThreads, 0, stream, dv, out, a, b, n, squared ? 1 : 0);
     DCG_LAUNCH_CHECK("moment_kernel");
     return DCG_OK;
 }
@@ -151,7 +154,7 @@ int adam_apply_launch(const float* m, const float* v, float* out, float lr_t, fl
 {
     DCG_CHECK_ARG(m && v && out, "adam_update: null pointer");
     if (n == 0) return DCG_OK;
-    adam_apply_kernel<<<flat_grid(n), kAdamThreads, 0, stream>>>(m, v, out, lr_t, eps, n);
+    launch_pdl(adam_apply_kernel, flat_grid(n), kAdamThreads, 0, stream, m, v, out, lr_t, eps, n);
     DCG_LAUNCH_CHECK("adam_apply_kernel");
     return DCG_OK;
 }
@@ -180,7 +183,7 @@ int adam_multi_launch(const dcg_adam_tensor* tensors, int count, float lr_t, flo
         }
         if (batch.count == 0) continue;
         batch.block_begin[batch.count] = blocks;
-        adam_multi_kernel<<<blocks, kAdamThreads, 0, stream>>>(batch, c);
+        launch_pdl(adam_multi_kernel, blocks, kAdamThreads, 0, stream, batch, c);
         DCG_LAUNCH_CHECK("adam_multi_kernel");
     }
     return DCG_OK;

@@ -48,6 +48,38 @@ uint64_t launches_total();
 
 inline cudaStream_t as_stream(dcg_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
+// ---- programmatic dependent launch --------------------------------------------------------------
+// Every kernel of the library is launched with programmatic stream serialisation and begins with
+// pdl_enter(): it waits for the previous kernel of the stream to have completed (its memory
+// visible) before touching memory, then lets the next kernel be scheduled.  The data dependencies
+// are the ordinary in-order ones; what overlaps is the launch latency and block set-up of kernel
+// N+1 with the tail of kernel N.  A kernel launched without the attribute (or first in its stream)
+// sees both instructions as no-ops.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_enter()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       Args&&... args)
+{
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);   // errors surface in DCG_LAUNCH_CHECK
+}
+#endif
+
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Number of SMs of the current device (cached per device id).

@@ -769,6 +769,7 @@ __global__ void __launch_bounds__(256)
 dk_narrow_finish_kernel(const float* __restrict__ partial, float* __restrict__ dk, int parts, int bn,
                         int KH, int KW, int C, int O)
 {
+    pdl_enter();
     __shared__ float lane_sum[8][32];
     const int col = blockIdx.x;
     const int di = col >> 5, dj = (col & 31) >> 2, c = col & 3;
@@ -805,6 +806,7 @@ __global__ void __launch_bounds__(256)
 repack_narrow_kernel(const float* __restrict__ x, float4* __restrict__ xp, int N, int H, int W, int C,
                      int Hp, int Wp, int pt, int pl)
 {
+    pdl_enter();
     const size_t total = (size_t)N * Hp * Wp;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -825,6 +827,7 @@ repack_narrow_kernel(const float* __restrict__ x, float4* __restrict__ xp, int N
 __global__ void __launch_bounds__(256)
 repack_k4_kernel(const float* __restrict__ k, float* __restrict__ k4, int KH, int KW, int C, int O)
 {
+    pdl_enter();
     const int total = KH * 32 * O;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
         const int o = i % O, slot = (i / O) % 32, di = i / (O * 32);
@@ -843,6 +846,7 @@ repack_k4_kernel(const float* __restrict__ k, float* __restrict__ k4, int KH, in
 __global__ void __launch_bounds__(256)
 repack_k2_kernel(const float* __restrict__ k, float* __restrict__ k2, int taps, int C, int Jp, int O)
 {
+    pdl_enter();
     const int total = O * Jp;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
         const int j = i % Jp, o = i / Jp;
@@ -857,6 +861,7 @@ __global__ void __launch_bounds__(256)
 col2im_kernel(const float4* __restrict__ ycol, float* __restrict__ out, int N, int H, int W, int C, int Ho, int Wo,
               int KH, int KW, int sh, int sw, int pt, int pl, const EpilogueArgs ep)
 {
+    pdl_enter();
     const size_t total = (size_t)N * H * W;
     const size_t pixels = (size_t)N * Ho * Wo;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -1228,7 +1233,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, Plan& pl, float* out, c
     count_launch();
     if (p.ext_finish) {
         const dim3 fgrid((unsigned)p.bn, (unsigned)((p.O + 31) / 32));
-        dk_narrow_finish_kernel<<<fgrid, 256, 0, stream>>>(p.scratch, out, p.splits, p.bn, p.KH, p.KW, p.C, p.O);
+        launch_pdl(dk_narrow_finish_kernel, fgrid, 256, 0, stream, p.scratch, out, p.splits, p.bn, p.KH, p.KW, p.C, p.O);
         DCG_LAUNCH_CHECK("dk_narrow_finish_kernel");
     }
     return DCG_OK;
@@ -1247,14 +1252,14 @@ int narrow_prepare(const dcg_conv_desc& d, const Plan& pl, const float* x, const
     size_t blocks = (pixels + 255) / 256;
     const size_t cap = (size_t)sm_count() * 16;
     if (blocks > cap) blocks = cap;
-    repack_narrow_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, reinterpret_cast<float4*>(xp), d.n, d.h, d.w, d.c,
+    launch_pdl(repack_narrow_kernel, (unsigned)blocks, 256, 0, stream, x, reinterpret_cast<float4*>(xp), d.n, d.h, d.w, d.c,
                                                                 pl.Hp, pl.Wp, d.pad_top, d.pad_left);
     DCG_LAUNCH_CHECK("repack_narrow_kernel");
     *xp_out = xp;
     if (k4_out) {
         float* k4 = reinterpret_cast<float*>(base + pl.k4_off());
         const int total = d.kh * 32 * d.o;
-        repack_k4_kernel<<<(total + 255) / 256, 256, 0, stream>>>(k, k4, d.kh, d.kw, d.c, d.o);
+        launch_pdl(repack_k4_kernel, (total + 255) / 256, 256, 0, stream, k, k4, d.kh, d.kw, d.c, d.o);
         DCG_LAUNCH_CHECK("repack_k4_kernel");
         *k4_out = k4;
     }
@@ -1336,7 +1341,7 @@ int conv_tc_dx(const dcg_conv_desc& d, const float* dy, const float* k, float* d
         float* k2 = reinterpret_cast<float*>(base + pl.k2_off());
         float* ycol = reinterpret_cast<float*>(base + pl.ycol_off());
         const int Jp = pl.Jp;
-        repack_k2_kernel<<<(d.o * Jp + 255) / 256, 256, 0, stream>>>(k, k2, d.kh * d.kw, d.c, Jp, d.o);
+        launch_pdl(repack_k2_kernel, (d.o * Jp + 255) / 256, 256, 0, stream, k, k2, d.kh * d.kw, d.c, Jp, d.o);
         DCG_LAUNCH_CHECK("repack_k2_kernel");
         // k2 [o][Jp] as (j%32, o, 1, j/32), box (32, 32, 1, bn/32): the FWD kernel's weight view with one tap
         const cuuint64_t dims[4] = {32, (cuuint64_t)d.o, 1, (cuuint64_t)(Jp / 32)};
@@ -1350,7 +1355,7 @@ int conv_tc_dx(const dcg_conv_desc& d, const float* dy, const float* k, float* d
         size_t blocks = (total + 255) / 256;
         const size_t cap = (size_t)sm_count() * 16;
         if (blocks > cap) blocks = cap;
-        col2im_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const float4*>(ycol), dx, d.n, d.h, d.w, d.c,
+        launch_pdl(col2im_kernel, (unsigned)blocks, 256, 0, stream, reinterpret_cast<const float4*>(ycol), dx, d.n, d.h, d.w, d.c,
                                                             d.ho, d.wo, d.kh, d.kw, d.stride_h, d.stride_w, d.pad_top,
                                                             d.pad_left, ep);
         DCG_LAUNCH_CHECK("col2im_kernel");

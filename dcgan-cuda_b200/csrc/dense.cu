@@ -33,6 +33,7 @@ gemm_tiled_kernel(const float* __restrict__ a, const float* __restrict__ b,
                   const float* __restrict__ bias, float* __restrict__ out,
                   size_t m, size_t n, size_t p)
 {
+    pdl_enter();
     __shared__ float As[KT][TILE + 1];  // [k][row]
     __shared__ float Bs[KT][TILE + 1];  // [k][col]
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
@@ -94,6 +95,7 @@ gemm_long_k_kernel(const float* __restrict__ a, const float* __restrict__ b,
                    const float* __restrict__ bias, float* __restrict__ out,
                    size_t m, size_t n, size_t p)
 {
+    pdl_enter();
     __shared__ float part[TPB];
     const size_t o = blockIdx.x;
     const size_t r = o / p, c = o % p;
@@ -128,6 +130,7 @@ gemm_wide_kernel(const float* __restrict__ a, const float* __restrict__ b,
                  const float* __restrict__ bias, float* __restrict__ out,
                  size_t m, size_t n, size_t p)
 {
+    pdl_enter();
     __shared__ __align__(16) float As[256 * RB];   // [k][RB]
     const size_t row0 = (size_t)blockIdx.y * RB;
     for (int e = threadIdx.x; e < (int)n * RB; e += 128) {
@@ -200,6 +203,7 @@ __global__ void __launch_bounds__(TPB)
 gemm_tall_tn_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
                     size_t m, size_t n, size_t p)
 {
+    pdl_enter();
     const size_t o = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (o >= m * p) return;
     const size_t c = o / m, r = o % m;   // r fastest across threads: coalesced reads of A^T
@@ -221,7 +225,7 @@ int launch_wide(const float* a, const float* b, const float* bias, float* out, s
                 size_t p, cudaStream_t stream)
 {
     const dim3 grid((unsigned)((p + 127) / 128), (unsigned)((m + RB - 1) / RB));
-    gemm_wide_kernel<TA><<<grid, 128, 0, stream>>>(a, b, bias, out, m, n, p);
+    launch_pdl(gemm_wide_kernel<TA>, grid, 128, 0, stream, a, b, bias, out, m, n, p);
     DCG_LAUNCH_CHECK("gemm_wide_kernel");
     return DCG_OK;
 }
@@ -233,7 +237,7 @@ int launch_tiled(const float* a, const float* b, const float* bias, float* out, 
                  size_t p, cudaStream_t stream, const char* name)
 {
     const dim3 grid((unsigned)((p + TILE - 1) / TILE), (unsigned)((m + TILE - 1) / TILE));
-    gemm_tiled_kernel<TA, TB><<<grid, TPB, 0, stream>>>(a, b, bias, out, m, n, p);
+    launch_pdl(gemm_tiled_kernel<TA, TB>, grid, TPB, 0, stream, a, b, bias, out, m, n, p);
     DCG_LAUNCH_CHECK(name);
     return DCG_OK;
 }
@@ -248,7 +252,7 @@ extern "C" int dcg_matmul(const float* a, const float* b, const float* bias, flo
 {
     DCG_CHECK_ARG(a && b && out && m > 0 && n > 0 && p > 0, "dcg_matmul: bad arguments");
     if (m * p <= 4096 && n >= 1024) {
-        gemm_long_k_kernel<<<(unsigned)(m * p), TPB, 0, as_stream(stream)>>>(a, b, bias, out, m, n, p);
+        launch_pdl(gemm_long_k_kernel, (unsigned)(m * p), TPB, 0, as_stream(stream), a, b, bias, out, m, n, p);
         DCG_LAUNCH_CHECK("gemm_long_k_kernel");
         return DCG_OK;
     }
@@ -262,7 +266,7 @@ extern "C" int dcg_matmul_tn(const float* a, const float* b, float* out, size_t 
     DCG_CHECK_ARG(a && b && out && m > 0 && n > 0 && p > 0, "dcg_matmul_tn: bad arguments");
     if (wide_shape(m, n, p)) return launch_wide<true>(a, b, nullptr, out, m, n, p, as_stream(stream));
     if (p <= 8 && m >= 1024) {
-        gemm_tall_tn_kernel<<<(unsigned)((m * p + 63) / 64), 64, 0, as_stream(stream)>>>(a, b, out, m, n, p);
+        launch_pdl(gemm_tall_tn_kernel, (unsigned)((m * p + 63) / 64), 64, 0, as_stream(stream), a, b, out, m, n, p);
         DCG_LAUNCH_CHECK("gemm_tall_tn_kernel");
         return DCG_OK;
     }

@@ -33,6 +33,7 @@ bias_act_kernel(const float* __restrict__ a, const float* __restrict__ bias,
                 float* __restrict__ z_out, float* __restrict__ act_out,
                 size_t total, unsigned cols, int act, float alpha)
 {
+    pdl_enter();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (VEC) {
@@ -68,6 +69,7 @@ __global__ void __launch_bounds__(kThreads)
 act_grad_kernel(const float* __restrict__ gate, const float* __restrict__ dout,
                 float* __restrict__ out, size_t total, int act, float alpha)
 {
+    pdl_enter();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (VEC) {
@@ -92,6 +94,7 @@ __global__ void __launch_bounds__(kThreads)
 add_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
            size_t total)
 {
+    pdl_enter();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (VEC) {
@@ -112,6 +115,7 @@ __global__ void __launch_bounds__(kThreads)
 update_kernel(const float* __restrict__ dv, float* __restrict__ out,
               const float* __restrict__ coeff, size_t total)
 {
+    pdl_enter();
     const float c = __ldg(coeff);
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride)
@@ -134,6 +138,7 @@ colsum_partial_kernel(const float* __restrict__ a, float* __restrict__ partial,
                       size_t rows, unsigned cols, unsigned rows_per_slab, int tx_count,
                       float* __restrict__ out, unsigned* __restrict__ tickets)
 {
+    pdl_enter();
     extern __shared__ float smem[];  // [ty_count][tx_count * (VEC ? 4 : 1)]
     const int ty_count = blockDim.x / tx_count;
     const int tx = threadIdx.x % tx_count;
@@ -239,6 +244,7 @@ __global__ void __launch_bounds__(256)
 colsum_final_kernel(const float* __restrict__ partial, float* __restrict__ out,
                     unsigned slabs, unsigned cols)
 {
+    pdl_enter();
     __shared__ float part[8][33];
     const unsigned tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const unsigned c = blockIdx.x * 32 + tx;
@@ -268,6 +274,7 @@ colsum_final_kernel(const float* __restrict__ partial, float* __restrict__ out,
 __global__ void __launch_bounds__(kThreads)
 rowsum_kernel(const float* __restrict__ a, float* __restrict__ out, size_t rows, size_t cols)
 {
+    pdl_enter();
     const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (warp >= rows) return;
@@ -301,6 +308,7 @@ __global__ void __launch_bounds__(512)
 sigmoid_xent_kernel(const float* __restrict__ y, const float* __restrict__ x,
                     float* __restrict__ out, size_t n)
 {
+    pdl_enter();
     __shared__ float red[32];
     float s = 0.f;
     for (size_t i = threadIdx.x; i < n; i += blockDim.x) {
@@ -315,6 +323,7 @@ __global__ void __launch_bounds__(kThreads)
 sigmoid_xent_grad_kernel(const float* __restrict__ y, const float* __restrict__ x,
                          float* __restrict__ out, size_t n)
 {
+    pdl_enter();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
         out[i] = (act_apply(__ldg(x + i), DCG_ACT_SIGMOID, 0.f) - __ldg(y + i)) / (float)n;
@@ -324,6 +333,7 @@ __global__ void __launch_bounds__(512)
 mse_kernel(const float* __restrict__ y, const float* __restrict__ y_hat, float* __restrict__ out,
            size_t n)
 {
+    pdl_enter();
     __shared__ float red[32];
     float s = 0.f;
     for (size_t i = threadIdx.x; i < n; i += blockDim.x) {
@@ -338,6 +348,7 @@ __global__ void __launch_bounds__(kThreads)
 mse_grad_kernel(const float* __restrict__ y, const float* __restrict__ y_hat,
                 float* __restrict__ out, size_t n, float coeff)
 {
+    pdl_enter();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
         out[i] = __fmul_rn(coeff, __fsub_rn(__ldg(y_hat + i), __ldg(y + i)));
@@ -349,6 +360,7 @@ __global__ void __launch_bounds__(kThreads)
 softmax_rows_kernel(const float* __restrict__ a, const float* __restrict__ y,
                     float* __restrict__ out, size_t rows, size_t cols, int mode)
 {
+    pdl_enter();
     const size_t row = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (row >= rows) return;
@@ -377,6 +389,7 @@ __global__ void __launch_bounds__(512)
 softmax_xent_kernel(const float* __restrict__ y, const float* __restrict__ logits,
                     float* __restrict__ out, size_t rows, size_t cols)
 {
+    pdl_enter();
     __shared__ float red[32];
     float acc = 0.f;
     for (size_t r = threadIdx.x; r < rows; r += blockDim.x) {
@@ -398,6 +411,7 @@ __global__ void __launch_bounds__(512)
 argmax_acc_kernel(const float* __restrict__ a, const float* __restrict__ b,
                   float* __restrict__ out, size_t rows, size_t cols)
 {
+    pdl_enter();
     __shared__ unsigned count;
     if (threadIdx.x == 0) count = 0;
     __syncthreads();
@@ -433,10 +447,10 @@ extern "C" int dcg_bias_act(const float* a, const float* bias, float* z_out, flo
     const bool vec = (cols % 4 == 0) && aligned16(a) && (!bias || aligned16(bias)) &&
                      (!z_out || aligned16(z_out)) && (!act_out || aligned16(act_out));
     if (vec)
-        bias_act_kernel<true><<<stream_grid(total / 4), kThreads, 0, as_stream(stream)>>>(
+        launch_pdl(bias_act_kernel<true>, stream_grid(total / 4), kThreads, 0, as_stream(stream), 
             a, bias, z_out, act_out, total, (unsigned)cols, act, alpha);
     else
-        bias_act_kernel<false><<<stream_grid(total), kThreads, 0, as_stream(stream)>>>(
+        launch_pdl(bias_act_kernel<false>, stream_grid(total), kThreads, 0, as_stream(stream), 
             a, bias, z_out, act_out, total, (unsigned)cols, act, alpha);
     DCG_LAUNCH_CHECK("bias_act_kernel");
     return DCG_OK;
@@ -458,9 +472,9 @@ extern "C" int dcg_act_grad(const float* gate, const float* dout, float* out, si
     if (n == 0) return DCG_OK;
     const bool vec = (n % 4 == 0) && aligned16(gate) && aligned16(dout) && aligned16(out);
     if (vec)
-        act_grad_kernel<true><<<stream_grid(n / 4), kThreads, 0, as_stream(stream)>>>(gate, dout, out, n, act, alpha);
+        launch_pdl(act_grad_kernel<true>, stream_grid(n / 4), kThreads, 0, as_stream(stream), gate, dout, out, n, act, alpha);
     else
-        act_grad_kernel<false><<<stream_grid(n), kThreads, 0, as_stream(stream)>>>(gate, dout, out, n, act, alpha);
+        launch_pdl(act_grad_kernel<false>, stream_grid(n), kThreads, 0, as_stream(stream), gate, dout, out, n, act, alpha);
     DCG_LAUNCH_CHECK("act_grad_kernel");
     return DCG_OK;
 }
@@ -471,9 +485,9 @@ extern "C" int dcg_add(const float* a, const float* b, float* out, size_t n, dcg
     if (n == 0) return DCG_OK;
     const bool vec = (n % 4 == 0) && aligned16(a) && aligned16(b) && aligned16(out);
     if (vec)
-        add_kernel<true><<<stream_grid(n / 4), kThreads, 0, as_stream(stream)>>>(a, b, out, n);
+        launch_pdl(add_kernel<true>, stream_grid(n / 4), kThreads, 0, as_stream(stream), a, b, out, n);
     else
-        add_kernel<false><<<stream_grid(n), kThreads, 0, as_stream(stream)>>>(a, b, out, n);
+        launch_pdl(add_kernel<false>, stream_grid(n), kThreads, 0, as_stream(stream), a, b, out, n);
     DCG_LAUNCH_CHECK("add_kernel");
     return DCG_OK;
 }
@@ -483,7 +497,7 @@ extern "C" int dcg_update(const float* dv, float* out, const float* coeff, size_
 {
     DCG_CHECK_ARG(dv && out && coeff, "dcg_update: null pointer");
     if (n == 0) return DCG_OK;
-    update_kernel<<<stream_grid(n), kThreads, 0, as_stream(stream)>>>(dv, out, coeff, n);
+    launch_pdl(update_kernel, stream_grid(n), kThreads, 0, as_stream(stream), dv, out, coeff, n);
     DCG_LAUNCH_CHECK("update_kernel");
     return DCG_OK;
 }
@@ -558,14 +572,14 @@ extern "C" int dcg_colsum(const float* a, float* out, size_t rows, size_t cols, 
         tickets = static_cast<unsigned*>(base) + (size_t)(seq.fetch_add(1) % kTicketSets) * kTicketTiles;
     }
     if (p.vec)
-        colsum_partial_kernel<true><<<grid, kThreads, smem, as_stream(stream)>>>(
+        launch_pdl(colsum_partial_kernel<true>, grid, kThreads, smem, as_stream(stream), 
             a, partial, rows, (unsigned)cols, p.rows_per_slab, p.tx_count, out, tickets);
     else
-        colsum_partial_kernel<false><<<grid, kThreads, smem, as_stream(stream)>>>(
+        launch_pdl(colsum_partial_kernel<false>, grid, kThreads, smem, as_stream(stream), 
             a, partial, rows, (unsigned)cols, p.rows_per_slab, p.tx_count, out, tickets);
     DCG_LAUNCH_CHECK("colsum_partial_kernel");
     if (p.slabs > 1 && !tickets) {
-        colsum_final_kernel<<<(unsigned)((cols + 31) / 32), 256, 0, as_stream(stream)>>>(
+        launch_pdl(colsum_final_kernel, (unsigned)((cols + 31) / 32), 256, 0, as_stream(stream), 
             partial, out, p.slabs, (unsigned)cols);
         DCG_LAUNCH_CHECK("colsum_final_kernel");
     }
@@ -576,7 +590,7 @@ extern "C" int dcg_rowsum(const float* a, float* out, size_t rows, size_t cols, 
 {
     DCG_CHECK_ARG(a && out && rows > 0 && cols > 0, "dcg_rowsum: bad arguments");
     const size_t blocks = (rows * 32 + kThreads - 1) / kThreads;
-    rowsum_kernel<<<(unsigned)blocks, kThreads, 0, as_stream(stream)>>>(a, out, rows, cols);
+    launch_pdl(rowsum_kernel, (unsigned)blocks, kThreads, 0, as_stream(stream), a, out, rows, cols);
     DCG_LAUNCH_CHECK("rowsum_kernel");
     return DCG_OK;
 }
@@ -585,7 +599,7 @@ extern "C" int dcg_sigmoid_xent(const float* y, const float* logits, float* out,
                                 dcg_stream_t stream)
 {
     DCG_CHECK_ARG(y && logits && out && n > 0, "dcg_sigmoid_xent: bad arguments");
-    sigmoid_xent_kernel<<<1, 512, 0, as_stream(stream)>>>(y, logits, out, n);
+    launch_pdl(sigmoid_xent_kernel, 1, 512, 0, as_stream(stream), y, logits, out, n);
     DCG_LAUNCH_CHECK("sigmoid_xent_kernel");
     return DCG_OK;
 }
@@ -594,7 +608,7 @@ extern "C" int dcg_sigmoid_xent_grad(const float* y, const float* logits, float*
                                      dcg_stream_t stream)
 {
     DCG_CHECK_ARG(y && logits && out && n > 0, "dcg_sigmoid_xent_grad: bad arguments");
-    sigmoid_xent_grad_kernel<<<stream_grid(n), kThreads, 0, as_stream(stream)>>>(y, logits, out, n);
+    launch_pdl(sigmoid_xent_grad_kernel, stream_grid(n), kThreads, 0, as_stream(stream), y, logits, out, n);
     DCG_LAUNCH_CHECK("sigmoid_xent_grad_kernel");
     return DCG_OK;
 }
@@ -603,7 +617,7 @@ extern "C" int dcg_mse(const float* y, const float* y_hat, float* out, size_t ro
                        dcg_stream_t stream)
 {
     DCG_CHECK_ARG(y && y_hat && out && rows * cols > 0, "dcg_mse: bad arguments");
-    mse_kernel<<<1, 512, 0, as_stream(stream)>>>(y, y_hat, out, rows * cols);
+    launch_pdl(mse_kernel, 1, 512, 0, as_stream(stream), y, y_hat, out, rows * cols);
     DCG_LAUNCH_CHECK("mse_kernel");
     return DCG_OK;
 }
@@ -612,7 +626,7 @@ extern "C" int dcg_mse_grad(const float* y, const float* y_hat, float* out, size
                             dcg_stream_t stream)
 {
     DCG_CHECK_ARG(y && y_hat && out && n > 0, "dcg_mse_grad: bad arguments");
-    mse_grad_kernel<<<stream_grid(n), kThreads, 0, as_stream(stream)>>>(y, y_hat, out, n,
+    launch_pdl(mse_grad_kernel, stream_grid(n), kThreads, 0, as_stream(stream), y, y_hat, out, n,
                                                                         (float)(2. / (double)n));
     DCG_LAUNCH_CHECK("mse_grad_kernel");
     return DCG_OK;
@@ -623,7 +637,7 @@ static int softmax_rows(const float* a, const float* y, float* out, size_t rows,
 {
     DCG_CHECK_ARG(a && out && rows > 0 && cols > 0, "softmax: bad arguments");
     const size_t blocks = (rows * 32 + kThreads - 1) / kThreads;
-    softmax_rows_kernel<<<(unsigned)blocks, kThreads, 0, as_stream(stream)>>>(a, y, out, rows, cols, mode);
+    launch_pdl(softmax_rows_kernel, (unsigned)blocks, kThreads, 0, as_stream(stream), a, y, out, rows, cols, mode);
     DCG_LAUNCH_CHECK("softmax_rows_kernel");
     return DCG_OK;
 }
@@ -650,7 +664,7 @@ extern "C" int dcg_softmax_xent(const float* y, const float* logits, float* out,
                                 size_t cols, dcg_stream_t stream)
 {
     DCG_CHECK_ARG(y && logits && out && rows > 0 && cols > 0, "dcg_softmax_xent: bad arguments");
-    softmax_xent_kernel<<<1, 512, 0, as_stream(stream)>>>(y, logits, out, rows, cols);
+    launch_pdl(softmax_xent_kernel, 1, 512, 0, as_stream(stream), y, logits, out, rows, cols);
     DCG_LAUNCH_CHECK("softmax_xent_kernel");
     return DCG_OK;
 }
@@ -659,7 +673,7 @@ extern "C" int dcg_argmax_acc(const float* y, const float* y_hat, float* out, si
                               size_t cols, dcg_stream_t stream)
 {
     DCG_CHECK_ARG(y && y_hat && out && rows > 0 && cols > 0, "dcg_argmax_acc: bad arguments");
-    argmax_acc_kernel<<<1, 512, 0, as_stream(stream)>>>(y, y_hat, out, rows, cols);
+    launch_pdl(argmax_acc_kernel, 1, 512, 0, as_stream(stream), y, y_hat, out, rows, cols);
     DCG_LAUNCH_CHECK("argmax_acc_kernel");
     return DCG_OK;
 }
