@@ -290,7 +290,10 @@ def run_ours(args, rank, local_rank, world):
         "bound": "tensor", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
         "frac": achieved / tf32_peak if tf32_peak else None,
         "peak_source": "%s: dense bf16 %.1f TFLOP/s / 2 for TF32" % (peaks["_source"], peaks["bf16_tflops"]),
-        "share_of_step": conv_ms / total_ms, "traffic": None,
+        "share_of_step": conv_ms / total_ms,
+        # dram__bytes_read.sum + dram__bytes_write.sum per launch, mean of the FWD / DX / DK captures of the
+        # 128 -> 256 channel layer at batch 64 (profiles/conv_tc_kernel_D2_b64.md): the operands, read once
+        "traffic": NCU_CONV_DRAM_BYTES_PER_LAUNCH,
     }
     kernels = sorted(rows, key=lambda r: -r["ms"])[:14]
     kernel_table = [{"name": r["name"], "calls_per_step": r["calls"] / 3.0, "us_per_call": 1e3 * r["ms"] / r["calls"],
@@ -335,6 +338,30 @@ def run_ours(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+NCU_CONV_DRAM_BYTES_PER_LAUNCH = (11.73376e6 + 256 + 7.539456e6 + 512 + 12.649472e6) / 3.0
+
+
+def cta_timeline(pkg):
+    """Per-CTA phases of the last tensor-path launch (library built-in trace, DCG_TC_DEBUG=8): median / max
+    over CTAs, in microseconds of the GPU's global timer."""
+    import numpy as np
+    buf = (ctypes.c_ulonglong * (1024 * 8))()
+    pkg.lib.dcg_debug_cta_trace.argtypes = [ctypes.c_void_p]
+    pkg.lib.dcg_debug_cta_trace.restype = ctypes.c_int
+    pkg._lib.check(pkg.lib.dcg_debug_cta_trace(buf))
+    a = np.frombuffer(buf, dtype=np.uint64).reshape(1024, 8).astype(np.int64)
+    a = a[a[:, 0] > 0]
+    if len(a) == 0:
+        return None
+    rel = (a[:, :6] - a[:, 0].min()) / 1e3
+    d = np.diff(rel, axis=1)
+    out = {"ctas": int(len(a)), "sms": int(len(set(a[:, 6].tolist()))),
+           "first_to_last_end": float(rel[:, 5].max()), "entry_max": float(rel[:, 0].max())}
+    for i, nm in enumerate(["setup", "main_loop", "hand_over", "meet", "finish"]):
+        out[nm] = {"median": float(np.median(d[:, i])), "max": float(d[:, i].max())}
+    return out
+
+
 def run_sweep(args):
     """Config 4: the eight DCGAN conv shapes x {fwd, dx, dk} x batch, isolated, L2 flushed."""
     import torch
@@ -377,6 +404,8 @@ def run_sweep(args):
                 tflops = flops / (med * 1e-3) / 1e12
                 rows.append({"layer": name, "op": op, "batch": B, "us": med * 1e3, "tflops": tflops,
                              "frac_tf32_peak": tflops / tf32_peak})
+                if int(os.environ.get("DCG_TC_DEBUG", "0") or 0) & 8:
+                    rows[-1]["cta_timeline_us"] = cta_timeline(pkg)
     pkg._lib.check(pkg.lib.dcg_device_status())
     print(json.dumps({"sweep": rows, "tf32_peak_tflops": tf32_peak, "peak_source": peaks["_source"],
                       "timing": "median of %d, CUDA events, 256 MB L2 flush before each" % args.sweep_iters}))

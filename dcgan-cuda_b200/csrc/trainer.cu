@@ -10,6 +10,7 @@
 // at creation; parameters and gradients of each network are contiguous so a data-parallel caller
 // can average a network's gradients with a single all-reduce between *_backward and *_apply.
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -67,6 +68,11 @@ struct dcg_trainer {
     Tensor d_param[10], d_grad[10], d_grad2[10], d_m[10], d_v[10];
     Tensor g_params_all, g_grads_all, d_params_all, d_grads_all;
     float g_t = 0.f, d_t = 0.f;   // Adam step counters (host, as rt::Node::out2 of adam_update)
+    // Tensor path: the discriminator's fake and real passes of the D run are one pass over
+    // [g_out | x] with batch 2B (half the launches, twice the work per launch); d_grad then holds the
+    // sum of both gradient paths and d_grad2 stays zero.  The fp32 path keeps the reference's two
+    // passes and its summation order.
+    bool batched_d = false;
 
     // inputs, constants, losses
     Tensor x, z, ones, zeros, d_loss, d1_loss, d2_loss, g_loss;
@@ -131,7 +137,12 @@ void layout(dcg_trainer* t, Alloc& a)
     pack(t->d_m, ds, dummy);
     pack(t->d_v, ds, dummy);
 
-    t->x = a.get((size_t)B * kImg * kImg * 3);
+    // [g_out | x] are one buffer so that the batched discriminator pass reads both as one batch
+    const size_t img_n = (size_t)B * kImg * kImg * 3;
+    Tensor img2 = a.get(2 * img_n);
+    t->g_out = img2; t->g_out.n = img_n;
+    t->x = img2; t->x.n = img_n;
+    if (!a.dry) t->x.p = img2.p + img_n;
     t->z = a.get((size_t)B * kZ);
     t->ones = a.get(B); t->zeros = a.get(B);
     t->d_loss = a.get(1); t->d1_loss = a.get(1); t->d2_loss = a.get(1); t->g_loss = a.get(1);
@@ -143,22 +154,28 @@ void layout(dcg_trainer* t, Alloc& a)
         if (i < kLayers - 1) t->ga[i] = a.get(n);
         t->dgz[i] = a.get(n); t->dga[i] = a.get(n);
     }
-    t->g_out = a.get((size_t)B * kImg * kImg * 3);
     t->dg_out = a.get((size_t)B * kImg * kImg * 3);
     t->dg0a = a.get((size_t)B * 8192); t->dg0z = a.get((size_t)B * 8192);
-    for (int pss = 0; pss < 2; ++pss) {
-        for (int i = 0; i < kLayers; ++i) {
-            const int hw = 32 >> i;
-            const size_t n = (size_t)B * hw * hw * kDChan[i + 1];
-            t->dc[pss][i] = a.get(n); t->dz[pss][i] = a.get(n); t->da[pss][i] = a.get(n);
-        }
-        t->logits[pss] = a.get(B);
-        t->dlogits[pss] = a.get(B);
-    }
+    // pass 0 (fake) and pass 1 (real) of every discriminator tensor are adjacent: [fake | real]
+    auto pair = [&](Tensor& t0, Tensor& t1, size_t n) {
+        Tensor both = a.get(2 * n);
+        t0 = both; t0.n = n;
+        t1 = both; t1.n = n;
+        if (!a.dry) t1.p = both.p + n;
+    };
     for (int i = 0; i < kLayers; ++i) {
         const int hw = 32 >> i;
-        t->ddz[i] = a.get((size_t)B * hw * hw * kDChan[i + 1]);
-        t->dda[i + 1] = a.get((size_t)B * hw * hw * kDChan[i + 1]);
+        const size_t n = (size_t)B * hw * hw * kDChan[i + 1];
+        pair(t->dc[0][i], t->dc[1][i], n);
+        pair(t->dz[0][i], t->dz[1][i], n);
+        pair(t->da[0][i], t->da[1][i], n);
+    }
+    pair(t->logits[0], t->logits[1], B);
+    pair(t->dlogits[0], t->dlogits[1], B);
+    for (int i = 0; i < kLayers; ++i) {   // backward scratch, sized for the batched pass
+        const int hw = 32 >> i;
+        t->ddz[i] = a.get((size_t)2 * B * hw * hw * kDChan[i + 1]);
+        t->dda[i + 1] = a.get((size_t)2 * B * hw * hw * kDChan[i + 1]);
     }
 }
 
@@ -305,9 +322,8 @@ void build_generator(dcg_trainer* t, std::vector<dcg_node>& L)
 }
 
 // Discriminator forward on `img` into pass `ps` buffers: dcgan/main.cu:123-249.
-void build_discriminator(dcg_trainer* t, std::vector<dcg_node>& L, const float* img, int ps)
+void build_discriminator(dcg_trainer* t, std::vector<dcg_node>& L, const float* img, int ps, int B)
 {
-    const int B = t->cfg.batch;
     const float* in = img;
     for (int i = 0; i < kLayers; ++i) {
         const int h = 64 >> i, ho = h / 2;
@@ -323,9 +339,8 @@ void build_discriminator(dcg_trainer* t, std::vector<dcg_node>& L, const float* 
 // Backward through the discriminator for pass `ps`, starting from dlogits[ps].
 // grads != nullptr: weight gradients into grads[0..9]; to_image: also the gradient w.r.t. the input.
 void build_discriminator_backward(dcg_trainer* t, std::vector<dcg_node>& L, const float* img, int ps,
-                                  Tensor* grads, bool to_image)
+                                  Tensor* grads, bool to_image, int B)
 {
-    const int B = t->cfg.batch;
     if (grads) {
         L.push_back(n_mat3(DCG_OP_TMAT_MAT_MUL, t->da[ps][3].p, t->dlogits[ps].p, grads[8].p, 8192, B, 1));
         L.push_back(n_rows_cols(DCG_OP_MAT_SUM_COLS, t->dlogits[ps].p, nullptr, grads[9].p, B, 1));
@@ -358,23 +373,33 @@ void build_lists(dcg_trainer* t)
     // ---- D run: graph.run({d_opti, d_loss}) ----
     std::vector<dcg_node>& D = t->d_nodes;
     build_generator(t, D);
-    build_discriminator(t, D, t->g_out.p, 0);
-    build_discriminator(t, D, t->x.p, 1);
+    if (t->batched_d) {
+        build_discriminator(t, D, t->g_out.p, 0, 2 * B);   // [g_out | x] through pass-0 buffers of 2B
+    } else {
+        build_discriminator(t, D, t->g_out.p, 0, B);
+        build_discriminator(t, D, t->x.p, 1, B);
+    }
     D.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY, t->zeros.p, t->logits[0].p, t->d1_loss.p, B));
     D.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY, t->ones.p, t->logits[1].p, t->d2_loss.p, B));
     D.push_back(n_binary(DCG_OP_ADD, t->d1_loss.p, t->d2_loss.p, t->d_loss.p, 1));
     D.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY_GRAD, t->zeros.p, t->logits[0].p, t->dlogits[0].p, B));
     D.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY_GRAD, t->ones.p, t->logits[1].p, t->dlogits[1].p, B));
-    build_discriminator_backward(t, D, t->g_out.p, 0, t->d_grad, false);
-    build_discriminator_backward(t, D, t->x.p, 1, t->d_grad2, false);
+    if (t->batched_d) {
+        // dlogits = [fake | real], each half already divided by its own B: the 2B-row backward pass
+        // sums both gradient paths (the Add of src/ops/graph.cu:302-309) inside its reductions
+        build_discriminator_backward(t, D, t->g_out.p, 0, t->d_grad, false, 2 * B);
+    } else {
+        build_discriminator_backward(t, D, t->g_out.p, 0, t->d_grad, false, B);
+        build_discriminator_backward(t, D, t->x.p, 1, t->d_grad2, false, B);
+    }
 
     // ---- G run: graph.run({g_opti, g_loss}) ----
     std::vector<dcg_node>& G = t->g_nodes;
     build_generator(t, G);
-    build_discriminator(t, G, t->g_out.p, 0);
+    build_discriminator(t, G, t->g_out.p, 0, B);
     G.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY, t->ones.p, t->logits[0].p, t->g_loss.p, B));
     G.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY_GRAD, t->ones.p, t->logits[0].p, t->dlogits[0].p, B));
-    build_discriminator_backward(t, G, t->g_out.p, 0, nullptr, true);
+    build_discriminator_backward(t, G, t->g_out.p, 0, nullptr, true, B);
     // through tanh and the generator (src/ops/vect-tanh.cu:41: the gradient takes the tanh OUTPUT)
     G.push_back(n_binary(DCG_OP_TANH_GRAD, t->g_out.p, t->dg_out.p, t->dgz[3].p, (size_t)B * 64 * 64 * 3));
     const int gact_grad = t->cfg.g_leaky ? DCG_OP_LEAKY_RELU_GRAD : DCG_OP_RELU_GRAD;
@@ -422,6 +447,10 @@ extern "C" int dcg_trainer_create(dcg_trainer** out, const dcg_trainer_config* c
     dcg_trainer* t = new dcg_trainer();
     t->cfg = *cfg;
     t->stream = dcg::as_stream(stream);
+    {
+        const char* off = getenv("DCG_TRAINER_TWO_PASSES");   // experiments: keep the two passes on the tensor path too
+        t->batched_d = cfg->precision != DCG_PREC_FP32 && !(off && atoi(off) != 0);
+    }
     Alloc dry{t, true};
     layout(t, dry);
     t->arena_bytes = dcg::align_up(dry.off, 256) + 256;
@@ -477,7 +506,7 @@ extern "C" int dcg_trainer_d_backward(dcg_trainer* t)
     DCG_CHECK_ARG(t, "dcg_trainer_d_backward: null trainer");
     int st = run_list(t, t->d_nodes);
     if (st) return st;
-    if (t->cfg.world > 1) {
+    if (t->cfg.world > 1 && !t->batched_d) {
         // sum the two gradient paths now (the Add op of src/ops/graph.cu:302-309) so that one
         // all-reduce of the gradient arena averages the final gradients
         for (int i = 0; i < 10; ++i)
@@ -489,8 +518,8 @@ extern "C" int dcg_trainer_d_backward(dcg_trainer* t)
 extern "C" int dcg_trainer_d_apply(dcg_trainer* t, float grad_scale)
 {
     DCG_CHECK_ARG(t, "dcg_trainer_d_apply: null trainer");
-    return apply_adam(t, t->d_param, t->d_grad, t->cfg.world > 1 ? nullptr : t->d_grad2, t->d_m, t->d_v, &t->d_t,
-                      grad_scale);
+    return apply_adam(t, t->d_param, t->d_grad, (t->cfg.world > 1 || t->batched_d) ? nullptr : t->d_grad2, t->d_m,
+                      t->d_v, &t->d_t, grad_scale);
 }
 
 extern "C" int dcg_trainer_g_backward(dcg_trainer* t)

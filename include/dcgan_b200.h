@@ -354,7 +354,12 @@ void dcg_trainer_destroy(dcg_trainer* t);
  * fills), "g_out", "d_loss", "g_loss", "logits_fake", "logits_real", the contiguous per-network
  * arenas "d_params", "g_params", "d_grads", "g_grads", and single variables "d_param0".."d_param9",
  * "g_param0".., "d_grad0".., "d_gradb0".. (second path), "g_grad0".., "d_m0", "d_v0", "g_m0", "g_v0"..
- * Variable order: (kernel, bias) of conv layers 0..3, then dense weight, dense bias. */
+ * Variable order: (kernel, bias) of conv layers 0..3, then dense weight, dense bias.
+ * With DCG_PREC_FP32 the D run is the reference's two discriminator passes: "d_grad*" holds the
+ * gradients of the fake pass, "d_gradb*" those of the real pass, and Adam adds them
+ * (src/ops/graph.cu:302-309).  On the tensor path the two passes run as ONE pass over the batch
+ * [g_out | x] of 2*batch images (same math per image, half the launches): "d_grad*" then holds
+ * the sum of both paths and "d_gradb*" stays zero. */
 int dcg_trainer_tensor(dcg_trainer* t, const char* name, float** ptr, size_t* count);
 /* Generator forward only (z -> g_out): dcgan/main.cu:252-269. */
 int dcg_trainer_generate(dcg_trainer* t);

@@ -57,8 +57,13 @@ def test_gradients_match_cpu_model(pkg, dev, orc, prec_name, tol, fuse):
     assert pkg.lib.dcg_device_status() == 0
     assert abs(tr.d_loss.item() - float(d_loss)) <= loss_tol * abs(float(d_loss)) + 1e-6
     for i in range(10):
-        assert err(tr.tensor("d_grad%d" % i).cpu().numpy(), gf[i].reshape(-1)) <= tol, ("fake", i)
-        assert err(tr.tensor("d_gradb%d" % i).cpu().numpy(), gr[i].reshape(-1)) <= tol, ("real", i)
+        got_f, got_r = tr.tensor("d_grad%d" % i).cpu().numpy(), tr.tensor("d_gradb%d" % i).cpu().numpy()
+        if prec_name == "fp32":   # the reference's two passes, one gradient set each
+            assert err(got_f, gf[i].reshape(-1)) <= tol, ("fake", i)
+            assert err(got_r, gr[i].reshape(-1)) <= tol, ("real", i)
+        else:   # tensor path: one pass over [fake | real]; d_grad holds the sum, d_gradb stays zero
+            assert not got_r.any()
+            assert err(got_f, (gf[i] + gr[i]).reshape(-1)) <= tol, ("fake + real", i)
 
     g_loss, gg = M.run(M.g_gradients(orc, st, z))
     pkg._lib.check(pkg.lib.dcg_trainer_g_backward(tr._h))
