@@ -23,6 +23,9 @@ SHAPES = [
     (2, 8, 8, 4, 5, 8, 2), (2, 16, 16, 32, 5, 64, 2), (2, 12, 20, 36, 5, 40, 2),
     (2, 64, 64, 3, 5, 64, 2), (2, 32, 32, 64, 5, 128, 2), (2, 16, 16, 128, 5, 256, 2),
     (2, 8, 8, 256, 5, 512, 2),
+    # narrow-channel paths (<= 4 input channels, O a multiple of 32): window-map forward, one-tile
+    # kernel gradient over pixel partitions, GEMM + gather input gradient; stride 1, even kernel
+    (3, 20, 12, 1, 3, 32, 1), (2, 16, 16, 4, 5, 96, 2), (5, 32, 32, 2, 4, 64, 2), (2, 10, 14, 3, 5, 160, 2),
 ]
 
 
@@ -80,7 +83,7 @@ def test_golden_reference_cases(pkg, dev, golden, prec_name):
 
 
 @pytest.mark.parametrize("prec_name", ["fp32", "tf32"])
-@pytest.mark.parametrize("shape", [(2, 9, 9, 5, 5, 6, 2), (2, 16, 16, 32, 5, 64, 2)])
+@pytest.mark.parametrize("shape", [(2, 9, 9, 5, 5, 6, 2), (2, 16, 16, 32, 5, 64, 2), (2, 16, 16, 3, 5, 64, 2)])
 def test_fused_epilogues(pkg, dev, orc, shape, prec_name):
     F = pkg.functional
     prec = pkg.PREC_FP32 if prec_name == "fp32" else pkg.PREC_TF32
@@ -172,6 +175,29 @@ def test_full_batch_layers_tf32_vs_fp32_path(pkg, dev, layer):
     tol = 5e-3 * terms.pow(2).sum().sqrt().item() + 1e-3
     assert abs(lhs - (dx * x.double()).sum().item()) <= tol
     assert abs(lhs - (dk * k.double()).sum().item()) <= tol
+
+
+@pytest.mark.parametrize("batch", [20, 28, 40, 56, 100])
+def test_k_partition_counts(pkg, dev, batch):
+    """The number of K partitions of a tile (= thread-block cluster size) follows the tile count:
+    these batches give clusters of 8, 8/7, 7/5, 5/4 and 2/3 CTAs on a 148-SM part for the
+    128 -> 256 channel layer, odd sizes included.  Each must agree with the fp32 path and with itself."""
+    F = pkg.functional
+    g = torch.Generator(device="cpu").manual_seed(11)
+    x = (torch.rand((batch, 16, 16, 128), generator=g) * 2 - 1).to(dev)
+    k = (torch.randn((5, 5, 128, 256), generator=g) * 0.02).to(dev)
+    dy = (torch.rand((batch, 8, 8, 256), generator=g) * 2 - 1).to(dev)
+    bias = torch.randn((256,), generator=g).to(dev)
+    ref = (F.conv2d_fwd(x, k, precision=pkg.PREC_FP32) + bias, F.conv2d_dx(dy, k, (16, 16), precision=pkg.PREC_FP32),
+           F.conv2d_dk(x, dy, (5, 5), precision=pkg.PREC_FP32))
+    run = lambda: (F.conv2d_fwd(x, k, epilogue=F.make_epilogue(bias=bias)), F.conv2d_dx(dy, k, (16, 16)),
+                   F.conv2d_dk(x, dy, (5, 5)))
+    a, b = run(), run()
+    torch.cuda.synchronize()
+    assert pkg.lib.dcg_device_status() == 0
+    for name, r, u, v in zip(("fwd+bias", "dx", "dk"), ref, a, b):
+        assert (r - u).abs().max().item() <= TF32_TOL * r.abs().max().item(), name
+        assert torch.equal(u, v), name
 
 
 def test_deterministic(pkg, dev):
