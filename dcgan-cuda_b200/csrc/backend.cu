@@ -37,6 +37,9 @@ struct dcg_context {
 
 namespace dcg {
 
+bool context_is_profiling(const dcg_context* ctx) { return ctx && ctx->profiling; }
+const void* context_workspace(const dcg_context* ctx) { return ctx ? ctx->ws : nullptr; }
+
 // Times everything enqueued on the context's stream during its lifetime when profiling is on.
 ProfScope::ProfScope(dcg_context* c, const char* name, double flops) : ctx(c), active(c && c->profiling)
 {

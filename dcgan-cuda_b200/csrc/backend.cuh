@@ -17,3 +17,10 @@ struct ProfScope {
 };
 
 }  // namespace dcg
+
+namespace dcg {
+// For the trainer: whether the context is in profiling mode, and the address of its scratch
+// buffer (captured CUDA graphs bake it in).
+bool context_is_profiling(const dcg_context* ctx);
+const void* context_workspace(const dcg_context* ctx);
+}  // namespace dcg

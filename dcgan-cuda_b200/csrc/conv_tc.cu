@@ -996,7 +996,18 @@ int env_int(const char* name)
     return v ? atoi(v) : 0;
 }
 
-int choose_splits(int tiles, int min_stages_per_tile)
+// Accumulator width for a layer with n_ch output columns.  256-column tiles (DCG_TC_WIDE=1) halve
+// how often an A tile is fetched from L2 but need the whole shared memory of an SM: one CTA per SM,
+// nothing to overlap its set-up and epilogue with.  Measured slower at batch 64 (the 256 -> 512
+// forward layer 38 us against 23 us), so they are off unless asked for.
+int tile_width(int n_ch)
+{
+    static const int wide = [] { const char* v = getenv("DCG_TC_WIDE"); return v ? atoi(v) : 0; }();
+    if (wide && n_ch >= 256) return 256;
+    return n_ch >= 128 ? 128 : n_ch;
+}
+
+int choose_splits(int tiles, int min_stages_per_tile, int ctas_per_sm = 2)
 {
     static const int forced = env_int("DCG_TC_SPLITS");
     if (forced > 0) {
@@ -1005,7 +1016,7 @@ int choose_splits(int tiles, int min_stages_per_tile)
     }
     const int sms = sm_count();
     if (tiles >= sms) return 1;
-    int s = (2 * sms) / tiles;                       // aim at ~2 CTAs per SM
+    int s = (ctas_per_sm * sms) / tiles;             // aim at ~2 CTAs per SM (1 for 256-column tiles)
     const int cap = min_stages_per_tile / 4;         // keep at least 4 K stages per CTA
     if (s > cap) s = cap;
     if (s > kMaxCluster) s = kMaxCluster;
@@ -1018,7 +1029,7 @@ void finish_plan(Plan& pl)
     const int b_stage = p.bn * BK * 4;
     const int per_stage = A_STAGE_BYTES + b_stage;
     // two CTAs per SM when the grid has more CTAs than SMs, else one deep pipeline
-    const int budget = (pl.grid > sm_count()) ? (kMaxSmem / 2 - 2048) : (kMaxSmem - 2048);
+    const int budget = (pl.grid > sm_count() && p.bn <= 128) ? (kMaxSmem / 2 - 2048) : (kMaxSmem - 2048);
     int stages = budget / per_stage;
     if (stages > 8) stages = 8;
     static const int forced_stages = env_int("DCG_TC_STAGES");
@@ -1069,7 +1080,7 @@ bool plan_fwd(const dcg_conv_desc& d, Plan& pl)
     pixel_tile(BM, d.wo, d.ho, p.TW, p.TH, p.TN);
     if (p.TW * d.stride_w > 256 || p.TH * d.stride_h > 256) return false;
     p.tiles_w = (d.wo + p.TW - 1) / p.TW; p.tiles_h = (d.ho + p.TH - 1) / p.TH; p.tiles_n = (d.n + p.TN - 1) / p.TN;
-    p.bn = d.o >= 128 ? 128 : d.o;
+    p.bn = narrow ? (d.o >= 128 ? 128 : d.o) : tile_width(d.o);
     p.n_tiles = (d.o + p.bn - 1) / p.bn;
     p.kchunks = (d.c + BK - 1) / BK;
     const int tiles = p.tiles_w * p.tiles_h * p.tiles_n * p.n_tiles;
@@ -1079,7 +1090,7 @@ bool plan_fwd(const dcg_conv_desc& d, Plan& pl)
         narrow_geometry(d, pl);
         pl.k4_bytes = (size_t)d.kh * 32 * d.o * sizeof(float);
     }
-    p.splits = choose_splits(tiles, narrow ? d.kh : d.kh * d.kw * p.kchunks);
+    p.splits = choose_splits(tiles, narrow ? d.kh : d.kh * d.kw * p.kchunks, p.bn > 128 ? 1 : 2);
     pl.grid = tiles * p.splits;
     finish_plan(pl);
     return true;
@@ -1118,14 +1129,14 @@ bool plan_dx(const dcg_conv_desc& d, Plan& pl)
     pixel_tile(BM, wa, ha, p.TW, p.TH, p.TN);
     p.tiles_w = (wa + p.TW - 1) / p.TW; p.tiles_h = (ha + p.TH - 1) / p.TH; p.tiles_n = (d.n + p.TN - 1) / p.TN;
     int bn = (d.c + 15) / 16 * 16;
-    if (bn > 128) bn = 128;
+    if (bn > 128) bn = tile_width(bn);
     p.bn = bn;
     p.n_tiles = (d.c + p.bn - 1) / p.bn;
     p.kchunks = (d.o + BK - 1) / BK;
     const int classes = d.stride_h * d.stride_w;
     const int tiles = classes * p.tiles_w * p.tiles_h * p.tiles_n * p.n_tiles;
     const int min_taps = (d.kh / d.stride_h) * (d.kw / d.stride_w);
-    p.splits = choose_splits(tiles, (min_taps < 1 ? 1 : min_taps) * p.kchunks);
+    p.splits = choose_splits(tiles, (min_taps < 1 ? 1 : min_taps) * p.kchunks, p.bn > 128 ? 1 : 2);
     pl.grid = tiles * p.splits;
     finish_plan(pl);
     return true;
@@ -1166,10 +1177,10 @@ bool plan_dk(const dcg_conv_desc& d, Plan& pl)
     p.swap = (d.c < BM && d.o > d.c) ? 1 : 0;
     const int m_ch = p.swap ? d.o : d.c, n_ch = p.swap ? d.c : d.o;
     p.m_tiles = (m_ch + BM - 1) / BM;
-    p.bn = n_ch >= 128 ? 128 : n_ch;
+    p.bn = tile_width(n_ch);
     p.n_tiles = (n_ch + p.bn - 1) / p.bn;
     const int tiles = d.kh * d.kw * p.m_tiles * p.n_tiles;
-    p.splits = choose_splits(tiles, p.tiles_w * p.tiles_h * p.tiles_n);
+    p.splits = choose_splits(tiles, p.tiles_w * p.tiles_h * p.tiles_n, p.bn > 128 ? 1 : 2);
     pl.grid = tiles * p.splits;
     finish_plan(pl);
     return true;

@@ -123,7 +123,7 @@ gemm_long_k_kernel(const float* __restrict__ a, const float* __restrict__ b,
 // RB rows: the RB x n slab of A sits in shared memory, every thread walks one column of B
 // (coalesced across the block) and keeps RB accumulators.  k ascends, multiply and add stay
 // unfused: the same rounding sequence as the reference loops (src/cpu/ops.hxx:56-105).
-constexpr int RB = 16;
+constexpr int RB = 8;
 template <bool TA>
 __global__ void __launch_bounds__(128)
 gemm_wide_kernel(const float* __restrict__ a, const float* __restrict__ b,

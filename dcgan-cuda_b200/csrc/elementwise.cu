@@ -129,8 +129,62 @@ update_kernel(const float* __restrict__ dv, float* __restrict__ out,
 // lane l adds slabs l, l+L, ... and the lane sums are added in lane order, so the result depends
 // on the launch shape only, never on which block came last.  `tickets` == nullptr leaves the
 // slabs to colsum_final_kernel.
-constexpr int kTicketSets = 64, kTicketTiles = 64;
-__device__ unsigned g_colsum_tickets[kTicketSets][kTicketTiles];   // zero at load, reset by the last block
+constexpr int kTicketSets = 64, kTicketTiles = 16, kSlabGroup = 16, kMaxSlabs = 1008;
+constexpr int kTicketsPerTile = 1 + kMaxSlabs / kSlabGroup;         // group-level ticket + one per slab group
+__device__ unsigned g_colsum_tickets[kTicketSets][kTicketTiles * kTicketsPerTile];   // zero at load, reset by the adders
+
+// One block adds `nrows` rows of src ([nrows][cols]) for its column tile into dst: thread = (column
+// group, lane); lane l adds rows l, l+L, ... through four independent accumulators (four loads in
+// flight), combined in a fixed order; the lane sums are then added in lane order.  The result
+// depends on the launch shape only.
+template <bool VEC>
+__device__ __forceinline__ void colsum_add_rows(const float* __restrict__ src, unsigned nrows, float* __restrict__ dst,
+                                                unsigned cols, int tx_count, unsigned groups, float* smem)
+{
+    constexpr int W = VEC ? 4 : 1;
+    const int lanes = blockDim.x / tx_count;     // >= 8
+    const int g = threadIdx.x % tx_count, l = threadIdx.x / tx_count;
+    const unsigned grp = blockIdx.x * tx_count + g;
+    float4 t[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) t[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (grp < groups) {
+        unsigned k = l;
+        for (; k + 3 * lanes < nrows; k += 4 * lanes) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float* p = src + (size_t)(k + u * lanes) * cols + (size_t)grp * W;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (VEC) v = __ldcg(reinterpret_cast<const float4*>(p));
+                else v.x = __ldcg(p);
+                t[u].x += v.x; t[u].y += v.y; t[u].z += v.z; t[u].w += v.w;
+            }
+        }
+        for (int u = 0; k < nrows; k += lanes, ++u) {   // at most three rows left per lane
+            const float* p = src + (size_t)k * cols + (size_t)grp * W;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (VEC) v = __ldcg(reinterpret_cast<const float4*>(p));
+            else v.x = __ldcg(p);
+            t[u & 3].x += v.x; t[u & 3].y += v.y; t[u & 3].z += v.z; t[u & 3].w += v.w;
+        }
+    }
+    float4 s4;
+    s4.x = (t[0].x + t[1].x) + (t[2].x + t[3].x); s4.y = (t[0].y + t[1].y) + (t[2].y + t[3].y);
+    s4.z = (t[0].z + t[1].z) + (t[2].z + t[3].z); s4.w = (t[0].w + t[1].w) + (t[2].w + t[3].w);
+    __syncthreads();                             // smem is reused: [lane][group][W]
+    float* slot = smem + ((size_t)l * tx_count + g) * W;
+    slot[0] = s4.x;
+    if (VEC) { slot[1] = s4.y; slot[2] = s4.z; slot[3] = s4.w; }
+    __syncthreads();
+    if (l == 0 && grp < groups) {
+#pragma unroll
+        for (int q = 0; q < W; ++q) {
+            float r = smem[(size_t)g * W + q];
+            for (int j = 1; j < lanes; ++j) r += smem[((size_t)j * tx_count + g) * W + q];
+            dst[(size_t)grp * W + q] = r;
+        }
+    }
+}
 
 template <bool VEC>
 __global__ void __launch_bounds__(kThreads)
@@ -151,7 +205,20 @@ colsum_partial_kernel(const float* __restrict__ a, float* __restrict__ partial,
 
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (group < groups) {
-        for (size_t r = r0 + ty; r < r1; r += ty_count) {
+        size_t r = r0 + ty;
+        if (VEC) {   // four rows in flight per thread
+            for (; r + 3 * (size_t)ty_count < r1; r += 4 * (size_t)ty_count) {
+                const float4 v0 = __ldg(reinterpret_cast<const float4*>(a + r * cols) + group);
+                const float4 v1 = __ldg(reinterpret_cast<const float4*>(a + (r + ty_count) * cols) + group);
+                const float4 v2 = __ldg(reinterpret_cast<const float4*>(a + (r + 2 * (size_t)ty_count) * cols) + group);
+                const float4 v3 = __ldg(reinterpret_cast<const float4*>(a + (r + 3 * (size_t)ty_count) * cols) + group);
+                acc.x += v0.x; acc.y += v0.y; acc.z += v0.z; acc.w += v0.w;
+                acc.x += v1.x; acc.y += v1.y; acc.z += v1.z; acc.w += v1.w;
+                acc.x += v2.x; acc.y += v2.y; acc.z += v2.z; acc.w += v2.w;
+                acc.x += v3.x; acc.y += v3.y; acc.z += v3.z; acc.w += v3.w;
+            }
+        }
+        for (; r < r1; r += ty_count) {
             if (VEC) {
                 const float4 v = __ldg(reinterpret_cast<const float4*>(a + r * cols) + group);
                 acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
@@ -179,62 +246,40 @@ colsum_partial_kernel(const float* __restrict__ a, float* __restrict__ partial,
         for (int q = 0; q < W; ++q) dst[q] = mine[q];
     }
     if (tickets == nullptr) return;
-    // ---- the last block of this column tile adds the slabs ----
+    // ---- two levels of "whoever finishes last adds": 16 slabs -> one group row, all group rows -> out ----
+    // tickets of this column tile: [0] the group level, [1 + g] slab group g.  Each adder resets its
+    // ticket, so a set is ready for the next launch that uses it.
+    unsigned* my_tickets = tickets + (size_t)blockIdx.x * kTicketsPerTile;
+    const unsigned slabs = gridDim.y, n_groups = (slabs + kSlabGroup - 1) / kSlabGroup;
+    const unsigned g_idx = blockIdx.y / kSlabGroup;
+    const unsigned g_first = g_idx * kSlabGroup;
+    const unsigned g_count = slabs - g_first < (unsigned)kSlabGroup ? slabs - g_first : (unsigned)kSlabGroup;
+    float* level2 = partial + (size_t)slabs * cols;      // [n_groups][cols], behind the slab rows
     __shared__ unsigned s_last;
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-        const unsigned t = atomicAdd(tickets + blockIdx.x, 1u);
-        s_last = (t == gridDim.y - 1) ? 1u : 0u;
-        if (s_last) tickets[blockIdx.x] = 0u;   // ready for the next launch that uses this set
+        const unsigned t = atomicAdd(my_tickets + 1 + g_idx, 1u);
+        s_last = (t == g_count - 1) ? 1u : 0u;
+        if (s_last) my_tickets[1 + g_idx] = 0u;
     }
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // thread = (column group, slab lane): lane l adds slabs l, l+L, ... through four independent
-    // accumulators (four loads in flight), combined in a fixed order
-    const int lanes = blockDim.x / tx_count;     // >= 8
-    const int g = threadIdx.x % tx_count, l = threadIdx.x / tx_count;
-    const unsigned grp = blockIdx.x * tx_count + g;
-    float4 t[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) t[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (grp < groups) {
-        unsigned k = l;
-        for (; k + 3 * lanes < gridDim.y; k += 4 * lanes) {
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float* src = partial + (size_t)(k + u * lanes) * cols + (size_t)grp * W;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (VEC) v = __ldcg(reinterpret_cast<const float4*>(src));
-                else v.x = __ldcg(src);
-                t[u].x += v.x; t[u].y += v.y; t[u].z += v.z; t[u].w += v.w;
-            }
-        }
-        for (; k < gridDim.y; k += lanes) {
-            const float* src = partial + (size_t)k * cols + (size_t)grp * W;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (VEC) v = __ldcg(reinterpret_cast<const float4*>(src));
-            else v.x = __ldcg(src);
-            t[0].x += v.x; t[0].y += v.y; t[0].z += v.z; t[0].w += v.w;
-        }
-    }
-    float4 s4;
-    s4.x = (t[0].x + t[1].x) + (t[2].x + t[3].x); s4.y = (t[0].y + t[1].y) + (t[2].y + t[3].y);
-    s4.z = (t[0].z + t[1].z) + (t[2].z + t[3].z); s4.w = (t[0].w + t[1].w) + (t[2].w + t[3].w);
-    __syncthreads();                             // smem is reused: [lane][group][W]
-    float* slot = smem + ((size_t)l * tx_count + g) * W;
-    slot[0] = s4.x;
-    if (VEC) { slot[1] = s4.y; slot[2] = s4.z; slot[3] = s4.w; }
+    colsum_add_rows<VEC>(partial + (size_t)g_first * cols, g_count, n_groups > 1 ? level2 + (size_t)g_idx * cols : out,
+                         cols, tx_count, groups, smem);
+    if (n_groups == 1) return;
+    __threadfence();
     __syncthreads();
-    if (l == 0 && grp < groups) {
-#pragma unroll
-        for (int q = 0; q < W; ++q) {
-            float r = smem[(size_t)g * W + q];
-            for (int j = 1; j < lanes; ++j) r += smem[((size_t)j * tx_count + g) * W + q];
-            out[(size_t)grp * W + q] = r;
-        }
+    if (threadIdx.x == 0) {
+        const unsigned t = atomicAdd(my_tickets, 1u);
+        s_last = (t == n_groups - 1) ? 1u : 0u;
+        if (s_last) my_tickets[0] = 0u;
     }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    colsum_add_rows<VEC>(level2, n_groups, out, cols, tx_count, groups, smem);
 }
 
 // Stage 2: block = 32 columns x 8 slab lanes.  Lane ty adds slabs ty, ty+8, ... (four loads in
@@ -522,8 +567,9 @@ ColsumPlan colsum_plan(size_t rows, size_t cols, bool ptr_aligned)
     p.tx_count = tx;
     p.grid_x = (p.groups + tx - 1) / tx;
     const int ty = kThreads / tx;
-    // enough slabs to fill the machine a few times over, each at least 4 row passes deep
+    // enough blocks to fill the machine a few times over, each at least 4 row passes deep
     size_t want = ((size_t)sm_count() * 4 + p.grid_x - 1) / p.grid_x;
+    if (want > (size_t)kMaxSlabs) want = kMaxSlabs;
     size_t max_slabs = (rows + (size_t)ty * 4 - 1) / ((size_t)ty * 4);
     if (max_slabs < 1) max_slabs = 1;
     if (want > max_slabs) want = max_slabs;
@@ -542,7 +588,8 @@ extern "C" size_t dcg_colsum_workspace_bytes(size_t rows, size_t cols)
     const ColsumPlan a = colsum_plan(rows, cols, true), b = colsum_plan(rows, cols, false);
     const unsigned slabs = a.slabs > b.slabs ? a.slabs : b.slabs;
     if (slabs <= 1) return 0;   // a single slab writes the result directly
-    return (size_t)slabs * cols * sizeof(float);
+    // slab rows plus one row per group of kSlabGroup slabs (the second level of the in-kernel sum)
+    return (size_t)(slabs + (slabs + kSlabGroup - 1) / kSlabGroup) * cols * sizeof(float);
 }
 
 extern "C" int dcg_colsum(const float* a, float* out, size_t rows, size_t cols, void* workspace,
@@ -551,7 +598,7 @@ extern "C" int dcg_colsum(const float* a, float* out, size_t rows, size_t cols, 
     DCG_CHECK_ARG(a && out, "dcg_colsum: null pointer");
     DCG_CHECK_ARG(cols > 0 && cols <= 0x7fffffffu && rows > 0, "dcg_colsum: bad shape %zu x %zu", rows, cols);
     const ColsumPlan p = colsum_plan(rows, cols, aligned16(a));
-    const size_t need = (size_t)p.slabs * cols * sizeof(float);
+    const size_t need = (size_t)(p.slabs + (p.slabs + kSlabGroup - 1) / kSlabGroup) * cols * sizeof(float);
     float* partial;
     if (p.slabs == 1) {
         partial = out;  // a single slab writes the result directly
@@ -567,9 +614,18 @@ extern "C" int dcg_colsum(const float* a, float* out, size_t rows, size_t cols, 
     unsigned* tickets = nullptr;
     if (p.slabs > 1 && p.grid_x <= (unsigned)kTicketTiles) {
         static std::atomic<unsigned> seq{0};
-        void* base = nullptr;
-        DCG_CUDA(cudaGetSymbolAddress(&base, g_colsum_tickets));
-        tickets = static_cast<unsigned*>(base) + (size_t)(seq.fetch_add(1) % kTicketSets) * kTicketTiles;
+        static void* base_of_device[64];   // per device ordinal; looked up once (not while a stream is capturing)
+        int dev = 0;
+        DCG_CUDA(cudaGetDevice(&dev));
+        DCG_CHECK_ARG(dev >= 0 && dev < 64, "dcg_colsum: device ordinal %d out of range", dev);
+        if (!base_of_device[dev]) {
+            void* b = nullptr;
+            DCG_CUDA(cudaGetSymbolAddress(&b, g_colsum_tickets));
+            base_of_device[dev] = b;
+        }
+        void* base = base_of_device[dev];
+        tickets = static_cast<unsigned*>(base) +
+                  (size_t)(seq.fetch_add(1) % kTicketSets) * kTicketTiles * kTicketsPerTile;
     }
     if (p.vec)
         launch_pdl(colsum_partial_kernel<true>, grid, kThreads, smem, as_stream(stream), 

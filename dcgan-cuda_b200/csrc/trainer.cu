@@ -10,6 +10,7 @@
 // at creation; parameters and gradients of each network are contiguous so a data-parallel caller
 // can average a network's gradients with a single all-reduce between *_backward and *_apply.
 #include <cmath>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <string>
@@ -85,6 +86,20 @@ struct dcg_trainer {
 
     std::vector<dcg_node> d_nodes, g_nodes, gen_nodes;
     uint64_t last_step_launches = 0;
+
+    // A node list is launched eagerly twice (scratch grows to its final size, one-time attributes
+    // get set), then captured from the stream into a CUDA graph and replayed: the list, its operand
+    // addresses and its launch shapes never change, and a replay costs the host one call and the
+    // GPU less inter-kernel latency than ~100 dependent launches.
+    struct ListGraph {
+        cudaGraphExec_t exec = nullptr;
+        int eager_runs = 0;
+        uint64_t launches = 0;     // kernels in the graph (the library's launch counter advances by this per replay)
+        const void* ws = nullptr;  // scratch address baked into the captured launches
+        bool failed = false;
+    };
+    ListGraph d_graph, g_graph, gen_graph;
+    bool use_graphs = true;
 };
 
 namespace {
@@ -420,9 +435,50 @@ void build_lists(dcg_trainer* t)
     G.push_back(n_rows_cols(DCG_OP_MAT_SUM_COLS, t->dg0z.p, nullptr, t->g_grad[9].p, B, 8192));
 }
 
-int run_list(dcg_trainer* t, const std::vector<dcg_node>& L)
+int run_list(dcg_trainer* t, const std::vector<dcg_node>& L, dcg_trainer::ListGraph& g)
 {
-    return dcg_run_nodes(t->ctx, L.data(), (int)L.size(), t->cfg.fuse);
+    const bool eager = !t->use_graphs || g.failed || dcg::context_is_profiling(t->ctx);
+    if (eager || g.eager_runs < 2) {
+        if (!eager) ++g.eager_runs;
+        return dcg_run_nodes(t->ctx, L.data(), (int)L.size(), t->cfg.fuse);
+    }
+    if (g.exec && g.ws != dcg::context_workspace(t->ctx)) {   // scratch moved: the captured addresses are stale
+        cudaGraphExecDestroy(g.exec);
+        g.exec = nullptr;
+    }
+    if (!g.exec) {
+        const uint64_t before = dcg_launches_total();
+        cudaGraph_t graph = nullptr;
+        if (cudaStreamBeginCapture(t->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+            if (getenv("DCG_TRAINER_VERBOSE"))
+                fprintf(stderr, "dcg_trainer: cudaStreamBeginCapture failed: %s\n", cudaGetErrorString(cudaGetLastError()));
+            cudaGetLastError();
+            g.failed = true;
+            return dcg_run_nodes(t->ctx, L.data(), (int)L.size(), t->cfg.fuse);
+        }
+        const int st = dcg_run_nodes(t->ctx, L.data(), (int)L.size(), t->cfg.fuse);
+        const cudaError_t ce = cudaStreamEndCapture(t->stream, &graph);
+        cudaError_t ie = cudaSuccess;
+        if (st != DCG_OK || ce != cudaSuccess || !graph ||
+            (ie = cudaGraphInstantiate(&g.exec, graph, 0)) != cudaSuccess) {
+            if (getenv("DCG_TRAINER_VERBOSE"))
+                fprintf(stderr, "dcg_trainer: graph capture failed (list status %d, end capture: %s, instantiate: %s); "
+                                "staying eager\n", st, cudaGetErrorString(ce), cudaGetErrorString(ie));
+            cudaGetLastError();
+            if (graph) cudaGraphDestroy(graph);
+            g.exec = nullptr;
+            g.failed = true;   // stay eager from here on
+            return dcg_run_nodes(t->ctx, L.data(), (int)L.size(), t->cfg.fuse);
+        }
+        cudaGraphDestroy(graph);
+        g.launches = dcg_launches_total() - before;
+        g.ws = dcg::context_workspace(t->ctx);
+        dcg::count_launch(-(int)g.launches);   // the capture launched nothing; the replay below counts
+    }
+    if (cudaGraphLaunch(g.exec, t->stream) != cudaSuccess)
+        return fail(DCG_ERR_CUDA, "cudaGraphLaunch: %s", cudaGetErrorString(cudaGetLastError()));
+    dcg::count_launch((int)g.launches);
+    return DCG_OK;
 }
 
 int apply_adam(dcg_trainer* t, Tensor* param, Tensor* grad, Tensor* grad2, Tensor* m, Tensor* v, float* step,
@@ -450,6 +506,8 @@ extern "C" int dcg_trainer_create(dcg_trainer** out, const dcg_trainer_config* c
     {
         const char* off = getenv("DCG_TRAINER_TWO_PASSES");   // experiments: keep the two passes on the tensor path too
         t->batched_d = cfg->precision != DCG_PREC_FP32 && !(off && atoi(off) != 0);
+        const char* eager = getenv("DCG_TRAINER_EAGER");       // experiments: no CUDA graphs
+        t->use_graphs = !(eager && atoi(eager) != 0);
     }
     Alloc dry{t, true};
     layout(t, dry);
@@ -490,6 +548,8 @@ extern "C" int dcg_trainer_create(dcg_trainer** out, const dcg_trainer_config* c
 extern "C" void dcg_trainer_destroy(dcg_trainer* t)
 {
     if (!t) return;
+    for (dcg_trainer::ListGraph* g : {&t->d_graph, &t->g_graph, &t->gen_graph})
+        if (g->exec) cudaGraphExecDestroy(g->exec);
     if (t->ctx) dcg_context_destroy(t->ctx);
     if (t->arena) cudaFree(t->arena);
     delete t;
@@ -498,13 +558,13 @@ extern "C" void dcg_trainer_destroy(dcg_trainer* t)
 extern "C" int dcg_trainer_generate(dcg_trainer* t)
 {
     DCG_CHECK_ARG(t, "dcg_trainer_generate: null trainer");
-    return run_list(t, t->gen_nodes);
+    return run_list(t, t->gen_nodes, t->gen_graph);
 }
 
 extern "C" int dcg_trainer_d_backward(dcg_trainer* t)
 {
     DCG_CHECK_ARG(t, "dcg_trainer_d_backward: null trainer");
-    int st = run_list(t, t->d_nodes);
+    int st = run_list(t, t->d_nodes, t->d_graph);
     if (st) return st;
     if (t->cfg.world > 1 && !t->batched_d) {
         // sum the two gradient paths now (the Add op of src/ops/graph.cu:302-309) so that one
@@ -525,7 +585,7 @@ extern "C" int dcg_trainer_d_apply(dcg_trainer* t, float grad_scale)
 extern "C" int dcg_trainer_g_backward(dcg_trainer* t)
 {
     DCG_CHECK_ARG(t, "dcg_trainer_g_backward: null trainer");
-    return run_list(t, t->g_nodes);
+    return run_list(t, t->g_nodes, t->g_graph);
 }
 
 extern "C" int dcg_trainer_g_apply(dcg_trainer* t, float grad_scale)

@@ -13,6 +13,7 @@ one training iteration.  This wrapper adds what lives above the C ABI:
   Adam divides by the world size.  Replicas start from the same seed and apply
   identical updates, so parameters stay identical on every rank.
 """
+import contextlib
 import ctypes
 
 import torch
@@ -38,7 +39,12 @@ class Trainer:
         self.cfg = TrainerConfig(batch, world, precision, 1 if fuse else 0, 1 if g_leaky else 0, lr, beta1,
                                  beta2, eps, seed)
         self._h = ctypes.c_void_p()
-        self.stream = torch.cuda.current_stream(self.device)
+        # The trainer replays its node lists as CUDA graphs, which cannot be captured on the legacy
+        # default stream: when that is the caller's current stream the trainer works on a stream of its
+        # own and every method orders itself against the caller's stream on entry and exit.
+        caller = torch.cuda.current_stream(self.device)
+        self._own_stream = caller.cuda_stream == 0
+        self.stream = torch.cuda.Stream(self.device) if self._own_stream else caller
         check(lib.dcg_trainer_create(ctypes.byref(self._h), ctypes.byref(self.cfg), self.stream.cuda_stream))
         self._views = {}
         self.x = self.tensor("x").view(batch, 64, 64, 3)
@@ -64,16 +70,39 @@ class Trainer:
         return int(lib.dcg_trainer_arena_bytes(self._h))
 
     # ---- phases ----------------------------------------------------------------
+    @contextlib.contextmanager
+    def _on_stream(self):
+        """Runs the body on the trainer's stream, after what the caller's stream has enqueued so far;
+        the caller's stream then waits for the body."""
+        if not self._own_stream:
+            yield
+            return
+        caller = torch.cuda.current_stream(self.device)
+        self.stream.wait_stream(caller)
+        with torch.cuda.stream(self.stream):
+            yield
+        caller.wait_stream(self.stream)
+
     def generate(self):
-        check(lib.dcg_trainer_generate(self._h))
+        with self._on_stream():
+            check(lib.dcg_trainer_generate(self._h))
         return self.g_out
+
+    def d_backward(self):
+        """G forward, D on fake and real, d_loss, D gradients (no update)."""
+        with self._on_stream():
+            check(lib.dcg_trainer_d_backward(self._h))
+
+    def g_backward(self):
+        """G forward, D on fake, g_loss, G gradients (no update)."""
+        with self._on_stream():
+            check(lib.dcg_trainer_g_backward(self._h))
 
     def _allreduce(self, grads):
         if self.world > 1:
             torch.distributed.all_reduce(grads, group=self.group)
 
-    def step(self):
-        """One training iteration on inputs already resident in self.x / self.z."""
+    def _step(self):
         scale = 1.0 / self.world
         check(lib.dcg_trainer_d_backward(self._h))
         self._allreduce(self.d_grads)
@@ -83,16 +112,22 @@ class Trainer:
             self._allreduce(self.g_grads)
             check(lib.dcg_trainer_g_apply(self._h, scale))
 
+    def step(self):
+        """One training iteration on inputs already resident in self.x / self.z."""
+        with self._on_stream():
+            self._step()
+
     def step_host(self, x_host, z_host):
         """End-to-end iteration: x_host [B,64,64,3] and z_host [B,100] are HOST arrays (numpy or
         CPU torch); returns (d_loss, g_loss) as Python floats read back from the device."""
         self._hx.copy_(torch.as_tensor(x_host).reshape(self._hx.shape))
         self._hz.copy_(torch.as_tensor(z_host).reshape(self._hz.shape))
-        self.x.copy_(self._hx, non_blocking=True)
-        self.z.copy_(self._hz, non_blocking=True)
-        self.step()
-        self._hloss[0:1].copy_(self.d_loss, non_blocking=True)
-        self._hloss[1:2].copy_(self.g_loss, non_blocking=True)
+        with self._on_stream():
+            self.x.copy_(self._hx, non_blocking=True)
+            self.z.copy_(self._hz, non_blocking=True)
+            self._step()
+            self._hloss[0:1].copy_(self.d_loss, non_blocking=True)
+            self._hloss[1:2].copy_(self.g_loss, non_blocking=True)
         self.stream.synchronize()
         return float(self._hloss[0]), float(self._hloss[1])
 

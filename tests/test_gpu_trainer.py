@@ -52,7 +52,7 @@ def test_gradients_match_cpu_model(pkg, dev, orc, prec_name, tol, fuse):
     tr.z.copy_(torch.from_numpy(z))
 
     d_loss, gf, gr = M.run(M.d_gradients(orc, st, x, z))
-    pkg._lib.check(pkg.lib.dcg_trainer_d_backward(tr._h))
+    tr.d_backward()
     torch.cuda.synchronize()
     assert pkg.lib.dcg_device_status() == 0
     assert abs(tr.d_loss.item() - float(d_loss)) <= loss_tol * abs(float(d_loss)) + 1e-6
@@ -66,7 +66,7 @@ def test_gradients_match_cpu_model(pkg, dev, orc, prec_name, tol, fuse):
             assert err(got_f, (gf[i] + gr[i]).reshape(-1)) <= tol, ("fake + real", i)
 
     g_loss, gg = M.run(M.g_gradients(orc, st, z))
-    pkg._lib.check(pkg.lib.dcg_trainer_g_backward(tr._h))
+    tr.g_backward()
     torch.cuda.synchronize()
     assert pkg.lib.dcg_device_status() == 0
     assert abs(tr.g_loss.item() - float(g_loss)) <= loss_tol * abs(float(g_loss)) + 1e-6
@@ -136,3 +136,26 @@ def test_generate_matches_cpu_model(pkg, dev, orc):
         torch.cuda.synchronize()
         assert _maxrel(out.cpu().numpy(), ref) <= tol
         tr.close()
+
+
+def test_graph_replay_equals_eager(pkg, dev, monkeypatch):
+    """After two eager runs every node list is captured into a CUDA graph and replayed.  The replay
+    launches the same kernels with the same arguments in the same order, so five iterations with and
+    without graphs must leave bit-identical parameters and losses."""
+    B = 4
+    g = torch.Generator(device="cpu").manual_seed(21)
+    xs = [(torch.rand((B, 64, 64, 3), generator=g) * 2 - 1).numpy() for _ in range(5)]
+    zs = [(torch.rand((B, 100), generator=g) * 2 - 1).numpy() for _ in range(5)]
+    results = []
+    for eager in ("1", "0"):
+        monkeypatch.setenv("DCG_TRAINER_EAGER", eager)
+        tr = pkg.Trainer(batch=B, precision=pkg.PREC_TF32, fuse=True, seed=77)
+        losses = [tr.step_host(x, z) for x, z in zip(xs, zs)]
+        torch.cuda.synchronize()
+        assert pkg.lib.dcg_device_status() == 0
+        results.append((losses, tr.tensor("d_params").clone(), tr.tensor("g_params").clone()))
+        tr.close()
+    (l0, d0, g0), (l1, d1, g1) = results
+    assert l0 == l1
+    assert torch.equal(d0, d1) and torch.equal(g0, g1)
+
