@@ -37,8 +37,6 @@ static int check_precision(int precision, const char* who)
     DCG_CHECK_ARG(precision == DCG_PREC_TF32 || precision == DCG_PREC_3XTF32 ||
                       precision == DCG_PREC_FP32,
                   "%s: unknown precision %d", who, precision);
-    if (precision == DCG_PREC_3XTF32)
-        return fail(DCG_ERR_UNSUPPORTED, "%s: the 3xTF32 split path is not built yet", who);
     return DCG_OK;
 }
 
@@ -50,8 +48,9 @@ extern "C" size_t dcg_conv_workspace_bytes(const dcg_conv_desc* desc, int kind, 
 {
     if (!desc || precision == DCG_PREC_FP32) return 0;
     if (kind < kConvFwd || kind > kConvDk) return 0;
-    if (!conv_tc_supported(*desc, kind)) return 0;
-    return conv_tc_workspace(*desc, kind);
+    const bool x3 = precision == DCG_PREC_3XTF32;
+    if (!conv_tc_supported(*desc, kind, x3)) return 0;
+    return conv_tc_workspace(*desc, kind, x3);
 }
 
 extern "C" int dcg_conv2d_fwd(const dcg_conv_desc* desc, const float* x, const float* k, float* y,
@@ -63,9 +62,10 @@ extern "C" int dcg_conv2d_fwd(const dcg_conv_desc* desc, const float* x, const f
     if ((st = check_precision(precision, "dcg_conv2d_fwd"))) return st;
     DCG_CHECK_ARG(x && k && y, "dcg_conv2d_fwd: null tensor pointer");
     const EpilogueArgs e = make_epilogue(ep);
-    if (precision != DCG_PREC_FP32 && conv_tc_supported(*desc, kConvFwd) && aligned16(x) && aligned16(k) &&
+    const bool x3 = precision == DCG_PREC_3XTF32;
+    if (precision != DCG_PREC_FP32 && conv_tc_supported(*desc, kConvFwd, x3) && aligned16(x) && aligned16(k) &&
         aligned16(y) && epilogue_aligned(e))
-        return conv_tc_fwd(*desc, x, k, y, e, workspace, workspace_bytes, as_stream(stream));
+        return conv_tc_fwd(*desc, x, k, y, e, workspace, workspace_bytes, as_stream(stream), x3);
     return conv_fwd_generic(*desc, x, k, y, e, as_stream(stream));
 }
 
@@ -78,9 +78,10 @@ extern "C" int dcg_conv2d_dx(const dcg_conv_desc* desc, const float* dy, const f
     if ((st = check_precision(precision, "dcg_conv2d_dx"))) return st;
     DCG_CHECK_ARG(dy && k && dx, "dcg_conv2d_dx: null tensor pointer");
     const EpilogueArgs e = make_epilogue(ep);
-    if (precision != DCG_PREC_FP32 && conv_tc_supported(*desc, kConvDx) && aligned16(dy) && aligned16(k) &&
+    const bool x3 = precision == DCG_PREC_3XTF32;
+    if (precision != DCG_PREC_FP32 && conv_tc_supported(*desc, kConvDx, x3) && aligned16(dy) && aligned16(k) &&
         aligned16(dx) && epilogue_aligned(e))
-        return conv_tc_dx(*desc, dy, k, dx, e, workspace, workspace_bytes, as_stream(stream));
+        return conv_tc_dx(*desc, dy, k, dx, e, workspace, workspace_bytes, as_stream(stream), x3);
     return conv_dx_generic(*desc, dy, k, dx, e, as_stream(stream));
 }
 
@@ -92,8 +93,9 @@ extern "C" int dcg_conv2d_dk(const dcg_conv_desc* desc, const float* x, const fl
     if (st) return st;
     if ((st = check_precision(precision, "dcg_conv2d_dk"))) return st;
     DCG_CHECK_ARG(x && dy && dk, "dcg_conv2d_dk: null tensor pointer");
-    if (precision != DCG_PREC_FP32 && conv_tc_supported(*desc, kConvDk) && aligned16(x) && aligned16(dy) &&
+    const bool x3 = precision == DCG_PREC_3XTF32;
+    if (precision != DCG_PREC_FP32 && conv_tc_supported(*desc, kConvDk, x3) && aligned16(x) && aligned16(dy) &&
         aligned16(dk))
-        return conv_tc_dk(*desc, x, dy, dk, workspace, workspace_bytes, as_stream(stream));
+        return conv_tc_dk(*desc, x, dy, dk, workspace, workspace_bytes, as_stream(stream), x3);
     return conv_dk_generic(*desc, x, dy, dk, as_stream(stream));
 }

@@ -16,16 +16,17 @@ int conv_dx_generic(const dcg_conv_desc& d, const float* dy, const float* k, flo
 int conv_dk_generic(const dcg_conv_desc& d, const float* x, const float* dy, float* dk,
                     cudaStream_t stream);
 
-// tcgen05 TF32 implicit-GEMM kernels (conv_tc.cu).  *_supported tells whether the
+// tcgen05 TF32 implicit-GEMM kernels (conv_tc.cu); x3 selects the 3xTF32 variant (operand = TF32 part +
+// residual, three MMAs per K step).  *_supported tells whether the
 // tensor path takes the shape; *_workspace its scratch need in bytes.
-bool conv_tc_supported(const dcg_conv_desc& d, int kind);
-size_t conv_tc_workspace(const dcg_conv_desc& d, int kind);
+bool conv_tc_supported(const dcg_conv_desc& d, int kind, bool x3 = false);
+size_t conv_tc_workspace(const dcg_conv_desc& d, int kind, bool x3 = false);
 int conv_tc_fwd(const dcg_conv_desc& d, const float* x, const float* k, float* y,
-                const EpilogueArgs& ep, void* ws, size_t ws_bytes, cudaStream_t stream);
+                const EpilogueArgs& ep, void* ws, size_t ws_bytes, cudaStream_t stream, bool x3 = false);
 int conv_tc_dx(const dcg_conv_desc& d, const float* dy, const float* k, float* dx,
-               const EpilogueArgs& ep, void* ws, size_t ws_bytes, cudaStream_t stream);
+               const EpilogueArgs& ep, void* ws, size_t ws_bytes, cudaStream_t stream, bool x3 = false);
 int conv_tc_dk(const dcg_conv_desc& d, const float* x, const float* dy, float* dk,
-               void* ws, size_t ws_bytes, cudaStream_t stream);
+               void* ws, size_t ws_bytes, cudaStream_t stream, bool x3 = false);
 
 // Shape validation shared by the entry points: 0 or a negative dcg_status.
 int conv_check_desc(const dcg_conv_desc* d, const char* who);

@@ -93,6 +93,8 @@ struct Params {
     int narrow;                   // FWD/DK with <= 4 input channels: x is read through the window map
     int ext_finish;               // the K partitions only write partials; a second kernel adds them (narrow DK)
     int planes;                   // FWD: 16-byte column quad q of output pixel r goes to out[(q * pixels + r) * 4]
+    int o_store;                  // FWD: output columns >= o_store are padding and never stored (0: store all O)
+    int x3;                       // 3xTF32: every operand tile gets a residual tile, three MMAs per K step
     unsigned long long plane_stride;  // planes: elements between two quads' planes (4 * pixels)
     int debug;                    // timing experiments (DCG_TC_DEBUG): 1 = no MMA, 2 = no TMA; results are garbage
     int stages;                   // pipeline depth
@@ -248,6 +250,19 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t* r)
         : "r"(taddr) : "memory");
 }
 
+// 3xTF32: what the TF32 part of a value (its top 19 bits, which is what the tensor core reads) leaves over.
+// The residual is itself rounded to nearest TF32 here (the tensor core would truncate it, and a
+// truncation error always points the same way, so it would add up over a long reduction).
+__device__ __forceinline__ float tf32_residual_1(float v)
+{
+    const float r = __fsub_rn(v, __uint_as_float(__float_as_uint(v) & 0xFFFFE000u));
+    return __uint_as_float((__float_as_uint(r) + 0x1000u) & 0xFFFFE000u);
+}
+__device__ __forceinline__ float4 tf32_residual(float4 v)
+{
+    return make_float4(tf32_residual_1(v.x), tf32_residual_1(v.y), tf32_residual_1(v.z), tf32_residual_1(v.w));
+}
+
 // Shared-memory operand descriptor (tcgen05): start address, leading / stride byte offsets in
 // 16-byte units, version 1, swizzle layout.  Layout 2 = 128-byte swizzle of 16-byte chunks (what
 // K-major tiles use); layout 1 = 128-byte swizzle of 32-byte chunks, the only swizzled layout the
@@ -274,8 +289,8 @@ __device__ __forceinline__ uint32_t make_idesc(int a_mn_major, int b_mn_major, i
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------
-template <int MODE>
-__global__ void __launch_bounds__(kThreads, 2)
+template <int MODE, bool X3>
+__global__ void __launch_bounds__(kThreads, X3 ? 1 : 2)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ Params p)
 {
@@ -286,11 +301,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int b_stage_bytes = p.bn * BK * 4;
     const uint32_t a_base = smem_base;
     const uint32_t b_base = a_base + (uint32_t)p.stages * A_STAGE_BYTES;
-    const uint32_t bar_base = b_base + (uint32_t)p.stages * b_stage_bytes;
+    // 3xTF32: residual tiles (operand minus its TF32 part) of every stage follow the operand tiles
+    const uint32_t as_base = b_base + (uint32_t)p.stages * b_stage_bytes;
+    const uint32_t bs_base = as_base + (uint32_t)p.stages * A_STAGE_BYTES;
+    const uint32_t bar_base = X3 ? bs_base + (uint32_t)p.stages * b_stage_bytes : as_base;
     // barriers: full[stages], empty[stages], tmem_full; then the TMEM base address word
     const uint32_t full_bar = bar_base;
     const uint32_t empty_bar = bar_base + 8u * p.stages;
-    const uint32_t tmem_full_bar = bar_base + 16u * p.stages;
+    const uint32_t resid_bar = bar_base + 16u * p.stages;     // 3xTF32: residual tiles of the stage are written
+    const uint32_t tmem_full_bar = bar_base + 24u * p.stages;
     const uint32_t tmem_slot = tmem_full_bar + 8u;
     uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
@@ -341,14 +360,19 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int s = 0; s < p.stages; ++s) {
             mbar_init(full_bar + 8u * s, 1);
             mbar_init(empty_bar + 8u * s, 1);
+            mbar_init(resid_bar + 8u * s, 128);
         }
         mbar_init(tmem_full_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
     }
+    // 3xTF32 keeps the two small cross terms in an accumulator of their own (columns bn .. 2*bn): the
+    // tensor core rounds its accumulator toward zero at every step, an error that grows with the
+    // number of steps and with the accumulator's size, so the long chain of large terms is kept as
+    // short as in the plain TF32 kernel and the small terms round among themselves
     int tmem_cols = 32;
-    while (tmem_cols < p.bn) tmem_cols <<= 1;
+    while (tmem_cols < (X3 ? 2 * p.bn : p.bn)) tmem_cols <<= 1;
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -374,7 +398,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int ch0 = n_tile * p.bn;    // channel index of accumulator column 0 (bias axis) unless DK
     int ncols_valid;                  // valid columns in this N tile
     long long col_stride = 1;         // element stride between accumulator columns in the output
-    if (MODE == MODE_FWD) ncols_valid = min(p.bn, p.O - ch0);
+    if (MODE == MODE_FWD) ncols_valid = min(p.bn, (p.o_store ? p.o_store : p.O) - ch0);
     else if (MODE == MODE_DX) ncols_valid = min(p.bn, p.C - ch0);
     else if (p.narrow) { ncols_valid = 32 * p.KH; col_stride = p.O; }
     else if (!p.swap) ncols_valid = min(p.bn, p.O - ch0);
@@ -483,6 +507,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t phase = 0;
             for (int it = 0; it < nq; ++it) {
                 if (!mbar_wait_warp(full_bar + 8u * s, phase, 1, it)) break;
+                if (X3 && !mbar_wait_warp(resid_bar + 8u * s, phase, 3, it)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 if (elect_one()) {
                 TC_TRACE(1024 + it);
@@ -491,10 +516,25 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 } else {
                     const uint64_t adesc = adesc0 + (uint64_t)(s * a_stage16);
                     const uint64_t bdesc = bdesc0 + (uint64_t)(s * b_stage16);
+                    if (X3) {
+                        // a*b ~ a_hi*b_lo + a_lo*b_hi + a_hi*b_hi, the small terms first; the tensor core
+                        // reads the TF32 part (top 19 bits) of whatever fp32 word it is given
+                        const uint64_t ares = adesc + (uint64_t)((as_base - a_base) >> 4);
+                        const uint64_t bres = bdesc + (uint64_t)((bs_base - b_base) >> 4);
 #pragma unroll
-                    for (int kk = 0; kk < BK / 8; ++kk)
-                        tcgen05_mma_tf32(tmem_d, adesc + (uint64_t)(kk * (a_step >> 4)), bdesc + (uint64_t)(kk * (b_step >> 4)),
-                                         idesc, (it > 0 || kk > 0) ? 1u : 0u);
+                        for (int kk = 0; kk < BK / 8; ++kk) {
+                            const uint64_t ka = (uint64_t)(kk * (a_step >> 4)), kb = (uint64_t)(kk * (b_step >> 4));
+                            const uint32_t first = (it > 0 || kk > 0) ? 1u : 0u;
+                            tcgen05_mma_tf32(tmem_d + (uint32_t)p.bn, adesc + ka, bres + kb, idesc, first);
+                            tcgen05_mma_tf32(tmem_d + (uint32_t)p.bn, ares + ka, bdesc + kb, idesc, 1u);
+                            tcgen05_mma_tf32(tmem_d, adesc + ka, bdesc + kb, idesc, first);
+                        }
+                    } else {
+#pragma unroll
+                        for (int kk = 0; kk < BK / 8; ++kk)
+                            tcgen05_mma_tf32(tmem_d, adesc + (uint64_t)(kk * (a_step >> 4)), bdesc + (uint64_t)(kk * (b_step >> 4)),
+                                             idesc, (it > 0 || kk > 0) ? 1u : 0u);
+                    }
                     tcgen05_commit(empty_bar + 8u * s);  // frees the stage once these MMAs have read it
                 }
                 TC_TRACE(2048 + it);
@@ -535,6 +575,29 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int o = m_tile * BM + row;
                 row_valid = o < p.O;
                 row_off = tap_off + (unsigned long long)ch0 * p.O + o;
+            }
+        }
+        if (X3) {
+            // ===== 3xTF32: these four warps turn every landed stage into its residual tiles =====
+            // residual = value - (value with the low 13 mantissa bits cleared); element-wise on the raw
+            // bytes of the stage, so the swizzled layout carries over unchanged
+            const int tid_r = threadIdx.x - 64;
+            int s = 0;
+            uint32_t phase = 0;
+            const int a_q = A_STAGE_BYTES / 16, b_q = b_stage_bytes / 16;   // 16-byte words per tile
+            for (int it = 0; it < nq; ++it) {
+                if (!mbar_wait(full_bar + 8u * s, phase, 4, it)) break;
+                const float4* asrc = reinterpret_cast<const float4*>(smem_raw + (a_base + (uint32_t)s * A_STAGE_BYTES - smem_u32(smem_raw)));
+                float4* adst = reinterpret_cast<float4*>(smem_raw + (as_base + (uint32_t)s * A_STAGE_BYTES - smem_u32(smem_raw)));
+                const float4* bsrc = reinterpret_cast<const float4*>(smem_raw + (b_base + (uint32_t)s * b_stage_bytes - smem_u32(smem_raw)));
+                float4* bdst = reinterpret_cast<float4*>(smem_raw + (bs_base + (uint32_t)s * b_stage_bytes - smem_u32(smem_raw)));
+#pragma unroll 4
+                for (int i = tid_r; i < a_q; i += 128) adst[i] = tf32_residual(asrc[i]);
+#pragma unroll 4
+                for (int i = tid_r; i < b_q; i += 128) bdst[i] = tf32_residual(bsrc[i]);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor core reads
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(resid_bar + 8u * s) : "memory");
+                if (++s == p.stages) { s = 0; phase ^= 1u; }
             }
         }
         bool ok = mbar_wait(tmem_full_bar, 0, 2, 0);
@@ -578,6 +641,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (full) tmem_ld_32x32b_x32(taddr, r);
             else tmem_ld_32x32b_x16(taddr, r);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (X3) {   // add the accumulator of the small terms
+                uint32_t r2[32];
+                if (full) tmem_ld_32x32b_x32(taddr + (uint32_t)p.bn, r2);
+                else tmem_ld_32x32b_x16(taddr + (uint32_t)p.bn, r2);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int q = 0; q < 32; ++q)
+                    if (q < 16 || full) r[q] = __float_as_uint(__fadd_rn(__uint_as_float(r[q]), __uint_as_float(r2[q])));
+            }
             if (vec) {
                 if (multi) {
                     float4* d4 = reinterpret_cast<float4*>(my_scratch) + (size_t)(c0 >> 2) * BM + row;
@@ -996,6 +1068,14 @@ int env_int(const char* name)
     return v ? atoi(v) : 0;
 }
 
+// Set by the entry points for the duration of a call: plan for the 3xTF32 variant.
+thread_local int t_plan_x3 = 0;
+struct PlanX3 {
+    int saved;
+    explicit PlanX3(bool x3) : saved(t_plan_x3) { t_plan_x3 = x3 ? 1 : 0; }
+    ~PlanX3() { t_plan_x3 = saved; }
+};
+
 // Accumulator width for a layer with n_ch output columns.  256-column tiles (DCG_TC_WIDE=1) halve
 // how often an A tile is fetched from L2 but need the whole shared memory of an SM: one CTA per SM,
 // nothing to overlap its set-up and epilogue with.  Measured slower at batch 64 (the 256 -> 512
@@ -1015,6 +1095,13 @@ int choose_splits(int tiles, int min_stages_per_tile, int ctas_per_sm = 2)
         return f > kMaxCluster ? kMaxCluster : f;
     }
     const int sms = sm_count();
+    if (t_plan_x3) {
+        // 3xTF32: as many partitions as the cluster allows - each accumulation chain in the tensor
+        // core gets shorter, and the partitions are added in fp32 round-to-nearest
+        int s = min_stages_per_tile / 4;
+        if (s > kMaxCluster) s = kMaxCluster;
+        return s < 1 ? 1 : s;
+    }
     if (tiles >= sms) return 1;
     int s = (ctas_per_sm * sms) / tiles;             // aim at ~2 CTAs per SM (1 for 256-column tiles)
     const int cap = min_stages_per_tile / 4;         // keep at least 4 K stages per CTA
@@ -1027,9 +1114,9 @@ void finish_plan(Plan& pl)
 {
     Params& p = pl.p;
     const int b_stage = p.bn * BK * 4;
-    const int per_stage = A_STAGE_BYTES + b_stage;
+    const int per_stage = (A_STAGE_BYTES + b_stage) * (p.x3 ? 2 : 1);   // 3xTF32: operand + residual tiles
     // two CTAs per SM when the grid has more CTAs than SMs, else one deep pipeline
-    const int budget = (pl.grid > sm_count() && p.bn <= 128) ? (kMaxSmem / 2 - 2048) : (kMaxSmem - 2048);
+    const int budget = (pl.grid > sm_count() && p.bn <= 128 && !p.x3) ? (kMaxSmem / 2 - 2048) : (kMaxSmem - 2048);
     int stages = budget / per_stage;
     if (stages > 8) stages = 8;
     static const int forced_stages = env_int("DCG_TC_STAGES");
@@ -1040,7 +1127,7 @@ void finish_plan(Plan& pl)
     p.stages = stages;
     static const int debug = env_int("DCG_TC_DEBUG");
     p.debug = debug;
-    pl.smem = (size_t)stages * per_stage + 1024 /*alignment slack*/ + 16 * stages + 32;
+    pl.smem = (size_t)stages * per_stage + 1024 /*alignment slack*/ + 24 * stages + 32;
     pl.partial_bytes = p.splits > 1 ? (size_t)pl.grid * BM * p.bn * sizeof(float) : 0;
     pl.ws_bytes = pl.partial_bytes;
     if (pl.xp_bytes || pl.k4_bytes) pl.ws_bytes = pl.k4_off() + align_up(pl.k4_bytes, 256);
@@ -1066,6 +1153,7 @@ bool narrow_ok(const dcg_conv_desc& d)
 void base_params(Params& p, const dcg_conv_desc& d)
 {
     p = Params{};
+    p.x3 = t_plan_x3;
     p.N = d.n; p.H = d.h; p.W = d.w; p.C = d.c; p.KH = d.kh; p.KW = d.kw; p.O = d.o;
     p.Ho = d.ho; p.Wo = d.wo; p.sh = d.stride_h; p.sw = d.stride_w; p.pt = d.pad_top; p.pl = d.pad_left;
     p.m_tiles = 1; p.n_tiles = 1; p.splits = 1; p.kchunks = 1;
@@ -1117,6 +1205,7 @@ bool plan_dx(const dcg_conv_desc& d, Plan& pl)
         if (plan_fwd(dx_gemm_desc(d, Jp), pl)) {
             pl.p.planes = 1;
             pl.p.plane_stride = (unsigned long long)d.n * d.ho * d.wo * 4ull;
+            pl.p.o_store = d.kh * d.kw * 4;   // the planes beyond the last tap are padding
             return true;
         }
         pl = Plan{};
@@ -1203,7 +1292,9 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, Plan& pl, float* out, c
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(conv_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+        attr_err = cudaFuncSetAttribute(conv_tc_kernel<MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+        if (attr_err == cudaSuccess)
+            attr_err = cudaFuncSetAttribute(conv_tc_kernel<MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
     });
     if (attr_err != cudaSuccess)
         return fail(DCG_ERR_CUDA, "cudaFuncSetAttribute(conv_tc_kernel): %s", cudaGetErrorString(attr_err));
@@ -1239,7 +1330,8 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, Plan& pl, float* out, c
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    const cudaError_t err = cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE>, ma, mb, p);
+    const cudaError_t err = p.x3 ? cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE, true>, ma, mb, p)
+                                 : cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE, false>, ma, mb, p);
     if (err != cudaSuccess) return fail(DCG_ERR_CUDA, "conv_tc_kernel launch: %s", cudaGetErrorString(err));
     count_launch();
     if (p.ext_finish) {
@@ -1292,22 +1384,25 @@ int map_window(CUtensorMap* map, const float* xp, const dcg_conv_desc& d, const 
 
 }  // namespace
 
-bool conv_tc_supported(const dcg_conv_desc& d, int kind)
+bool conv_tc_supported(const dcg_conv_desc& d, int kind, bool x3)
 {
+    PlanX3 scope(x3);
     Plan pl;
     return make_plan(d, kind, pl);
 }
 
-size_t conv_tc_workspace(const dcg_conv_desc& d, int kind)
+size_t conv_tc_workspace(const dcg_conv_desc& d, int kind, bool x3)
 {
+    PlanX3 scope(x3);
     Plan pl;
     if (!make_plan(d, kind, pl)) return 0;
     return pl.ws_bytes;
 }
 
 int conv_tc_fwd(const dcg_conv_desc& d, const float* x, const float* k, float* y, const EpilogueArgs& ep,
-                void* ws, size_t ws_bytes, cudaStream_t stream)
+                void* ws, size_t ws_bytes, cudaStream_t stream, bool x3)
 {
+    PlanX3 scope(x3);
     Plan pl;
     if (!plan_fwd(d, pl)) return fail(DCG_ERR_UNSUPPORTED, "conv fwd: shape not supported by the tensor path");
     const Params& p = pl.p;
@@ -1337,8 +1432,9 @@ int conv_tc_fwd(const dcg_conv_desc& d, const float* x, const float* k, float* y
 }
 
 int conv_tc_dx(const dcg_conv_desc& d, const float* dy, const float* k, float* dx, const EpilogueArgs& ep,
-               void* ws, size_t ws_bytes, cudaStream_t stream)
+               void* ws, size_t ws_bytes, cudaStream_t stream, bool x3)
 {
+    PlanX3 scope(x3);
     Plan pl;
     if (!plan_dx(d, pl)) return fail(DCG_ERR_UNSUPPORTED, "conv dx: shape not supported by the tensor path");
     const Params& p = pl.p;
@@ -1382,8 +1478,9 @@ int conv_tc_dx(const dcg_conv_desc& d, const float* dy, const float* k, float* d
 }
 
 int conv_tc_dk(const dcg_conv_desc& d, const float* x, const float* dy, float* dk, void* ws, size_t ws_bytes,
-               cudaStream_t stream)
+               cudaStream_t stream, bool x3)
 {
+    PlanX3 scope(x3);
     Plan pl;
     if (!plan_dk(d, pl)) return fail(DCG_ERR_UNSUPPORTED, "conv dk: shape not supported by the tensor path");
     const Params& p = pl.p;

@@ -48,7 +48,8 @@ enum dcg_act {
 enum dcg_precision {
     DCG_PREC_TF32 = 0,   /* tcgen05 kind::tf32, fp32 accumulate in TMEM; falls back to
                             DCG_PREC_FP32 kernels for shapes the tensor path cannot take */
-    DCG_PREC_3XTF32 = 1, /* error-compensated split, fp32-level accuracy (opt-in) */
+    DCG_PREC_3XTF32 = 1, /* opt-in: operand = TF32 part + residual, three tensor-core products per
+                            K step; <= 1e-5 * max|ref|, about three times the TF32 cost */
     DCG_PREC_FP32 = 2    /* CUDA-core fp32 with the reference CPU's summation order,
                             unfused multiply/add: bit-comparable with src/cpu/ops.hxx */
 };

@@ -24,7 +24,7 @@ def _l2rel(got, ref):
     return float(np.linalg.norm(got.astype(np.float64) - ref) / max(np.linalg.norm(ref.astype(np.float64)), 1e-30))
 
 
-@pytest.mark.parametrize("prec_name,tol", [("fp32", 2e-5), ("tf32", 1e-1)])
+@pytest.mark.parametrize("prec_name,tol", [("fp32", 2e-5), ("tf32", 1e-1), ("3xtf32", 1e-2)])
 @pytest.mark.parametrize("fuse", [False, True])
 def test_gradients_match_cpu_model(pkg, dev, orc, prec_name, tol, fuse):
     """Every weight gradient of the D run and the G run, per layer.
@@ -34,7 +34,9 @@ def test_gradients_match_cpu_model(pkg, dev, orc, prec_name, tol, fuse):
     side of a leaky-relu / relu kink, which moves that element's gradient by a finite step; at
     batch 2 a kernel gradient sums as few as 32 pixels, so single flips show up at the percent level
     element-wise.  The whole-graph check therefore bounds the relative L2 error of each gradient
-    and holds the losses to 1e-4."""
+    and holds the losses to 1e-4.  3xTF32 (operators within 1e-5) sits in between: kink flips become
+    rare (measured: 1e-6 on most gradients, 2.5e-3 where one pre-activation flipped), the relative L2
+    bound tightens to 1e-2."""
     B = 2
     rng = np.random.default_rng(3)
     st = M.init_state(rng, B)
@@ -43,7 +45,7 @@ def test_gradients_match_cpu_model(pkg, dev, orc, prec_name, tol, fuse):
         st["d"][i] = (rng.standard_normal(st["d"][i].shape) * 0.05).astype(np.float32)
     x = rng.uniform(-1, 1, (B, 64, 64, 3)).astype(np.float32)
     z = rng.uniform(-1, 1, (B, 100)).astype(np.float32)
-    prec = pkg.PREC_FP32 if prec_name == "fp32" else pkg.PREC_TF32
+    prec = {"fp32": pkg.PREC_FP32, "tf32": pkg.PREC_TF32, "3xtf32": pkg.PREC_3XTF32}[prec_name]
     err = _maxrel if prec_name == "fp32" else _l2rel
     loss_tol = 2e-5 if prec_name == "fp32" else 1e-4
     tr = pkg.Trainer(batch=B, precision=prec, fuse=fuse)
