@@ -9,6 +9,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "adam.cuh"
@@ -30,6 +31,14 @@ struct dcg_context {
     void* ws = nullptr;
     size_t ws_bytes = 0;
     bool owns_ws = false;
+    // Second stream with scratch of its own for nodes flagged DCG_NODE_SIDE (created on first use,
+    // only when the context owns its scratch): they fork off the main stream, run concurrently with
+    // the nodes that follow, and are joined at the end of the list.
+    cudaStream_t side = nullptr;
+    void* side_ws = nullptr;
+    size_t side_ws_bytes = 0;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    bool side_busy = false, side_failed = false;
     uint64_t launches_base = 0;
     bool profiling = false;
     std::vector<ProfRec> recs;
@@ -365,6 +374,10 @@ extern "C" void dcg_context_destroy(dcg_context* ctx)
 {
     if (!ctx) return;
     if (ctx->owns_ws && ctx->ws) cudaFree(ctx->ws);
+    if (ctx->side_ws) cudaFree(ctx->side_ws);
+    if (ctx->ev_fork) cudaEventDestroy(ctx->ev_fork);
+    if (ctx->ev_join) cudaEventDestroy(ctx->ev_join);
+    if (ctx->side) cudaStreamDestroy(ctx->side);
     delete ctx;
 }
 
@@ -482,11 +495,78 @@ extern "C" int dcg_run_node(dcg_context* ctx, const dcg_node* nd)
     }
 }
 
+namespace {
+
+// Whether DCG_NODE_SIDE nodes can leave the main stream: the context must be free to allocate a
+// second scratch buffer, and not be profiling (whose event pairs sit on the main stream).
+bool side_usable(dcg_context* ctx)
+{
+    if (ctx->side_failed || ctx->profiling || (ctx->ws && !ctx->owns_ws)) return false;
+    if (ctx->side) return true;
+    static const bool off = [] { const char* v = getenv("DCG_NO_SIDE_STREAM"); return v && atoi(v) != 0; }();
+    if (off || cudaStreamCreateWithFlags(&ctx->side, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&ctx->ev_join, cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        ctx->side_failed = true;
+        ctx->side = nullptr;
+        return false;
+    }
+    return true;
+}
+
+// Runs one node on the side stream, after everything enqueued on the main stream so far.
+int run_side_node(dcg_context* ctx, const dcg_node* nd)
+{
+    DCG_CUDA(cudaEventRecord(ctx->ev_fork, ctx->stream));
+    DCG_CUDA(cudaStreamWaitEvent(ctx->side, ctx->ev_fork, 0));
+    std::swap(ctx->stream, ctx->side);
+    std::swap(ctx->ws, ctx->side_ws);
+    std::swap(ctx->ws_bytes, ctx->side_ws_bytes);
+    const bool owns = ctx->owns_ws;
+    ctx->owns_ws = true;
+    const int st = dcg_run_node(ctx, nd);
+    ctx->owns_ws = owns;
+    std::swap(ctx->stream, ctx->side);
+    std::swap(ctx->ws, ctx->side_ws);
+    std::swap(ctx->ws_bytes, ctx->side_ws_bytes);
+    ctx->side_busy = true;
+    return st;
+}
+
+// The main stream waits for whatever the side stream still has to do.
+int join_side(dcg_context* ctx)
+{
+    if (!ctx->side_busy) return DCG_OK;
+    ctx->side_busy = false;
+    DCG_CUDA(cudaEventRecord(ctx->ev_join, ctx->side));
+    DCG_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->ev_join, 0));
+    return DCG_OK;
+}
+
+int run_nodes_impl(dcg_context* ctx, const dcg_node* nodes, int count, int fuse);
+
+}  // namespace
+
 extern "C" int dcg_run_nodes(dcg_context* ctx, const dcg_node* nodes, int count, int fuse)
 {
     DCG_CHECK_ARG(ctx && (nodes || count == 0) && count >= 0, "dcg_run_nodes: bad arguments");
+    const int st = run_nodes_impl(ctx, nodes, count, fuse);
+    const int js = join_side(ctx);   // on every path: a capture must never end with the side stream forked
+    return st ? st : js;
+}
+
+namespace {
+int run_nodes_impl(dcg_context* ctx, const dcg_node* nodes, int count, int fuse)
+{
     int i = 0;
     while (i < count) {
+        if ((nodes[i].flags & DCG_NODE_SIDE) && side_usable(ctx)) {
+            int st = run_side_node(ctx, &nodes[i]);
+            if (st) return st;
+            ++i;
+            continue;
+        }
         if (!fuse) {
             int st = dcg_run_node(ctx, &nodes[i]);
             if (st) return st;
@@ -539,6 +619,7 @@ extern "C" int dcg_run_nodes(dcg_context* ctx, const dcg_node* nodes, int count,
     }
     return DCG_OK;
 }
+}  // namespace
 
 // ---- profiling mode ---------------------------------------------------------------------------
 extern "C" int dcg_context_profile_begin(dcg_context* ctx)

@@ -314,6 +314,13 @@ dcg_node dead(dcg_node n)
     return n;
 }
 
+// Weight and bias gradients are read by nobody before Adam: they may leave the main stream.
+dcg_node side(dcg_node n)
+{
+    n.flags |= DCG_NODE_SIDE;
+    return n;
+}
+
 // Generator forward: dcgan/main.cu:89-120 and :288 (tanh on the last layer's pre-activation).
 void build_generator(dcg_trainer* t, std::vector<dcg_node>& L)
 {
@@ -356,9 +363,12 @@ void build_discriminator(dcg_trainer* t, std::vector<dcg_node>& L, const float* 
 void build_discriminator_backward(dcg_trainer* t, std::vector<dcg_node>& L, const float* img, int ps,
                                   Tensor* grads, bool to_image, int B)
 {
+    // The two-pass (fp32) D run sends both passes through the same backward scratch, so there a
+    // gradient node must finish before the next pass overwrites what it reads: main stream only.
+    auto grad_node = [&](dcg_node n) { return t->batched_d ? side(n) : n; };
     if (grads) {
-        L.push_back(n_mat3(DCG_OP_TMAT_MAT_MUL, t->da[ps][3].p, t->dlogits[ps].p, grads[8].p, 8192, B, 1));
-        L.push_back(n_rows_cols(DCG_OP_MAT_SUM_COLS, t->dlogits[ps].p, nullptr, grads[9].p, B, 1));
+        L.push_back(grad_node(n_mat3(DCG_OP_TMAT_MAT_MUL, t->da[ps][3].p, t->dlogits[ps].p, grads[8].p, 8192, B, 1)));
+        L.push_back(grad_node(n_rows_cols(DCG_OP_MAT_SUM_COLS, t->dlogits[ps].p, nullptr, grads[9].p, B, 1)));
     }
     L.push_back(n_mat3(DCG_OP_MAT_TMAT_MUL, t->dlogits[ps].p, t->d_param[8].p, t->dda[4].p, B, 1, 8192));
     for (int i = kLayers - 1; i >= 0; --i) {
@@ -368,8 +378,8 @@ void build_discriminator_backward(dcg_trainer* t, std::vector<dcg_node>& L, cons
         // dda[i+1] is produced by the layer above; its leaky gradient is this layer's dz
         L.push_back(n_binary(DCG_OP_LEAKY_RELU_GRAD, t->dz[ps][i].p, t->dda[i + 1].p, t->ddz[i].p, rows * kDChan[i + 1], 0.2f));
         if (grads) {
-            L.push_back(n_rows_cols(DCG_OP_MAT_SUM_COLS, t->ddz[i].p, nullptr, grads[2 * i + 1].p, rows, kDChan[i + 1]));
-            L.push_back(n_conv2d_kernel_grad(t->ddz[i].p, in, grads[2 * i].p, B, h, kDChan[i], kDChan[i + 1]));
+            L.push_back(grad_node(n_rows_cols(DCG_OP_MAT_SUM_COLS, t->ddz[i].p, nullptr, grads[2 * i + 1].p, rows, kDChan[i + 1])));
+            L.push_back(grad_node(n_conv2d_kernel_grad(t->ddz[i].p, in, grads[2 * i].p, B, h, kDChan[i], kDChan[i + 1])));
         }
         // the input gradient is only ever read by the activation gradient that follows it
         if (i > 0)
@@ -422,8 +432,8 @@ void build_lists(dcg_trainer* t)
         const int h = 4 << i, hw = 2 * h;
         const size_t rows = (size_t)B * hw * hw;
         const float* in = i == 0 ? t->g0a.p : t->ga[i - 1].p;
-        G.push_back(n_rows_cols(DCG_OP_MAT_SUM_COLS, t->dgz[i].p, nullptr, t->g_grad[2 * i + 1].p, rows, kGChan[i + 1]));
-        G.push_back(n_conv2d_transpose_kernel_grad(t->dgz[i].p, in, t->g_grad[2 * i].p, B, h, kGChan[i], kGChan[i + 1]));
+        G.push_back(side(n_rows_cols(DCG_OP_MAT_SUM_COLS, t->dgz[i].p, nullptr, t->g_grad[2 * i + 1].p, rows, kGChan[i + 1])));
+        G.push_back(side(n_conv2d_transpose_kernel_grad(t->dgz[i].p, in, t->g_grad[2 * i].p, B, h, kGChan[i], kGChan[i + 1])));
         float* dprev_a = i == 0 ? t->dg0a.p : t->dga[i - 1].p;
         G.push_back(dead(n_conv2d_transpose_input_grad(t->dgz[i].p, t->g_param[2 * i].p, dprev_a, B, h, kGChan[i], kGChan[i + 1])));
         const float* zprev = i == 0 ? t->g0z.p : t->gz[i - 1].p;
@@ -431,8 +441,8 @@ void build_lists(dcg_trainer* t)
         const size_t nprev = i == 0 ? (size_t)B * 8192 : (size_t)B * h * h * kGChan[i];
         G.push_back(n_binary(gact_grad, zprev, dprev_a, dprev_z, nprev, 0.2f));
     }
-    G.push_back(n_mat3(DCG_OP_TMAT_MAT_MUL, t->z.p, t->dg0z.p, t->g_grad[8].p, kZ, B, 8192));
-    G.push_back(n_rows_cols(DCG_OP_MAT_SUM_COLS, t->dg0z.p, nullptr, t->g_grad[9].p, B, 8192));
+    G.push_back(side(n_mat3(DCG_OP_TMAT_MAT_MUL, t->z.p, t->dg0z.p, t->g_grad[8].p, kZ, B, 8192)));
+    G.push_back(side(n_rows_cols(DCG_OP_MAT_SUM_COLS, t->dg0z.p, nullptr, t->g_grad[9].p, B, 8192)));
 }
 
 int run_list(dcg_trainer* t, const std::vector<dcg_node>& L, dcg_trainer::ListGraph& g)

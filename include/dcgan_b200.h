@@ -247,6 +247,10 @@ typedef struct dcg_node {
 
 #define DCG_NODE_OUT_DEAD 1u /* out1 is read by nobody but the next fusable node: a fused
                                 kernel may skip storing it */
+#define DCG_NODE_SIDE 2u     /* nothing later in the list reads this node's outputs or overwrites its
+                                inputs (a weight or bias gradient): dcg_run_nodes may run it on a
+                                second stream, concurrently with the nodes that follow, and joins it
+                                before returning.  Honoured only by contexts that own their scratch. */
 
 #define DCG_OP_MAT_MAT_MUL 0
 #define DCG_OP_MAT_RVECT_ADD 1
