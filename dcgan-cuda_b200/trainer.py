@@ -6,7 +6,9 @@ one training iteration.  This wrapper adds what lives above the C ABI:
 * zero-copy torch views of the trainer's device tensors (inputs, losses,
   parameter and gradient arenas);
 * the end-to-end step with HOST inputs: pinned host -> device copies of the real
-  images and the noise, the iteration, a device -> host read of the two losses;
+  images and the noise, the iteration, a device -> host read of the two losses -
+  blocking (step_host) or pipelined (submit_host / result: the copies of iteration
+  i+1 overlap the compute of iteration i);
 * data-parallel training: one process per GPU, each on its own 64-image shard;
   between *_backward and *_apply the gradient arena of the network being updated
   is summed over ranks with one torch.distributed all_reduce (NCCL on GPUs), and
@@ -52,10 +54,7 @@ class Trainer:
         self.g_out = self.tensor("g_out").view(batch, 64, 64, 3)
         self.d_loss, self.g_loss = self.tensor("d_loss"), self.tensor("g_loss")
         self.d_grads, self.g_grads = self.tensor("d_grads"), self.tensor("g_grads")
-        # pinned staging for the end-to-end step
-        self._hx = torch.empty((batch, 64, 64, 3), dtype=torch.float32).pin_memory()
-        self._hz = torch.empty((batch, 100), dtype=torch.float32).pin_memory()
-        self._hloss = torch.empty((2,), dtype=torch.float32).pin_memory()
+        self._pipe = None   # staging of the end-to-end path, built on first use
 
     # ---- device tensors ------------------------------------------------------
     def tensor(self, name):
@@ -117,19 +116,76 @@ class Trainer:
         with self._on_stream():
             self._step()
 
+    # ---- end to end: host inputs in, losses out ---------------------------------------------
+    _RING = 32   # iterations that may be in flight between submit_host and result
+
+    def _pipeline(self):
+        """Staging for submit_host, built on first use: two device slots for the inputs, filled by a
+        copy stream while the previous iteration computes, and a ring of pinned loss pairs."""
+        if getattr(self, "_pipe", None) is None:
+            B, dev = self.batch, self.device
+            self._pipe = {
+                "copy": torch.cuda.Stream(dev),
+                "xs": [torch.empty((B, 64, 64, 3), device=dev) for _ in range(2)],
+                "zs": [torch.empty((B, 100), device=dev) for _ in range(2)],
+                "hx": [torch.empty((B, 64, 64, 3)).pin_memory() for _ in range(2)],
+                "hz": [torch.empty((B, 100)).pin_memory() for _ in range(2)],
+                "copied": [torch.cuda.Event() for _ in range(2)],    # slot's host -> device copy done
+                "consumed": [torch.cuda.Event() for _ in range(2)],  # slot read by its iteration
+                "loss": torch.empty((self._RING, 2)).pin_memory(),
+                "done": [torch.cuda.Event() for _ in range(self._RING)],
+                "n": 0,
+            }
+        return self._pipe
+
+    def submit_host(self, x_host, z_host):
+        """Enqueues one end-to-end iteration and returns a ticket for result(): the host -> device
+        copy of x_host [B,64,64,3] and z_host [B,100] (HOST arrays; pinned torch tensors are copied
+        from directly, anything else is staged through pinned memory first) runs on a copy stream
+        and overlaps the iteration submitted before; the losses are read back into pinned memory.
+        At most _RING iterations may be outstanding."""
+        p = self._pipeline()
+        n = p["n"]
+        p["n"] = n + 1
+        slot, ring = n % 2, n % self._RING
+        if n >= self._RING:
+            p["done"][ring].synchronize()   # the ring entry is about to be reused: its reader must have had its chance
+        if n >= 2:
+            p["consumed"][slot].synchronize()   # the slot's previous iteration has taken its inputs
+        xh, zh = torch.as_tensor(x_host), torch.as_tensor(z_host)
+        if not (xh.is_pinned() and xh.dtype == torch.float32 and xh.is_contiguous()):
+            p["hx"][slot].copy_(xh.reshape(p["hx"][slot].shape))
+            xh = p["hx"][slot]
+        if not (zh.is_pinned() and zh.dtype == torch.float32 and zh.is_contiguous()):
+            p["hz"][slot].copy_(zh.reshape(p["hz"][slot].shape))
+            zh = p["hz"][slot]
+        with torch.cuda.stream(p["copy"]):
+            p["xs"][slot].copy_(xh.reshape(p["xs"][slot].shape), non_blocking=True)
+            p["zs"][slot].copy_(zh.reshape(p["zs"][slot].shape), non_blocking=True)
+            p["copied"][slot].record()
+        with self._on_stream():
+            self.stream.wait_event(p["copied"][slot])
+            self.x.copy_(p["xs"][slot], non_blocking=True)   # device -> device, a few microseconds
+            self.z.copy_(p["zs"][slot], non_blocking=True)
+            p["consumed"][slot].record()
+            self._step()
+            p["loss"][ring, 0:1].copy_(self.d_loss, non_blocking=True)
+            p["loss"][ring, 1:2].copy_(self.g_loss, non_blocking=True)
+            p["done"][ring].record()
+        return n
+
+    def result(self, ticket):
+        """(d_loss, g_loss) of the iteration submit_host returned `ticket` for; waits for it."""
+        p = self._pipeline()
+        assert p["n"] - self._RING <= ticket < p["n"], "ticket no longer (or not yet) in the ring"
+        ring = ticket % self._RING
+        p["done"][ring].synchronize()
+        return float(p["loss"][ring, 0]), float(p["loss"][ring, 1])
+
     def step_host(self, x_host, z_host):
         """End-to-end iteration: x_host [B,64,64,3] and z_host [B,100] are HOST arrays (numpy or
         CPU torch); returns (d_loss, g_loss) as Python floats read back from the device."""
-        self._hx.copy_(torch.as_tensor(x_host).reshape(self._hx.shape))
-        self._hz.copy_(torch.as_tensor(z_host).reshape(self._hz.shape))
-        with self._on_stream():
-            self.x.copy_(self._hx, non_blocking=True)
-            self.z.copy_(self._hz, non_blocking=True)
-            self._step()
-            self._hloss[0:1].copy_(self.d_loss, non_blocking=True)
-            self._hloss[1:2].copy_(self.g_loss, non_blocking=True)
-        self.stream.synchronize()
-        return float(self._hloss[0]), float(self._hloss[1])
+        return self.result(self.submit_host(x_host, z_host))
 
     h2d_bytes_per_step = property(lambda self: self.batch * (64 * 64 * 3 + 100) * 4)
     d2h_bytes_per_step = property(lambda self: 8)
