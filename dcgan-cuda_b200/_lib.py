@@ -117,6 +117,7 @@ SIGNATURES = {
     "dcg_trainer_d_backward": (c_int, [_P]),
     "dcg_trainer_d_apply": (c_int, [_P, c_float]),
     "dcg_trainer_g_backward": (c_int, [_P]),
+    "dcg_trainer_g_backward_part": (c_int, [_P, c_int]),
     "dcg_trainer_g_apply": (c_int, [_P, c_float]),
     "dcg_trainer_step": (c_int, [_P]),
     "dcg_trainer_context": (_P, [_P]),

@@ -98,7 +98,8 @@ struct dcg_trainer {
         const void* ws = nullptr;  // scratch address baked into the captured launches
         bool failed = false;
     };
-    ListGraph d_graph, g_graph, gen_graph;
+    ListGraph d_graph, g_graph, gen_graph, g_part_graph[2];
+    size_t g_forward_nodes = 0;   // the G run's leading nodes that only compute the generator's forward pass
     bool use_graphs = true;
 };
 
@@ -421,6 +422,7 @@ void build_lists(dcg_trainer* t)
     // ---- G run: graph.run({g_opti, g_loss}) ----
     std::vector<dcg_node>& G = t->g_nodes;
     build_generator(t, G);
+    t->g_forward_nodes = G.size();
     build_discriminator(t, G, t->g_out.p, 0, B);
     G.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY, t->ones.p, t->logits[0].p, t->g_loss.p, B));
     G.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY_GRAD, t->ones.p, t->logits[0].p, t->dlogits[0].p, B));
@@ -445,8 +447,11 @@ void build_lists(dcg_trainer* t)
     G.push_back(side(n_rows_cols(DCG_OP_MAT_SUM_COLS, t->dg0z.p, nullptr, t->g_grad[9].p, B, 8192)));
 }
 
-int run_list(dcg_trainer* t, const std::vector<dcg_node>& L, dcg_trainer::ListGraph& g)
+int run_list(dcg_trainer* t, const std::vector<dcg_node>& all, dcg_trainer::ListGraph& g, size_t begin = 0,
+             size_t end = (size_t)-1)
 {
+    if (end > all.size()) end = all.size();
+    const std::vector<dcg_node> L(all.begin() + begin, all.begin() + end);   // ~100 small records
     const bool eager = !t->use_graphs || g.failed || dcg::context_is_profiling(t->ctx);
     if (eager || g.eager_runs < 2) {
         if (!eager) ++g.eager_runs;
@@ -558,7 +563,7 @@ extern "C" int dcg_trainer_create(dcg_trainer** out, const dcg_trainer_config* c
 extern "C" void dcg_trainer_destroy(dcg_trainer* t)
 {
     if (!t) return;
-    for (dcg_trainer::ListGraph* g : {&t->d_graph, &t->g_graph, &t->gen_graph})
+    for (dcg_trainer::ListGraph* g : {&t->d_graph, &t->g_graph, &t->gen_graph, &t->g_part_graph[0], &t->g_part_graph[1]})
         if (g->exec) cudaGraphExecDestroy(g->exec);
     if (t->ctx) dcg_context_destroy(t->ctx);
     if (t->arena) cudaFree(t->arena);
@@ -596,6 +601,13 @@ extern "C" int dcg_trainer_g_backward(dcg_trainer* t)
 {
     DCG_CHECK_ARG(t, "dcg_trainer_g_backward: null trainer");
     return run_list(t, t->g_nodes, t->g_graph);
+}
+
+extern "C" int dcg_trainer_g_backward_part(dcg_trainer* t, int part)
+{
+    DCG_CHECK_ARG(t && (part == 0 || part == 1), "dcg_trainer_g_backward_part: bad arguments");
+    if (part == 0) return run_list(t, t->g_nodes, t->g_part_graph[0], 0, t->g_forward_nodes);
+    return run_list(t, t->g_nodes, t->g_part_graph[1], t->g_forward_nodes);
 }
 
 extern "C" int dcg_trainer_g_apply(dcg_trainer* t, float grad_scale)

@@ -55,6 +55,7 @@ class Trainer:
         self.d_loss, self.g_loss = self.tensor("d_loss"), self.tensor("g_loss")
         self.d_grads, self.g_grads = self.tensor("d_grads"), self.tensor("g_grads")
         self._pipe = None   # staging of the end-to-end path, built on first use
+        self._comm = None   # communication stream of the data-parallel step, built on first use
 
     # ---- device tensors ------------------------------------------------------
     def tensor(self, name):
@@ -102,13 +103,32 @@ class Trainer:
             torch.distributed.all_reduce(grads, group=self.group)
 
     def _step(self):
+        """Body of one iteration; runs with the trainer's stream current."""
         scale = 1.0 / self.world
         check(lib.dcg_trainer_d_backward(self._h))
-        self._allreduce(self.d_grads)
+        if self.world > 1:
+            # The discriminator's gradients are summed over ranks on a communication stream while
+            # this stream already computes the generator's forward pass of the first G update, which
+            # reads neither the discriminator's gradients nor its parameters.
+            if self._comm is None:
+                self._comm = torch.cuda.Stream(self.device)
+            main = torch.cuda.current_stream(self.device)
+            self._comm.wait_stream(main)
+            with torch.cuda.stream(self._comm):
+                self._allreduce(self.d_grads)
+            check(lib.dcg_trainer_g_backward_part(self._h, 0))
+            main.wait_stream(self._comm)
+            check(lib.dcg_trainer_d_apply(self._h, scale))
+            check(lib.dcg_trainer_g_backward_part(self._h, 1))
+            self._allreduce(self.g_grads)
+            check(lib.dcg_trainer_g_apply(self._h, scale))
+            check(lib.dcg_trainer_g_backward(self._h))
+            self._allreduce(self.g_grads)
+            check(lib.dcg_trainer_g_apply(self._h, scale))
+            return
         check(lib.dcg_trainer_d_apply(self._h, scale))
         for _ in range(2):
             check(lib.dcg_trainer_g_backward(self._h))
-            self._allreduce(self.g_grads)
             check(lib.dcg_trainer_g_apply(self._h, scale))
 
     def step(self):

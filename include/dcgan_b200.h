@@ -374,6 +374,10 @@ int dcg_trainer_d_backward(dcg_trainer* t);
 int dcg_trainer_d_apply(dcg_trainer* t, float grad_scale);
 /* graph.run({g_opti, g_loss}) minus the update: G forward, D on fake, g_loss, G gradients. */
 int dcg_trainer_g_backward(dcg_trainer* t);
+/* The same in two parts, for callers that overlap something with the first: part 0 is the generator's
+ * forward pass (reads z and the generator's parameters only - in data-parallel training it can run
+ * while the discriminator's gradients are still being all-reduced), part 1 everything after it. */
+int dcg_trainer_g_backward_part(dcg_trainer* t, int part);
 int dcg_trainer_g_apply(dcg_trainer* t, float grad_scale);
 /* One whole iteration on a single GPU: d_backward, d_apply, then twice g_backward, g_apply. */
 int dcg_trainer_step(dcg_trainer* t);

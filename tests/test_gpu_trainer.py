@@ -161,3 +161,28 @@ def test_graph_replay_equals_eager(pkg, dev, monkeypatch):
     assert l0 == l1
     assert torch.equal(d0, d1) and torch.equal(g0, g1)
 
+
+def test_g_backward_in_two_parts(pkg, dev):
+    """dcg_trainer_g_backward_part(0) then (1) - the split the data-parallel step uses to overlap the
+    discriminator's all-reduce with the generator's forward pass - leaves the same gradients and loss
+    as the one-call form, bit for bit, also once the parts replay as graphs."""
+    B = 4
+    g = torch.Generator(device="cpu").manual_seed(31)
+    z = (torch.rand((B, 100), generator=g) * 2 - 1).to(dev)
+    out = []
+    for split in (False, True):
+        tr = pkg.Trainer(batch=B, precision=pkg.PREC_TF32, fuse=True, seed=99)
+        tr.z.copy_(z)
+        for _ in range(4):   # two eager runs, capture, replay
+            if split:
+                with tr._on_stream():
+                    pkg._lib.check(pkg.lib.dcg_trainer_g_backward_part(tr._h, 0))
+                    pkg._lib.check(pkg.lib.dcg_trainer_g_backward_part(tr._h, 1))
+            else:
+                tr.g_backward()
+        torch.cuda.synchronize()
+        assert pkg.lib.dcg_device_status() == 0
+        out.append((tr.g_loss.clone(), tr.g_grads.clone()))
+        tr.close()
+    assert torch.equal(out[0][0], out[1][0]) and torch.equal(out[0][1], out[1][1])
+
