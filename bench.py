@@ -364,6 +364,7 @@ def cta_timeline(pkg):
     a = a[a[:, 0] > 0]
     if len(a) == 0:
         return None
+    a = a[a[:, 0] > a[:, 0].max() - 500000]   # rows of earlier, larger grids are still in the buffer: last launch only
     rel = (a[:, :6] - a[:, 0].min()) / 1e3
     d = np.diff(rel, axis=1)
     out = {"ctas": int(len(a)), "sms": int(len(set(a[:, 6].tolist()))),
