@@ -315,6 +315,29 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
 
+    // ---- one-time setup (first: thread 0 and warp 1 are busy with it while everyone decodes) ---------
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(full_bar + 8u * s, 1);
+            mbar_init(empty_bar + 8u * s, 1);
+            mbar_init(resid_bar + 8u * s, 128);
+        }
+        mbar_init(tmem_full_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    }
+    // 3xTF32 keeps the two small cross terms in an accumulator of their own (columns bn .. 2*bn): the
+    // tensor core rounds its accumulator toward zero at every step, an error that grows with the
+    // number of steps and with the accumulator's size, so the long chain of large terms is kept as
+    // short as in the plain TF32 kernel and the small terms round among themselves
+    int tmem_cols = 32;
+    while (tmem_cols < (X3 ? 2 * p.bn : p.bn)) tmem_cols <<= 1;
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+
     // ---- decode this CTA's work item -------------------------------------------------------------
     // blockIdx.x = ((group * m_count + m) * n_tiles + n) * splits + split, where group is the parity
     // class (DX), the kernel tap (DK) or absent (FWD), and m a pixel tile (FWD/DX) or channel tile (DK).
@@ -355,28 +378,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int q1 = (int)((long long)total_stages * (split + 1) / p.splits);
     const int nq = q1 - q0;
 
-    // ---- one-time setup ----------------------------------------------------------------------------
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < p.stages; ++s) {
-            mbar_init(full_bar + 8u * s, 1);
-            mbar_init(empty_bar + 8u * s, 1);
-            mbar_init(resid_bar + 8u * s, 128);
-        }
-        mbar_init(tmem_full_bar, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
-    }
-    // 3xTF32 keeps the two small cross terms in an accumulator of their own (columns bn .. 2*bn): the
-    // tensor core rounds its accumulator toward zero at every step, an error that grows with the
-    // number of steps and with the accumulator's size, so the long chain of large terms is kept as
-    // short as in the plain TF32 kernel and the small terms round among themselves
-    int tmem_cols = 32;
-    while (tmem_cols < (X3 ? 2 * p.bn : p.bn)) tmem_cols <<= 1;
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(tmem_cols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -719,7 +720,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     }
 #pragma unroll
                     for (int u = 0; u < 4; ++u) acc[u] = multi ? __ldcg(src[u]) : *src[u];
-                    for (int sidx = 1; sidx < S; ++sidx) {
+#pragma unroll 2
+                    for (int sidx = 1; sidx < S; ++sidx) {   // two partitions' loads in flight; the adds keep partition order
                         float4 v[4];
 #pragma unroll
                         for (int u = 0; u < 4; ++u) v[u] = __ldcg(src[u] + (size_t)sidx * BM * qpr);
@@ -797,26 +799,40 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // memory (DK with the channel roles swapped, narrow-channel DK) and for channel counts
             // that rule out 16-byte stores.
             const long long ro = s_rowoff[tid_e];
-            for (int cl = 0; cl < CL; ++cl) {
-                const int col = cl * S + part;
-                if (col >= ncols_valid) break;
-                float acc;
+            for (int cl0 = 0; cl0 < CL; cl0 += 4) {   // four columns at a time: their loads are in flight together
+                float acc[4];
+                int cols[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int col = (cl0 + u) * S + part;
+                    cols[u] = (cl0 + u < CL && col < ncols_valid) ? col : -1;
+                    const int cc = cols[u] < 0 ? 0 : cols[u];
+                    acc[u] = multi ? __ldcg(tile_scratch + (size_t)cc * BM + tid_e) : red[cc * BM + tid_e];
+                }
                 if (multi) {
-                    const float* src = tile_scratch + (size_t)col * BM + tid_e;
-                    acc = __ldcg(src);
-                    for (int sidx = 1; sidx < S; ++sidx) acc = __fadd_rn(acc, __ldcg(src + (size_t)sidx * BM * p.bn));
-                } else {
-                    acc = red[col * BM + tid_e];
+                    for (int sidx = 1; sidx < S; ++sidx) {
+                        float v[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            v[u] = __ldcg(tile_scratch + ((size_t)sidx * p.bn + (cols[u] < 0 ? 0 : cols[u])) * BM + tid_e);
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) acc[u] = __fadd_rn(acc[u], v[u]);
+                    }
                 }
                 if (ro < 0) continue;
-                unsigned long long id = (unsigned long long)ro + (unsigned long long)col * col_stride;
-                if (MODE == MODE_DK && p.narrow) {
-                    const int di = col >> 5, dj = (col & 31) >> 2, c = col & 3;   // slot = 4*dj + channel
-                    if (dj >= p.KW || c >= p.C) continue;                          // padding slots
-                    id = (unsigned long long)ro + (unsigned long long)((di * p.KW + dj) * p.C + c) * p.O;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int col = cols[u];
+                    if (col < 0) continue;
+                    unsigned long long id = (unsigned long long)ro + (unsigned long long)col * col_stride;
+                    if (MODE == MODE_DK && p.narrow) {
+                        const int di = col >> 5, dj = (col & 31) >> 2, c = col & 3;   // slot = 4*dj + channel
+                        if (dj >= p.KW || c >= p.C) continue;                          // padding slots
+                        id = (unsigned long long)ro + (unsigned long long)((di * p.KW + dj) * p.C + c) * p.O;
+                    }
+                    // the fused chain only exists for FWD/DX; DK stores raw sums
+                    p.out[id] = (MODE == MODE_DK) ? acc[u] : epilogue_apply(e, acc[u], id, ch0 + col);
                 }
-                // the fused chain only exists for FWD/DX; DK stores raw sums
-                p.out[id] = (MODE == MODE_DK) ? acc : epilogue_apply(e, acc, id, ch0 + col);
             }
         }
     }
