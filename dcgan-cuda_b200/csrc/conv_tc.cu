@@ -43,7 +43,8 @@ namespace {
 constexpr int BM = 128;                 // accumulator rows (TMEM lanes)
 constexpr int BK = 32;                  // K elements per pipeline stage (one 128-byte swizzle row)
 constexpr int A_STAGE_BYTES = BM * BK * 4;
-constexpr int kThreads = 192;
+constexpr int kEpi = 256;               // epilogue threads: warps 2..9, two per TMEM lane quadrant
+constexpr int kThreads = 64 + kEpi;
 constexpr int kMaxSmem = 227 * 1024;
 constexpr int kMaxCluster = 8;          // portable thread-block cluster size: the cap on K partitions
 // Floats of shared memory the epilogue's transposition buffer takes for a 128 x bn tile (quads at a
@@ -320,7 +321,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int s = 0; s < p.stages; ++s) {
             mbar_init(full_bar + 8u * s, 1);
             mbar_init(empty_bar + 8u * s, 1);
-            mbar_init(resid_bar + 8u * s, 128);
+            mbar_init(resid_bar + 8u * s, kEpi);
         }
         mbar_init(tmem_full_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -593,9 +594,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const float4* bsrc = reinterpret_cast<const float4*>(smem_raw + (b_base + (uint32_t)s * b_stage_bytes - smem_u32(smem_raw)));
                 float4* bdst = reinterpret_cast<float4*>(smem_raw + (bs_base + (uint32_t)s * b_stage_bytes - smem_u32(smem_raw)));
 #pragma unroll 4
-                for (int i = tid_r; i < a_q; i += 128) adst[i] = tf32_residual(asrc[i]);
+                for (int i = tid_r; i < a_q; i += kEpi) adst[i] = tf32_residual(asrc[i]);
 #pragma unroll 4
-                for (int i = tid_r; i < b_q; i += 128) bdst[i] = tf32_residual(bsrc[i]);
+                for (int i = tid_r; i < b_q; i += kEpi) bdst[i] = tf32_residual(bsrc[i]);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor core reads
                 asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(resid_bar + 8u * s) : "memory");
                 if (++s == p.stages) { s = 0; phase ^= 1u; }
@@ -635,7 +636,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp >= 2) {
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
-        for (int c0 = 0; c0 < p.bn; c0 += 32) {
+        // the two warps of a lane quadrant (2..5 and 6..9) take alternate 32-column slabs
+        for (int c0 = ((warp - 2) >> 2) * 32; c0 < p.bn; c0 += 64) {
             uint32_t r[32];
             const uint32_t taddr = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0;
             const bool full = p.bn - c0 >= 32;   // bn is a multiple of 16: the last slab has 32 or 16 columns
@@ -681,7 +683,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     TC_CTA_TRACE(3);
     __syncwarp();
     if (multi && finish_here) cluster_sync_all();
-    else if (warp >= 2) asm volatile("bar.sync 1, 128;" ::: "memory");
+    else if (warp >= 2) asm volatile("bar.sync 1, %0;" ::"n"(kEpi) : "memory");
     if (threadIdx.x == 64) TC_TRACE(3002);
     TC_CTA_TRACE(4);
 
@@ -695,11 +697,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // consecutive lanes on consecutive quads, so a warp stores whole 128-byte row segments.
             const int Qm = min(QPO, qpr - part * QPO);
             const bool by_row = multi || p.planes;               // thread = row (else: lanes walk the quads of a row)
-            const int per_thread = multi ? Qm : qpr;             // items per thread (128 * qpr items / 128 threads)
+            // by_row: the two threads of a row (tid_e and tid_e + 128) take alternate quads
+            const int my_row = tid_e & (BM - 1), my_half = tid_e >> 7;
+            const int row_quads = multi ? Qm : qpr;              // by_row: quads of this row's share
+            const int per_thread = by_row ? (row_quads > my_half ? (row_quads - my_half + 1) / 2 : 0)
+                                          : qpr / 2;            // single: 128 * qpr items over 256 threads (qpr is even)
             const int quad0 = ch0 >> 2;                          // planes: global index of this tile's first quad
-            const int step_r = 128 / qpr, step_q = 128 % qpr;    // single: how (row, quad) moves when the item index grows by 128
+            const int step_r = kEpi / qpr, step_q = kEpi % qpr;  // single: how (row, quad) moves when the item index grows by kEpi
             int rr = tid_e / qpr, q = tid_e % qpr;
-            const long long my_ro = s_rowoff[tid_e];
+            const long long my_ro = s_rowoff[my_row];
             const float4* red4 = reinterpret_cast<const float4*>(red);
             const float4* ts4 = reinterpret_cast<const float4*>(tile_scratch);
             for (int base = 0; base < per_thread; base += 4) {
@@ -711,12 +717,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
                         const bool in = base + u < per_thread;
-                        const int qd = part * QPO + (in ? base + u : 0);
+                        const int qd = part * QPO + (in ? my_half + 2 * (base + u) : 0);
                         cq[u] = qd << 2;
                         goff[u] = (!in || my_ro < 0 || cq[u] >= ncols_valid) ? -1
                                   : p.planes ? my_ro + (long long)((unsigned long long)(quad0 + qd) * p.plane_stride)
                                              : my_ro + cq[u];
-                        src[u] = (multi ? ts4 + (size_t)qd * BM : red4 + qd * QS) + tid_e;
+                        src[u] = (multi ? ts4 + (size_t)qd * BM : red4 + qd * QS) + my_row;
                     }
 #pragma unroll
                     for (int u = 0; u < 4; ++u) acc[u] = multi ? __ldcg(src[u]) : *src[u];
@@ -798,23 +804,25 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // thread = row; share = every S-th column.  Used where consecutive ROWS are adjacent in
             // memory (DK with the channel roles swapped, narrow-channel DK) and for channel counts
             // that rule out 16-byte stores.
-            const long long ro = s_rowoff[tid_e];
-            for (int cl0 = 0; cl0 < CL; cl0 += 4) {   // four columns at a time: their loads are in flight together
+            const int my_row = tid_e & (BM - 1), my_half = tid_e >> 7;   // the two threads of a row take alternate columns
+            const long long ro = s_rowoff[my_row];
+            for (int cl0 = 0; 2 * cl0 + my_half < CL; cl0 += 4) {   // four columns at a time: their loads are in flight together
                 float acc[4];
                 int cols[4];
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
-                    const int col = (cl0 + u) * S + part;
-                    cols[u] = (cl0 + u < CL && col < ncols_valid) ? col : -1;
+                    const int cl = 2 * (cl0 + u) + my_half;
+                    const int col = cl * S + part;
+                    cols[u] = (cl < CL && col < ncols_valid) ? col : -1;
                     const int cc = cols[u] < 0 ? 0 : cols[u];
-                    acc[u] = multi ? __ldcg(tile_scratch + (size_t)cc * BM + tid_e) : red[cc * BM + tid_e];
+                    acc[u] = multi ? __ldcg(tile_scratch + (size_t)cc * BM + my_row) : red[cc * BM + my_row];
                 }
                 if (multi) {
                     for (int sidx = 1; sidx < S; ++sidx) {
                         float v[4];
 #pragma unroll
                         for (int u = 0; u < 4; ++u)
-                            v[u] = __ldcg(tile_scratch + ((size_t)sidx * p.bn + (cols[u] < 0 ? 0 : cols[u])) * BM + tid_e);
+                            v[u] = __ldcg(tile_scratch + ((size_t)sidx * p.bn + (cols[u] < 0 ? 0 : cols[u])) * BM + my_row);
 #pragma unroll
                         for (int u = 0; u < 4; ++u) acc[u] = __fadd_rn(acc[u], v[u]);
                     }
