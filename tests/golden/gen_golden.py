@@ -7,8 +7,8 @@ reference's own CPU implementation (src/cpu/ops.hxx), compiled from its sources
 into oracle/_ref/ and called through oracle.reference() - the same arithmetic
 `RT_MODE=CPU` runs.  The graph each case evaluates follows the test's main().
 
-Needs a reference checkout (DCGAN_REFERENCE_DIR, default /root/reference); the
-committed .npz is what travels.
+Needs a reference checkout (environment variable DCGAN_REFERENCE_DIR, or the default
+of oracle/build_oracle.py); the committed .npz is what travels.
 
 Run: ``python tests/golden/gen_golden.py``
 """
