@@ -32,6 +32,8 @@ struct AdamBatch {
 
 struct AdamCoeffs {
     float lr_t, a1, b1, a2, b2, eps, scale;
+    const float* lr_t_dev;   // non-null: the step size is read from device memory instead (a captured
+                             // launch then serves every step: the host only rewrites the scalar)
 };
 
 __device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, const AdamCoeffs& c)
@@ -42,9 +44,11 @@ __device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, 
 }
 
 __global__ void __launch_bounds__(kAdamThreads)
-adam_multi_kernel(const __grid_constant__ AdamBatch batch, const AdamCoeffs c)
+adam_multi_kernel(const __grid_constant__ AdamBatch batch, const AdamCoeffs c_in)
 {
     pdl_enter();
+    AdamCoeffs c = c_in;
+    if (c.lr_t_dev) c.lr_t = __ldg(c.lr_t_dev);
     // which tensor does this block belong to?
     int t = 0;
     while (t + 1 < batch.count && blockIdx.x >= batch.block_begin[t + 1]) ++t;
@@ -160,10 +164,11 @@ int adam_apply_launch(const float* m, const float* v, float* out, float lr_t, fl
 }
 
 int adam_multi_launch(const dcg_adam_tensor* tensors, int count, float lr_t, float a1, float b1,
-                      float a2, float b2, float eps, float grad_scale, cudaStream_t stream)
+                      float a2, float b2, float eps, float grad_scale, cudaStream_t stream,
+                      const float* lr_t_dev)
 {
     DCG_CHECK_ARG(count >= 0 && (count == 0 || tensors), "adam: bad tensor list");
-    AdamCoeffs c{lr_t, a1, b1, a2, b2, eps, grad_scale};
+    AdamCoeffs c{lr_t, a1, b1, a2, b2, eps, grad_scale, lr_t_dev};
     int done = 0;
     while (done < count) {
         AdamBatch batch;

@@ -96,6 +96,7 @@ struct Params {
     int planes;                   // FWD: 16-byte column quad q of output pixel r goes to out[(q * pixels + r) * 4]
     int o_store;                  // FWD: output columns >= o_store are padding and never stored (0: store all O)
     int x3;                       // 3xTF32: every operand tile gets a residual tile, three MMAs per K step
+    int group0;                   // added to the group decoded from blockIdx (DX launched one parity class at a time)
     unsigned long long plane_stride;  // planes: elements between two quads' planes (4 * pixels)
     int debug;                    // timing experiments (DCG_TC_DEBUG): 1 = no MMA, 2 = no TMA; results are garbage
     int stages;                   // pipeline depth
@@ -349,7 +350,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (MODE == MODE_DK) m_count = p.m_tiles;
     else m_count = p.tiles_w * p.tiles_h * p.tiles_n;
     const int m_tile = rem % m_count;
-    const int group = rem / m_count;
+    const int group = p.group0 + rem / m_count;
 
     // pixel-tile origin (FWD/DX)
     int j0 = 0, i0 = 0, n0 = 0;
@@ -1078,6 +1079,10 @@ struct Plan {
     // weights k2 and the GEMM result ycol follow the partial tiles in the scratch area
     int Jp = 0;
     size_t k2_bytes = 0, ycol_bytes = 0;
+    // DX with few tiles: one launch per parity class, each with its own number of K partitions, so
+    // that a CTA of the 9-tap class does as many pipeline stages as a CTA of the 4-tap class
+    int n_class = 0;
+    int class_splits[16] = {0}, class_grid[16] = {0};
     size_t k2_off() const { return align_up(partial_bytes, 256); }
     size_t ycol_off() const { return k2_off() + align_up(k2_bytes, 256); }
     size_t xp_off() const { return align_up(partial_bytes, 256); }
@@ -1251,6 +1256,51 @@ bool plan_dx(const dcg_conv_desc& d, Plan& pl)
     const int min_taps = (d.kh / d.stride_h) * (d.kw / d.stride_w);
     p.splits = choose_splits(tiles, (min_taps < 1 ? 1 : min_taps) * p.kchunks, p.bn > 128 ? 1 : 2);
     pl.grid = tiles * p.splits;
+    // The parity classes have different tap counts (9, 6, 6, 4 for 5x5 stride 2).  When all CTAs of
+    // the layer are resident at once, the launch lasts as long as its slowest CTA.  DCG_TC_CLASS_BALANCE=1
+    // gives every class its own launch (side by side on four streams) and as many K partitions as
+    // make its CTAs about equally long.  Measured: the main loops do level out, but four launches
+    // with four cluster shapes cost more than that wins (1.826 against 1.784 ms per training step),
+    // so it is off unless asked for.
+    static const int balance = env_int("DCG_TC_CLASS_BALANCE");
+    const int slots = 2 * sm_count();
+    if (balance && !t_plan_x3 && !env_int("DCG_TC_SPLITS") && classes > 1 && classes <= 16 && p.bn <= 128 &&
+        tiles < slots) {
+        const int per_class = tiles / classes;
+        int stages_c[16];
+        for (int c = 0; c < classes; ++c) {
+            const int ph = c / d.stride_w, pw = c % d.stride_w;
+            const int rh = (ph + d.pad_top) % d.stride_h, rw = (pw + d.pad_left) % d.stride_w;
+            const int th = rh < d.kh ? (d.kh - rh + d.stride_h - 1) / d.stride_h : 0;
+            const int tw = rw < d.kw ? (d.kw - rw + d.stride_w - 1) / d.stride_w : 0;
+            stages_c[c] = th * tw * p.kchunks;
+        }
+        // smallest stage count per CTA (>= 4) whose partition counts fit the resident slots
+        for (int len = 4; len <= 4096; ++len) {
+            int ctas = 0;
+            bool ok = true;
+            for (int c = 0; c < classes; ++c) {
+                int sc = (stages_c[c] + len - 1) / len;
+                if (sc < 1) sc = 1;
+                if (sc > kMaxCluster) ok = false;
+                ctas += per_class * sc;
+            }
+            if (!ok || ctas > slots) continue;
+            pl.n_class = classes;
+            pl.grid = 0;
+            int smax = 1;
+            for (int c = 0; c < classes; ++c) {
+                int sc = (stages_c[c] + len - 1) / len;
+                if (sc < 1) sc = 1;
+                pl.class_splits[c] = sc;
+                pl.class_grid[c] = per_class * sc;
+                pl.grid += pl.class_grid[c];
+                if (sc > smax) smax = sc;
+            }
+            p.splits = smax;   // "has K partitions" for the scratch sizing below
+            break;
+        }
+    }
     finish_plan(pl);
     return true;
 }
@@ -1309,6 +1359,67 @@ bool make_plan(const dcg_conv_desc& d, int kind, Plan& pl)
     }
 }
 
+// Streams and events for launching the parity classes of a DX side by side (per device, made on
+// first use; calls that use them are serialised by the mutex).
+struct ClassStreams {
+    cudaStream_t side[3] = {nullptr, nullptr, nullptr};
+    cudaEvent_t fork = nullptr, join[3] = {nullptr, nullptr, nullptr};
+    std::mutex mutex;
+    bool ok = false, tried = false;
+};
+
+ClassStreams* class_streams()
+{
+    static ClassStreams per_device[64];
+    static std::mutex init_mutex;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    ClassStreams& cs = per_device[dev];
+    std::lock_guard<std::mutex> lock(init_mutex);
+    if (!cs.tried) {
+        cs.tried = true;
+        bool ok = cudaEventCreateWithFlags(&cs.fork, cudaEventDisableTiming) == cudaSuccess;
+        for (int i = 0; i < 3 && ok; ++i)
+            ok = cudaStreamCreateWithFlags(&cs.side[i], cudaStreamNonBlocking) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&cs.join[i], cudaEventDisableTiming) == cudaSuccess;
+        if (!ok) cudaGetLastError();
+        cs.ok = ok;
+    }
+    return cs.ok ? &cs : nullptr;
+}
+
+template <int MODE>
+int launch_grid(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, int grid, size_t smem, cudaStream_t stream)
+{
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    static const int no_pdl = env_int("DCG_TC_NO_PDL");
+    if (!no_pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (p.splits > 1 && !p.ext_finish) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = (unsigned)p.splits;   // blockIdx.x = tile * splits + split: one cluster per tile
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    const cudaError_t err = p.x3 ? cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE, true>, ma, mb, p)
+                                 : cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE, false>, ma, mb, p);
+    if (err != cudaSuccess) return fail(DCG_ERR_CUDA, "conv_tc_kernel launch: %s", cudaGetErrorString(err));
+    count_launch();
+    return DCG_OK;
+}
+
 template <int MODE>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, Plan& pl, float* out, const EpilogueArgs& ep,
            int channels, void* ws, size_t ws_bytes, cudaStream_t stream)
@@ -1332,32 +1443,33 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, Plan& pl, float* out, c
         p.scratch = static_cast<float*>(ws);
     }
     (void)channels;
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3((unsigned)pl.grid);
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = pl.smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
-    int na = 0;
-    static const int no_pdl = env_int("DCG_TC_NO_PDL");
-    if (!no_pdl) {
-        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[na].val.programmaticStreamSerializationAllowed = 1;
-        ++na;
+    if (pl.n_class > 0) {
+        // one launch per parity class, concurrently: class 0 on the caller's stream, the others on
+        // side streams forked from it and joined back
+        ClassStreams* cs = class_streams();
+        if (!cs) return fail(DCG_ERR_CUDA, "conv dx: could not create the per-class streams");
+        std::lock_guard<std::mutex> lock(cs->mutex);
+        DCG_CUDA(cudaEventRecord(cs->fork, stream));
+        size_t ctas_before = 0;
+        for (int c = 0; c < pl.n_class; ++c) {
+            Params pc = p;
+            pc.group0 = c;
+            pc.splits = pl.class_splits[c];
+            if (p.scratch) pc.scratch = p.scratch + ctas_before * BM * p.bn;
+            ctas_before += (size_t)pl.class_grid[c];
+            cudaStream_t sc = c == 0 ? stream : cs->side[(c - 1) % 3];
+            if (c > 0 && c <= 3) DCG_CUDA(cudaStreamWaitEvent(sc, cs->fork, 0));
+            const int st = launch_grid<MODE>(ma, mb, pc, pl.class_grid[c], pl.smem, sc);
+            if (st) return st;
+        }
+        for (int i = 0; i < 3 && i + 1 < pl.n_class; ++i) {
+            DCG_CUDA(cudaEventRecord(cs->join[i], cs->side[i]));
+            DCG_CUDA(cudaStreamWaitEvent(stream, cs->join[i], 0));
+        }
+        return DCG_OK;
     }
-    if (p.splits > 1 && !p.ext_finish) {
-        attr[na].id = cudaLaunchAttributeClusterDimension;
-        attr[na].val.clusterDim.x = (unsigned)p.splits;   // blockIdx.x = tile * splits + split: one cluster per tile
-        attr[na].val.clusterDim.y = 1;
-        attr[na].val.clusterDim.z = 1;
-        ++na;
-    }
-    cfg.attrs = attr;
-    cfg.numAttrs = na;
-    const cudaError_t err = p.x3 ? cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE, true>, ma, mb, p)
-                                 : cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE, false>, ma, mb, p);
-    if (err != cudaSuccess) return fail(DCG_ERR_CUDA, "conv_tc_kernel launch: %s", cudaGetErrorString(err));
-    count_launch();
+    const int st = launch_grid<MODE>(ma, mb, p, pl.grid, pl.smem, stream);
+    if (st) return st;
     if (p.ext_finish) {
         const dim3 fgrid((unsigned)p.bn, (unsigned)((p.O + 31) / 32));
         launch_pdl(dk_narrow_finish_kernel, fgrid, 256, 0, stream, p.scratch, out, p.splits, p.bn, p.KH, p.KW, p.C, p.O);

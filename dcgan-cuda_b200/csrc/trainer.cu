@@ -99,6 +99,11 @@ struct dcg_trainer {
         bool failed = false;
     };
     ListGraph d_graph, g_graph, gen_graph, g_part_graph[2];
+    // Single-GPU iteration as ONE graph: D list, Adam, G list, Adam, G list, Adam.  The three Adam
+    // step sizes change every iteration, so the captured launches read them from `lr_dev`, which the
+    // host rewrites (one 12-byte copy) before each replay.
+    ListGraph step_graph;
+    Tensor lr_dev;
     size_t g_forward_nodes = 0;   // the G run's leading nodes that only compute the generator's forward pass
     bool use_graphs = true;
 };
@@ -161,6 +166,7 @@ void layout(dcg_trainer* t, Alloc& a)
     if (!a.dry) t->x.p = img2.p + img_n;
     t->z = a.get((size_t)B * kZ);
     t->ones = a.get(B); t->zeros = a.get(B);
+    t->lr_dev = a.get(4);
     t->d_loss = a.get(1); t->d1_loss = a.get(1); t->d2_loss = a.get(1); t->g_loss = a.get(1);
     t->g0z = a.get((size_t)B * 8192); t->g0a = a.get((size_t)B * 8192);
     for (int i = 0; i < kLayers; ++i) {
@@ -496,17 +502,85 @@ int run_list(dcg_trainer* t, const std::vector<dcg_node>& all, dcg_trainer::List
     return DCG_OK;
 }
 
+// step != nullptr: advances the host step counter and passes the step size by value.
+// lr_dev != nullptr: the launch reads the step size from that device scalar (whole-step graph).
 int apply_adam(dcg_trainer* t, Tensor* param, Tensor* grad, Tensor* grad2, Tensor* m, Tensor* v, float* step,
-               float grad_scale)
+               float grad_scale, const float* lr_dev = nullptr)
 {
     dcg_adam_tensor ts[10];
     for (int i = 0; i < 10; ++i) {
         ts[i].p = param[i].p; ts[i].g = grad[i].p; ts[i].g2 = grad2 ? grad2[i].p : nullptr;
         ts[i].m = m[i].p; ts[i].v = v[i].p; ts[i].n = param[i].n;
     }
-    const float lr_t = dcg_adam_lr_t(step, t->cfg.lr, t->cfg.beta1, t->cfg.beta2);
+    const float lr_t = lr_dev ? 0.f : dcg_adam_lr_t(step, t->cfg.lr, t->cfg.beta1, t->cfg.beta2);
     dcg::ProfScope scope(t->ctx, "adam_multi", 0.0);
-    return dcg_adam_multi(ts, 10, lr_t, t->cfg.beta1, t->cfg.beta2, t->cfg.eps, grad_scale, t->stream);
+    return dcg::adam_multi_launch(ts, 10, lr_t, t->cfg.beta1, 1.f - t->cfg.beta1, t->cfg.beta2, 1.f - t->cfg.beta2,
+                                  t->cfg.eps, grad_scale, t->stream, lr_dev);
+}
+
+// The whole single-GPU iteration, enqueued node list by node list (used eagerly and under capture).
+int enqueue_step(dcg_trainer* t, const float* lr_dev)
+{
+    int st;
+    Tensor* d_second = (t->cfg.world > 1 || t->batched_d) ? nullptr : t->d_grad2;
+    if ((st = dcg_run_nodes(t->ctx, t->d_nodes.data(), (int)t->d_nodes.size(), t->cfg.fuse))) return st;
+    if ((st = apply_adam(t, t->d_param, t->d_grad, d_second, t->d_m, t->d_v, &t->d_t, 1.f, lr_dev))) return st;
+    for (int rep = 0; rep < 2; ++rep) {
+        if ((st = dcg_run_nodes(t->ctx, t->g_nodes.data(), (int)t->g_nodes.size(), t->cfg.fuse))) return st;
+        if ((st = apply_adam(t, t->g_param, t->g_grad, nullptr, t->g_m, t->g_v, &t->g_t, 1.f,
+                             lr_dev ? lr_dev + 1 + rep : nullptr)))
+            return st;
+    }
+    return DCG_OK;
+}
+
+// Replays (capturing first if need be) the whole-iteration graph.  Returns 1 if it did, 0 if the
+// caller should run the phases instead, a negative status on error.
+int step_as_one_graph(dcg_trainer* t)
+{
+    dcg_trainer::ListGraph& g = t->step_graph;
+    if (!t->use_graphs || g.failed || t->cfg.world > 1 || dcg::context_is_profiling(t->ctx)) return 0;
+    if (t->d_graph.eager_runs < 2 || t->g_graph.eager_runs < 2) return 0;   // lists not warmed up yet
+    if (g.exec && g.ws != dcg::context_workspace(t->ctx)) {
+        cudaGraphExecDestroy(g.exec);
+        g.exec = nullptr;
+    }
+    // this iteration's three step sizes; the copy is from pageable memory, which the runtime stages
+    // before the call returns, so the array may go out of scope
+    float lr[3];
+    lr[0] = dcg_adam_lr_t(&t->d_t, t->cfg.lr, t->cfg.beta1, t->cfg.beta2);
+    lr[1] = dcg_adam_lr_t(&t->g_t, t->cfg.lr, t->cfg.beta1, t->cfg.beta2);
+    lr[2] = dcg_adam_lr_t(&t->g_t, t->cfg.lr, t->cfg.beta1, t->cfg.beta2);
+    if (cudaMemcpyAsync(t->lr_dev.p, lr, sizeof(lr), cudaMemcpyHostToDevice, t->stream) != cudaSuccess)
+        return fail(DCG_ERR_CUDA, "dcg_trainer_step: copy of the Adam step sizes failed");
+    if (!g.exec) {
+        const uint64_t before = dcg_launches_total();
+        cudaGraph_t graph = nullptr;
+        bool ok = cudaStreamBeginCapture(t->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+        int st = DCG_OK;
+        if (ok) {
+            st = enqueue_step(t, t->lr_dev.p);
+            ok = cudaStreamEndCapture(t->stream, &graph) == cudaSuccess && st == DCG_OK && graph &&
+                 cudaGraphInstantiate(&g.exec, graph, 0) == cudaSuccess;
+        }
+        if (graph) cudaGraphDestroy(graph);
+        const uint64_t captured = dcg_launches_total() - before;
+        dcg::count_launch(-(int)captured);   // a capture launches nothing
+        if (!ok) {
+            cudaGetLastError();
+            g.exec = nullptr;
+            g.failed = true;
+            if (getenv("DCG_TRAINER_VERBOSE")) fprintf(stderr, "dcg_trainer: whole-step graph capture failed; using per-list graphs\n");
+            // the step counters already advanced: finish this iteration eagerly with the same step sizes
+            return (st = enqueue_step(t, t->lr_dev.p)) ? st : 1;
+        }
+        g.launches = captured;
+        g.ws = dcg::context_workspace(t->ctx);
+    }
+    if (cudaGraphLaunch(g.exec, t->stream) != cudaSuccess)
+        return fail(DCG_ERR_CUDA, "cudaGraphLaunch: %s", cudaGetErrorString(cudaGetLastError()));
+    dcg::count_launch((int)g.launches);
+    return 1;
 }
 
 }  // namespace
@@ -563,7 +637,8 @@ extern "C" int dcg_trainer_create(dcg_trainer** out, const dcg_trainer_config* c
 extern "C" void dcg_trainer_destroy(dcg_trainer* t)
 {
     if (!t) return;
-    for (dcg_trainer::ListGraph* g : {&t->d_graph, &t->g_graph, &t->gen_graph, &t->g_part_graph[0], &t->g_part_graph[1]})
+    for (dcg_trainer::ListGraph* g : {&t->d_graph, &t->g_graph, &t->gen_graph, &t->g_part_graph[0], &t->g_part_graph[1],
+                                      &t->step_graph})
         if (g->exec) cudaGraphExecDestroy(g->exec);
     if (t->ctx) dcg_context_destroy(t->ctx);
     if (t->arena) cudaFree(t->arena);
@@ -621,7 +696,12 @@ extern "C" int dcg_trainer_step(dcg_trainer* t)
     DCG_CHECK_ARG(t, "dcg_trainer_step: null trainer");
     DCG_CHECK_ARG(t->cfg.world <= 1, "dcg_trainer_step: data-parallel callers drive the phases themselves");
     const uint64_t before = dcg_launches_total();
-    int st;
+    int st = step_as_one_graph(t);
+    if (st < 0) return st;
+    if (st == 1) {
+        t->last_step_launches = dcg_launches_total() - before;
+        return DCG_OK;
+    }
     if ((st = dcg_trainer_d_backward(t))) return st;
     if ((st = dcg_trainer_d_apply(t, 1.f))) return st;
     for (int rep = 0; rep < 2; ++rep) {

@@ -104,32 +104,29 @@ class Trainer:
 
     def _step(self):
         """Body of one iteration; runs with the trainer's stream current."""
+        if self.world == 1:
+            check(lib.dcg_trainer_step(self._h))   # the whole iteration, one CUDA graph once warmed up
+            return
+        # Data parallel: the discriminator's gradients are summed over ranks on a communication stream
+        # while this stream already computes the generator's forward pass of the first G update, which
+        # reads neither the discriminator's gradients nor its parameters.
         scale = 1.0 / self.world
         check(lib.dcg_trainer_d_backward(self._h))
-        if self.world > 1:
-            # The discriminator's gradients are summed over ranks on a communication stream while
-            # this stream already computes the generator's forward pass of the first G update, which
-            # reads neither the discriminator's gradients nor its parameters.
-            if self._comm is None:
-                self._comm = torch.cuda.Stream(self.device)
-            main = torch.cuda.current_stream(self.device)
-            self._comm.wait_stream(main)
-            with torch.cuda.stream(self._comm):
-                self._allreduce(self.d_grads)
-            check(lib.dcg_trainer_g_backward_part(self._h, 0))
-            main.wait_stream(self._comm)
-            check(lib.dcg_trainer_d_apply(self._h, scale))
-            check(lib.dcg_trainer_g_backward_part(self._h, 1))
-            self._allreduce(self.g_grads)
-            check(lib.dcg_trainer_g_apply(self._h, scale))
-            check(lib.dcg_trainer_g_backward(self._h))
-            self._allreduce(self.g_grads)
-            check(lib.dcg_trainer_g_apply(self._h, scale))
-            return
+        if self._comm is None:
+            self._comm = torch.cuda.Stream(self.device)
+        main = torch.cuda.current_stream(self.device)
+        self._comm.wait_stream(main)
+        with torch.cuda.stream(self._comm):
+            self._allreduce(self.d_grads)
+        check(lib.dcg_trainer_g_backward_part(self._h, 0))
+        main.wait_stream(self._comm)
         check(lib.dcg_trainer_d_apply(self._h, scale))
-        for _ in range(2):
-            check(lib.dcg_trainer_g_backward(self._h))
-            check(lib.dcg_trainer_g_apply(self._h, scale))
+        check(lib.dcg_trainer_g_backward_part(self._h, 1))
+        self._allreduce(self.g_grads)
+        check(lib.dcg_trainer_g_apply(self._h, scale))
+        check(lib.dcg_trainer_g_backward(self._h))
+        self._allreduce(self.g_grads)
+        check(lib.dcg_trainer_g_apply(self._h, scale))
 
     def step(self):
         """One training iteration on inputs already resident in self.x / self.z."""

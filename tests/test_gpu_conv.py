@@ -233,3 +233,39 @@ def test_deterministic(pkg, dev):
     torch.cuda.synchronize()
     for u, v in zip(a, b):
         assert torch.equal(u, v)
+
+
+def test_workspace_and_alignment_contract(pkg, dev, orc):
+    """What the entry points promise about their operands: a tensor-path call that needs scratch
+    refuses a buffer that is too small (nothing is launched, the output stays untouched) and says how
+    much it wants; operands that are not 16-byte aligned (which TMA cannot address) silently take the
+    CUDA-core path, whose result is the oracle's bit for bit."""
+    import ctypes
+    F, L = pkg.functional, pkg.lib
+    # 128 -> 256 channels at batch 8: few tiles, so the K partitions need scratch
+    g = torch.Generator(device="cpu").manual_seed(41)
+    x = (torch.rand((8, 16, 16, 128), generator=g) * 2 - 1).to(dev)
+    k = (torch.randn((5, 5, 128, 256), generator=g) * 0.02).to(dev)
+    d = F.conv_desc(x.shape, k.shape, (2, 2), None, None)
+    need = L.dcg_conv_workspace_bytes(ctypes.byref(d), pkg._lib.KIND_FWD, pkg.PREC_TF32)
+    assert need > 0
+    y = torch.full((8, 8, 8, 256), 7.0, device=dev)
+    small = torch.empty(need // 2, dtype=torch.uint8, device=dev)
+    st = L.dcg_conv2d_fwd(ctypes.byref(d), x.data_ptr(), k.data_ptr(), y.data_ptr(), None, pkg.PREC_TF32,
+                          small.data_ptr(), small.numel(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert st == pkg._lib.ERR_WORKSPACE and b"workspace" in L.dcg_last_error()
+    assert bool((y == 7.0).all())
+    assert L.dcg_conv_workspace_bytes(ctypes.byref(d), pkg._lib.KIND_FWD, pkg.PREC_FP32) == 0
+
+    # the same small layer from a buffer that starts 4 bytes off a 16-byte boundary
+    xs = seeded((2, 8, 8, 32), 42)
+    ks = seeded((5, 5, 32, 64), 43) * np.float32(0.1)
+    raw = torch.empty(xs.size + 1, device=dev)
+    xo = raw[1:].view(2, 8, 8, 32)
+    xo.copy_(torch.from_numpy(xs))
+    assert xo.data_ptr() % 16 == 4
+    y_off = F.conv2d_fwd(xo, torch.from_numpy(ks).to(dev), precision=pkg.PREC_TF32)
+    torch.cuda.synchronize()
+    assert np.array_equal(y_off.cpu().numpy(), orc.conv2d(xs, ks, (2, 2)))
+
