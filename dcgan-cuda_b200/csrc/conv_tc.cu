@@ -1116,7 +1116,13 @@ int tile_width(int n_ch)
     return n_ch >= 128 ? 128 : n_ch;
 }
 
-int choose_splits(int tiles, int min_stages_per_tile, int ctas_per_sm = 2)
+// K partitions of a tile.  Measured on every DCGAN layer at batch 64 (per-CTA timelines, partition
+// counts 1..8 forced): the shortest launch is the one with about ONE CTA per SM - a deeper pipeline
+// per CTA and half the partial-tile traffic beat a second resident CTA (e.g. the 256 -> 512 forward
+// layer: 18.5 us with 4 partitions = 128 CTAs against 22.3 us with 8 = 256).  The exception is the
+// kernel gradient with the channel roles swapped (its finish phase walks columns one by one and
+// gains from more, smaller shares): two CTAs per SM there.
+int choose_splits(int tiles, int min_stages_per_tile, int ctas_per_sm = 1)
 {
     static const int forced = env_int("DCG_TC_SPLITS");
     if (forced > 0) {
@@ -1132,7 +1138,7 @@ int choose_splits(int tiles, int min_stages_per_tile, int ctas_per_sm = 2)
         return s < 1 ? 1 : s;
     }
     if (tiles >= sms) return 1;
-    int s = (ctas_per_sm * sms) / tiles;             // aim at ~2 CTAs per SM (1 for 256-column tiles)
+    int s = (ctas_per_sm * sms) / tiles;
     const int cap = min_stages_per_tile / 4;         // keep at least 4 K stages per CTA
     if (s > cap) s = cap;
     if (s > kMaxCluster) s = kMaxCluster;
@@ -1207,7 +1213,7 @@ bool plan_fwd(const dcg_conv_desc& d, Plan& pl)
         narrow_geometry(d, pl);
         pl.k4_bytes = (size_t)d.kh * 32 * d.o * sizeof(float);
     }
-    p.splits = choose_splits(tiles, narrow ? d.kh : d.kh * d.kw * p.kchunks, p.bn > 128 ? 1 : 2);
+    p.splits = choose_splits(tiles, narrow ? d.kh : d.kh * d.kw * p.kchunks);
     pl.grid = tiles * p.splits;
     finish_plan(pl);
     return true;
@@ -1254,7 +1260,7 @@ bool plan_dx(const dcg_conv_desc& d, Plan& pl)
     const int classes = d.stride_h * d.stride_w;
     const int tiles = classes * p.tiles_w * p.tiles_h * p.tiles_n * p.n_tiles;
     const int min_taps = (d.kh / d.stride_h) * (d.kw / d.stride_w);
-    p.splits = choose_splits(tiles, (min_taps < 1 ? 1 : min_taps) * p.kchunks, p.bn > 128 ? 1 : 2);
+    p.splits = choose_splits(tiles, (min_taps < 1 ? 1 : min_taps) * p.kchunks);
     pl.grid = tiles * p.splits;
     // The parity classes have different tap counts (9, 6, 6, 4 for 5x5 stride 2).  When all CTAs of
     // the layer are resident at once, the launch lasts as long as its slowest CTA.  DCG_TC_CLASS_BALANCE=1
@@ -1343,7 +1349,7 @@ bool plan_dk(const dcg_conv_desc& d, Plan& pl)
     p.bn = tile_width(n_ch);
     p.n_tiles = (n_ch + p.bn - 1) / p.bn;
     const int tiles = d.kh * d.kw * p.m_tiles * p.n_tiles;
-    p.splits = choose_splits(tiles, p.tiles_w * p.tiles_h * p.tiles_n, p.bn > 128 ? 1 : 2);
+    p.splits = choose_splits(tiles, p.tiles_w * p.tiles_h * p.tiles_n, p.swap ? 2 : 1);
     pl.grid = tiles * p.splits;
     finish_plan(pl);
     return true;
