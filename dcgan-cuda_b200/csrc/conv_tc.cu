@@ -1269,7 +1269,7 @@ bool plan_dx(const dcg_conv_desc& d, Plan& pl)
     // with four cluster shapes cost more than that wins (1.826 against 1.784 ms per training step),
     // so it is off unless asked for.
     static const int balance = env_int("DCG_TC_CLASS_BALANCE");
-    const int slots = 2 * sm_count();
+    const int slots = sm_count();
     if (balance && !t_plan_x3 && !env_int("DCG_TC_SPLITS") && classes > 1 && classes <= 16 && p.bn <= 128 &&
         tiles < slots) {
         const int per_class = tiles / classes;
