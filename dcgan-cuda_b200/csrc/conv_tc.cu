@@ -18,10 +18,12 @@
 //        reduction over pixels; both operands have the reduction index outermost in memory, so
 //        both tiles are MN-major (32 pixels x 128 channels / BN channels), 5-D maps.
 //
-// CTA = 192 threads: warp 0 issues TMA, warp 1 owns TMEM and issues tcgen05.mma, warps 2-5 drain the
+// CTA = 320 threads: warp 0 issues TMA, warp 1 owns TMEM and issues tcgen05.mma (both walked by the
+// whole warp with one elected lane issuing), warps 2-9 - two per TMEM lane quadrant - drain the
 // accumulator (tcgen05.ld) through the fused epilogue (raw / bias / pre-activation / activation /
-// activation-gradient gate) into HBM.  A ring of smem stages (A 16 KB + B BN*128 B, 128-byte
-// swizzle) is handed over with mbarriers: TMA complete_tx -> MMA, tcgen05.commit -> TMA.
+// activation-gradient gate) into HBM; in the 3xTF32 variant they also build the residual tiles of
+// every stage.  A ring of smem stages (A 16 KB + B BN*128 B, 128-byte swizzle; 7 deep with one
+// CTA per SM) is handed over with mbarriers: TMA complete_tx -> MMA, tcgen05.commit -> TMA.
 // The K partitions of one tile form a thread-block cluster: each writes its fp32 partial tile to
 // scratch (L2-resident), the cluster meets at a hardware barrier, and every CTA then adds the
 // partials of its share of the tile in partition order (deterministic) and finishes it, fused
