@@ -34,11 +34,13 @@ struct dcg_context {
     // Second stream with scratch of its own for nodes flagged DCG_NODE_SIDE (created on first use,
     // only when the context owns its scratch): they fork off the main stream, run concurrently with
     // the nodes that follow, and are joined at the end of the list.
-    cudaStream_t side = nullptr;
-    void* side_ws = nullptr;
-    size_t side_ws_bytes = 0;
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
-    bool side_busy = false, side_failed = false;
+    // Two of them: kernel gradients (convolutions) on one, the small reductions and dense weight
+    // gradients on the other, so that a 10 us column sum does not queue behind a 20 us convolution.
+    cudaStream_t side[2] = {nullptr, nullptr};
+    void* side_ws[2] = {nullptr, nullptr};
+    size_t side_ws_bytes[2] = {0, 0};
+    cudaEvent_t ev_fork = nullptr, ev_join[2] = {nullptr, nullptr};
+    bool side_busy[2] = {false, false}, side_failed = false;
     uint64_t launches_base = 0;
     bool profiling = false;
     std::vector<ProfRec> recs;
@@ -374,10 +376,12 @@ extern "C" void dcg_context_destroy(dcg_context* ctx)
 {
     if (!ctx) return;
     if (ctx->owns_ws && ctx->ws) cudaFree(ctx->ws);
-    if (ctx->side_ws) cudaFree(ctx->side_ws);
+    for (int i = 0; i < 2; ++i) {
+        if (ctx->side_ws[i]) cudaFree(ctx->side_ws[i]);
+        if (ctx->ev_join[i]) cudaEventDestroy(ctx->ev_join[i]);
+        if (ctx->side[i]) cudaStreamDestroy(ctx->side[i]);
+    }
     if (ctx->ev_fork) cudaEventDestroy(ctx->ev_fork);
-    if (ctx->ev_join) cudaEventDestroy(ctx->ev_join);
-    if (ctx->side) cudaStreamDestroy(ctx->side);
     delete ctx;
 }
 
@@ -502,14 +506,16 @@ namespace {
 bool side_usable(dcg_context* ctx)
 {
     if (ctx->side_failed || ctx->profiling || (ctx->ws && !ctx->owns_ws)) return false;
-    if (ctx->side) return true;
+    if (ctx->side[0]) return true;
     static const bool off = [] { const char* v = getenv("DCG_NO_SIDE_STREAM"); return v && atoi(v) != 0; }();
-    if (off || cudaStreamCreateWithFlags(&ctx->side, cudaStreamNonBlocking) != cudaSuccess ||
-        cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
-        cudaEventCreateWithFlags(&ctx->ev_join, cudaEventDisableTiming) != cudaSuccess) {
+    bool ok = !off && cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; i < 2 && ok; ++i)
+        ok = cudaStreamCreateWithFlags(&ctx->side[i], cudaStreamNonBlocking) == cudaSuccess &&
+             cudaEventCreateWithFlags(&ctx->ev_join[i], cudaEventDisableTiming) == cudaSuccess;
+    if (!ok) {
         cudaGetLastError();
         ctx->side_failed = true;
-        ctx->side = nullptr;
+        ctx->side[0] = nullptr;
         return false;
     }
     return true;
@@ -518,29 +524,32 @@ bool side_usable(dcg_context* ctx)
 // Runs one node on the side stream, after everything enqueued on the main stream so far.
 int run_side_node(dcg_context* ctx, const dcg_node* nd)
 {
+    const int i = (nd->type == DCG_OP_CONV2D_KERNEL_GRAD || nd->type == DCG_OP_CONV2D_TRANSPOSE_KERNEL_GRAD) ? 0 : 1;
     DCG_CUDA(cudaEventRecord(ctx->ev_fork, ctx->stream));
-    DCG_CUDA(cudaStreamWaitEvent(ctx->side, ctx->ev_fork, 0));
-    std::swap(ctx->stream, ctx->side);
-    std::swap(ctx->ws, ctx->side_ws);
-    std::swap(ctx->ws_bytes, ctx->side_ws_bytes);
+    DCG_CUDA(cudaStreamWaitEvent(ctx->side[i], ctx->ev_fork, 0));
+    std::swap(ctx->stream, ctx->side[i]);
+    std::swap(ctx->ws, ctx->side_ws[i]);
+    std::swap(ctx->ws_bytes, ctx->side_ws_bytes[i]);
     const bool owns = ctx->owns_ws;
     ctx->owns_ws = true;
     const int st = dcg_run_node(ctx, nd);
     ctx->owns_ws = owns;
-    std::swap(ctx->stream, ctx->side);
-    std::swap(ctx->ws, ctx->side_ws);
-    std::swap(ctx->ws_bytes, ctx->side_ws_bytes);
-    ctx->side_busy = true;
+    std::swap(ctx->stream, ctx->side[i]);
+    std::swap(ctx->ws, ctx->side_ws[i]);
+    std::swap(ctx->ws_bytes, ctx->side_ws_bytes[i]);
+    ctx->side_busy[i] = true;
     return st;
 }
 
 // The main stream waits for whatever the side stream still has to do.
 int join_side(dcg_context* ctx)
 {
-    if (!ctx->side_busy) return DCG_OK;
-    ctx->side_busy = false;
-    DCG_CUDA(cudaEventRecord(ctx->ev_join, ctx->side));
-    DCG_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->ev_join, 0));
+    for (int i = 0; i < 2; ++i) {
+        if (!ctx->side_busy[i]) continue;
+        ctx->side_busy[i] = false;
+        DCG_CUDA(cudaEventRecord(ctx->ev_join[i], ctx->side[i]));
+        DCG_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->ev_join[i], 0));
+    }
     return DCG_OK;
 }
 
