@@ -431,8 +431,30 @@ extern "C" int dcg_run_node(dcg_context* ctx, const dcg_node* nd)
         return dcg_mse_grad(nd->in1, nd->in2, nd->out1, nd->len1, s);
     case DCG_OP_SIGMOID_GRAD:  // src/gpu/sigmoid.cu:138-146
         return dcg_act_grad(nd->in1, nd->in2, nd->out1, nd->len1, DCG_ACT_SIGMOID, 0.f, s);
-    case DCG_OP_MAT_MUL_ADD:  // src/gpu/matmul.cu:121-137
-        return dcg_matmul(nd->in1, nd->in2, nd->in3, nd->out1, nd->len1, nd->len2, nd->len3, s);
+    case DCG_OP_MAT_MUL_ADD: {  // src/gpu/matmul.cu:121-137
+        // On the tensor path a wide dense layer (the generator's 100 -> 8192 projection) is a 1x1
+        // convolution over a 1x1 image: x [m,1,1,n], k [1,1,n,p], bias in the epilogue.  K that is
+        // not a multiple of 32 is zero-filled by TMA.
+        const size_t m = nd->len1, n = nd->len2, pp = nd->len3;
+        if (ctx->precision != DCG_PREC_FP32 && pp >= 1024 && pp % 32 == 0 && n % 4 == 0 && n >= 32 && m >= 32 &&
+            m <= 65536 && n <= 65536 && pp <= 65536 &&
+            ((reinterpret_cast<uintptr_t>(nd->in1) | reinterpret_cast<uintptr_t>(nd->in2) |
+              reinterpret_cast<uintptr_t>(nd->in3) | reinterpret_cast<uintptr_t>(nd->out1)) & 15u) == 0) {
+            dcg_conv_desc d{};
+            d.n = (int)m; d.h = 1; d.w = 1; d.c = (int)n; d.kh = 1; d.kw = 1; d.o = (int)pp; d.ho = 1; d.wo = 1;
+            d.stride_h = 1; d.stride_w = 1; d.pad_top = 0; d.pad_left = 0;
+            const bool x3 = ctx->precision == DCG_PREC_3XTF32;
+            if (conv_tc_supported(d, kConvFwd, x3)) {
+                int st = ensure_workspace(ctx, conv_tc_workspace(d, kConvFwd, x3));
+                if (st) return st;
+                dcg_epilogue ep{};
+                ep.bias = nd->in3;
+                ep.act = DCG_ACT_NONE;
+                return dcg_conv2d_fwd(&d, nd->in1, nd->in2, nd->out1, &ep, ctx->precision, ctx->ws, ctx->ws_bytes, s);
+            }
+        }
+        return dcg_matmul(nd->in1, nd->in2, nd->in3, nd->out1, m, n, pp, s);
+    }
     case DCG_OP_TMAT_MAT_MUL:  // src/gpu/matmul.cu:139-153
         return dcg_matmul_tn(nd->in1, nd->in2, nd->out1, nd->len1, nd->len2, nd->len3, s);
     case DCG_OP_MAT_TMAT_MUL:  // src/gpu/matmul.cu:155-169
