@@ -922,16 +922,37 @@ repack_narrow_kernel(const float* __restrict__ x, float4* __restrict__ xp, int N
     }
 }
 
-// k [KH][KW][C][O] -> k4 [KH][32][O], row 4*dj + c; rows of unused slots are zero.
+// Both repacks of a narrow-channel forward in one launch: blocks [0, gridDim.x - k4_blocks) build
+// the padded 4-channel image, the last k4_blocks blocks the weights k4 [KH][32][O] (row 4*dj + c).
 __global__ void __launch_bounds__(256)
-repack_k4_kernel(const float* __restrict__ k, float* __restrict__ k4, int KH, int KW, int C, int O)
+repack_narrow_k4_kernel(const float* __restrict__ x, float4* __restrict__ xp, int N, int H, int W, int C,
+                        int Hp, int Wp, int pt, int pl, const float* __restrict__ k, float* __restrict__ k4,
+                        int KH, int KW, int O, int k4_blocks)
 {
     pdl_enter();
-    const int total = KH * 32 * O;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-        const int o = i % O, slot = (i / O) % 32, di = i / (O * 32);
-        const int dj = slot >> 2, c = slot & 3;
-        k4[i] = (dj < KW && c < C) ? __ldg(k + (((size_t)di * KW + dj) * C + c) * O + o) : 0.f;
+    const int x_blocks = (int)gridDim.x - k4_blocks;
+    if ((int)blockIdx.x >= x_blocks) {
+        const int total = KH * 32 * O;
+        for (int i = ((int)blockIdx.x - x_blocks) * blockDim.x + threadIdx.x; i < total; i += k4_blocks * blockDim.x) {
+            const int o = i % O, slot = (i / O) % 32, di = i / (O * 32);
+            const int dj = slot >> 2, c = slot & 3;
+            k4[i] = (dj < KW && c < C) ? __ldg(k + (((size_t)di * KW + dj) * C + c) * O + o) : 0.f;
+        }
+        return;
+    }
+    const size_t total = (size_t)N * Hp * Wp;
+    const size_t stride = (size_t)x_blocks * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int wp = (int)(i % Wp);
+        const int hp = (int)((i / Wp) % Hp);
+        const int n = (int)(i / ((size_t)Wp * Hp));
+        const int h = hp - pt, w = wp - pl;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (h >= 0 && h < H && w >= 0 && w < W) {
+            const float* src = x + (((size_t)n * H + h) * W + w) * C;
+            for (int c = 0; c < C; ++c) v[c] = __ldg(src + c);
+        }
+        xp[i] = make_float4(v[0], v[1], v[2], v[3]);
     }
 }
 
@@ -1499,16 +1520,19 @@ int narrow_prepare(const dcg_conv_desc& d, const Plan& pl, const float* x, const
     size_t blocks = (pixels + 255) / 256;
     const size_t cap = (size_t)sm_count() * 16;
     if (blocks > cap) blocks = cap;
-    launch_pdl(repack_narrow_kernel, (unsigned)blocks, 256, 0, stream, x, reinterpret_cast<float4*>(xp), d.n, d.h, d.w, d.c,
-                                                                pl.Hp, pl.Wp, d.pad_top, d.pad_left);
-    DCG_LAUNCH_CHECK("repack_narrow_kernel");
     *xp_out = xp;
-    if (k4_out) {
+    if (k4_out) {   // forward: image and weights in one launch
         float* k4 = reinterpret_cast<float*>(base + pl.k4_off());
         const int total = d.kh * 32 * d.o;
-        launch_pdl(repack_k4_kernel, (total + 255) / 256, 256, 0, stream, k, k4, d.kh, d.kw, d.c, d.o);
-        DCG_LAUNCH_CHECK("repack_k4_kernel");
+        const int k4_blocks = (total + 255) / 256;
+        launch_pdl(repack_narrow_k4_kernel, (unsigned)(blocks + k4_blocks), 256, 0, stream, x, reinterpret_cast<float4*>(xp),
+                   d.n, d.h, d.w, d.c, pl.Hp, pl.Wp, d.pad_top, d.pad_left, k, k4, d.kh, d.kw, d.o, k4_blocks);
+        DCG_LAUNCH_CHECK("repack_narrow_k4_kernel");
         *k4_out = k4;
+    } else {
+        launch_pdl(repack_narrow_kernel, (unsigned)blocks, 256, 0, stream, x, reinterpret_cast<float4*>(xp), d.n, d.h, d.w,
+                   d.c, pl.Hp, pl.Wp, d.pad_top, d.pad_left);
+        DCG_LAUNCH_CHECK("repack_narrow_kernel");
     }
     return DCG_OK;
 }
