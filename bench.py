@@ -219,7 +219,7 @@ def run_ours(args, rank, local_rank, world):
         dist.init_process_group("nccl", device_id=dev)
     assert world == args.gpus, "launch with torchrun --nproc-per-node equal to --gpus"
 
-    precision = {"tf32": pkg.PREC_TF32, "fp32": pkg.PREC_FP32}[args.precision]
+    precision = {"tf32": pkg.PREC_TF32, "3xtf32": pkg.PREC_3XTF32, "fp32": pkg.PREC_FP32}[args.precision]
     trainer = pkg.Trainer(batch=BATCH, precision=precision, fuse=True, seed=234, world=world)
     batches = synthetic_batches(rank, 4)
     trainer.x.copy_(batches[0][0])
@@ -324,7 +324,7 @@ def run_ours(args, rank, local_rank, world):
         line = {
             "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "tf32" if args.precision == "tf32" else "f32", "data": "synthetic",
+            "vs_baseline": None, "dtype": {"tf32": "tf32", "3xtf32": "3xtf32", "fp32": "f32"}[args.precision], "data": "synthetic",
             "config": {"workload": "configs[2]: full DCGAN training iteration (1 D update + 2 G updates, forwards "
                                    "recomputed per update as dcgan/main.cu:378-391), batch 64 per GPU",
                        "global_batch": BATCH * world, "parallelism": "dp%d" % world,
@@ -429,7 +429,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--precision", choices=["tf32", "fp32"], default="tf32")
+    ap.add_argument("--precision", choices=["tf32", "3xtf32", "fp32"], default="tf32")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=20.0)
     ap.add_argument("--sweep", action="store_true")
