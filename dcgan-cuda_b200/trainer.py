@@ -46,7 +46,9 @@ class Trainer:
         # own and every method orders itself against the caller's stream on entry and exit.
         caller = torch.cuda.current_stream(self.device)
         self._own_stream = caller.cuda_stream == 0
-        self.stream = torch.cuda.Stream(self.device) if self._own_stream else caller
+        # high priority: the library's side streams (weight / bias gradients) run at the default one, so
+        # blocks of the critical path are scheduled first when both have work ready
+        self.stream = torch.cuda.Stream(self.device, priority=-1) if self._own_stream else caller
         check(lib.dcg_trainer_create(ctypes.byref(self._h), ctypes.byref(self.cfg), self.stream.cuda_stream))
         self._views = {}
         self.x = self.tensor("x").view(batch, 64, 64, 3)
