@@ -269,3 +269,49 @@ def test_workspace_and_alignment_contract(pkg, dev, orc):
     torch.cuda.synchronize()
     assert np.array_equal(y_off.cpu().numpy(), orc.conv2d(xs, ks, (2, 2)))
 
+
+
+# (batch, H, Cin, Cout): the four DCGAN layers at the batch the benchmark runs (64) and at the 128
+# images of the discriminator's single pass over [fake | real]
+BENCH_LAYERS = [(b, h, c, o) for b in (64, 128) for (h, c, o) in ((64, 3, 64), (32, 64, 128), (16, 128, 256), (8, 256, 512))]
+
+
+@pytest.mark.parametrize("layer", BENCH_LAYERS)
+def test_benchmark_shapes_vs_reference_cpu_code(pkg, dev, ref, layer):
+    """The shapes bench.py times - with their K partitions, cluster shapes and two-wave grids -
+    against the reference's own CPU code (oracle/_ref = src/cpu/ops.hxx compiled from its sources) on
+    xorshift inputs (seed 234 as tests/test_conv_s1.cu:31).  The scalar CPU code needs minutes for a
+    whole batch-64 layer, so it is run on what is independent: forward and input gradient on the
+    first and last image (images do not interact), the kernel gradient over the WHOLE batch on
+    two 4-channel slices of x and dy (dk[:, :, c, o] only reads x[..., c] and dy[..., o]; the slice
+    keeps the reference's (n, i, j) summation order, src/cpu/ops.hxx:754-772).
+    Bounds: fp32 path bit-equal, TF32 path 1e-2 * max|ref|."""
+    F = pkg.functional
+    B, H, C, O = layer
+    Ho = H // 2
+    x = seeded((B, H, H, C), 234)
+    k = (seeded((5, 5, C, O), 235) * np.float32(0.05)).astype(np.float32)
+    dy = seeded((B, Ho, Ho, O), 236)
+    xd, kd, dyd = (torch.from_numpy(a).to(dev) for a in (x, k, dy))
+    ends = [0, B - 1]
+    y_ref = ref.conv2d(x[ends], k, (2, 2))
+    dx_ref = ref.conv2d_input_grad(dy[ends], k, 2, (H, H))
+    slices = [(0, 0), (max(C - 4, 0), O - 4)]
+    pad = (oracle.same_pad(H, 5, 2), oracle.same_pad(H, 5, 2))
+    dk_refs = [ref.conv2d_kernel_grad(np.ascontiguousarray(dy[..., o0:o0 + 4]), np.ascontiguousarray(x[..., c0:c0 + 4]), 2, pad)
+               for c0, o0 in slices]
+    for prec in (pkg.PREC_FP32, pkg.PREC_TF32):
+        y = F.conv2d_fwd(xd, kd, precision=prec)
+        dx = F.conv2d_dx(dyd, kd, (H, H), precision=prec)
+        dk = F.conv2d_dk(xd, dyd, (5, 5), precision=prec)
+        torch.cuda.synchronize()
+        assert pkg.lib.dcg_device_status() == 0
+        _check(y[ends], y_ref, prec, pkg, "fwd images 0 and %d" % (B - 1))
+        _check(dx[ends], dx_ref, prec, pkg, "dx images 0 and %d" % (B - 1))
+        for (c0, o0), dk_ref in zip(slices, dk_refs):
+            got = dk[:, :, c0:c0 + 4, o0:o0 + 4].contiguous()
+            if prec == pkg.PREC_FP32:
+                _check(got, dk_ref, prec, pkg, "dk slice c%d o%d" % (c0, o0))
+            else:   # the bound is on the operator's output tensor: scale by the whole dk
+                lim = TF32_TOL * float(dk.abs().max())
+                assert float(np.abs(got.cpu().numpy() - dk_ref).max()) <= lim, "dk slice c%d o%d" % (c0, o0)

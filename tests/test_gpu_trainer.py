@@ -186,3 +186,46 @@ def test_g_backward_in_two_parts(pkg, dev):
         tr.close()
     assert torch.equal(out[0][0], out[1][0]) and torch.equal(out[0][1], out[1][1])
 
+
+
+def test_batch64_tensor_path_vs_fp32_path(pkg, dev):
+    """The benchmarked configuration (batch 64: the discriminator's single pass over 128 images, side
+    streams, K-partition clusters at the shapes bench.py times) on the TF32 tensor path against the
+    fp32 CUDA-core path on identical parameters and inputs; the fp32 path is itself pinned to the
+    CPU oracle at batch 2 (test_gradients_match_cpu_model).  Losses to 1e-4; every gradient by
+    relative L2.  Measured on B200: D gradients <= 1.5e-3, G gradients <= 4e-3 (kink flips of single
+    pre-activations average out over 64 images); the bounds are 3x that."""
+    B = 64
+    g = torch.Generator().manual_seed(17)
+    x = torch.rand((B, 64, 64, 3), generator=g) * 2 - 1
+    z = torch.rand((B, 100), generator=g) * 2 - 1
+    grads, losses = {}, {}
+    for name, prec in (("fp32", pkg.PREC_FP32), ("tf32", pkg.PREC_TF32)):
+        tr = pkg.Trainer(batch=B, precision=prec, fuse=True, seed=234)
+        tr.x.copy_(x)
+        tr.z.copy_(z)
+        for i in (1, 3, 5, 7):   # biases away from zero so that the bias path carries signal
+            tr.tensor("d_param%d" % i).copy_(0.05 * torch.randn(tr.tensor("d_param%d" % i).shape, generator=torch.Generator().manual_seed(100 + i)))
+            tr.tensor("g_param%d" % i).copy_(0.05 * torch.randn(tr.tensor("g_param%d" % i).shape, generator=torch.Generator().manual_seed(200 + i)))
+        tr.d_backward()
+        torch.cuda.synchronize()
+        d = [tr.tensor("d_grad%d" % i).clone() for i in range(10)]
+        if name == "fp32":   # the two passes of the fp32 path: fake + real
+            d = [a + tr.tensor("d_gradb%d" % i) for i, a in enumerate(d)]
+        dl = tr.d_loss.item()
+        tr.g_backward()
+        torch.cuda.synchronize()
+        assert pkg.lib.dcg_device_status() == 0
+        grads[name] = (d, [tr.tensor("g_grad%d" % i).clone() for i in range(10)])
+        losses[name] = (dl, tr.g_loss.item())
+        tr.close()
+    for a, b in zip(losses["fp32"], losses["tf32"]):
+        assert abs(a - b) <= 1e-4 * max(1.0, abs(a))
+    worst = {}
+    for net, idx, bound in (("d", 0, 5e-3), ("g", 1, 1.2e-2)):
+        for i in range(10):
+            r, t = grads["fp32"][idx][i].double(), grads["tf32"][idx][i].double()
+            rel = float((r - t).norm() / max(float(r.norm()), 1e-30))
+            worst[(net, i)] = rel
+            assert rel <= bound, (net, i, rel)
+    print("batch-64 relative L2 of the TF32 gradients against the fp32 path:", worst)
