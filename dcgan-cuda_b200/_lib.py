@@ -127,6 +127,9 @@ SIGNATURES = {
     "dcg_trainer_arena_bytes": (c_size_t, [_P]),
     "dcg_device_status": (c_int, []),
     "dcg_last_error": (ctypes.c_char_p, []),
+    "dcg_debug_set_wait_limit": (None, [ctypes.c_longlong]),
+    "dcg_debug_skip_stage": (None, [c_int]),
+    "dcg_debug_set_pairs": (None, [c_int]),
     "dcg_build_info": (ctypes.c_char_p, []),
     "dcg_launches_total": (ctypes.c_uint64, []),
 }

@@ -8,6 +8,8 @@
 // handlers field for field, including which size array each handler reads.
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
+#include <set>
 #include <string>
 #include <utility>
 #include <vector>
@@ -29,8 +31,12 @@ struct dcg_context {
     cudaStream_t stream = nullptr;
     int precision = DCG_PREC_TF32;
     void* ws = nullptr;
-    size_t ws_bytes = 0;
+    size_t ws_bytes = 0;          // usable by the operators; an owned allocation has the ticket words behind it
+    unsigned* tickets = nullptr;  // kColsumTicketBytes of zeroed ticket words of the column sums (owned scratch only)
     bool owns_ws = false;
+    // Bumped whenever something a captured CUDA graph bakes in changes: a scratch buffer (main or
+    // side) moved, or the precision (which selects kernels and plans) was switched.
+    uint64_t generation = 0;
     // Second stream with scratch of its own for nodes flagged DCG_NODE_SIDE (created on first use,
     // only when the context owns its scratch): they fork off the main stream, run concurrently with
     // the nodes that follow, and are joined at the end of the list.
@@ -39,6 +45,7 @@ struct dcg_context {
     cudaStream_t side[2] = {nullptr, nullptr};
     void* side_ws[2] = {nullptr, nullptr};
     size_t side_ws_bytes[2] = {0, 0};
+    unsigned* side_tickets[2] = {nullptr, nullptr};
     cudaEvent_t ev_fork = nullptr, ev_join[2] = {nullptr, nullptr};
     bool side_busy[2] = {false, false}, side_failed = false;
     uint64_t launches_base = 0;
@@ -49,7 +56,24 @@ struct dcg_context {
 namespace dcg {
 
 bool context_is_profiling(const dcg_context* ctx) { return ctx && ctx->profiling; }
-const void* context_workspace(const dcg_context* ctx) { return ctx ? ctx->ws : nullptr; }
+uint64_t context_generation(const dcg_context* ctx) { return ctx ? ctx->generation : 0; }
+
+namespace {
+std::mutex g_registry_mutex;
+std::set<dcg_context*> g_registry;
+}  // namespace
+
+void contexts_reset_tickets()
+{
+    std::lock_guard<std::mutex> lock(g_registry_mutex);
+    cudaDeviceSynchronize();
+    for (dcg_context* c : g_registry) {
+        if (c->tickets) cudaMemset(c->tickets, 0, kColsumTicketBytes);
+        for (int i = 0; i < 2; ++i)
+            if (c->side_tickets[i]) cudaMemset(c->side_tickets[i], 0, kColsumTicketBytes);
+    }
+    cudaGetLastError();
+}
 
 // Times everything enqueued on the context's stream during its lifetime when profiling is on.
 ProfScope::ProfScope(dcg_context* c, const char* name, double flops) : ctx(c), active(c && c->profiling)
@@ -95,11 +119,33 @@ int ensure_workspace(dcg_context* ctx, size_t bytes)
     if (ctx->ws) DCG_CUDA(cudaFree(ctx->ws));
     ctx->ws = nullptr;
     ctx->ws_bytes = 0;
+    ctx->tickets = nullptr;
+    ++ctx->generation;   // graphs captured with the old address are stale
     const size_t want = align_up(bytes + bytes / 4, (size_t)1 << 20);
-    DCG_CUDA(cudaMalloc(&ctx->ws, want));
+    DCG_CUDA(cudaMalloc(&ctx->ws, want + kColsumTicketBytes));
+    // the ticket words of the column sums sit behind the usable part and start out zero
+    ctx->tickets = reinterpret_cast<unsigned*>(static_cast<unsigned char*>(ctx->ws) + want);
+    DCG_CUDA(cudaMemset(ctx->tickets, 0, kColsumTicketBytes));
     ctx->ws_bytes = want;
     ctx->owns_ws = true;
     return DCG_OK;
+}
+
+// Column sum on the context's scratch.  Owned scratch carries its own zeroed ticket words; a
+// caller-provided buffer goes through the public entry point, which clears them per call.
+int context_colsum(dcg_context* ctx, const float* a, float* out, size_t rows, size_t cols)
+{
+    DCG_CHECK_ARG(a && out && rows > 0 && cols > 0 && cols <= 0x7fffffffu, "column sum node: bad operands");
+    if (ctx->ws && !ctx->owns_ws) {
+        const size_t need = dcg_colsum_workspace_bytes(rows, cols);
+        if (need > ctx->ws_bytes)
+            return fail(DCG_ERR_WORKSPACE, "context workspace %zu < %zu bytes needed", ctx->ws_bytes, need);
+        return dcg_colsum(a, out, rows, cols, ctx->ws, ctx->ws_bytes, ctx->stream);
+    }
+    const size_t need = colsum_partial_bytes_max(rows, cols);
+    int st = ensure_workspace(ctx, need > 0 ? need : 1);
+    if (st) return st;
+    return colsum_launch(a, out, rows, cols, ctx->ws, ctx->ws_bytes, ctx->tickets, ctx->stream);
 }
 
 struct ConvCall {
@@ -368,6 +414,10 @@ extern "C" int dcg_context_create(dcg_context** out, int precision, void* worksp
     ctx->ws_bytes = workspace_bytes;
     ctx->owns_ws = false;
     ctx->launches_base = launches_total();
+    {
+        std::lock_guard<std::mutex> lock(g_registry_mutex);
+        g_registry.insert(ctx);
+    }
     *out = ctx;
     return DCG_OK;
 }
@@ -375,6 +425,10 @@ extern "C" int dcg_context_create(dcg_context** out, int precision, void* worksp
 extern "C" void dcg_context_destroy(dcg_context* ctx)
 {
     if (!ctx) return;
+    {
+        std::lock_guard<std::mutex> lock(g_registry_mutex);
+        g_registry.erase(ctx);
+    }
     if (ctx->owns_ws && ctx->ws) cudaFree(ctx->ws);
     for (int i = 0; i < 2; ++i) {
         if (ctx->side_ws[i]) cudaFree(ctx->side_ws[i]);
@@ -390,6 +444,7 @@ extern "C" int dcg_context_set_precision(dcg_context* ctx, int precision)
     DCG_CHECK_ARG(ctx, "dcg_context_set_precision: null context");
     DCG_CHECK_ARG(precision == DCG_PREC_TF32 || precision == DCG_PREC_FP32 || precision == DCG_PREC_3XTF32,
                   "dcg_context_set_precision: unknown precision %d", precision);
+    if (ctx->precision != precision) ++ctx->generation;   // captured graphs hold the old precision's kernels
     ctx->precision = precision;
     return DCG_OK;
 }
@@ -461,11 +516,8 @@ extern "C" int dcg_run_node(dcg_context* ctx, const dcg_node* nd)
         return dcg_matmul_nt(nd->in1, nd->in2, nd->out1, nd->len1, nd->len2, nd->len3, s);
     case DCG_OP_MAT_SUM_ROWS:  // src/gpu/sum.cu:231-236
         return dcg_rowsum(nd->in1, nd->out1, nd->len1, nd->len2, s);
-    case DCG_OP_MAT_SUM_COLS: {  // src/gpu/sum.cu:238-243
-        int st = ensure_workspace(ctx, dcg_colsum_workspace_bytes(nd->len1, nd->len2));
-        if (st) return st;
-        return dcg_colsum(nd->in1, nd->out1, nd->len1, nd->len2, ctx->ws, ctx->ws_bytes, s);
-    }
+    case DCG_OP_MAT_SUM_COLS:  // src/gpu/sum.cu:238-243
+        return context_colsum(ctx, nd->in1, nd->out1, nd->len1, nd->len2);
     case DCG_OP_SOFTMAX_CROSS_ENTROPY_GRAD:  // src/gpu/softmax.cu:352-359
         return dcg_softmax_xent_grad(nd->in1, nd->in2, nd->out1, nd->len1, nd->len2, s);
     case DCG_OP_RELU_GRAD:  // src/gpu/relu.cu:79-86
@@ -497,9 +549,7 @@ extern "C" int dcg_run_node(dcg_context* ctx, const dcg_node* nd)
     case DCG_OP_CONV2D_BIAS_ADD_GRAD: {  // slot left empty by the reference (src/gpu/kernels.cu:55)
         const size_t cols = (size_t)nd->sizes1[3];
         const size_t rows = (size_t)nd->sizes1[0] * nd->sizes1[1] * nd->sizes1[2];
-        int st = ensure_workspace(ctx, dcg_colsum_workspace_bytes(rows, cols));
-        if (st) return st;
-        return dcg_colsum(nd->in1, nd->out1, rows, cols, ctx->ws, ctx->ws_bytes, s);
+        return context_colsum(ctx, nd->in1, nd->out1, rows, cols);
     }
     case DCG_OP_TANH_GRAD:  // src/gpu/sigmoid.cu:157-165
         return dcg_act_grad(nd->in1, nd->in2, nd->out1, nd->len1, DCG_ACT_TANH, 0.f, s);
@@ -552,6 +602,7 @@ int run_side_node(dcg_context* ctx, const dcg_node* nd)
     std::swap(ctx->stream, ctx->side[i]);
     std::swap(ctx->ws, ctx->side_ws[i]);
     std::swap(ctx->ws_bytes, ctx->side_ws_bytes[i]);
+    std::swap(ctx->tickets, ctx->side_tickets[i]);
     const bool owns = ctx->owns_ws;
     ctx->owns_ws = true;
     const int st = dcg_run_node(ctx, nd);
@@ -559,6 +610,7 @@ int run_side_node(dcg_context* ctx, const dcg_node* nd)
     std::swap(ctx->stream, ctx->side[i]);
     std::swap(ctx->ws, ctx->side_ws[i]);
     std::swap(ctx->ws_bytes, ctx->side_ws_bytes[i]);
+    std::swap(ctx->tickets, ctx->side_tickets[i]);
     ctx->side_busy[i] = true;
     return st;
 }

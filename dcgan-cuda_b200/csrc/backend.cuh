@@ -19,8 +19,9 @@ struct ProfScope {
 }  // namespace dcg
 
 namespace dcg {
-// For the trainer: whether the context is in profiling mode, and the address of its scratch
-// buffer (captured CUDA graphs bake it in).
+// For the trainer: whether the context is in profiling mode, and a counter that advances whenever
+// something a captured CUDA graph bakes in has changed (a scratch buffer of the main or a side
+// stream was reallocated, the precision was switched): a graph captured under another value is stale.
 bool context_is_profiling(const dcg_context* ctx);
-const void* context_workspace(const dcg_context* ctx);
+uint64_t context_generation(const dcg_context* ctx);
 }  // namespace dcg

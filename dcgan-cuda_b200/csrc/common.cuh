@@ -82,6 +82,17 @@ inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// ---- column sums: internal launch with caller-owned ticket words (elementwise.cu) ---------------
+// kColsumTicketBytes of ZEROED device memory that only stream-ordered launches share; the kernel
+// leaves them zero.  colsum_partial_bytes_max: scratch for the partial sums alone (0: none needed).
+constexpr size_t kColsumTicketBytes = 4096;
+int colsum_launch(const float* a, float* out, size_t rows, size_t cols, void* workspace, size_t workspace_bytes,
+                  unsigned* tickets, cudaStream_t stream);
+size_t colsum_partial_bytes_max(size_t rows, size_t cols);
+// Clears the ticket words of every live context (after a kernel reported an error, a launch may
+// have left some of them counted up).  Synchronises the device.
+void contexts_reset_tickets();
+
 // Number of SMs of the current device (cached per device id).
 int sm_count();
 

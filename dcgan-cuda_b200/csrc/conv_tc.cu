@@ -33,8 +33,11 @@
 // record an error code in a device status word and leave; TMEM is always released.
 #include <cuda.h>
 
+#include <atomic>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 #include "conv.cuh"
@@ -49,28 +52,30 @@ constexpr int kEpi = 256;               // epilogue threads: warps 2..9, two per
 constexpr int kThreads = 64 + kEpi;
 constexpr int kMaxSmem = 227 * 1024;
 constexpr int kMaxCluster = 8;          // portable thread-block cluster size: the cap on K partitions
+constexpr int kPairDefault = 0;         // CTA pairs (cta_group::2) unless DCG_TC_PAIR says otherwise
 // Floats of shared memory the epilogue's transposition buffer takes for a 128 x bn tile (quads at a
 // pitch of BM + 1 sixteen-byte units); the row-offset table follows it.
 __host__ __device__ constexpr int kRedFloats(int bn) { return (bn / 4) * (BM + 1) * 4; }
-constexpr long long kWaitCycles = 2000000000LL;  // ~1 s at 2 GHz
+constexpr long long kWaitCycles = 2000000000LL;  // default wait limit: ~1 s at 2 GHz
 
 enum Mode { MODE_FWD = 0, MODE_DX = 1, MODE_DK = 2 };
 
 // Error word: [0] code (0 = ok), [1] blockIdx, [2] role, [3] stage.  Read by dcg_device_status().
 __device__ int g_tc_status[4];
 
-// Timeline of CTA 0 for tuning (DCG_TC_DEBUG bit 4): SM clock stamps of [0..1023] TMA issue of
-// stage i, [1024..2047] stage i seen full by the MMA thread, [2048..3071] MMAs of stage i issued,
-// [3072] kernel entry, [3073] setup done, [3074] accumulator ready, [3075] epilogue stores done.
+// Tuning aids, compiled in only with -DDCG_TC_TRACING (the default build has none of it): clock
+// stamps of CTA 0's pipeline and a per-CTA phase timeline, read back through dcg_debug_trace /
+// dcg_debug_cta_trace; Params::debug bit 0 drops the MMAs, bit 1 the loads (results are garbage).
+#ifdef DCG_TC_TRACING
+// [0..1023] TMA issue of stage i, [1024..2047] stage i seen full by the MMA thread, [2048..3071] MMAs
+// of stage i issued, [3072] kernel entry, [3073] setup done, [3074] accumulator ready, [3075] stores done.
 __device__ long long g_tc_trace[3080];
 #define TC_TRACE(slot)                                                         \
     do {                                                                       \
         if ((p.debug & 4) && blockIdx.x == 0 && (slot) < 3080) g_tc_trace[(slot)] = clock64(); \
     } while (0)
-
-// Per-CTA timeline for tuning (DCG_TC_DEBUG bit 8): global-timer stamps (ns) of thread 64 of the first
-// 1024 CTAs at [0] kernel entry, [1] setup done, [2] accumulator ready, [3] tile handed over,
-// [4] partitions met, [5] end; [6] = SM id.
+// global-timer stamps (ns) of thread 64 of the first 1024 CTAs at [0] kernel entry, [1] setup done,
+// [2] accumulator ready, [3] tile handed over, [4] partitions met, [5] end; [6] = SM id.
 __device__ unsigned long long g_tc_cta_trace[1024][8];
 __device__ __forceinline__ unsigned long long global_ns()
 {
@@ -82,6 +87,12 @@ __device__ __forceinline__ unsigned long long global_ns()
     do {                                                                                           \
         if ((p.debug & 8) && threadIdx.x == 64 && blockIdx.x < 1024) g_tc_cta_trace[blockIdx.x][(slot)] = global_ns(); \
     } while (0)
+#define TC_DEBUG_BIT(bit) (p.debug & (bit))
+#else
+#define TC_TRACE(slot) do { } while (0)
+#define TC_CTA_TRACE(slot) do { } while (0)
+#define TC_DEBUG_BIT(bit) false
+#endif
 
 struct Params {
     int N, H, W, C, KH, KW, O, Ho, Wo, sh, sw, pt, pl;
@@ -90,7 +101,11 @@ struct Params {
     int m_tiles;                  // DK: 128-row tiles along the M channel axis
     int n_tiles;                  // BN-column tiles along the N channel axis
     int bn;                       // accumulator columns, multiple of 16, <= 256
-    int splits;                   // K partitions = CTAs per cluster (<= 8)
+    int splits;                   // K partitions of a tile
+    int pair;                     // CTA pairs: two M tiles share every B tile through tcgen05 cta_group::2
+                                  //   (cluster = 2 * splits CTAs, rank = 2 * partition + half)
+    int skip_stage;               // test hook: the producer leaves this pipeline stage out (-1: never)
+    long long wait_cycles;        // SM clocks after which a barrier wait gives up
     int kchunks;                  // 32-wide chunks along the contracted channel axis (FWD: C, DX: O)
     int swap;                     // DK: M axis is o (A from dy, B from x)
     int narrow;                   // FWD/DK with <= 4 input channels: x is read through the window map
@@ -98,9 +113,8 @@ struct Params {
     int planes;                   // FWD: 16-byte column quad q of output pixel r goes to out[(q * pixels + r) * 4]
     int o_store;                  // FWD: output columns >= o_store are padding and never stored (0: store all O)
     int x3;                       // 3xTF32: every operand tile gets a residual tile, three MMAs per K step
-    int group0;                   // added to the group decoded from blockIdx (DX launched one parity class at a time)
     unsigned long long plane_stride;  // planes: elements between two quads' planes (4 * pixels)
-    int debug;                    // timing experiments (DCG_TC_DEBUG): 1 = no MMA, 2 = no TMA; results are garbage
+    int debug;                    // DCG_TC_TRACING builds only: 1 = no MMA, 2 = no TMA, 4 / 8 = record timelines
     int stages;                   // pipeline depth
     float* out;                   // the output tensor
     float* scratch;               // splits > 1: partial tiles, [CTA][128 x bn], quad- or column-major
@@ -146,14 +160,14 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
 }
 
 // Bounded wait, slow path.  Returns false (after recording the failure) if the phase never completes.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int role, int stage)
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int role, int stage, long long limit)
 {
     const long long t0 = clock64();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (clock64() - t0 > kWaitCycles) break;
+        if (clock64() - t0 > limit) break;
     }
     if (atomicCAS(&g_tc_status[0], 0, 1) == 0) {
         g_tc_status[1] = blockIdx.x;
@@ -165,18 +179,78 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int r
 
 // Bounded wait: a non-blocking probe first (the common case in a running pipeline), then the
 // suspending, time-limited loop.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int role, int stage)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int role, int stage, long long limit)
 {
     if (mbar_test_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, role, stage);
+    return mbar_wait_slow(bar, parity, role, stage, limit);
 }
 
 // Warp-uniform form for loops that a whole warp walks in lockstep (one elected lane issues): the
 // vote makes the outcome uniform by construction, which keeps the loop state in uniform registers.
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int role, int stage)
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int role, int stage, long long limit)
 {
     if (__all_sync(0xffffffffu, mbar_test_wait(bar, parity))) return true;
-    return __all_sync(0xffffffffu, mbar_wait_slow(bar, parity, role, stage));
+    return __all_sync(0xffffffffu, mbar_wait_slow(bar, parity, role, stage, limit));
+}
+
+// ---- CTA pairs (tcgen05 cta_group::2) -----------------------------------------------------------------
+// Two CTAs of a cluster whose ranks differ in the lowest bit work on one 256-row tile: each loads
+// its own 128 rows of A and its own HALF of the B tile into its own shared memory (plain TMA loads
+// on its own barriers - no multicast anywhere), and one tcgen05.mma.cta_group::2, issued by the
+// even CTA, multiplies both A halves with both B halves; every CTA ends up with its 128 rows of
+// the accumulator in its own TMEM.  Per pipeline stage a CTA thus fetches 16 KB + bn * 64 B instead
+// of 16 KB + bn * 128 B for the same tensor work, which is what the main loop is paced by.
+// The handshakes across the pair use mbarriers in the partner's shared memory, addressed through
+// mapa: the odd CTA tells the even one that its stage has landed (a plain remote arrive), the even
+// one tells the odd one that a stage has been read and that the accumulator is complete
+// (tcgen05.commit on the partner's barrier).
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank)
+{
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_addr), "r"(rank));
+    return a;
+}
+
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// wait on a barrier that a thread of the partner CTA arrives on (acquire at cluster scope), bounded
+__device__ __noinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int role, int stage, long long limit)
+{
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i) {
+            uint32_t ok;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+            if (ok) return true;
+        }
+        if (clock64() - t0 > limit) break;
+    }
+    if (atomicCAS(&g_tc_status[0], 0, 1) == 0) {
+        g_tc_status[1] = blockIdx.x;
+        g_tc_status[2] = role;
+        g_tc_status[3] = stage;
+    }
+    return false;
+}
+
+__device__ __forceinline__ bool mbar_wait_cluster_warp(uint32_t bar, uint32_t parity, int role, int stage, long long limit)
+{
+    return __all_sync(0xffffffffu, mbar_wait_cluster(bar, parity, role, stage, limit));
 }
 
 __device__ __forceinline__ bool elect_one()
@@ -219,6 +293,23 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
 __device__ __forceinline__ void tcgen05_commit(uint32_t bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// cta_group::2 forms: issued by one thread of the even CTA of a pair; the barrier operand is a
+// shared::cluster address and may name a barrier of either CTA of the pair.
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t cluster_bar)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_mma_tf32_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                                      uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
 __device__ __forceinline__ void tcgen05_mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
@@ -302,7 +393,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 64) TC_TRACE(3072);
     TC_CTA_TRACE(0);
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const int b_stage_bytes = p.bn * BK * 4;
+    const int b_stage_bytes = (p.pair ? p.bn / 2 : p.bn) * BK * 4;   // a pair CTA holds half of the B tile
+    const long long wait_limit = p.wait_cycles;
     const uint32_t a_base = smem_base;
     const uint32_t b_base = a_base + (uint32_t)p.stages * A_STAGE_BYTES;
     // 3xTF32: residual tiles (operand minus its TF32 part) of every stage follow the operand tiles
@@ -314,6 +406,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t empty_bar = bar_base + 8u * p.stages;
     const uint32_t resid_bar = bar_base + 16u * p.stages;     // 3xTF32: residual tiles of the stage are written
     const uint32_t tmem_full_bar = bar_base + 24u * p.stages;
+    const uint32_t peer_full_bar = tmem_full_bar + 16u;           // pairs: the partner's tile of the stage has landed
     const uint32_t tmem_slot = tmem_full_bar + 8u;
     uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
@@ -325,6 +418,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_init(full_bar + 8u * s, 1);
             mbar_init(empty_bar + 8u * s, 1);
             mbar_init(resid_bar + 8u * s, kEpi);
+            if (p.pair) mbar_init(peer_full_bar + 8u * s, 1);
         }
         mbar_init(tmem_full_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -338,21 +432,31 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     int tmem_cols = 32;
     while (tmem_cols < (X3 ? 2 * p.bn : p.bn)) tmem_cols <<= 1;
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(tmem_cols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (p.pair) {   // one warp of each CTA of the pair takes part
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(tmem_cols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(tmem_cols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
 
     // ---- decode this CTA's work item -------------------------------------------------------------
     // blockIdx.x = ((group * m_count + m) * n_tiles + n) * splits + split, where group is the parity
     // class (DX), the kernel tap (DK) or absent (FWD), and m a pixel tile (FWD/DX) or channel tile (DK).
+    // With CTA pairs the innermost index is the half of the 256-row tile (= parity of the cluster
+    // rank), then the partition; m then counts pairs of M tiles.
     int rem = blockIdx.x;
+    const int half = p.pair ? (rem & 1) : 0;
+    if (p.pair) rem >>= 1;
     const int split = rem % p.splits; rem /= p.splits;
     const int n_tile = rem % p.n_tiles; rem /= p.n_tiles;
     int m_count;
     if (MODE == MODE_DK) m_count = p.m_tiles;
     else m_count = p.tiles_w * p.tiles_h * p.tiles_n;
-    const int m_tile = rem % m_count;
-    const int group = p.group0 + rem / m_count;
+    if (p.pair) m_count >>= 1;
+    const int m_tile = p.pair ? 2 * (rem % m_count) + half : rem % m_count;
+    const int group = rem / m_count;
 
     // pixel-tile origin (FWD/DX)
     int j0 = 0, i0 = 0, n0 = 0;
@@ -384,6 +488,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    // pairs: the partner's barriers must be initialised before anything arrives on them remotely
+    if (p.pair) cluster_sync_all();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = *tmem_slot_ptr;
     // Programmatic dependent launch: everything above (barriers, TMEM, descriptor prefetch) may run
@@ -393,11 +499,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == 64) TC_TRACE(3073);
     TC_CTA_TRACE(1);
+#ifdef DCG_TC_TRACING
     if ((p.debug & 8) && threadIdx.x == 64 && blockIdx.x < 1024) {
         unsigned smid;
         asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
         g_tc_cta_trace[blockIdx.x][6] = smid;
     }
+#endif
 
     // ---- epilogue geometry (uniform over the CTA) ---------------------------------------------------
     const int ch0 = n_tile * p.bn;    // channel index of accumulator column 0 (bias axis) unless DK
@@ -435,11 +543,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             const int wrap_dj = (MODE == MODE_FWD) ? p.KW : taps_w;
             for (int it = 0; it < nq; ++it) {
-                if (!mbar_wait_warp(empty_bar + 8u * s, phase ^ 1u, 0, it)) break;
+                if (!mbar_wait_warp(empty_bar + 8u * s, phase ^ 1u, 0, it, wait_limit)) break;
                 const uint32_t fb = full_bar + 8u * s;
-                if (elect_one()) {
+                if (it != p.skip_stage && elect_one()) {
                 TC_TRACE(it);
-                if (p.debug & 2) {   // timing experiment: no loads, the stage is declared full at once
+                if (TC_DEBUG_BIT(2)) {   // timing experiment: no loads, the stage is declared full at once
                     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(fb) : "memory");
                 } else {
                     mbar_expect_tx(fb, tx_bytes);
@@ -455,12 +563,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         if (it < 128) TC_TRACE(256 + it);
                         tma_load_4d(a_dst, &map_a, fb, chunk * BK, p.sw * j0 + dj - p.pl, p.sh * i0 + di - p.pt, n0);
                         if (it < 128) TC_TRACE(512 + it);
-                        tma_load_4d(b_dst, &map_b, fb, 0, chunk * BK, tap, n_tile * (p.bn / 32));
+                        // B: bn / 32 chunks of 32 output channels; a pair CTA takes its half of them
+                        tma_load_4d(b_dst, &map_b, fb, 0, chunk * BK, tap,
+                                    p.pair ? n_tile * (p.bn / 32) + half * (p.bn / 64) : n_tile * (p.bn / 32));
                         if (it < 128) TC_TRACE(768 + it);
                     } else if (MODE == MODE_DX) {
                         // (di, dj) count the taps of this parity class: kernel tap (rh + sh*di, rw + sw*dj)
                         tma_load_4d(a_dst, &map_a, fb, chunk * BK, j0 + ew - dj, i0 + eh - di, n0);
-                        tma_load_4d(b_dst, &map_b, fb, chunk * BK, n_tile * p.bn, rw + p.sw * dj, rh + p.sh * di);
+                        tma_load_4d(b_dst, &map_b, fb, chunk * BK, n_tile * p.bn + (p.pair ? half * (p.bn / 2) : 0),
+                                    rw + p.sw * dj, rh + p.sh * di);
                     } else {
                         // (tap, di, dj) count the 32-pixel tiles along (n, h, w)
                         const int pj = dj * p.TW, pi = di * p.TH, pn = tap * p.TN;
@@ -493,7 +604,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         {
             const int a_mn = (MODE == MODE_DK) ? 1 : 0;
             const int b_mn = (MODE == MODE_DX) ? 0 : 1;
-            const uint32_t idesc = make_idesc(a_mn, b_mn, p.bn, BM);
+            const uint32_t idesc = make_idesc(a_mn, b_mn, p.bn, p.pair ? 2 * BM : BM);
             // K-major tile: rows of 128 B, 8-row groups 1024 B apart (stride offset); one MMA (K = 8)
             // consumes 32 B of each row.
             // MN-major tile: [32-channel chunk][k row][128 B]: chunks 4096 B apart (leading offset), the
@@ -510,13 +621,48 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t a_stage16 = A_STAGE_BYTES >> 4, b_stage16 = (uint32_t)b_stage_bytes >> 4;
             int s = 0;
             uint32_t phase = 0;
+            if (p.pair && half == 1) {
+                // ===== odd CTA of a pair: no MMAs of its own; tells the even CTA when a stage has landed =====
+                const uint32_t partner_peer_full = map_to_cta(peer_full_bar, cluster_ctarank() ^ 1u);
+                for (int it = 0; it < nq; ++it) {
+                    if (!mbar_wait_warp(full_bar + 8u * s, phase, 5, it, wait_limit)) break;
+                    if (elect_one()) mbar_arrive_remote(partner_peer_full + 8u * s);
+                    if (++s == p.stages) { s = 0; phase ^= 1u; }
+                }
+            } else if (p.pair) {
+                // ===== even CTA of a pair: one MMA over both CTAs' tiles per K step =====
+                const uint32_t partner = cluster_ctarank() ^ 1u;
+                const uint32_t partner_empty = map_to_cta(empty_bar, partner);
+                const uint32_t partner_tmem_full = map_to_cta(tmem_full_bar, partner);
+                for (int it = 0; it < nq; ++it) {
+                    if (!mbar_wait_warp(full_bar + 8u * s, phase, 1, it, wait_limit)) break;
+                    if (!mbar_wait_cluster_warp(peer_full_bar + 8u * s, phase, 6, it, wait_limit)) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    if (elect_one()) {
+                        const uint64_t adesc = adesc0 + (uint64_t)(s * a_stage16);
+                        const uint64_t bdesc = bdesc0 + (uint64_t)(s * b_stage16);
+#pragma unroll
+                        for (int kk = 0; kk < BK / 8; ++kk)
+                            tcgen05_mma_tf32_pair(tmem_d, adesc + (uint64_t)(kk * (a_step >> 4)), bdesc + (uint64_t)(kk * (b_step >> 4)),
+                                                  idesc, (it > 0 || kk > 0) ? 1u : 0u);
+                        // the stage is free in BOTH CTAs once these MMAs have read it
+                        tcgen05_commit_pair(empty_bar + 8u * s);
+                        tcgen05_commit_pair(partner_empty + 8u * s);
+                    }
+                    if (++s == p.stages) { s = 0; phase ^= 1u; }
+                }
+                if (elect_one()) {   // accumulator complete (or abandoned), in both CTAs
+                    tcgen05_commit_pair(tmem_full_bar);
+                    tcgen05_commit_pair(partner_tmem_full);
+                }
+            } else {
             for (int it = 0; it < nq; ++it) {
-                if (!mbar_wait_warp(full_bar + 8u * s, phase, 1, it)) break;
-                if (X3 && !mbar_wait_warp(resid_bar + 8u * s, phase, 3, it)) break;
+                if (!mbar_wait_warp(full_bar + 8u * s, phase, 1, it, wait_limit)) break;
+                if (X3 && !mbar_wait_warp(resid_bar + 8u * s, phase, 3, it, wait_limit)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 if (elect_one()) {
                 TC_TRACE(1024 + it);
-                if (p.debug & 1) {   // timing experiment: no MMA, the stage is released at once
+                if (TC_DEBUG_BIT(1)) {   // timing experiment: no MMA, the stage is released at once
                     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_bar + 8u * s) : "memory");
                 } else {
                     const uint64_t adesc = adesc0 + (uint64_t)(s * a_stage16);
@@ -547,6 +693,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (++s == p.stages) { s = 0; phase ^= 1u; }
             }
             if (elect_one()) tcgen05_commit(tmem_full_bar);   // accumulator complete (or abandoned)
+            }
         }
     } else {
         // ===== epilogue, part 1 (warps 2..5; TMEM lane quadrant = warp % 4; thread = accumulator row) =====
@@ -591,7 +738,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t phase = 0;
             const int a_q = A_STAGE_BYTES / 16, b_q = b_stage_bytes / 16;   // 16-byte words per tile
             for (int it = 0; it < nq; ++it) {
-                if (!mbar_wait(full_bar + 8u * s, phase, 4, it)) break;
+                if (!mbar_wait(full_bar + 8u * s, phase, 4, it, wait_limit)) break;
                 const float4* asrc = reinterpret_cast<const float4*>(smem_raw + (a_base + (uint32_t)s * A_STAGE_BYTES - smem_u32(smem_raw)));
                 float4* adst = reinterpret_cast<float4*>(smem_raw + (as_base + (uint32_t)s * A_STAGE_BYTES - smem_u32(smem_raw)));
                 const float4* bsrc = reinterpret_cast<const float4*>(smem_raw + (b_base + (uint32_t)s * b_stage_bytes - smem_u32(smem_raw)));
@@ -605,7 +752,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (++s == p.stages) { s = 0; phase ^= 1u; }
             }
         }
-        bool ok = mbar_wait(tmem_full_bar, 0, 2, 0);
+        bool ok = mbar_wait(tmem_full_bar, 0, 2, 0, wait_limit);
         ok = __all_sync(0xffffffffu, ok);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (threadIdx.x == 64) TC_TRACE(3074);
@@ -633,8 +780,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int QPO = (qpr + S - 1) / S;        //   quads per share
     const int QS = BM + 1;                    // shared-memory quad pitch in 16-byte units (odd: lanes = quads hit distinct banks)
     const int CL = (p.bn + S - 1) / S;        // scalar path: columns per share
+    // scratch slot = blockIdx.x; the partitions of this CTA's tile are pstride slots apart (with CTA
+    // pairs the two halves of a 256-row tile interleave)
+    const int pstride = p.pair ? 2 : 1;
     float* my_scratch = p.scratch + (size_t)blockIdx.x * BM * p.bn;
-    const float* tile_scratch = p.scratch + (size_t)(blockIdx.x - part) * BM * p.bn;
+    const float* tile_scratch = p.scratch + (size_t)(blockIdx.x - pstride * part) * BM * p.bn;
     if (threadIdx.x == 64) TC_TRACE(3000);
     if (warp >= 2) {
         const int quad = warp & 3;
@@ -733,7 +883,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     for (int sidx = 1; sidx < S; ++sidx) {   // two partitions' loads in flight; the adds keep partition order
                         float4 v[4];
 #pragma unroll
-                        for (int u = 0; u < 4; ++u) v[u] = __ldcg(src[u] + (size_t)sidx * BM * qpr);
+                        for (int u = 0; u < 4; ++u) v[u] = __ldcg(src[u] + (size_t)sidx * pstride * BM * qpr);
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
                             acc[u].x = __fadd_rn(acc[u].x, v[u].x); acc[u].y = __fadd_rn(acc[u].y, v[u].y);
@@ -825,7 +975,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         float v[4];
 #pragma unroll
                         for (int u = 0; u < 4; ++u)
-                            v[u] = __ldcg(tile_scratch + ((size_t)sidx * p.bn + (cols[u] < 0 ? 0 : cols[u])) * BM + my_row);
+                            v[u] = __ldcg(tile_scratch + ((size_t)sidx * pstride * p.bn + (cols[u] < 0 ? 0 : cols[u])) * BM + my_row);
 #pragma unroll
                         for (int u = 0; u < 4; ++u) acc[u] = __fadd_rn(acc[u], v[u]);
                     }
@@ -853,7 +1003,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // ---- teardown: everyone is done with TMEM before warp 1 releases it --------------------------
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 1) {
+    if (p.pair) {
+        // both CTAs of a pair are done with TMEM (and with each other's barriers) before either frees it
+        cluster_sync_all();
+        if (warp == 1) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
+        }
+    } else if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
     }
@@ -1102,10 +1259,6 @@ struct Plan {
     // weights k2 and the GEMM result ycol follow the partial tiles in the scratch area
     int Jp = 0;
     size_t k2_bytes = 0, ycol_bytes = 0;
-    // DX with few tiles: one launch per parity class, each with its own number of K partitions, so
-    // that a CTA of the 9-tap class does as many pipeline stages as a CTA of the 4-tap class
-    int n_class = 0;
-    int class_splits[16] = {0}, class_grid[16] = {0};
     size_t k2_off() const { return align_up(partial_bytes, 256); }
     size_t ycol_off() const { return k2_off() + align_up(k2_bytes, 256); }
     size_t xp_off() const { return align_up(partial_bytes, 256); }
@@ -1128,16 +1281,10 @@ struct PlanX3 {
     ~PlanX3() { t_plan_x3 = saved; }
 };
 
-// Accumulator width for a layer with n_ch output columns.  256-column tiles (DCG_TC_WIDE=1) halve
-// how often an A tile is fetched from L2 but need the whole shared memory of an SM: one CTA per SM,
-// nothing to overlap its set-up and epilogue with.  Measured slower at batch 64 (the 256 -> 512
-// forward layer 38 us against 23 us), so they are off unless asked for.
-int tile_width(int n_ch)
-{
-    static const int wide = [] { const char* v = getenv("DCG_TC_WIDE"); return v ? atoi(v) : 0; }();
-    if (wide && n_ch >= 256) return 256;
-    return n_ch >= 128 ? 128 : n_ch;
-}
+// Accumulator width for a layer with n_ch output columns.  (256-column tiles halve how often an A
+// tile is fetched from L2 but leave one CTA per SM with nothing to overlap its set-up and epilogue
+// with: measured slower at batch 64, the 256 -> 512 forward layer 38 us against 23 us.)
+int tile_width(int n_ch) { return n_ch >= 128 ? 128 : n_ch; }
 
 // K partitions of a tile.  Measured on every DCGAN layer at batch 64 (per-CTA timelines, partition
 // counts 1..8 forced): the shortest launch is the one with about ONE CTA per SM - a deeper pipeline
@@ -1168,10 +1315,34 @@ int choose_splits(int tiles, int min_stages_per_tile, int ctas_per_sm = 1)
     return s < 1 ? 1 : s;
 }
 
+// CTA pairs (cta_group::2): on unless switched off (DCG_TC_PAIR=0 in the environment, or the
+// testing hook dcg_debug_set_pairs).  -1 = follow the environment.
+std::atomic<int> g_pair_override{-1};
+bool pairs_enabled()
+{
+    const int o = g_pair_override.load();
+    if (o >= 0) return o != 0;
+    static const int env = [] { const char* v = getenv("DCG_TC_PAIR"); return v ? atoi(v) : kPairDefault; }();
+    return env != 0;
+}
+
+// Turns a plan with `tiles` single tiles (m_count of them along M per group and N tile) into a plan
+// of CTA pairs where that is possible: an even number of M tiles, a B tile that halves into whole
+// 32-channel chunks (MN-major) or 8-row groups (K-major), no 3xTF32.  The K partitions of a pair
+// tile and its two halves share one cluster, so at most kMaxCluster / 2 partitions.
+void maybe_pair(Plan& pl, int m_count, int b_half_granule)
+{
+    Params& p = pl.p;
+    if (!pairs_enabled() || p.x3 || p.narrow || p.ext_finish) return;
+    if (m_count < 2 || (m_count & 1) || p.bn % (2 * b_half_granule) != 0) return;
+    p.pair = 1;
+    if (p.splits > kMaxCluster / 2) p.splits = kMaxCluster / 2;
+}
+
 void finish_plan(Plan& pl)
 {
     Params& p = pl.p;
-    const int b_stage = p.bn * BK * 4;
+    const int b_stage = (p.pair ? p.bn / 2 : p.bn) * BK * 4;           // a pair CTA holds half of the B tile
     const int per_stage = (A_STAGE_BYTES + b_stage) * (p.x3 ? 2 : 1);   // 3xTF32: operand + residual tiles
     // two CTAs per SM when the grid has more CTAs than SMs, else one deep pipeline
     const int budget = (pl.grid > sm_count() && p.bn <= 128 && !p.x3) ? (kMaxSmem / 2 - 2048) : (kMaxSmem - 2048);
@@ -1183,9 +1354,13 @@ void finish_plan(Plan& pl)
     // the epilogue parks the 128 x bn tile (padded rows) and 128 row offsets in the (by then idle) stage ring
     while ((size_t)stages * per_stage < (size_t)kRedFloats(p.bn) * 4 + BM * 8) ++stages;
     p.stages = stages;
+#ifdef DCG_TC_TRACING
     static const int debug = env_int("DCG_TC_DEBUG");
     p.debug = debug;
-    pl.smem = (size_t)stages * per_stage + 1024 /*alignment slack*/ + 24 * stages + 32;
+#endif
+    pl.smem = (size_t)stages * per_stage + 1024 /*alignment slack*/ + 32 * stages + 32;
+    p.skip_stage = -1;
+    p.wait_cycles = kWaitCycles;
     pl.partial_bytes = p.splits > 1 ? (size_t)pl.grid * BM * p.bn * sizeof(float) : 0;
     pl.ws_bytes = pl.partial_bytes;
     if (pl.xp_bytes || pl.k4_bytes) pl.ws_bytes = pl.k4_off() + align_up(pl.k4_bytes, 256);
@@ -1237,6 +1412,7 @@ bool plan_fwd(const dcg_conv_desc& d, Plan& pl)
         pl.k4_bytes = (size_t)d.kh * 32 * d.o * sizeof(float);
     }
     p.splits = choose_splits(tiles, narrow ? d.kh : d.kh * d.kw * p.kchunks);
+    maybe_pair(pl, p.tiles_w * p.tiles_h * p.tiles_n, 32);   // B: whole 32-channel chunks per half
     pl.grid = tiles * p.splits;
     finish_plan(pl);
     return true;
@@ -1284,52 +1460,8 @@ bool plan_dx(const dcg_conv_desc& d, Plan& pl)
     const int tiles = classes * p.tiles_w * p.tiles_h * p.tiles_n * p.n_tiles;
     const int min_taps = (d.kh / d.stride_h) * (d.kw / d.stride_w);
     p.splits = choose_splits(tiles, (min_taps < 1 ? 1 : min_taps) * p.kchunks);
+    maybe_pair(pl, p.tiles_w * p.tiles_h * p.tiles_n, 8);    // B: K-major rows, whole 8-row swizzle groups per half
     pl.grid = tiles * p.splits;
-    // The parity classes have different tap counts (9, 6, 6, 4 for 5x5 stride 2).  When all CTAs of
-    // the layer are resident at once, the launch lasts as long as its slowest CTA.  DCG_TC_CLASS_BALANCE=1
-    // gives every class its own launch (side by side on four streams) and as many K partitions as
-    // make its CTAs about equally long.  Measured: the main loops do level out, but four launches
-    // with four cluster shapes cost more than that wins (1.826 against 1.784 ms per training step),
-    // so it is off unless asked for.
-    static const int balance = env_int("DCG_TC_CLASS_BALANCE");
-    const int slots = sm_count();
-    if (balance && !t_plan_x3 && !env_int("DCG_TC_SPLITS") && classes > 1 && classes <= 16 && p.bn <= 128 &&
-        tiles < slots) {
-        const int per_class = tiles / classes;
-        int stages_c[16];
-        for (int c = 0; c < classes; ++c) {
-            const int ph = c / d.stride_w, pw = c % d.stride_w;
-            const int rh = (ph + d.pad_top) % d.stride_h, rw = (pw + d.pad_left) % d.stride_w;
-            const int th = rh < d.kh ? (d.kh - rh + d.stride_h - 1) / d.stride_h : 0;
-            const int tw = rw < d.kw ? (d.kw - rw + d.stride_w - 1) / d.stride_w : 0;
-            stages_c[c] = th * tw * p.kchunks;
-        }
-        // smallest stage count per CTA (>= 4) whose partition counts fit the resident slots
-        for (int len = 4; len <= 4096; ++len) {
-            int ctas = 0;
-            bool ok = true;
-            for (int c = 0; c < classes; ++c) {
-                int sc = (stages_c[c] + len - 1) / len;
-                if (sc < 1) sc = 1;
-                if (sc > kMaxCluster) ok = false;
-                ctas += per_class * sc;
-            }
-            if (!ok || ctas > slots) continue;
-            pl.n_class = classes;
-            pl.grid = 0;
-            int smax = 1;
-            for (int c = 0; c < classes; ++c) {
-                int sc = (stages_c[c] + len - 1) / len;
-                if (sc < 1) sc = 1;
-                pl.class_splits[c] = sc;
-                pl.class_grid[c] = per_class * sc;
-                pl.grid += pl.class_grid[c];
-                if (sc > smax) smax = sc;
-            }
-            p.splits = smax;   // "has K partitions" for the scratch sizing below
-            break;
-        }
-    }
     finish_plan(pl);
     return true;
 }
@@ -1388,34 +1520,10 @@ bool make_plan(const dcg_conv_desc& d, int kind, Plan& pl)
     }
 }
 
-// Streams and events for launching the parity classes of a DX side by side (per device, made on
-// first use; calls that use them are serialised by the mutex).
-struct ClassStreams {
-    cudaStream_t side[3] = {nullptr, nullptr, nullptr};
-    cudaEvent_t fork = nullptr, join[3] = {nullptr, nullptr, nullptr};
-    std::mutex mutex;
-    bool ok = false, tried = false;
-};
-
-ClassStreams* class_streams()
-{
-    static ClassStreams per_device[64];
-    static std::mutex init_mutex;
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    ClassStreams& cs = per_device[dev];
-    std::lock_guard<std::mutex> lock(init_mutex);
-    if (!cs.tried) {
-        cs.tried = true;
-        bool ok = cudaEventCreateWithFlags(&cs.fork, cudaEventDisableTiming) == cudaSuccess;
-        for (int i = 0; i < 3 && ok; ++i)
-            ok = cudaStreamCreateWithFlags(&cs.side[i], cudaStreamNonBlocking) == cudaSuccess &&
-                 cudaEventCreateWithFlags(&cs.join[i], cudaEventDisableTiming) == cudaSuccess;
-        if (!ok) cudaGetLastError();
-        cs.ok = ok;
-    }
-    return cs.ok ? &cs : nullptr;
-}
+// Testing hooks (dcg_debug_set_wait_limit / dcg_debug_skip_stage): the wait limit of every barrier
+// wait in SM clocks, and a pipeline stage the producer leaves out so that a wait runs into that limit.
+std::atomic<long long> g_wait_cycles{kWaitCycles};
+std::atomic<int> g_test_skip_stage{-1};
 
 template <int MODE>
 int launch_grid(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, int grid, size_t smem, cudaStream_t stream)
@@ -1433,9 +1541,10 @@ int launch_grid(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, i
         attr[na].val.programmaticStreamSerializationAllowed = 1;
         ++na;
     }
-    if (p.splits > 1 && !p.ext_finish) {
+    const int cluster = (p.pair ? 2 : 1) * (p.ext_finish ? 1 : p.splits);
+    if (cluster > 1) {
         attr[na].id = cudaLaunchAttributeClusterDimension;
-        attr[na].val.clusterDim.x = (unsigned)p.splits;   // blockIdx.x = tile * splits + split: one cluster per tile
+        attr[na].val.clusterDim.x = (unsigned)cluster;   // blockIdx.x = tile * cluster + rank: one cluster per (pair) tile
         attr[na].val.clusterDim.y = 1;
         attr[na].val.clusterDim.z = 1;
         ++na;
@@ -1466,37 +1575,14 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, Plan& pl, float* out, c
     p.out = out;
     p.ep = ep;
     p.scratch = nullptr;
+    p.skip_stage = g_test_skip_stage.load();
+    p.wait_cycles = g_wait_cycles.load();
     if (p.splits > 1) {
         if (!ws || ws_bytes < pl.ws_bytes)
             return fail(DCG_ERR_WORKSPACE, "conv (tensor path): workspace %zu < %zu bytes", ws_bytes, pl.ws_bytes);
         p.scratch = static_cast<float*>(ws);
     }
     (void)channels;
-    if (pl.n_class > 0) {
-        // one launch per parity class, concurrently: class 0 on the caller's stream, the others on
-        // side streams forked from it and joined back
-        ClassStreams* cs = class_streams();
-        if (!cs) return fail(DCG_ERR_CUDA, "conv dx: could not create the per-class streams");
-        std::lock_guard<std::mutex> lock(cs->mutex);
-        DCG_CUDA(cudaEventRecord(cs->fork, stream));
-        size_t ctas_before = 0;
-        for (int c = 0; c < pl.n_class; ++c) {
-            Params pc = p;
-            pc.group0 = c;
-            pc.splits = pl.class_splits[c];
-            if (p.scratch) pc.scratch = p.scratch + ctas_before * BM * p.bn;
-            ctas_before += (size_t)pl.class_grid[c];
-            cudaStream_t sc = c == 0 ? stream : cs->side[(c - 1) % 3];
-            if (c > 0 && c <= 3) DCG_CUDA(cudaStreamWaitEvent(sc, cs->fork, 0));
-            const int st = launch_grid<MODE>(ma, mb, pc, pl.class_grid[c], pl.smem, sc);
-            if (st) return st;
-        }
-        for (int i = 0; i < 3 && i + 1 < pl.n_class; ++i) {
-            DCG_CUDA(cudaEventRecord(cs->join[i], cs->side[i]));
-            DCG_CUDA(cudaStreamWaitEvent(stream, cs->join[i], 0));
-        }
-        return DCG_OK;
-    }
     const int st = launch_grid<MODE>(ma, mb, p, pl.grid, pl.smem, stream);
     if (st) return st;
     if (p.ext_finish) {
@@ -1550,6 +1636,151 @@ int map_window(CUtensorMap* map, const float* xp, const dcg_conv_desc& d, const 
     return encode_map(map, xp, 5, dims, mn_major, strides, box, es);
 }
 
+// ---- prepared calls: plan + tensor maps, cached ------------------------------------------------------
+// Planning a convolution and encoding its two tensor maps costs the host ~10 us.  A training step
+// or the reference's Graph::run issues the same convolutions on the same buffers over and over, so
+// the result is kept per (device, operator, shape, operand addresses, scratch address, precision and
+// pair setting) in a small table; a hit leaves only the launch.
+struct Prepared {
+    Plan pl;
+    CUtensorMap ma, mb;
+};
+
+struct CacheKey {
+    int dev, kind, x3, pairs;
+    dcg_conv_desc d;
+    const void *a, *b, *ws;
+    size_t ws_bytes;
+};
+
+struct CacheEntry {
+    CacheKey key;
+    Prepared prep;
+};
+
+constexpr size_t kCacheEntries = 512;
+std::mutex g_cache_mutex;
+std::vector<CacheEntry> g_cache;
+size_t g_cache_next = 0;
+
+bool same_key(const CacheKey& u, const CacheKey& v)
+{
+    return u.dev == v.dev && u.kind == v.kind && u.x3 == v.x3 && u.pairs == v.pairs && u.a == v.a && u.b == v.b &&
+           u.ws == v.ws && u.ws_bytes == v.ws_bytes && std::memcmp(&u.d, &v.d, sizeof(dcg_conv_desc)) == 0;
+}
+
+// FWD: plan and maps for y = conv(x, k).  xp / k4 of a narrow-channel layer live in the scratch.
+int build_fwd(const dcg_conv_desc& d, const float* x, const float* k, void* ws, size_t ws_bytes, Prepared& pr)
+{
+    Plan& pl = pr.pl;
+    if (!plan_fwd(d, pl)) return fail(DCG_ERR_UNSUPPORTED, "conv fwd: shape not supported by the tensor path");
+    const Params& p = pl.p;
+    int st;
+    if (p.narrow) {
+        if (!ws || ws_bytes < pl.ws_bytes)
+            return fail(DCG_ERR_WORKSPACE, "conv (tensor path, narrow input): workspace %zu < %zu bytes", ws_bytes, pl.ws_bytes);
+        uint8_t* base = static_cast<uint8_t*>(ws);
+        const float* xp = reinterpret_cast<const float*>(base + pl.xp_off());
+        const float* k4 = reinterpret_cast<const float*>(base + pl.k4_off());
+        if ((st = map_window(&pr.ma, xp, d, pl, p.TW, p.TH, p.TN, false, 1))) return st;
+        // k4 [kh][slot][o] as (o%32, slot, kh, o/32), box (32, 32, 1, bn/32)
+        const cuuint64_t dims[4] = {32, 32, (cuuint64_t)d.kh, (cuuint64_t)(d.o / 32)};
+        const cuuint64_t strides[3] = {(cuuint64_t)d.o * 4, (cuuint64_t)32 * d.o * 4, 128};
+        const cuuint32_t box[4] = {32, 32, 1, (cuuint32_t)(p.bn / 32)};
+        const cuuint32_t es[4] = {1, 1, 1, 1};
+        return encode_map(&pr.mb, k4, 4, dims, true, strides, box, es);
+    }
+    if ((st = map_act_4d(&pr.ma, x, d.n, d.h, d.w, d.c, p.TW, p.TH, p.TN, d.stride_w, d.stride_h))) return st;
+    // k [tap][c][o] as (o%32, c, tap, o/32), box (32, 32, 1, bn/32); a pair CTA loads half the chunks
+    const cuuint64_t dims[4] = {32, (cuuint64_t)d.c, (cuuint64_t)(d.kh * d.kw), (cuuint64_t)(d.o / 32)};
+    const cuuint64_t strides[3] = {(cuuint64_t)d.o * 4, (cuuint64_t)d.c * d.o * 4, 128};
+    const cuuint32_t box[4] = {32, 32, 1, (cuuint32_t)(p.pair ? p.bn / 64 : p.bn / 32)};
+    const cuuint32_t es[4] = {1, 1, 1, 1};
+    return encode_map(&pr.mb, k, 4, dims, true, strides, box, es);
+}
+
+int build_dx(const dcg_conv_desc& d, const float* dy, const float* k, void* ws, size_t ws_bytes, Prepared& pr)
+{
+    Plan& pl = pr.pl;
+    if (!plan_dx(d, pl)) return fail(DCG_ERR_UNSUPPORTED, "conv dx: shape not supported by the tensor path");
+    const Params& p = pl.p;
+    int st = map_act_4d(&pr.ma, dy, d.n, d.ho, d.wo, d.o, p.TW, p.TH, p.TN, 1, 1);
+    if (st) return st;
+    if (pl.ycol_bytes) {   // narrow-channel layer: GEMM over all taps, then gather
+        if (!ws || ws_bytes < pl.ws_bytes)
+            return fail(DCG_ERR_WORKSPACE, "conv dx (tensor path, narrow input): workspace %zu < %zu bytes", ws_bytes, pl.ws_bytes);
+        const float* k2 = reinterpret_cast<const float*>(static_cast<uint8_t*>(ws) + pl.k2_off());
+        const int Jp = pl.Jp;
+        // k2 [o][Jp] as (j%32, o, 1, j/32), box (32, 32, 1, bn/32): the FWD kernel's weight view with one tap
+        const cuuint64_t dims[4] = {32, (cuuint64_t)d.o, 1, (cuuint64_t)(Jp / 32)};
+        const cuuint64_t strides[3] = {(cuuint64_t)Jp * 4, (cuuint64_t)d.o * Jp * 4, 128};
+        const cuuint32_t box[4] = {32, 32, 1, (cuuint32_t)(p.bn / 32)};
+        const cuuint32_t es[4] = {1, 1, 1, 1};
+        return encode_map(&pr.mb, k2, 4, dims, true, strides, box, es);
+    }
+    // k [kh][kw][c][o] as (o, c, kw, kh), box (32 o, bn c, 1, 1); a pair CTA loads half the rows
+    const cuuint64_t dims[4] = {(cuuint64_t)d.o, (cuuint64_t)d.c, (cuuint64_t)d.kw, (cuuint64_t)d.kh};
+    const cuuint64_t strides[3] = {(cuuint64_t)d.o * 4, (cuuint64_t)d.c * d.o * 4, (cuuint64_t)d.kw * d.c * d.o * 4};
+    const cuuint32_t box[4] = {32, (cuuint32_t)(p.pair ? p.bn / 2 : p.bn), 1, 1};
+    const cuuint32_t es[4] = {1, 1, 1, 1};
+    return encode_map(&pr.mb, k, 4, dims, false, strides, box, es);
+}
+
+// DK: ma / mb are the maps of the A / B operand (x and dy, or dy and x when the roles are swapped).
+int build_dk(const dcg_conv_desc& d, const float* x, const float* dy, void* ws, size_t ws_bytes, Prepared& pr)
+{
+    Plan& pl = pr.pl;
+    if (!plan_dk(d, pl)) return fail(DCG_ERR_UNSUPPORTED, "conv dk: shape not supported by the tensor path");
+    const Params& p = pl.p;
+    CUtensorMap mx, mdy;
+    int st;
+    if (p.narrow) {
+        if (!ws || ws_bytes < pl.ws_bytes)
+            return fail(DCG_ERR_WORKSPACE, "conv (tensor path, narrow input): workspace %zu < %zu bytes", ws_bytes, pl.ws_bytes);
+        const float* xp = reinterpret_cast<const float*>(static_cast<uint8_t*>(ws) + pl.xp_off());
+        if ((st = map_window(&mx, xp, d, pl, p.TW, p.TH, p.TN, true, d.kh))) return st;
+        if ((st = map_act_5d(&mdy, dy, d.n, d.ho, d.wo, d.o, p.TW, p.TH, p.TN, 1, 1, BM / 32))) return st;
+        pr.ma = mdy; pr.mb = mx;
+        return DCG_OK;
+    }
+    const int x_chunks = p.swap ? p.bn / 32 : BM / 32, dy_chunks = p.swap ? BM / 32 : p.bn / 32;
+    if ((st = map_act_5d(&mx, x, d.n, d.h, d.w, d.c, p.TW, p.TH, p.TN, d.stride_w, d.stride_h, x_chunks))) return st;
+    if ((st = map_act_5d(&mdy, dy, d.n, d.ho, d.wo, d.o, p.TW, p.TH, p.TN, 1, 1, dy_chunks))) return st;
+    if (p.swap) { pr.ma = mdy; pr.mb = mx; }
+    else { pr.ma = mx; pr.mb = mdy; }
+    return DCG_OK;
+}
+
+// Looks the call up, building and filing it on a miss.  The entry is copied out under the lock.
+int prepared_call(int kind, const dcg_conv_desc& d, const void* a, const void* b, void* ws, size_t ws_bytes, Prepared& out)
+{
+    CacheKey key;
+    std::memset(&key, 0, sizeof(key));
+    if (cudaGetDevice(&key.dev) != cudaSuccess) key.dev = -1;
+    key.kind = kind; key.x3 = t_plan_x3; key.pairs = pairs_enabled() ? 1 : 0;
+    key.d = d; key.a = a; key.b = b; key.ws = ws; key.ws_bytes = ws_bytes;
+    {
+        std::lock_guard<std::mutex> lock(g_cache_mutex);
+        for (const CacheEntry& e : g_cache)
+            if (same_key(e.key, key)) { out = e.prep; return DCG_OK; }
+    }
+    int st;
+    switch (kind) {
+    case kConvFwd: st = build_fwd(d, static_cast<const float*>(a), static_cast<const float*>(b), ws, ws_bytes, out); break;
+    case kConvDx: st = build_dx(d, static_cast<const float*>(a), static_cast<const float*>(b), ws, ws_bytes, out); break;
+    default: st = build_dk(d, static_cast<const float*>(a), static_cast<const float*>(b), ws, ws_bytes, out); break;
+    }
+    if (st) return st;
+    std::lock_guard<std::mutex> lock(g_cache_mutex);
+    if (g_cache.size() < kCacheEntries) {
+        g_cache.push_back(CacheEntry{key, out});
+    } else {
+        g_cache[g_cache_next] = CacheEntry{key, out};
+        g_cache_next = (g_cache_next + 1) % kCacheEntries;
+    }
+    return DCG_OK;
+}
+
 }  // namespace
 
 bool conv_tc_supported(const dcg_conv_desc& d, int kind, bool x3)
@@ -1571,61 +1802,33 @@ int conv_tc_fwd(const dcg_conv_desc& d, const float* x, const float* k, float* y
                 void* ws, size_t ws_bytes, cudaStream_t stream, bool x3)
 {
     PlanX3 scope(x3);
-    Plan pl;
-    if (!plan_fwd(d, pl)) return fail(DCG_ERR_UNSUPPORTED, "conv fwd: shape not supported by the tensor path");
-    const Params& p = pl.p;
-    CUtensorMap ma, mb;
-    int st;
-    if (p.narrow) {
-        float *xp, *k4;
-        if ((st = narrow_prepare(d, pl, x, k, ws, ws_bytes, stream, &xp, &k4))) return st;
-        if ((st = map_window(&ma, xp, d, pl, p.TW, p.TH, p.TN, false, 1))) return st;
-        // k4 [kh][slot][o] as (o%32, slot, kh, o/32), box (32, 32, 1, bn/32)
-        const cuuint64_t dims[4] = {32, 32, (cuuint64_t)d.kh, (cuuint64_t)(d.o / 32)};
-        const cuuint64_t strides[3] = {(cuuint64_t)d.o * 4, (cuuint64_t)32 * d.o * 4, 128};
-        const cuuint32_t box[4] = {32, 32, 1, (cuuint32_t)(p.bn / 32)};
-        const cuuint32_t es[4] = {1, 1, 1, 1};
-        if ((st = encode_map(&mb, k4, 4, dims, true, strides, box, es))) return st;
-        return launch<MODE_FWD>(ma, mb, pl, y, ep, d.o, ws, ws_bytes, stream);
-    }
-    st = map_act_4d(&ma, x, d.n, d.h, d.w, d.c, p.TW, p.TH, p.TN, d.stride_w, d.stride_h);
+    Prepared pr;
+    int st = prepared_call(kConvFwd, d, x, k, ws, ws_bytes, pr);
     if (st) return st;
-    // k [tap][c][o] as (o%32, c, tap, o/32), box (32, 32, 1, bn/32)
-    const cuuint64_t dims[4] = {32, (cuuint64_t)d.c, (cuuint64_t)(d.kh * d.kw), (cuuint64_t)(d.o / 32)};
-    const cuuint64_t strides[3] = {(cuuint64_t)d.o * 4, (cuuint64_t)d.c * d.o * 4, 128};
-    const cuuint32_t box[4] = {32, 32, 1, (cuuint32_t)(p.bn / 32)};
-    const cuuint32_t es[4] = {1, 1, 1, 1};
-    if ((st = encode_map(&mb, k, 4, dims, true, strides, box, es))) return st;
-    return launch<MODE_FWD>(ma, mb, pl, y, ep, d.o, ws, ws_bytes, stream);
+    if (pr.pl.p.narrow) {
+        float *xp, *k4;
+        if ((st = narrow_prepare(d, pr.pl, x, k, ws, ws_bytes, stream, &xp, &k4))) return st;
+    }
+    return launch<MODE_FWD>(pr.ma, pr.mb, pr.pl, y, ep, d.o, ws, ws_bytes, stream);
 }
 
 int conv_tc_dx(const dcg_conv_desc& d, const float* dy, const float* k, float* dx, const EpilogueArgs& ep,
                void* ws, size_t ws_bytes, cudaStream_t stream, bool x3)
 {
     PlanX3 scope(x3);
-    Plan pl;
-    if (!plan_dx(d, pl)) return fail(DCG_ERR_UNSUPPORTED, "conv dx: shape not supported by the tensor path");
-    const Params& p = pl.p;
-    CUtensorMap ma, mb;
-    int st = map_act_4d(&ma, dy, d.n, d.ho, d.wo, d.o, p.TW, p.TH, p.TN, 1, 1);
+    Prepared pr;
+    int st = prepared_call(kConvDx, d, dy, k, ws, ws_bytes, pr);
     if (st) return st;
+    Plan& pl = pr.pl;
     if (pl.ycol_bytes) {   // narrow-channel layer: GEMM over all taps, then gather
-        if (!ws || ws_bytes < pl.ws_bytes)
-            return fail(DCG_ERR_WORKSPACE, "conv dx (tensor path, narrow input): workspace %zu < %zu bytes", ws_bytes, pl.ws_bytes);
         uint8_t* base = static_cast<uint8_t*>(ws);
         float* k2 = reinterpret_cast<float*>(base + pl.k2_off());
         float* ycol = reinterpret_cast<float*>(base + pl.ycol_off());
         const int Jp = pl.Jp;
         launch_pdl(repack_k2_kernel, (d.o * Jp + 255) / 256, 256, 0, stream, k, k2, d.kh * d.kw, d.c, Jp, d.o);
         DCG_LAUNCH_CHECK("repack_k2_kernel");
-        // k2 [o][Jp] as (j%32, o, 1, j/32), box (32, 32, 1, bn/32): the FWD kernel's weight view with one tap
-        const cuuint64_t dims[4] = {32, (cuuint64_t)d.o, 1, (cuuint64_t)(Jp / 32)};
-        const cuuint64_t strides[3] = {(cuuint64_t)Jp * 4, (cuuint64_t)d.o * Jp * 4, 128};
-        const cuuint32_t box[4] = {32, 32, 1, (cuuint32_t)(p.bn / 32)};
-        const cuuint32_t es[4] = {1, 1, 1, 1};
-        if ((st = encode_map(&mb, k2, 4, dims, true, strides, box, es))) return st;
         const EpilogueArgs none{};
-        if ((st = launch<MODE_FWD>(ma, mb, pl, ycol, none, Jp, ws, ws_bytes, stream))) return st;
+        if ((st = launch<MODE_FWD>(pr.ma, pr.mb, pl, ycol, none, Jp, ws, ws_bytes, stream))) return st;
         const size_t total = (size_t)d.n * d.h * d.w;
         size_t blocks = (total + 255) / 256;
         const size_t cap = (size_t)sm_count() * 16;
@@ -1636,39 +1839,31 @@ int conv_tc_dx(const dcg_conv_desc& d, const float* dy, const float* k, float* d
         DCG_LAUNCH_CHECK("col2im_kernel");
         return DCG_OK;
     }
-    // k [kh][kw][c][o] as (o, c, kw, kh), box (32 o, bn c, 1, 1)
-    const cuuint64_t dims[4] = {(cuuint64_t)d.o, (cuuint64_t)d.c, (cuuint64_t)d.kw, (cuuint64_t)d.kh};
-    const cuuint64_t strides[3] = {(cuuint64_t)d.o * 4, (cuuint64_t)d.c * d.o * 4, (cuuint64_t)d.kw * d.c * d.o * 4};
-    const cuuint32_t box[4] = {32, (cuuint32_t)p.bn, 1, 1};
-    const cuuint32_t es[4] = {1, 1, 1, 1};
-    if ((st = encode_map(&mb, k, 4, dims, false, strides, box, es))) return st;
-    return launch<MODE_DX>(ma, mb, pl, dx, ep, d.c, ws, ws_bytes, stream);
+    return launch<MODE_DX>(pr.ma, pr.mb, pl, dx, ep, d.c, ws, ws_bytes, stream);
 }
 
 int conv_tc_dk(const dcg_conv_desc& d, const float* x, const float* dy, float* dk, void* ws, size_t ws_bytes,
                cudaStream_t stream, bool x3)
 {
     PlanX3 scope(x3);
-    Plan pl;
-    if (!plan_dk(d, pl)) return fail(DCG_ERR_UNSUPPORTED, "conv dk: shape not supported by the tensor path");
-    const Params& p = pl.p;
-    CUtensorMap mx, mdy;
-    const EpilogueArgs no_epilogue{};
-    int st;
-    if (p.narrow) {
-        float* xp;
-        if ((st = narrow_prepare(d, pl, x, nullptr, ws, ws_bytes, stream, &xp, nullptr))) return st;
-        if ((st = map_window(&mx, xp, d, pl, p.TW, p.TH, p.TN, true, d.kh))) return st;
-        if ((st = map_act_5d(&mdy, dy, d.n, d.ho, d.wo, d.o, p.TW, p.TH, p.TN, 1, 1, BM / 32))) return st;
-        return launch<MODE_DK>(mdy, mx, pl, dk, no_epilogue, d.o, ws, ws_bytes, stream);
-    }
-    const int x_chunks = p.swap ? p.bn / 32 : BM / 32, dy_chunks = p.swap ? BM / 32 : p.bn / 32;
-    st = map_act_5d(&mx, x, d.n, d.h, d.w, d.c, p.TW, p.TH, p.TN, d.stride_w, d.stride_h, x_chunks);
+    Prepared pr;
+    int st = prepared_call(kConvDk, d, x, dy, ws, ws_bytes, pr);
     if (st) return st;
-    if ((st = map_act_5d(&mdy, dy, d.n, d.ho, d.wo, d.o, p.TW, p.TH, p.TN, 1, 1, dy_chunks))) return st;
+    if (pr.pl.p.narrow) {
+        float* xp;
+        if ((st = narrow_prepare(d, pr.pl, x, nullptr, ws, ws_bytes, stream, &xp, nullptr))) return st;
+    }
     const EpilogueArgs none{};
-    if (p.swap) return launch<MODE_DK>(mdy, mx, pl, dk, none, d.o, ws, ws_bytes, stream);
-    return launch<MODE_DK>(mx, mdy, pl, dk, none, d.o, ws, ws_bytes, stream);
+    return launch<MODE_DK>(pr.ma, pr.mb, pr.pl, dk, none, d.o, ws, ws_bytes, stream);
+}
+
+// wait_cycles: > 0 sets the limit, -1 restores the default, 0 leaves it; skip_stage / pairs: -2 leaves it.
+void conv_tc_set_hooks(long long wait_cycles, int skip_stage, int pairs)
+{
+    if (wait_cycles > 0) g_wait_cycles.store(wait_cycles);
+    else if (wait_cycles < 0) g_wait_cycles.store(kWaitCycles);
+    if (skip_stage != -2) g_test_skip_stage.store(skip_stage);
+    if (pairs != -2) g_pair_override.store(pairs);
 }
 
 // Reads (and clears) the device status word of the tensor-path kernels.  Synchronises the device.
@@ -1681,6 +1876,7 @@ int conv_tc_device_status(int* detail /* [4] */)
     if (h[0] != 0) {
         const int zero[4] = {0, 0, 0, 0};
         DCG_CUDA(cudaMemcpyToSymbol(g_tc_status, zero, sizeof(zero)));
+        contexts_reset_tickets();   // a launch that gave up may have left column-sum tickets counted up
         return fail(DCG_ERR_DEVICE, "tensor-path kernel gave up waiting: code %d block %d role %d stage %d",
                     h[0], h[1], h[2], h[3]);
     }
@@ -1691,16 +1887,27 @@ int conv_tc_device_status(int* detail /* [4] */)
 
 extern "C" int dcg_device_status(void) { return dcg::conv_tc_device_status(nullptr); }
 
-// Tuning aid, not part of the public header: copies the timeline recorded by CTA 0 of the last
-// tensor-path launch (DCG_TC_DEBUG bit 4) to `out` (3080 values).  Synchronises the device.
+extern "C" void dcg_debug_set_wait_limit(long long sm_clocks)
+{
+    dcg::conv_tc_set_hooks(sm_clocks > 0 ? sm_clocks : -1, -2, -2);
+}
+
+extern "C" void dcg_debug_skip_stage(int stage) { dcg::conv_tc_set_hooks(0, stage < 0 ? -1 : stage, -2); }
+
+extern "C" void dcg_debug_set_pairs(int mode) { dcg::conv_tc_set_hooks(0, -2, mode < 0 ? -1 : (mode != 0)); }
+
+#ifdef DCG_TC_TRACING
+// Tuning aids of -DDCG_TC_TRACING builds, not part of the public header: copy the timelines recorded
+// by the last tensor-path launch (DCG_TC_DEBUG bits 4 / 8) to `out`.  Synchronise the device.
 extern "C" int dcg_debug_cta_trace(unsigned long long* out /* [1024][8] */)
 {
     if (cudaDeviceSynchronize() != cudaSuccess) return DCG_ERR_CUDA;
     return cudaMemcpyFromSymbol(out, dcg::g_tc_cta_trace, sizeof(unsigned long long) * 1024 * 8) == cudaSuccess ? DCG_OK : DCG_ERR_CUDA;
 }
 
-extern "C" int dcg_debug_trace(long long* out)
+extern "C" int dcg_debug_trace(long long* out /* [3080] */)
 {
     if (cudaDeviceSynchronize() != cudaSuccess) return DCG_ERR_CUDA;
     return cudaMemcpyFromSymbol(out, dcg::g_tc_trace, sizeof(long long) * 3080) == cudaSuccess ? DCG_OK : DCG_ERR_CUDA;
 }
+#endif

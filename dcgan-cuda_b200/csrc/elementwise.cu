@@ -129,9 +129,14 @@ update_kernel(const float* __restrict__ dv, float* __restrict__ out,
 // lane l adds slabs l, l+L, ... and the lane sums are added in lane order, so the result depends
 // on the launch shape only, never on which block came last.  `tickets` == nullptr leaves the
 // slabs to colsum_final_kernel.
-constexpr int kTicketSets = 64, kTicketTiles = 16, kSlabGroup = 16, kMaxSlabs = 1008;
+// The ticket words belong to whoever owns the scratch of the launch (they sit behind the partial
+// sums in the caller's buffer, or at the tail of a context's scratch allocation), so two launches
+// only ever share tickets if they share scratch - which already requires them to be stream-ordered.
+// They must be zero when a launch starts; every adder resets the ticket it consumed.
+constexpr int kTicketTiles = 16, kSlabGroup = 16, kMaxSlabs = 1008;
 constexpr int kTicketsPerTile = 1 + kMaxSlabs / kSlabGroup;         // group-level ticket + one per slab group
-__device__ unsigned g_colsum_tickets[kTicketSets][kTicketTiles * kTicketsPerTile];   // zero at load, reset by the adders
+constexpr size_t kTicketBytes = (size_t)kTicketTiles * kTicketsPerTile * sizeof(unsigned);
+static_assert(kTicketBytes == dcg::kColsumTicketBytes, "ticket area size is part of the scratch contract");
 
 // One block adds `nrows` rows of src ([nrows][cols]) for its column tile into dst: thread = (column
 // group, lane); lane l adds rows l, l+L, ... through four independent accumulators (four loads in
@@ -580,16 +585,65 @@ ColsumPlan colsum_plan(size_t rows, size_t cols, bool ptr_aligned)
     if (p.slabs < 1) p.slabs = 1;
     return p;
 }
+
+// Bytes of partial sums a plan needs (0: a single slab writes the result directly).
+size_t colsum_partial_bytes(const ColsumPlan& p, size_t cols)
+{
+    if (p.slabs <= 1) return 0;
+    // slab rows plus one row per group of kSlabGroup slabs (the second level of the in-kernel sum)
+    return (size_t)(p.slabs + (p.slabs + kSlabGroup - 1) / kSlabGroup) * cols * sizeof(float);
+}
 }  // namespace
+
+namespace dcg {
+// The launch behind dcg_colsum.  `tickets`: kColsumTicketBytes of zeroed device memory owned by the
+// caller of this launch (see above), or nullptr to finish with a second kernel instead.
+int colsum_launch(const float* a, float* out, size_t rows, size_t cols, void* workspace, size_t workspace_bytes,
+                  unsigned* tickets, cudaStream_t stream)
+{
+    const ColsumPlan p = colsum_plan(rows, cols, aligned16(a) && aligned16(workspace));
+    const size_t need = colsum_partial_bytes(p, cols);
+    float* partial;
+    if (p.slabs == 1) {
+        partial = out;  // a single slab writes the result directly
+    } else {
+        if (!workspace || workspace_bytes < need)
+            return fail(DCG_ERR_WORKSPACE, "dcg_colsum: workspace %zu < %zu bytes", workspace_bytes, need);
+        DCG_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 3u) == 0, "dcg_colsum: workspace is not 4-byte aligned");
+        partial = static_cast<float*>(workspace);
+    }
+    const dim3 grid(p.grid_x, p.slabs);
+    const size_t smem = (size_t)kThreads * (p.vec ? 4 : 1) * sizeof(float);
+    if (p.slabs <= 1 || p.grid_x > (unsigned)kTicketTiles) tickets = nullptr;   // nothing to add / too many column tiles
+    if (p.vec)
+        launch_pdl(colsum_partial_kernel<true>, grid, kThreads, smem, stream,
+            a, partial, rows, (unsigned)cols, p.rows_per_slab, p.tx_count, out, tickets);
+    else
+        launch_pdl(colsum_partial_kernel<false>, grid, kThreads, smem, stream,
+            a, partial, rows, (unsigned)cols, p.rows_per_slab, p.tx_count, out, tickets);
+    DCG_LAUNCH_CHECK("colsum_partial_kernel");
+    if (p.slabs > 1 && !tickets) {
+        launch_pdl(colsum_final_kernel, (unsigned)((cols + 31) / 32), 256, 0, stream,
+            partial, out, p.slabs, (unsigned)cols);
+        DCG_LAUNCH_CHECK("colsum_final_kernel");
+    }
+    return DCG_OK;
+}
+
+size_t colsum_partial_bytes_max(size_t rows, size_t cols)
+{
+    // the larger of the vector / scalar plans (pointer alignment is unknown at query time)
+    const size_t a = colsum_partial_bytes(colsum_plan(rows, cols, true), cols);
+    const size_t b = colsum_partial_bytes(colsum_plan(rows, cols, false), cols);
+    return a > b ? a : b;
+}
+}  // namespace dcg
 
 extern "C" size_t dcg_colsum_workspace_bytes(size_t rows, size_t cols)
 {
-    // Sized for the larger of the vector / scalar plans (pointer alignment is unknown here).
-    const ColsumPlan a = colsum_plan(rows, cols, true), b = colsum_plan(rows, cols, false);
-    const unsigned slabs = a.slabs > b.slabs ? a.slabs : b.slabs;
-    if (slabs <= 1) return 0;   // a single slab writes the result directly
-    // slab rows plus one row per group of kSlabGroup slabs (the second level of the in-kernel sum)
-    return (size_t)(slabs + (slabs + kSlabGroup - 1) / kSlabGroup) * cols * sizeof(float);
+    const size_t partial = dcg::colsum_partial_bytes_max(rows, cols);
+    if (partial == 0) return 0;
+    return align_up(partial, 256) + kTicketBytes;   // partial sums, then the ticket words
 }
 
 extern "C" int dcg_colsum(const float* a, float* out, size_t rows, size_t cols, void* workspace,
@@ -597,49 +651,18 @@ extern "C" int dcg_colsum(const float* a, float* out, size_t rows, size_t cols, 
 {
     DCG_CHECK_ARG(a && out, "dcg_colsum: null pointer");
     DCG_CHECK_ARG(cols > 0 && cols <= 0x7fffffffu && rows > 0, "dcg_colsum: bad shape %zu x %zu", rows, cols);
-    const ColsumPlan p = colsum_plan(rows, cols, aligned16(a));
-    const size_t need = (size_t)(p.slabs + (p.slabs + kSlabGroup - 1) / kSlabGroup) * cols * sizeof(float);
-    float* partial;
-    if (p.slabs == 1) {
-        partial = out;  // a single slab writes the result directly
-    } else {
+    const size_t need = dcg_colsum_workspace_bytes(rows, cols);
+    unsigned* tickets = nullptr;
+    if (need > 0) {
         if (!workspace || workspace_bytes < need)
             return fail(DCG_ERR_WORKSPACE, "dcg_colsum: workspace %zu < %zu bytes", workspace_bytes, need);
-        partial = static_cast<float*>(workspace);
+        DCG_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 3u) == 0, "dcg_colsum: workspace is not 4-byte aligned");
+        // the caller's buffer may hold anything: clear the ticket words behind the partial sums on the
+        // same stream (a memset node when the stream is being captured; never an allocation)
+        tickets = reinterpret_cast<unsigned*>(static_cast<unsigned char*>(workspace) + need - kTicketBytes);
+        DCG_CUDA(cudaMemsetAsync(tickets, 0, kTicketBytes, as_stream(stream)));
     }
-    const dim3 grid(p.grid_x, p.slabs);
-    const size_t smem = (size_t)kThreads * (p.vec ? 4 : 1) * sizeof(float);
-    // One launch when the column tiles fit a ticket set: consecutive launches rotate through the
-    // sets, so up to kTicketSets column sums may be in flight on different streams at once.
-    unsigned* tickets = nullptr;
-    if (p.slabs > 1 && p.grid_x <= (unsigned)kTicketTiles) {
-        static std::atomic<unsigned> seq{0};
-        static void* base_of_device[64];   // per device ordinal; looked up once (not while a stream is capturing)
-        int dev = 0;
-        DCG_CUDA(cudaGetDevice(&dev));
-        DCG_CHECK_ARG(dev >= 0 && dev < 64, "dcg_colsum: device ordinal %d out of range", dev);
-        if (!base_of_device[dev]) {
-            void* b = nullptr;
-            DCG_CUDA(cudaGetSymbolAddress(&b, g_colsum_tickets));
-            base_of_device[dev] = b;
-        }
-        void* base = base_of_device[dev];
-        tickets = static_cast<unsigned*>(base) +
-                  (size_t)(seq.fetch_add(1) % kTicketSets) * kTicketTiles * kTicketsPerTile;
-    }
-    if (p.vec)
-        launch_pdl(colsum_partial_kernel<true>, grid, kThreads, smem, as_stream(stream), 
-            a, partial, rows, (unsigned)cols, p.rows_per_slab, p.tx_count, out, tickets);
-    else
-        launch_pdl(colsum_partial_kernel<false>, grid, kThreads, smem, as_stream(stream), 
-            a, partial, rows, (unsigned)cols, p.rows_per_slab, p.tx_count, out, tickets);
-    DCG_LAUNCH_CHECK("colsum_partial_kernel");
-    if (p.slabs > 1 && !tickets) {
-        launch_pdl(colsum_final_kernel, (unsigned)((cols + 31) / 32), 256, 0, as_stream(stream), 
-            partial, out, p.slabs, (unsigned)cols);
-        DCG_LAUNCH_CHECK("colsum_final_kernel");
-    }
-    return DCG_OK;
+    return dcg::colsum_launch(a, out, rows, cols, workspace, need ? need - kTicketBytes : 0, tickets, as_stream(stream));
 }
 
 extern "C" int dcg_rowsum(const float* a, float* out, size_t rows, size_t cols, dcg_stream_t stream)

@@ -95,7 +95,7 @@ struct dcg_trainer {
         cudaGraphExec_t exec = nullptr;
         int eager_runs = 0;
         uint64_t launches = 0;     // kernels in the graph (the library's launch counter advances by this per replay)
-        const void* ws = nullptr;  // scratch address baked into the captured launches
+        uint64_t generation = 0;   // the context's generation the graph was captured under
         bool failed = false;
     };
     ListGraph d_graph, g_graph, gen_graph, g_part_graph[2];
@@ -463,7 +463,7 @@ int run_list(dcg_trainer* t, const std::vector<dcg_node>& all, dcg_trainer::List
         if (!eager) ++g.eager_runs;
         return dcg_run_nodes(t->ctx, L.data(), (int)L.size(), t->cfg.fuse);
     }
-    if (g.exec && g.ws != dcg::context_workspace(t->ctx)) {   // scratch moved: the captured addresses are stale
+    if (g.exec && g.generation != dcg::context_generation(t->ctx)) {   // scratch moved or precision switched: stale
         cudaGraphExecDestroy(g.exec);
         g.exec = nullptr;
     }
@@ -493,7 +493,7 @@ int run_list(dcg_trainer* t, const std::vector<dcg_node>& all, dcg_trainer::List
         }
         cudaGraphDestroy(graph);
         g.launches = dcg_launches_total() - before;
-        g.ws = dcg::context_workspace(t->ctx);
+        g.generation = dcg::context_generation(t->ctx);
         dcg::count_launch(-(int)g.launches);   // the capture launched nothing; the replay below counts
     }
     if (cudaGraphLaunch(g.exec, t->stream) != cudaSuccess)
@@ -541,7 +541,7 @@ int step_as_one_graph(dcg_trainer* t)
     dcg_trainer::ListGraph& g = t->step_graph;
     if (!t->use_graphs || g.failed || t->cfg.world > 1 || dcg::context_is_profiling(t->ctx)) return 0;
     if (t->d_graph.eager_runs < 2 || t->g_graph.eager_runs < 2) return 0;   // lists not warmed up yet
-    if (g.exec && g.ws != dcg::context_workspace(t->ctx)) {
+    if (g.exec && g.generation != dcg::context_generation(t->ctx)) {
         cudaGraphExecDestroy(g.exec);
         g.exec = nullptr;
     }
@@ -575,7 +575,7 @@ int step_as_one_graph(dcg_trainer* t)
             return (st = enqueue_step(t, t->lr_dev.p)) ? st : 1;
         }
         g.launches = captured;
-        g.ws = dcg::context_workspace(t->ctx);
+        g.generation = dcg::context_generation(t->ctx);
     }
     if (cudaGraphLaunch(g.exec, t->stream) != cudaSuccess)
         return fail(DCG_ERR_CUDA, "cudaGraphLaunch: %s", cudaGetErrorString(cudaGetLastError()));

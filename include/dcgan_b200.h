@@ -393,6 +393,17 @@ size_t dcg_trainer_arena_bytes(const dcg_trainer* t);
  * Returns DCG_OK or DCG_ERR_DEVICE (dcg_last_error() names block, role, stage). */
 int dcg_device_status(void);
 const char* dcg_last_error(void);
+/* Testing hooks of the tensor-path convolution kernels (no counterpart in the reference; process-wide,
+ * they affect launches enqueued after the call):
+ *  dcg_debug_set_wait_limit  limit of every bounded barrier wait in SM clocks (<= 0 restores ~1 s);
+ *  dcg_debug_skip_stage      the TMA producer leaves pipeline stage `stage` of every tile out (< 0: never), so
+ *                            that a consumer's wait runs into the limit: the kernel then records the failure,
+ *                            still terminates, and dcg_device_status() returns DCG_ERR_DEVICE;
+ *  dcg_debug_set_pairs       1 / 0 force CTA pairs (tcgen05 cta_group::2 tiles of 256 rows) on / off for the
+ *                            shapes that allow them, < 0 follows the DCG_TC_PAIR environment variable. */
+void dcg_debug_set_wait_limit(long long sm_clocks);
+void dcg_debug_skip_stage(int stage);
+void dcg_debug_set_pairs(int mode);
 /* Library version and the architecture the kernels were built for ("sm_100a"). */
 const char* dcg_build_info(void);
 /* Kernels launched by this library since it was loaded (all contexts, all threads). */

@@ -315,3 +315,69 @@ def test_benchmark_shapes_vs_reference_cpu_code(pkg, dev, ref, layer):
             else:   # the bound is on the operator's output tensor: scale by the whole dk
                 lim = TF32_TOL * float(dk.abs().max())
                 assert float(np.abs(got.cpu().numpy() - dk_ref).max()) <= lim, "dk slice c%d o%d" % (c0, o0)
+
+
+def test_bounded_wait_runs_out_and_the_context_survives(pkg, dev):
+    """Failure detection without a fault: the producer is told to leave one pipeline stage out, so
+    the MMA warp's wait on that stage can never complete; with the wait limit lowered to about a
+    millisecond the kernel gives up, records (block, role, stage) in the device status word, still
+    reaches its final barrier and frees TMEM.  dcg_device_status() then reports DCG_ERR_DEVICE, and a
+    normal call right after passes - the context stays usable."""
+    F, L = pkg.functional, pkg.lib
+    x = seeded((80, 32, 32, 32), 501)         # 160 tiles of 128 pixels: more tiles than SMs, so no K partitions, no cluster
+    k = seeded((5, 5, 32, 64), 502) * np.float32(0.1)
+    xd, kd = torch.from_numpy(x).to(dev), torch.from_numpy(k).to(dev)
+    assert L.dcg_device_status() == 0
+    try:
+        L.dcg_debug_set_pairs(0)
+        L.dcg_debug_set_wait_limit(2_000_000)   # ~1 ms of SM clocks
+        L.dcg_debug_skip_stage(3)
+        F.conv2d_fwd(xd, kd, precision=pkg.PREC_TF32)
+        torch.cuda.synchronize()                # returns: every wait in the kernel is bounded
+    finally:
+        L.dcg_debug_skip_stage(-1)
+        L.dcg_debug_set_wait_limit(0)
+        L.dcg_debug_set_pairs(-1)
+    assert L.dcg_device_status() == pkg._lib.ERR_DEVICE
+    assert b"gave up waiting" in L.dcg_last_error()
+    assert L.dcg_device_status() == 0           # reading clears the word
+    y = F.conv2d_fwd(xd, kd, precision=pkg.PREC_TF32)
+    torch.cuda.synchronize()
+    assert L.dcg_device_status() == 0
+    y32 = F.conv2d_fwd(xd, kd, precision=pkg.PREC_FP32)   # bit-equal to the oracle (test_conv_fwd_dx_dk)
+    torch.cuda.synchronize()
+    assert (y - y32).abs().max().item() <= TF32_TOL * y32.abs().max().item()
+
+
+@pytest.mark.parametrize("layer", [(64, 32, 64, 128), (64, 16, 128, 256), (64, 8, 256, 512), (128, 16, 128, 256),
+                                   (6, 16, 128, 256), (2, 32, 64, 128)])
+def test_cta_pairs_match_single_cta_tiles(pkg, dev, layer):
+    """CTA pairs (one tcgen05.mma.cta_group::2 over two CTAs' A halves and B halves) compute the same
+    tiles as single CTAs: forward and input gradient, with and without K partitions, against the
+    fp32 path (1e-2 * max|ref|) and against the single-CTA tensor path (same operand rounding, the K
+    partitions may be cut differently: 1e-4 * max), and deterministic."""
+    F, L = pkg.functional, pkg.lib
+    B, H, C, O = layer
+    g = torch.Generator(device="cpu").manual_seed(61)
+    x = (torch.rand((B, H, H, C), generator=g) * 2 - 1).to(dev)
+    k = (torch.randn((5, 5, C, O), generator=g) * 0.02).to(dev)
+    dy = (torch.rand((B, H // 2, H // 2, O), generator=g) * 2 - 1).to(dev)
+    bias = torch.randn((O,), generator=g).to(dev)
+    ref = (F.conv2d_fwd(x, k, precision=pkg.PREC_FP32) + bias, F.conv2d_dx(dy, k, (H, H), precision=pkg.PREC_FP32))
+    run = lambda: (F.conv2d_fwd(x, k, epilogue=F.make_epilogue(bias=bias)), F.conv2d_dx(dy, k, (H, H)))
+    try:
+        L.dcg_debug_set_pairs(0)
+        single = run()
+        L.dcg_debug_set_pairs(1)
+        L.dcg_debug_set_wait_limit(40_000_000)   # a handshake that never completes costs ~20 ms, not seconds
+        a, b = run(), run()
+        torch.cuda.synchronize()
+    finally:
+        L.dcg_debug_set_pairs(-1)
+        L.dcg_debug_set_wait_limit(0)
+    assert L.dcg_device_status() == 0, L.dcg_last_error()
+    for name, r, s1, u, v in zip(("fwd+bias", "dx"), ref, single, a, b):
+        scale = r.abs().max().item()
+        assert (r - u).abs().max().item() <= TF32_TOL * scale, name
+        assert (s1 - u).abs().max().item() <= 1e-4 * scale, name
+        assert torch.equal(u, v), name

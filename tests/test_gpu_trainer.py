@@ -193,8 +193,8 @@ def test_batch64_tensor_path_vs_fp32_path(pkg, dev):
     streams, K-partition clusters at the shapes bench.py times) on the TF32 tensor path against the
     fp32 CUDA-core path on identical parameters and inputs; the fp32 path is itself pinned to the
     CPU oracle at batch 2 (test_gradients_match_cpu_model).  Losses to 1e-4; every gradient by
-    relative L2.  Measured on B200: D gradients <= 1.5e-3, G gradients <= 4e-3 (kink flips of single
-    pre-activations average out over 64 images); the bounds are 3x that."""
+    relative L2 (kink flips of single pre-activations average out over 64 images, so the bound is far
+    tighter than the 1e-1 of the batch-2 check); the test prints what it measured."""
     B = 64
     g = torch.Generator().manual_seed(17)
     x = torch.rand((B, 64, 64, 3), generator=g) * 2 - 1
