@@ -12,14 +12,19 @@ per update).  Inputs are synthetic with the data's shapes and ranges: images ~ U
 [64,64,64,3], z ~ U(-1,1) [64,100], weights ~ N(0,0.02), seeded.
 
 One JSON line is printed by rank 0:
-  value      images/s over all GPUs, device-timed (CUDA events, max over ranks), inputs resident in HBM
+  value      images/s over all GPUs, device-timed (CUDA events, max over ranks), inputs resident in HBM;
+             the K steps are timed as a block, the block is repeated until at least a second of device
+             time has been measured, and the median block is reported (blocks, min, max alongside)
   e2e        the same through Trainer.submit_host / result: every step's own pinned host -> device copies
              of its inputs and a device -> host read of both losses inside the timed region, the copies
              of step i+1 overlapping the compute of step i
   roofline   the tensor-path convolution kernel: algorithmic FLOPs / event-timed duration of its
              launches inside profiled steps, against the TF32 peak (half the measured dense bf16 peak)
   cpu_baseline  the reference's CPU code (oracle/_ref) on a bounded, FLOP-weighted sample of the same
-             iteration at batch 1, one thread
+             iteration at batch 1, one thread; plus, where the reference tree was built against this
+             backend (dcgan-cuda_b200/shim), its MCPU mode (4 pool threads) on the generator forward
+  gen_images_per_s / d_fwd_bwd_ms   BASELINE configs[0] (generator forward, leaky) and configs[1]
+             (discriminator forward + backward on real images) at batch 64, device-timed
 """
 import argparse
 import ctypes
@@ -36,6 +41,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 BATCH = 64
+MIN_TIMED_S = 1.0   # device time measured at least, whatever --steps is
 METRIC = "dcgan_train_images_per_s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -54,17 +60,58 @@ def read_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    """Samples SM clocks and throttle reasons while a timed region runs: read-only NVML queries from a
+    thread of this process every 10 ms (nvidia-smi every 100 ms where NVML cannot be imported)."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    # nvmlClocksEventReason bits: sw_power_cap 0x4, hw_slowdown 0x8, sw_thermal 0x20, hw_thermal 0x40
+    REASON_BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
     def __init__(self, gpu_index):
         self.gpu = gpu_index
         self.proc = None
         self.path = None
+        self.thread = None
+        self.stop_flag = None
+        self.sm, self.mx, self.reasons = [], [], set()
+
+    def _nvml_index(self):
+        """NVML enumerates all GPUs of the machine; CUDA_VISIBLE_DEVICES may remap the ordinals."""
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            parts = [p.strip() for p in vis.split(",") if p.strip()]
+            if self.gpu < len(parts) and parts[self.gpu].isdigit():
+                return int(parts[self.gpu])
+        return self.gpu
 
     def start(self):
+        try:
+            import threading
+
+            import pynvml
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self._nvml_index())
+            self.mx.append(float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+            self.stop_flag = threading.Event()
+
+            def loop():
+                while not self.stop_flag.is_set():
+                    try:
+                        self.sm.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                        bits = int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
+                        for name, bit in self.REASON_BITS.items():
+                            if bits & bit:
+                                self.reasons.add(name)
+                    except Exception:
+                        pass
+                    self.stop_flag.wait(0.01)
+
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             self.proc = subprocess.Popen(
@@ -75,6 +122,12 @@ class ClockSampler:
             self.proc = None
 
     def stop(self):
+        if self.thread is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            return {"sm_mhz": statistics.median(self.sm) if self.sm else None,
+                    "sm_min_mhz": min(self.sm) if self.sm else None, "sm_max_mhz": max(self.mx) if self.mx else None,
+                    "samples": len(self.sm), "reasons": sorted(self.reasons), "source": "nvml, 10 ms"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -102,7 +155,7 @@ class ClockSampler:
         except OSError:
             pass
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi, 100 ms"}
 
 
 def synthetic_batches(rank, count):
@@ -157,6 +210,36 @@ class CpuSampler:
                 "fraction_of_iteration": flops / per_image}
 
 
+def mcpu_generator_baseline(mode="MCPU", batch=4):
+    """BASELINE configs[0] (generator forward, leaky) through the reference's own ops graph in its
+    RT_MODE=MCPU mode - rt::optimize + ThreadPoolRunner(4), src/ops/graph.cu:32,180-192 - on this box's
+    host cores.  Needs the reference tree built against this repository's backend
+    (dcgan-cuda_b200/shim/build_reference.py leaves the binary under shim/_ref_build/); None otherwise.
+    The pool has 4 worker threads whatever the core count, and convolutions are not split across them
+    (src/runtime/optimizer.cu:239-246), so the batch only scales the run time: a batch of 4 keeps the
+    sample to seconds."""
+    exe = os.path.join(ROOT, "dcgan-cuda_b200", "shim", "_ref_build", "bin", "dcgan_graph_driver")
+    if not os.access(exe, os.X_OK):
+        return None
+    with tempfile.TemporaryDirectory() as tmp:
+        t0 = time.perf_counter()
+        try:
+            res = subprocess.run([exe, "gen", str(batch), "1", os.path.join(tmp, "out.bin"), "leaky"], cwd=tmp,
+                                 env=dict(os.environ, RT_MODE=mode), capture_output=True, text=True, timeout=600)
+        except (OSError, subprocess.TimeoutExpired):
+            return None
+        wall = time.perf_counter() - t0
+    if res.returncode != 0:
+        return None
+    try:
+        ms = json.loads(res.stdout.strip().splitlines()[-1])["ms"][0]
+    except (ValueError, KeyError, IndexError):
+        return None
+    return {"mode": mode, "workload": "configs[0]: generator forward through ops::Graph::run", "batch": batch,
+            "images_per_s": batch / (ms * 1e-3), "run_ms": ms, "threads": 4 if mode == "MCPU" else 1,
+            "nproc": os.cpu_count(), "wall_s": wall}
+
+
 def run_reference(args, rank):
     """--impl reference: the reference's own CPU implementation of the iteration, host cores."""
     if rank != 0:
@@ -180,7 +263,8 @@ def run_reference(args, rank):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "configs[2]: full DCGAN training iteration (1 D update + 2 G updates), "
                                "batch 64 per GPU; CPU arm runs a bounded batch-1 sample", "global_batch": BATCH},
-        "cpu_baseline": {"value": value, "unit": "images/s", "cores": 1, "kind": kind, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "images/s", "cores": 1, "kind": kind, "sample": sample,
+                         "mcpu_cfg0": mcpu_generator_baseline("MCPU"), "cpu_cfg0": mcpu_generator_baseline("CPU")},
         "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -238,23 +322,34 @@ def run_ours(args, rank, local_rank, world):
         return float(t.item())
 
     # ---- device-resident timing -------------------------------------------------------------
+    # K steps between two CUDA events on the launching stream, barrier + synchronize on both sides, max
+    # over ranks = one block.  Blocks are repeated until at least MIN_TIMED_S of device time has been
+    # measured (a 20-step block is 30 ms: too short for the clocks to be sampled or to settle), and
+    # the median block is the reported one.
     for _ in range(args.warmup):
         trainer.step()
     barrier()
     sampler = ClockSampler(local_rank)
     sampler.start()
-    launches0 = pkg.launches_total()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    h0 = time.perf_counter()
-    for _ in range(args.steps):
-        trainer.step()
-    host_enqueue_ms = (time.perf_counter() - h0) * 1e3 / args.steps   # host time to enqueue a step (no sync)
-    e1.record()
-    barrier()
-    launches = pkg.launches_total() - launches0
-    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    block_ms, host_ms, launches = [], [], 0
+    while True:
+        barrier()
+        launches0 = pkg.launches_total()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        h0 = time.perf_counter()
+        for _ in range(args.steps):
+            trainer.step()
+        host_ms.append((time.perf_counter() - h0) * 1e3 / args.steps)   # host time to enqueue a step (no sync)
+        e1.record()
+        barrier()
+        launches = pkg.launches_total() - launches0
+        block_ms.append(max_over_ranks(e0.elapsed_time(e1)))
+        if sum(block_ms) >= 1e3 * MIN_TIMED_S or len(block_ms) >= 200:
+            break
     pkg._lib.check(pkg.lib.dcg_device_status())
+    ms_total = statistics.median(block_ms)
+    host_enqueue_ms = statistics.median(host_ms)
     ms_per_step = ms_total / args.steps
     value = world * BATCH / (ms_per_step * 1e-3)
 
@@ -280,10 +375,69 @@ def run_ours(args, rank, local_rank, world):
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     barrier()
     clocks = sampler.stop()
+    if clocks.get("sm_mhz"):
+        clocks["ms_per_step_x_sm_mhz"] = ms_per_step * clocks["sm_mhz"]
     e2e_value = world * BATCH * args.steps / e2e_s
+
+    # ---- data parallel: replicas must have stayed bit-identical; what one gradient sum costs ----------
+    dp_extra = {}
+    if world > 1:
+        params = torch.cat([trainer.tensor("d_params"), trainer.tensor("g_params")])
+        # an order-independent 64-bit checksum of the parameter bits: min and max over ranks must agree
+        bits = params.view(torch.int32).to(torch.int64)
+        mine = torch.stack([bits.sum(), (bits * (torch.arange(bits.numel(), device=dev) % 1021 + 1)).sum()])
+        lo, hi = mine.clone(), mine.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        identical = bool(torch.equal(lo, hi))
+        if not identical:
+            raise SystemExit("rank %d: parameter replicas differ after the timed region" % rank)
+        dp_extra["replicas_identical"] = identical
+        us = {}
+        for name, buf in (("d", trainer.d_grads), ("g", trainer.g_grads)):
+            scratch = buf.clone()
+            for _ in range(3):
+                trainer.allreduce(scratch)
+            barrier()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with trainer._on_stream():
+                a0.record()
+            for _ in range(20):
+                trainer.allreduce(scratch)
+            with trainer._on_stream():
+                a1.record()
+            barrier()
+            us[name] = 1e3 * max_over_ranks(a0.elapsed_time(a1)) / 20
+        dp_extra["allreduce_us"] = us   # back to back, outside the timed region: an upper bound on what a step exposes
+        dp_extra["allreduce_bytes"] = {"d": trainer.d_grads.numel() * 4, "g": trainer.g_grads.numel() * 4}
+        dp_extra["comm"] = "nccl behind the C ABI (dcg_dp_*), version %s" % (trainer.dp_info() or (0, 0, "?"))[2]
+
+    # ---- BASELINE configs[0] and configs[1] at batch 64 (device-timed, inputs resident) ---------------
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(reps):
+            fn()
+        t1.record()
+        torch.cuda.synchronize()
+        return t0.elapsed_time(t1) / reps
+    extra_cfg = {}
+    if rank == 0 and not args.no_extra_configs:
+        d_ms = timed(trainer.d_fwd_bwd, 200)
+        gen = pkg.Trainer(batch=BATCH, precision=precision, fuse=True, seed=234, world=1, g_leaky=True)
+        gen.z.copy_(batches[0][1])
+        g_ms = timed(gen.generate, 400)
+        gen.close()
+        extra_cfg = {"gen_images_per_s": BATCH / (g_ms * 1e-3), "gen_ms": g_ms, "d_fwd_bwd_ms": d_ms,
+                     "d_fwd_bwd_images_per_s": BATCH / (d_ms * 1e-3)}
+    barrier()
 
     # ---- per-kernel view of the step (event-timed launch groups) --------------------------------
     peaks = read_peaks()
+    traffic = read_ncu_traffic()
     # launch groups of three more steps, each between two CUDA events on the trainer's stream; a
     # convolution group is launched DCG_PROFILE_REPEAT times between its events (same operands, same
     # results) so that the pair measures device time per launch, not launch plus inter-kernel gap
@@ -302,9 +456,8 @@ def run_ours(args, rank, local_rank, world):
         "frac": achieved / tf32_peak if tf32_peak else None,
         "peak_source": "%s: dense bf16 %.1f TFLOP/s / 2 for TF32" % (peaks["_source"], peaks["bf16_tflops"]),
         "share_of_step": conv_ms / total_ms,
-        # dram__bytes_read.sum + dram__bytes_write.sum per launch, mean of the FWD / DX / DK captures of the
-        # 128 -> 256 channel layer at batch 64 (profiles/conv_tc_kernel_D2_b64.md): the operands, read once
-        "traffic": NCU_CONV_DRAM_BYTES_PER_LAUNCH,
+        # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu capture summary
+        "traffic": traffic.get("dram_bytes_per_launch_mean"), "traffic_source": traffic.get("source"),
     }
     kernels = sorted(rows, key=lambda r: -r["ms"])[:14]
     kernel_table = [{"name": r["name"], "calls_per_step": r["calls"] / 3.0, "us_per_call": 1e3 * r["ms"] / r["calls"],
@@ -318,7 +471,8 @@ def run_ours(args, rank, local_rank, world):
         cpu = {"value": r["value"], "unit": "images/s", "cores": 1, "kind": r["kind"],
                "sample": "%.1f s (%d convolution calls, %.2f of one iteration) of the batch-1 training iteration, "
                          "images/s extrapolated by algorithmic FLOPs" % (r["seconds"], r["ops"],
-                                                                        r["fraction_of_iteration"])}
+                                                                        r["fraction_of_iteration"]),
+               "mcpu_cfg0": mcpu_generator_baseline("MCPU")}
 
     if rank == 0:
         line = {
@@ -332,6 +486,8 @@ def run_ours(args, rank, local_rank, world):
                              "gradients and Adam state, several times the 126 MB L2" % (trainer.arena_bytes() / 2 ** 20),
                        "adam": "lr 2e-4 beta1 0.5 beta2 0.999 eps 1e-8"},
             "steps_per_s": 1e3 / ms_per_step,
+            "blocks": len(block_ms), "block_ms_min": min(block_ms), "block_ms_max": max(block_ms),
+            "timed_s": sum(block_ms) * 1e-3,
             "conv_tflops": achieved,
             "host_enqueue_ms_per_step": host_enqueue_ms,
             "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": trainer.h2d_bytes_per_step,
@@ -343,13 +499,24 @@ def run_ours(args, rank, local_rank, world):
             "cpu_baseline": cpu,
             "clocks": clocks,
         }
+        line.update(extra_cfg)
+        line.update(dp_extra)
         print(json.dumps(line))
     trainer.close()
     if world > 1:
         dist.destroy_process_group()
 
 
-NCU_CONV_DRAM_BYTES_PER_LAUNCH = (11.73376e6 + 256 + 7.539456e6 + 512 + 12.649472e6) / 3.0
+def read_ncu_traffic():
+    """DRAM bytes per launch of the dominant kernel, from the summary committed with the ncu capture."""
+    path = os.path.join(ROOT, "profiles", "conv_tc_kernel_D2_b64.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        per_mode = [m["dram_bytes_read"] + m["dram_bytes_write"] for m in d["modes"].values()]
+        return {"dram_bytes_per_launch_mean": sum(per_mode) / len(per_mode), "source": "profiles/conv_tc_kernel_D2_b64.json: " + d["note"]}
+    except (OSError, ValueError, KeyError, ZeroDivisionError):
+        return {}
 
 
 def cta_timeline(pkg):
@@ -431,6 +598,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--precision", choices=["tf32", "3xtf32", "fp32"], default="tf32")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra-configs", action="store_true", help="skip the configs[0] / configs[1] timings")
     ap.add_argument("--cpu-seconds", type=float, default=20.0)
     ap.add_argument("--sweep", action="store_true")
     ap.add_argument("--sweep-batches", type=int, nargs="+", default=[64, 256, 1024])

@@ -73,6 +73,8 @@ class TrainerConfig(ctypes.Structure):
                 ("eps", c_float), ("seed", ctypes.c_uint64)]
 
 
+DP_ID_BYTES = 128   # DCG_DP_ID_BYTES
+
 # Every exported symbol of include/dcgan_b200.h: name -> (restype, argtypes)
 _P = c_void_p
 SIGNATURES = {
@@ -110,16 +112,26 @@ SIGNATURES = {
     "dcg_context_launch_count": (ctypes.c_uint64, [_P]),
     "dcg_run_node": (c_int, [_P, ctypes.POINTER(Node)]),
     "dcg_run_nodes": (c_int, [_P, ctypes.POINTER(Node), c_int, c_int]),
+    "dcg_dp_unique_id": (c_int, [_P]),
+    "dcg_dp_init": (c_int, [ctypes.POINTER(_P), c_int, c_int, _P]),
+    "dcg_dp_allreduce": (c_int, [_P, _P, c_size_t, _P]),
+    "dcg_dp_info": (c_int, [_P, ctypes.POINTER(c_int), ctypes.POINTER(c_int), ctypes.POINTER(c_int)]),
+    "dcg_dp_finalize": (None, [_P]),
     "dcg_trainer_create": (c_int, [ctypes.POINTER(_P), ctypes.POINTER(TrainerConfig), _P]),
+    "dcg_trainer_create_dp": (c_int, [ctypes.POINTER(_P), ctypes.POINTER(TrainerConfig), _P, _P]),
     "dcg_trainer_destroy": (None, [_P]),
     "dcg_trainer_tensor": (c_int, [_P, ctypes.c_char_p, ctypes.POINTER(_P), ctypes.POINTER(c_size_t)]),
     "dcg_trainer_generate": (c_int, [_P]),
+    "dcg_trainer_d_fwd_bwd": (c_int, [_P]),
     "dcg_trainer_d_backward": (c_int, [_P]),
     "dcg_trainer_d_apply": (c_int, [_P, c_float]),
     "dcg_trainer_g_backward": (c_int, [_P]),
     "dcg_trainer_g_backward_part": (c_int, [_P, c_int]),
     "dcg_trainer_g_apply": (c_int, [_P, c_float]),
     "dcg_trainer_step": (c_int, [_P]),
+    "dcg_trainer_save": (c_int, [_P, ctypes.c_char_p]),
+    "dcg_trainer_save_wait": (c_int, [_P]),
+    "dcg_trainer_load": (c_int, [_P, ctypes.c_char_p]),
     "dcg_trainer_context": (_P, [_P]),
     "dcg_context_profile_begin": (c_int, [_P]),
     "dcg_context_profile_end": (c_int, [_P, ctypes.POINTER(ProfileRow), c_int, ctypes.POINTER(c_int)]),
@@ -130,6 +142,7 @@ SIGNATURES = {
     "dcg_debug_set_wait_limit": (None, [ctypes.c_longlong]),
     "dcg_debug_skip_stage": (None, [c_int]),
     "dcg_debug_set_pairs": (None, [c_int]),
+    "dcg_debug_set_gather": (None, [c_int]),
     "dcg_build_info": (ctypes.c_char_p, []),
     "dcg_launches_total": (ctypes.c_uint64, []),
 }

@@ -104,6 +104,12 @@ struct Params {
     int splits;                   // K partitions of a tile
     int pair;                     // CTA pairs: two M tiles share every B tile through tcgen05 cta_group::2
                                   //   (cluster = 2 * splits CTAs, rank = 2 * partition + half)
+    // FWD as the GEMM behind the input gradient of a narrow-channel layer, with the gather fused in:
+    // the tile is a TH x TW patch of dy of ONE image (halo included) whose origin may be negative, its
+    // accumulator columns are the tap products ycol[tap][4 channels], and the CTA sums, for each pixel of
+    // its g_bh x g_bw block of the OUTPUT image, the products that land on it (0: off)
+    int gather;
+    int g_H, g_W, g_C, g_KH, g_KW, g_sh, g_sw, g_pt, g_pl, g_bh, g_bw;
     int skip_stage;               // test hook: the producer leaves this pipeline stage out (-1: never)
     long long wait_cycles;        // SM clocks after which a barrier wait gives up
     int kchunks;                  // 32-wide chunks along the contracted channel axis (FWD: C, DX: O)
@@ -384,8 +390,11 @@ __device__ __forceinline__ uint32_t make_idesc(int a_mn_major, int b_mn_major, i
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------
-template <int MODE, bool X3>
-__global__ void __launch_bounds__(kThreads, X3 ? 1 : 2)
+// PAIR: CTA pairs (cta_group::2).  A template flag rather than a run-time one: a kernel that contains
+// cta_group::2 instructions can only be launched with an even cluster size, so the single-CTA form
+// must not contain any.
+template <int MODE, bool X3, bool PAIR>
+__global__ void __launch_bounds__(kThreads, (X3 || PAIR) ? 1 : 2)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ Params p)
 {
@@ -393,7 +402,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 64) TC_TRACE(3072);
     TC_CTA_TRACE(0);
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const int b_stage_bytes = (p.pair ? p.bn / 2 : p.bn) * BK * 4;   // a pair CTA holds half of the B tile
+    const int b_stage_bytes = (PAIR ? p.bn / 2 : p.bn) * BK * 4;   // a pair CTA holds half of the B tile
     const long long wait_limit = p.wait_cycles;
     const uint32_t a_base = smem_base;
     const uint32_t b_base = a_base + (uint32_t)p.stages * A_STAGE_BYTES;
@@ -418,7 +427,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_init(full_bar + 8u * s, 1);
             mbar_init(empty_bar + 8u * s, 1);
             mbar_init(resid_bar + 8u * s, kEpi);
-            if (p.pair) mbar_init(peer_full_bar + 8u * s, 1);
+            if (PAIR) mbar_init(peer_full_bar + 8u * s, 1);
         }
         mbar_init(tmem_full_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -432,7 +441,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     int tmem_cols = 32;
     while (tmem_cols < (X3 ? 2 * p.bn : p.bn)) tmem_cols <<= 1;
     if (warp == 1) {
-        if (p.pair) {   // one warp of each CTA of the pair takes part
+        if (PAIR) {   // one warp of each CTA of the pair takes part
             asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(tmem_cols) : "memory");
             asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
         } else {
@@ -447,15 +456,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // With CTA pairs the innermost index is the half of the 256-row tile (= parity of the cluster
     // rank), then the partition; m then counts pairs of M tiles.
     int rem = blockIdx.x;
-    const int half = p.pair ? (rem & 1) : 0;
-    if (p.pair) rem >>= 1;
+    const int half = PAIR ? (rem & 1) : 0;
+    if (PAIR) rem >>= 1;
     const int split = rem % p.splits; rem /= p.splits;
     const int n_tile = rem % p.n_tiles; rem /= p.n_tiles;
     int m_count;
     if (MODE == MODE_DK) m_count = p.m_tiles;
     else m_count = p.tiles_w * p.tiles_h * p.tiles_n;
-    if (p.pair) m_count >>= 1;
-    const int m_tile = p.pair ? 2 * (rem % m_count) + half : rem % m_count;
+    if (PAIR) m_count >>= 1;
+    const int m_tile = PAIR ? 2 * (rem % m_count) + half : rem % m_count;
     const int group = rem / m_count;
 
     // pixel-tile origin (FWD/DX)
@@ -464,6 +473,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         j0 = (m_tile % p.tiles_w) * p.TW;
         i0 = ((m_tile / p.tiles_w) % p.tiles_h) * p.TH;
         n0 = (m_tile / (p.tiles_w * p.tiles_h)) * p.TN;
+    }
+    int g_h0 = 0, g_w0 = 0;   // gather: origin of this CTA's block of output pixels
+    if (MODE == MODE_FWD && p.gather) {
+        g_w0 = (m_tile % p.tiles_w) * p.g_bw;
+        g_h0 = ((m_tile / p.tiles_w) % p.tiles_h) * p.g_bh;
+        // first dy row / column any output pixel of the block reads: ceil((h0 + pad - (K - 1)) / s)
+        const int ah = g_h0 + p.g_pt - (p.g_KH - 1), aw = g_w0 + p.g_pl - (p.g_KW - 1);
+        i0 = ah >= 0 ? (ah + p.g_sh - 1) / p.g_sh : -((-ah) / p.g_sh);
+        j0 = aw >= 0 ? (aw + p.g_sw - 1) / p.g_sw : -((-aw) / p.g_sw);
     }
     // DX: parity class and its taps; DK: the kernel tap
     int ph = 0, pw = 0, rh = 0, rw = 0, eh = 0, ew = 0, taps_h = 1, taps_w = 1, tap_di = 0, tap_dj = 0;
@@ -489,7 +507,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     // pairs: the partner's barriers must be initialised before anything arrives on them remotely
-    if (p.pair) cluster_sync_all();
+    if (PAIR) cluster_sync_all();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = *tmem_slot_ptr;
     // Programmatic dependent launch: everything above (barriers, TMEM, descriptor prefetch) may run
@@ -565,12 +583,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         if (it < 128) TC_TRACE(512 + it);
                         // B: bn / 32 chunks of 32 output channels; a pair CTA takes its half of them
                         tma_load_4d(b_dst, &map_b, fb, 0, chunk * BK, tap,
-                                    p.pair ? n_tile * (p.bn / 32) + half * (p.bn / 64) : n_tile * (p.bn / 32));
+                                    PAIR ? n_tile * (p.bn / 32) + half * (p.bn / 64) : n_tile * (p.bn / 32));
                         if (it < 128) TC_TRACE(768 + it);
                     } else if (MODE == MODE_DX) {
                         // (di, dj) count the taps of this parity class: kernel tap (rh + sh*di, rw + sw*dj)
                         tma_load_4d(a_dst, &map_a, fb, chunk * BK, j0 + ew - dj, i0 + eh - di, n0);
-                        tma_load_4d(b_dst, &map_b, fb, chunk * BK, n_tile * p.bn + (p.pair ? half * (p.bn / 2) : 0),
+                        tma_load_4d(b_dst, &map_b, fb, chunk * BK, n_tile * p.bn + (PAIR ? half * (p.bn / 2) : 0),
                                     rw + p.sw * dj, rh + p.sh * di);
                     } else {
                         // (tap, di, dj) count the 32-pixel tiles along (n, h, w)
@@ -604,7 +622,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         {
             const int a_mn = (MODE == MODE_DK) ? 1 : 0;
             const int b_mn = (MODE == MODE_DX) ? 0 : 1;
-            const uint32_t idesc = make_idesc(a_mn, b_mn, p.bn, p.pair ? 2 * BM : BM);
+            const uint32_t idesc = make_idesc(a_mn, b_mn, p.bn, PAIR ? 2 * BM : BM);
             // K-major tile: rows of 128 B, 8-row groups 1024 B apart (stride offset); one MMA (K = 8)
             // consumes 32 B of each row.
             // MN-major tile: [32-channel chunk][k row][128 B]: chunks 4096 B apart (leading offset), the
@@ -621,7 +639,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t a_stage16 = A_STAGE_BYTES >> 4, b_stage16 = (uint32_t)b_stage_bytes >> 4;
             int s = 0;
             uint32_t phase = 0;
-            if (p.pair && half == 1) {
+            if (PAIR && half == 1) {
                 // ===== odd CTA of a pair: no MMAs of its own; tells the even CTA when a stage has landed =====
                 const uint32_t partner_peer_full = map_to_cta(peer_full_bar, cluster_ctarank() ^ 1u);
                 for (int it = 0; it < nq; ++it) {
@@ -629,7 +647,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (elect_one()) mbar_arrive_remote(partner_peer_full + 8u * s);
                     if (++s == p.stages) { s = 0; phase ^= 1u; }
                 }
-            } else if (p.pair) {
+            } else if (PAIR) {
                 // ===== even CTA of a pair: one MMA over both CTAs' tiles per K step =====
                 const uint32_t partner = cluster_ctarank() ^ 1u;
                 const uint32_t partner_empty = map_to_cta(empty_bar, partner);
@@ -782,7 +800,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int CL = (p.bn + S - 1) / S;        // scalar path: columns per share
     // scratch slot = blockIdx.x; the partitions of this CTA's tile are pstride slots apart (with CTA
     // pairs the two halves of a 256-row tile interleave)
-    const int pstride = p.pair ? 2 : 1;
+    const int pstride = PAIR ? 2 : 1;
     float* my_scratch = p.scratch + (size_t)blockIdx.x * BM * p.bn;
     const float* tile_scratch = p.scratch + (size_t)(blockIdx.x - pstride * part) * BM * p.bn;
     if (threadIdx.x == 64) TC_TRACE(3000);
@@ -840,7 +858,36 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 64) TC_TRACE(3002);
     TC_CTA_TRACE(4);
 
-    if (warp >= 2 && finish_here) {
+    if (MODE == MODE_FWD && p.gather) {
+        // ===== fused gather: the accumulator tile sits in shared memory as [tap][tile pixel] float4s
+        // (4 channels per tap); every output pixel of this CTA's block adds the products of the taps
+        // whose parity matches it - in (kernel row, kernel column) order - and goes through the fused
+        // chain.  dy pixels outside the image were zero-filled by TMA, so their products are zero.
+        if (warp >= 2) {
+            const int tid_e = threadIdx.x - 64;
+            const float4* red4 = reinterpret_cast<const float4*>(red);
+            const int block = p.g_bh * p.g_bw;
+            for (int idx = tid_e; idx < block; idx += kEpi) {
+                const int h = g_h0 + idx / p.g_bw, w = g_w0 + idx % p.g_bw;
+                if (h >= p.g_H || w >= p.g_W || n0 >= p.N) continue;
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int di = (h + p.g_pt) % p.g_sh; di < p.g_KH; di += p.g_sh) {
+                    const int i = (h + p.g_pt - di) / p.g_sh - i0;     // exact division (matching parity)
+                    for (int dj = (w + p.g_pl) % p.g_sw; dj < p.g_KW; dj += p.g_sw) {
+                        const int j = (w + p.g_pl - dj) / p.g_sw - j0;
+                        const float4 v = red4[(di * p.g_KW + dj) * QS + i * p.TW + j];
+                        acc[0] = __fadd_rn(acc[0], v.x); acc[1] = __fadd_rn(acc[1], v.y);
+                        acc[2] = __fadd_rn(acc[2], v.z); acc[3] = __fadd_rn(acc[3], v.w);
+                    }
+                }
+                const size_t pix = ((size_t)n0 * p.g_H + h) * p.g_W + w;
+                for (int c = 0; c < p.g_C; ++c) {
+                    const size_t o = pix * p.g_C + c;
+                    p.out[o] = epilogue_apply(p.ep, acc[c], o, c);
+                }
+            }
+        }
+    } else if (warp >= 2 && finish_here) {
         // ===== this partition's share: sum in partition order, fused chain, stores =====
         const int tid_e = threadIdx.x - 64;
         const EpilogueArgs& e = p.ep;
@@ -1003,7 +1050,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // ---- teardown: everyone is done with TMEM before warp 1 releases it --------------------------
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (p.pair) {
+    if (PAIR) {
         // both CTAs of a pair are done with TMEM (and with each other's barriers) before either frees it
         cluster_sync_all();
         if (warp == 1) {
@@ -1330,13 +1377,18 @@ bool pairs_enabled()
 // of CTA pairs where that is possible: an even number of M tiles, a B tile that halves into whole
 // 32-channel chunks (MN-major) or 8-row groups (K-major), no 3xTF32.  The K partitions of a pair
 // tile and its two halves share one cluster, so at most kMaxCluster / 2 partitions.
-void maybe_pair(Plan& pl, int m_count, int b_half_granule)
+void maybe_pair(Plan& pl, int tiles, int m_count, int b_half_granule)
 {
     Params& p = pl.p;
     if (!pairs_enabled() || p.x3 || p.narrow || p.ext_finish) return;
     if (m_count < 2 || (m_count & 1) || p.bn % (2 * b_half_granule) != 0) return;
+    // Only grids that are resident all at once with one CTA per SM.  With more CTAs than SMs the
+    // single-CTA form keeps two CTAs per SM; pair kernels in that regime (two pair halves sharing an
+    // SM, several waves) ran into their wait limits on B200 and are not used.
+    int splits = p.splits > kMaxCluster / 2 ? kMaxCluster / 2 : p.splits;
+    if (tiles * splits > sm_count()) return;
     p.pair = 1;
-    if (p.splits > kMaxCluster / 2) p.splits = kMaxCluster / 2;
+    p.splits = splits;
 }
 
 void finish_plan(Plan& pl)
@@ -1412,7 +1464,7 @@ bool plan_fwd(const dcg_conv_desc& d, Plan& pl)
         pl.k4_bytes = (size_t)d.kh * 32 * d.o * sizeof(float);
     }
     p.splits = choose_splits(tiles, narrow ? d.kh : d.kh * d.kw * p.kchunks);
-    maybe_pair(pl, p.tiles_w * p.tiles_h * p.tiles_n, 32);   // B: whole 32-channel chunks per half
+    maybe_pair(pl, tiles, p.tiles_w * p.tiles_h * p.tiles_n, 32);   // B: whole 32-channel chunks per half
     pl.grid = tiles * p.splits;
     finish_plan(pl);
     return true;
@@ -1429,9 +1481,71 @@ dcg_conv_desc dx_gemm_desc(const dcg_conv_desc& d, int Jp)
 
 bool plan_fwd(const dcg_conv_desc& d, Plan& pl);
 
+// Fused gather (the default for the input gradient of a narrow-channel layer; DCG_TC_GATHER=0 or the
+// testing hook switch back to GEMM + separate gather kernel).  -1 = follow the environment.
+std::atomic<int> g_gather_override{-1};
+bool gather_enabled()
+{
+    const int o = g_gather_override.load();
+    if (o >= 0) return o != 0;
+    static const int env = [] { const char* v = getenv("DCG_TC_GATHER"); return v ? atoi(v) : 1; }();
+    return env != 0;
+}
+
+// Largest block extent (a multiple of the stride, at most `limit` rounded up to one) such that the
+// dy rows any block of that extent reads fit into `tile` rows; 0 if even one stride does not fit.
+int gather_block_extent(int extent, int k, int s, int pad, int tile, int limit)
+{
+    for (int b = (limit + s - 1) / s * s; b >= s; b -= s) {
+        bool ok = true;
+        for (int h0 = 0; h0 < extent && ok; h0 += b) {
+            const int a = h0 + pad - (k - 1);
+            const int lo = a >= 0 ? (a + s - 1) / s : -((-a) / s);
+            const int last = (h0 + b < extent ? h0 + b : extent) - 1;
+            const int hi = (last + pad) / s;
+            ok = hi - lo + 1 <= tile;
+        }
+        if (ok) return b;
+    }
+    return 0;
+}
+
+// Input gradient of a narrow-channel layer as ONE launch: the GEMM of dy against all taps on tiles
+// of 8 x 16 dy pixels (halo included) with the gather in its epilogue.  Nothing but the output is
+// written: the tap-major GEMM result never exists in memory.
+bool plan_dx_gather(const dcg_conv_desc& d, Plan& pl)
+{
+    if (!gather_enabled() || t_plan_x3) return false;
+    const int Jp = (d.kh * d.kw * 4 + 31) / 32 * 32;   // four accumulator columns per tap
+    if (Jp > 128) return false;                          // one N tile holds every tap
+    if (!plan_fwd(dx_gemm_desc(d, Jp), pl)) return false;
+    Params& p = pl.p;
+    if (p.narrow || p.n_tiles != 1) return false;
+    p.TW = 16; p.TH = 8; p.TN = 1;
+    const int bh = gather_block_extent(d.h, d.kh, d.stride_h, d.pad_top, p.TH, d.h);
+    const int bw = gather_block_extent(d.w, d.kw, d.stride_w, d.pad_left, p.TW, d.w);
+    if (bh <= 0 || bw <= 0) return false;
+    p.gather = 1;
+    p.g_H = d.h; p.g_W = d.w; p.g_C = d.c; p.g_KH = d.kh; p.g_KW = d.kw;
+    p.g_sh = d.stride_h; p.g_sw = d.stride_w; p.g_pt = d.pad_top; p.g_pl = d.pad_left;
+    p.g_bh = bh; p.g_bw = bw;
+    p.tiles_w = (d.w + bw - 1) / bw; p.tiles_h = (d.h + bh - 1) / bh; p.tiles_n = d.n;
+    p.splits = 1; p.pair = 0;
+    p.o_store = d.kh * d.kw * 4;   // accumulator columns beyond the last tap are padding
+    pl.grid = p.tiles_w * p.tiles_h * p.tiles_n;
+    pl.Jp = Jp;
+    pl.k2_bytes = (size_t)d.o * Jp * sizeof(float);
+    pl.ycol_bytes = 0;
+    finish_plan(pl);
+    pl.ws_bytes = pl.k2_off() + align_up(pl.k2_bytes, 256);
+    return true;
+}
+
 bool plan_dx(const dcg_conv_desc& d, Plan& pl)
 {
     if (d.c <= 4 && d.o % 32 == 0 && d.stride_h <= d.kh && d.stride_w <= d.kw) {
+        if (plan_dx_gather(d, pl)) return true;
+        pl = Plan{};
         const int Jp = (d.kh * d.kw * 4 + 31) / 32 * 32;   // four columns per tap
         pl.Jp = Jp;
         pl.k2_bytes = (size_t)d.o * Jp * sizeof(float);
@@ -1460,7 +1574,7 @@ bool plan_dx(const dcg_conv_desc& d, Plan& pl)
     const int tiles = classes * p.tiles_w * p.tiles_h * p.tiles_n * p.n_tiles;
     const int min_taps = (d.kh / d.stride_h) * (d.kw / d.stride_w);
     p.splits = choose_splits(tiles, (min_taps < 1 ? 1 : min_taps) * p.kchunks);
-    maybe_pair(pl, p.tiles_w * p.tiles_h * p.tiles_n, 8);    // B: K-major rows, whole 8-row swizzle groups per half
+    maybe_pair(pl, tiles, p.tiles_w * p.tiles_h * p.tiles_n, 8);    // B: K-major rows, whole 8-row swizzle groups per half
     pl.grid = tiles * p.splits;
     finish_plan(pl);
     return true;
@@ -1522,7 +1636,13 @@ bool make_plan(const dcg_conv_desc& d, int kind, Plan& pl)
 
 // Testing hooks (dcg_debug_set_wait_limit / dcg_debug_skip_stage): the wait limit of every barrier
 // wait in SM clocks, and a pipeline stage the producer leaves out so that a wait runs into that limit.
-std::atomic<long long> g_wait_cycles{kWaitCycles};
+long long default_wait_cycles()
+{
+    const char* v = getenv("DCG_TC_WAIT_CYCLES");   // experiments: a shorter limit than the ~1 s default
+    const long long c = v ? atoll(v) : 0;
+    return c > 0 ? c : kWaitCycles;
+}
+std::atomic<long long> g_wait_cycles{default_wait_cycles()};
 std::atomic<int> g_test_skip_stage{-1};
 
 template <int MODE>
@@ -1551,8 +1671,9 @@ int launch_grid(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, i
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    const cudaError_t err = p.x3 ? cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE, true>, ma, mb, p)
-                                 : cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE, false>, ma, mb, p);
+    const cudaError_t err = p.x3 ? cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE, true, false>, ma, mb, p)
+                          : p.pair ? cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE, false, true>, ma, mb, p)
+                                   : cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE, false, false>, ma, mb, p);
     if (err != cudaSuccess) return fail(DCG_ERR_CUDA, "conv_tc_kernel launch: %s", cudaGetErrorString(err));
     count_launch();
     return DCG_OK;
@@ -1565,9 +1686,11 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, Plan& pl, float* out, c
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(conv_tc_kernel<MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+        attr_err = cudaFuncSetAttribute(conv_tc_kernel<MODE, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
         if (attr_err == cudaSuccess)
-            attr_err = cudaFuncSetAttribute(conv_tc_kernel<MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+            attr_err = cudaFuncSetAttribute(conv_tc_kernel<MODE, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+        if (attr_err == cudaSuccess && MODE != MODE_DK)
+            attr_err = cudaFuncSetAttribute(conv_tc_kernel<MODE, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
     });
     if (attr_err != cudaSuccess)
         return fail(DCG_ERR_CUDA, "cudaFuncSetAttribute(conv_tc_kernel): %s", cudaGetErrorString(attr_err));
@@ -1647,7 +1770,7 @@ struct Prepared {
 };
 
 struct CacheKey {
-    int dev, kind, x3, pairs;
+    int dev, kind, x3, pairs;   // pairs: bit 0 CTA pairs, bit 1 fused gather (the switches a plan depends on)
     dcg_conv_desc d;
     const void *a, *b, *ws;
     size_t ws_bytes;
@@ -1706,7 +1829,7 @@ int build_dx(const dcg_conv_desc& d, const float* dy, const float* k, void* ws, 
     const Params& p = pl.p;
     int st = map_act_4d(&pr.ma, dy, d.n, d.ho, d.wo, d.o, p.TW, p.TH, p.TN, 1, 1);
     if (st) return st;
-    if (pl.ycol_bytes) {   // narrow-channel layer: GEMM over all taps, then gather
+    if (pl.ycol_bytes || p.gather) {   // narrow-channel layer: GEMM over all taps, then (or fused with) the gather
         if (!ws || ws_bytes < pl.ws_bytes)
             return fail(DCG_ERR_WORKSPACE, "conv dx (tensor path, narrow input): workspace %zu < %zu bytes", ws_bytes, pl.ws_bytes);
         const float* k2 = reinterpret_cast<const float*>(static_cast<uint8_t*>(ws) + pl.k2_off());
@@ -1757,7 +1880,7 @@ int prepared_call(int kind, const dcg_conv_desc& d, const void* a, const void* b
     CacheKey key;
     std::memset(&key, 0, sizeof(key));
     if (cudaGetDevice(&key.dev) != cudaSuccess) key.dev = -1;
-    key.kind = kind; key.x3 = t_plan_x3; key.pairs = pairs_enabled() ? 1 : 0;
+    key.kind = kind; key.x3 = t_plan_x3; key.pairs = (pairs_enabled() ? 1 : 0) | (gather_enabled() ? 2 : 0);
     key.d = d; key.a = a; key.b = b; key.ws = ws; key.ws_bytes = ws_bytes;
     {
         std::lock_guard<std::mutex> lock(g_cache_mutex);
@@ -1820,6 +1943,12 @@ int conv_tc_dx(const dcg_conv_desc& d, const float* dy, const float* k, float* d
     int st = prepared_call(kConvDx, d, dy, k, ws, ws_bytes, pr);
     if (st) return st;
     Plan& pl = pr.pl;
+    if (pl.p.gather) {   // narrow-channel layer, one launch: GEMM over all taps with the gather in its epilogue
+        float* k2 = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + pl.k2_off());
+        launch_pdl(repack_k2_kernel, (d.o * pl.Jp + 255) / 256, 256, 0, stream, k, k2, d.kh * d.kw, d.c, pl.Jp, d.o);
+        DCG_LAUNCH_CHECK("repack_k2_kernel");
+        return launch<MODE_FWD>(pr.ma, pr.mb, pl, dx, ep, d.c, ws, ws_bytes, stream);
+    }
     if (pl.ycol_bytes) {   // narrow-channel layer: GEMM over all taps, then gather
         uint8_t* base = static_cast<uint8_t*>(ws);
         float* k2 = reinterpret_cast<float*>(base + pl.k2_off());
@@ -1858,10 +1987,12 @@ int conv_tc_dk(const dcg_conv_desc& d, const float* x, const float* dy, float* d
 }
 
 // wait_cycles: > 0 sets the limit, -1 restores the default, 0 leaves it; skip_stage / pairs: -2 leaves it.
+void conv_tc_set_gather(int mode) { g_gather_override.store(mode < 0 ? -1 : (mode != 0)); }
+
 void conv_tc_set_hooks(long long wait_cycles, int skip_stage, int pairs)
 {
     if (wait_cycles > 0) g_wait_cycles.store(wait_cycles);
-    else if (wait_cycles < 0) g_wait_cycles.store(kWaitCycles);
+    else if (wait_cycles < 0) g_wait_cycles.store(default_wait_cycles());
     if (skip_stage != -2) g_test_skip_stage.store(skip_stage);
     if (pairs != -2) g_pair_override.store(pairs);
 }
@@ -1895,6 +2026,8 @@ extern "C" void dcg_debug_set_wait_limit(long long sm_clocks)
 extern "C" void dcg_debug_skip_stage(int stage) { dcg::conv_tc_set_hooks(0, stage < 0 ? -1 : stage, -2); }
 
 extern "C" void dcg_debug_set_pairs(int mode) { dcg::conv_tc_set_hooks(0, -2, mode < 0 ? -1 : (mode != 0)); }
+
+extern "C" void dcg_debug_set_gather(int mode) { dcg::conv_tc_set_gather(mode); }
 
 #ifdef DCG_TC_TRACING
 // Tuning aids of -DDCG_TC_TRACING builds, not part of the public header: copy the timelines recorded

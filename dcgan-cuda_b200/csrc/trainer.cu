@@ -14,11 +14,21 @@
 #include <cstdlib>
 #include <cstring>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "adam.cuh"
 #include "backend.cuh"
 #include "common.cuh"
+
+namespace dcg {
+// data-parallel plumbing (dp.cu)
+void* dp_mem_alloc(size_t bytes);
+void dp_mem_free(void* p);
+void dp_register(dcg_dp* dp, void* buf, size_t bytes);
+int dp_world(const dcg_dp* dp);
+int dp_allreduce_group(dcg_dp* dp, float* const* bufs, const size_t* counts, int n, cudaStream_t stream);
+}  // namespace dcg
 
 namespace {
 
@@ -63,6 +73,12 @@ struct dcg_trainer {
     dcg_context* ctx = nullptr;
     uint8_t* arena = nullptr;
     size_t arena_bytes = 0, arena_used = 0;
+    bool arena_from_nccl = false;   // allocated by ncclMemAlloc (NCCL can then reduce it in the switch)
+    // Data parallelism: the communicator (not owned), and a stream for the discriminator's gradient
+    // sum, which runs while the main stream computes the generator's forward pass of the next update.
+    dcg_dp* dp = nullptr;
+    cudaStream_t comm_stream = nullptr;
+    cudaEvent_t ev_grads = nullptr, ev_summed = nullptr;
 
     // parameters / gradients / Adam moments: index 0..9 = (k0,b0,...,k3,b3,dense w,dense b)
     Tensor g_param[10], g_grad[10], g_m[10], g_v[10];
@@ -84,7 +100,7 @@ struct dcg_trainer {
     // backward scratch
     Tensor dlogits[2], dda[kLayers + 1], ddz[kLayers], dg_out, dgz[kLayers], dga[kLayers], dg0a, dg0z;
 
-    std::vector<dcg_node> d_nodes, g_nodes, gen_nodes;
+    std::vector<dcg_node> d_nodes, g_nodes, gen_nodes, dfb_nodes;
     uint64_t last_step_launches = 0;
 
     // A node list is launched eagerly twice (scratch grows to its final size, one-time attributes
@@ -98,14 +114,24 @@ struct dcg_trainer {
         uint64_t generation = 0;   // the context's generation the graph was captured under
         bool failed = false;
     };
-    ListGraph d_graph, g_graph, gen_graph, g_part_graph[2];
+    ListGraph d_graph, g_graph, gen_graph, dfb_graph, g_part_graph[2];
     // Single-GPU iteration as ONE graph: D list, Adam, G list, Adam, G list, Adam.  The three Adam
     // step sizes change every iteration, so the captured launches read them from `lr_dev`, which the
     // host rewrites (one 12-byte copy) before each replay.
     ListGraph step_graph;
     Tensor lr_dev;
     size_t g_forward_nodes = 0;   // the G run's leading nodes that only compute the generator's forward pass
+    int step_warm_runs = 0;       // eager whole iterations so far
     bool use_graphs = true;
+
+    // Checkpoint writer: a pinned snapshot buffer the device copies into (stream-ordered), and the
+    // host thread that waits for that copy and writes the file while training goes on.
+    float* snap = nullptr;
+    size_t snap_floats = 0;
+    cudaEvent_t ev_snap = nullptr;
+    std::thread writer;
+    int writer_status = DCG_OK;
+    std::string writer_error;
 };
 
 namespace {
@@ -402,6 +428,15 @@ void build_lists(dcg_trainer* t)
     // ---- generate: G forward only ----
     build_generator(t, t->gen_nodes);
 
+    // ---- discriminator forward + backward on the real images alone (labels all ones): every layer's
+    // kernel, bias and input gradient, the image gradient included.  Pass-1 buffers, gradients into
+    // the second gradient set, so the training lists are not disturbed.
+    std::vector<dcg_node>& F = t->dfb_nodes;
+    build_discriminator(t, F, t->x.p, 1, B);
+    F.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY, t->ones.p, t->logits[1].p, t->d2_loss.p, B));
+    F.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY_GRAD, t->ones.p, t->logits[1].p, t->dlogits[1].p, B));
+    build_discriminator_backward(t, F, t->x.p, 1, t->d_grad2, true, B);
+
     // ---- D run: graph.run({d_opti, d_loss}) ----
     std::vector<dcg_node>& D = t->d_nodes;
     build_generator(t, D);
@@ -518,9 +553,50 @@ int apply_adam(dcg_trainer* t, Tensor* param, Tensor* grad, Tensor* grad2, Tenso
                                   t->cfg.eps, grad_scale, t->stream, lr_dev);
 }
 
+int sum_over_ranks(dcg_trainer* t, Tensor& grads, cudaStream_t stream)
+{
+    float* bufs[1] = {grads.p};
+    const size_t counts[1] = {grads.n};
+    return dcg::dp_allreduce_group(t->dp, bufs, counts, 1, stream);
+}
+
+// The data-parallel iteration (world > 1, communicator attached): the same three runs, each followed
+// by ONE sum of that network's gradient arena over the ranks and the replicated Adam step, which
+// divides by the world size.  The discriminator's sum runs on the communication stream under the
+// generator's forward pass of the first G update (which reads neither the discriminator's
+// gradients nor its parameters).  Everything is stream-ordered, so the whole iteration - collectives
+// included - can be captured into one CUDA graph.
+int enqueue_step_dp(dcg_trainer* t, const float* lr_dev)
+{
+    int st;
+    const float scale = 1.f / (float)t->cfg.world;
+    const int fwd = (int)t->g_forward_nodes, all = (int)t->g_nodes.size();
+    if ((st = dcg_run_nodes(t->ctx, t->d_nodes.data(), (int)t->d_nodes.size(), t->cfg.fuse))) return st;
+    if (!t->batched_d)   // the two gradient paths are summed first (the Add of src/ops/graph.cu:302-309)
+        for (int i = 0; i < 10; ++i)
+            if ((st = dcg_add(t->d_grad[i].p, t->d_grad2[i].p, t->d_grad[i].p, t->d_grad[i].n, t->stream))) return st;
+    DCG_CUDA(cudaEventRecord(t->ev_grads, t->stream));
+    DCG_CUDA(cudaStreamWaitEvent(t->comm_stream, t->ev_grads, 0));
+    if ((st = sum_over_ranks(t, t->d_grads_all, t->comm_stream))) return st;
+    DCG_CUDA(cudaEventRecord(t->ev_summed, t->comm_stream));
+    if ((st = dcg_run_nodes(t->ctx, t->g_nodes.data(), fwd, t->cfg.fuse))) return st;
+    DCG_CUDA(cudaStreamWaitEvent(t->stream, t->ev_summed, 0));
+    if ((st = apply_adam(t, t->d_param, t->d_grad, nullptr, t->d_m, t->d_v, &t->d_t, scale, lr_dev))) return st;
+    if ((st = dcg_run_nodes(t->ctx, t->g_nodes.data() + fwd, all - fwd, t->cfg.fuse))) return st;
+    for (int rep = 0; rep < 2; ++rep) {
+        if (rep == 1 && (st = dcg_run_nodes(t->ctx, t->g_nodes.data(), all, t->cfg.fuse))) return st;
+        if ((st = sum_over_ranks(t, t->g_grads_all, t->stream))) return st;
+        if ((st = apply_adam(t, t->g_param, t->g_grad, nullptr, t->g_m, t->g_v, &t->g_t, scale,
+                             lr_dev ? lr_dev + 1 + rep : nullptr)))
+            return st;
+    }
+    return DCG_OK;
+}
+
 // The whole single-GPU iteration, enqueued node list by node list (used eagerly and under capture).
 int enqueue_step(dcg_trainer* t, const float* lr_dev)
 {
+    if (t->cfg.world > 1 && t->dp) return enqueue_step_dp(t, lr_dev);
     int st;
     Tensor* d_second = (t->cfg.world > 1 || t->batched_d) ? nullptr : t->d_grad2;
     if ((st = dcg_run_nodes(t->ctx, t->d_nodes.data(), (int)t->d_nodes.size(), t->cfg.fuse))) return st;
@@ -539,8 +615,8 @@ int enqueue_step(dcg_trainer* t, const float* lr_dev)
 int step_as_one_graph(dcg_trainer* t)
 {
     dcg_trainer::ListGraph& g = t->step_graph;
-    if (!t->use_graphs || g.failed || t->cfg.world > 1 || dcg::context_is_profiling(t->ctx)) return 0;
-    if (t->d_graph.eager_runs < 2 || t->g_graph.eager_runs < 2) return 0;   // lists not warmed up yet
+    if (!t->use_graphs || g.failed || (t->cfg.world > 1 && !t->dp) || dcg::context_is_profiling(t->ctx)) return 0;
+    if (t->step_warm_runs < 2) return 0;   // every list has to run eagerly twice first (scratch sizes, one-time attributes)
     if (g.exec && g.generation != dcg::context_generation(t->ctx)) {
         cudaGraphExecDestroy(g.exec);
         g.exec = nullptr;
@@ -587,10 +663,18 @@ int step_as_one_graph(dcg_trainer* t)
 
 extern "C" int dcg_trainer_create(dcg_trainer** out, const dcg_trainer_config* cfg, dcg_stream_t stream)
 {
+    return dcg_trainer_create_dp(out, cfg, stream, nullptr);
+}
+
+extern "C" int dcg_trainer_create_dp(dcg_trainer** out, const dcg_trainer_config* cfg, dcg_stream_t stream, dcg_dp* dp)
+{
     DCG_CHECK_ARG(out && cfg, "dcg_trainer_create: null argument");
     DCG_CHECK_ARG(cfg->batch > 0 && cfg->batch <= 4096, "dcg_trainer_create: bad batch %d", cfg->batch);
+    DCG_CHECK_ARG(!dp || dcg::dp_world(dp) == cfg->world, "dcg_trainer_create_dp: the communicator has %d ranks, the configuration %d",
+                  dcg::dp_world(dp), cfg->world);
     dcg_trainer* t = new dcg_trainer();
     t->cfg = *cfg;
+    t->dp = (dp && cfg->world > 1) ? dp : nullptr;
     t->stream = dcg::as_stream(stream);
     {
         const char* off = getenv("DCG_TRAINER_TWO_PASSES");   // experiments: keep the two passes on the tensor path too
@@ -601,17 +685,30 @@ extern "C" int dcg_trainer_create(dcg_trainer** out, const dcg_trainer_config* c
     Alloc dry{t, true};
     layout(t, dry);
     t->arena_bytes = dcg::align_up(dry.off, 256) + 256;
-    if (cudaMalloc(&t->arena, t->arena_bytes) != cudaSuccess) {
+    if (t->dp) {   // memory NCCL allocated itself is eligible for its in-switch reduction of user buffers
+        t->arena = static_cast<uint8_t*>(dcg::dp_mem_alloc(t->arena_bytes));
+        t->arena_from_nccl = t->arena != nullptr;
+    }
+    if (!t->arena && cudaMalloc(&t->arena, t->arena_bytes) != cudaSuccess) {
         const size_t want = t->arena_bytes;
         delete t;
         return fail(DCG_ERR_CUDA, "dcg_trainer_create: cudaMalloc of %zu bytes failed", want);
+    }
+    if (t->dp) {
+        bool ok = cudaStreamCreateWithFlags(&t->comm_stream, cudaStreamNonBlocking) == cudaSuccess &&
+                  cudaEventCreateWithFlags(&t->ev_grads, cudaEventDisableTiming) == cudaSuccess &&
+                  cudaEventCreateWithFlags(&t->ev_summed, cudaEventDisableTiming) == cudaSuccess;
+        if (!ok) {
+            dcg_trainer_destroy(t);
+            return fail(DCG_ERR_CUDA, "dcg_trainer_create_dp: could not create the communication stream");
+        }
     }
     cudaMemsetAsync(t->arena, 0, t->arena_bytes, t->stream);
     Alloc real{t, false};
     layout(t, real);
     t->arena_used = real.off;
     int st = dcg_context_create(&t->ctx, cfg->precision, nullptr, 0, stream);
-    if (st) { cudaFree(t->arena); delete t; return st; }
+    if (st) { dcg_trainer_destroy(t); return st; }
 
     // weights ~ N(0, 0.02), biases 0 (dcgan/main.cu:60-63, 148-151); labels
     Rng rng(cfg->seed ? cfg->seed : 234);
@@ -626,6 +723,10 @@ extern "C" int dcg_trainer_create(dcg_trainer** out, const dcg_trainer_config* c
     cudaMemcpyAsync(t->ones.p, one.data(), one.size() * sizeof(float), cudaMemcpyHostToDevice, t->stream);
     cudaStreamSynchronize(t->stream);
     build_lists(t);
+    if (t->dp) {   // the two buffers the communicator reduces every iteration
+        dcg::dp_register(t->dp, t->d_grads_all.p, t->d_grads_all.n * sizeof(float));
+        dcg::dp_register(t->dp, t->g_grads_all.p, t->g_grads_all.n * sizeof(float));
+    }
     if (cudaGetLastError() != cudaSuccess) {
         dcg_trainer_destroy(t);
         return fail(DCG_ERR_CUDA, "dcg_trainer_create: initialisation copies failed");
@@ -637,11 +738,20 @@ extern "C" int dcg_trainer_create(dcg_trainer** out, const dcg_trainer_config* c
 extern "C" void dcg_trainer_destroy(dcg_trainer* t)
 {
     if (!t) return;
-    for (dcg_trainer::ListGraph* g : {&t->d_graph, &t->g_graph, &t->gen_graph, &t->g_part_graph[0], &t->g_part_graph[1],
+    for (dcg_trainer::ListGraph* g : {&t->d_graph, &t->g_graph, &t->gen_graph, &t->dfb_graph, &t->g_part_graph[0], &t->g_part_graph[1],
                                       &t->step_graph})
         if (g->exec) cudaGraphExecDestroy(g->exec);
     if (t->ctx) dcg_context_destroy(t->ctx);
-    if (t->arena) cudaFree(t->arena);
+    if (t->arena) {
+        if (t->arena_from_nccl) dcg::dp_mem_free(t->arena);
+        else cudaFree(t->arena);
+    }
+    if (t->writer.joinable()) t->writer.join();
+    if (t->snap) cudaFreeHost(t->snap);
+    if (t->ev_snap) cudaEventDestroy(t->ev_snap);
+    if (t->ev_grads) cudaEventDestroy(t->ev_grads);
+    if (t->ev_summed) cudaEventDestroy(t->ev_summed);
+    if (t->comm_stream) cudaStreamDestroy(t->comm_stream);
     delete t;
 }
 
@@ -649,6 +759,12 @@ extern "C" int dcg_trainer_generate(dcg_trainer* t)
 {
     DCG_CHECK_ARG(t, "dcg_trainer_generate: null trainer");
     return run_list(t, t->gen_nodes, t->gen_graph);
+}
+
+extern "C" int dcg_trainer_d_fwd_bwd(dcg_trainer* t)
+{
+    DCG_CHECK_ARG(t, "dcg_trainer_d_fwd_bwd: null trainer");
+    return run_list(t, t->dfb_nodes, t->dfb_graph);
 }
 
 extern "C" int dcg_trainer_d_backward(dcg_trainer* t)
@@ -694,21 +810,178 @@ extern "C" int dcg_trainer_g_apply(dcg_trainer* t, float grad_scale)
 extern "C" int dcg_trainer_step(dcg_trainer* t)
 {
     DCG_CHECK_ARG(t, "dcg_trainer_step: null trainer");
-    DCG_CHECK_ARG(t->cfg.world <= 1, "dcg_trainer_step: data-parallel callers drive the phases themselves");
+    DCG_CHECK_ARG(t->cfg.world <= 1 || t->dp,
+                  "dcg_trainer_step: a data-parallel trainer without a communicator (dcg_trainer_create_dp) is driven phase by phase");
     const uint64_t before = dcg_launches_total();
-    int st = step_as_one_graph(t);
+    int st = step_as_one_graph(t);   // 1: replayed; 0: not (yet) available
     if (st < 0) return st;
-    if (st == 1) {
-        t->last_step_launches = dcg_launches_total() - before;
-        return DCG_OK;
-    }
-    if ((st = dcg_trainer_d_backward(t))) return st;
-    if ((st = dcg_trainer_d_apply(t, 1.f))) return st;
-    for (int rep = 0; rep < 2; ++rep) {
-        if ((st = dcg_trainer_g_backward(t))) return st;
-        if ((st = dcg_trainer_g_apply(t, 1.f))) return st;
+    if (st == 0) {
+        if (t->dp) {
+            st = enqueue_step(t, nullptr);   // eager, collectives included
+            if (st) return st;
+        } else {
+            if ((st = dcg_trainer_d_backward(t))) return st;
+            if ((st = dcg_trainer_d_apply(t, 1.f))) return st;
+            for (int rep = 0; rep < 2; ++rep) {
+                if ((st = dcg_trainer_g_backward(t))) return st;
+                if ((st = dcg_trainer_g_apply(t, 1.f))) return st;
+            }
+        }
+        if (!dcg::context_is_profiling(t->ctx)) ++t->step_warm_runs;
     }
     t->last_step_launches = dcg_launches_total() - before;
+    return DCG_OK;
+}
+
+// ---- checkpoints -----------------------------------------------------------------------------------
+// Counterpart of ops::Graph::save_vars / load_vars (src/ops/graph.cu:326-361), which write every
+// trainable variable as an fp32 tensor with its dims through the tensor-archive library.  The file
+// here is the raw archive of this repository's stand-in for that library (shim/tocha/tensor.hh):
+// "DCGT", u32 version 1, u32 count, then per tensor u32 rank, rank x u32 extents, fp32 values.
+// Tensors: the generator's 10 variables (k0,b0,..,k3,b3,dense w,dense b), the discriminator's 10,
+// then - which the reference drops (src/api/adam-optimizer.cu:39-45), so its restarts lose the
+// optimiser state - Adam's first and second moments of both networks in the same order, and the two
+// step counters [g_t, d_t].  A loader that only wants the variables reads the first 20 tensors.
+namespace {
+
+struct CkptTensor {
+    Tensor t;
+    int rank;
+    unsigned dims[4];
+};
+
+std::vector<CkptTensor> checkpoint_layout(dcg_trainer* t)
+{
+    std::vector<CkptTensor> v;
+    auto add_net = [&](Tensor* arr, bool gen) {
+        for (int i = 0; i < 10; ++i) {
+            CkptTensor c{};
+            c.t = arr[i];
+            if (i < 8 && i % 2 == 0) {
+                const int l = i / 2;
+                c.rank = 4; c.dims[0] = 5; c.dims[1] = 5;
+                c.dims[2] = gen ? kGChan[l + 1] : kDChan[l];
+                c.dims[3] = gen ? kGChan[l] : kDChan[l + 1];
+            } else if (i == 8) {
+                c.rank = 2; c.dims[0] = gen ? kZ : 8192; c.dims[1] = gen ? 8192 : 1;
+            } else {
+                c.rank = 1; c.dims[0] = (unsigned)arr[i].n;
+            }
+            v.push_back(c);
+        }
+    };
+    add_net(t->g_param, true); add_net(t->d_param, false);
+    add_net(t->g_m, true); add_net(t->g_v, true);
+    add_net(t->d_m, false); add_net(t->d_v, false);
+    return v;
+}
+
+int write_checkpoint(const std::string& path, const std::vector<CkptTensor>& lay, const float* host, float g_t, float d_t,
+                     std::string& err)
+{
+    std::FILE* f = std::fopen(path.c_str(), "wb");
+    if (!f) { err = "cannot write " + path; return DCG_ERR_INVALID; }
+    const unsigned head[2] = {1u, (unsigned)lay.size() + 1u};
+    bool ok = std::fwrite("DCGT", 1, 4, f) == 4 && std::fwrite(head, 4, 2, f) == 2;
+    size_t off = 0;
+    for (const CkptTensor& c : lay) {
+        const unsigned rank = (unsigned)c.rank;
+        ok = ok && std::fwrite(&rank, 4, 1, f) == 1 && std::fwrite(c.dims, 4, rank, f) == rank &&
+             std::fwrite(host + off, sizeof(float), c.t.n, f) == c.t.n;
+        off += c.t.n;
+    }
+    const unsigned tail[2] = {1u, 2u};
+    const float counters[2] = {g_t, d_t};
+    ok = ok && std::fwrite(tail, 4, 2, f) == 2 && std::fwrite(counters, sizeof(float), 2, f) == 2;
+    if (std::fclose(f) != 0 || !ok) { err = "write failed: " + path; return DCG_ERR_INVALID; }
+    return DCG_OK;
+}
+
+}  // namespace
+
+extern "C" int dcg_trainer_save_wait(dcg_trainer* t)
+{
+    DCG_CHECK_ARG(t, "dcg_trainer_save_wait: null trainer");
+    if (t->writer.joinable()) t->writer.join();
+    const int st = t->writer_status;
+    t->writer_status = DCG_OK;
+    if (st) return fail(st, "checkpoint: %s", t->writer_error.c_str());
+    return DCG_OK;
+}
+
+extern "C" int dcg_trainer_save(dcg_trainer* t, const char* path)
+{
+    DCG_CHECK_ARG(t && path, "dcg_trainer_save: null argument");
+    int st = dcg_trainer_save_wait(t);   // one checkpoint in flight at a time
+    if (st) return st;
+    const std::vector<CkptTensor> lay = checkpoint_layout(t);
+    size_t total = 0;
+    for (const CkptTensor& c : lay) total += c.t.n;
+    if (!t->snap) {
+        DCG_CUDA(cudaMallocHost(&t->snap, total * sizeof(float)));
+        t->snap_floats = total;
+        DCG_CUDA(cudaEventCreateWithFlags(&t->ev_snap, cudaEventDisableTiming));
+    }
+    size_t off = 0;
+    for (const CkptTensor& c : lay) {   // stream-ordered behind the updates enqueued so far
+        DCG_CUDA(cudaMemcpyAsync(t->snap + off, c.t.p, c.t.n * sizeof(float), cudaMemcpyDeviceToHost, t->stream));
+        off += c.t.n;
+    }
+    DCG_CUDA(cudaEventRecord(t->ev_snap, t->stream));
+    const float g_t = t->g_t, d_t = t->d_t;
+    const std::string file(path);
+    int dev = 0;
+    DCG_CUDA(cudaGetDevice(&dev));
+    t->writer = std::thread([t, lay, file, g_t, d_t, dev] {
+        cudaSetDevice(dev);
+        if (cudaEventSynchronize(t->ev_snap) != cudaSuccess) {
+            t->writer_status = DCG_ERR_CUDA;
+            t->writer_error = "the snapshot copy failed";
+            return;
+        }
+        t->writer_status = write_checkpoint(file, lay, t->snap, g_t, d_t, t->writer_error);
+    });
+    return DCG_OK;
+}
+
+extern "C" int dcg_trainer_load(dcg_trainer* t, const char* path)
+{
+    DCG_CHECK_ARG(t && path, "dcg_trainer_load: null argument");
+    int st = dcg_trainer_save_wait(t);
+    if (st) return st;
+    std::FILE* f = std::fopen(path, "rb");
+    if (!f) return fail(DCG_ERR_INVALID, "dcg_trainer_load: cannot read %s", path);
+    const std::vector<CkptTensor> lay = checkpoint_layout(t);
+    char magic[4];
+    unsigned head[2] = {0, 0};
+    bool ok = std::fread(magic, 1, 4, f) == 4 && std::memcmp(magic, "DCGT", 4) == 0 && std::fread(head, 4, 2, f) == 2 &&
+              head[0] == 1u;
+    // the variables alone (20 tensors, e.g. written by the reference's save_vars through the stand-in
+    // archive) or a full checkpoint (60 tensors + the counters)
+    const size_t have = head[1];
+    ok = ok && (have == 20 || have == lay.size() + 1);
+    std::vector<float> host;
+    for (size_t i = 0; ok && i < lay.size() && i < have; ++i) {
+        const CkptTensor& c = lay[i];
+        unsigned rank = 0, dims[8] = {0};
+        ok = std::fread(&rank, 4, 1, f) == 1 && rank >= 1 && rank <= 4 && std::fread(dims, 4, rank, f) == rank;
+        size_t n = 1;
+        for (unsigned r = 0; ok && r < rank; ++r) n *= dims[r];
+        ok = ok && n == c.t.n;
+        if (!ok) break;
+        host.resize(n);
+        ok = std::fread(host.data(), sizeof(float), n, f) == n;
+        if (ok && cudaMemcpyAsync(c.t.p, host.data(), n * sizeof(float), cudaMemcpyHostToDevice, t->stream) != cudaSuccess) ok = false;
+        if (ok && cudaStreamSynchronize(t->stream) != cudaSuccess) ok = false;   // `host` is reused
+    }
+    if (ok && have == lay.size() + 1) {
+        unsigned tail[2] = {0, 0};
+        float counters[2] = {0.f, 0.f};
+        ok = std::fread(tail, 4, 2, f) == 2 && tail[0] == 1u && tail[1] == 2u && std::fread(counters, sizeof(float), 2, f) == 2;
+        if (ok) { t->g_t = counters[0]; t->d_t = counters[1]; }
+    }
+    std::fclose(f);
+    if (!ok) return fail(DCG_ERR_INVALID, "dcg_trainer_load: %s is not a checkpoint of this model", path);
     return DCG_OK;
 }
 

@@ -16,6 +16,8 @@
 
 #include <dcgan_b200.h>
 
+#include <cuda_runtime.h>
+
 #include <cstdlib>
 #include <cstring>
 #include <stdexcept>
@@ -108,6 +110,14 @@ namespace gpu
         {
             for (int i = 0; i < 512; ++i) kernels_list[i] = nullptr;
             for (int i = 0; i < DCG_OP_COUNT; ++i) kernels_list[i] = dispatch;
+            // The reference frees its device tensors from the destructor of a function-local static
+            // (ops::Graph::instance(), src/ops/graph.cu:20-39, tensor_free throws on error,
+            // src/memory/alloc.cu:28-37).  Its own GPU objects register device code before main, which
+            // brings the CUDA runtime up - and queues its shutdown - before that static exists; without
+            // them the runtime would start at the first cudaMalloc, shut down BEFORE the graph's
+            // destructor, and every program would end in "driver shutting down".  Same order here:
+            const char* mode = std::getenv("RT_MODE");
+            if (mode && !std::strcmp(mode, "GPU")) cudaFree(nullptr);
         }
         FillTable fill_table;
     }

@@ -11,9 +11,13 @@ one training iteration.  This wrapper adds what lives above the C ABI:
   i+1 overlap the compute of iteration i);
 * data-parallel training: one process per GPU, each on its own 64-image shard;
   between *_backward and *_apply the gradient arena of the network being updated
-  is summed over ranks with one torch.distributed all_reduce (NCCL on GPUs), and
-  Adam divides by the world size.  Replicas start from the same seed and apply
-  identical updates, so parameters stay identical on every rank.
+  is summed over ranks with one all-reduce, and Adam divides by the world size.
+  Replicas start from the same seed and apply identical updates, so parameters
+  stay identical on every rank.  comm="abi" (the default): the NCCL communicator
+  lives behind the C ABI (dcg_dp_*; torch.distributed only carries its 128-byte
+  id to the ranks) and dcg_trainer_step runs the whole iteration - collectives
+  included - as one CUDA graph.  comm="torch": the collectives are
+  torch.distributed.all_reduce calls between the library's phases.
 """
 import contextlib
 import ctypes
@@ -34,7 +38,7 @@ class _CudaView:
 
 class Trainer:
     def __init__(self, batch=64, precision=_lib.PREC_TF32, fuse=True, g_leaky=False, lr=2e-4, beta1=0.5,
-                 beta2=0.999, eps=1e-8, seed=234, world=1, device=None, process_group=None):
+                 beta2=0.999, eps=1e-8, seed=234, world=1, device=None, process_group=None, comm="abi"):
         self.device = torch.device(device if device is not None else "cuda:%d" % torch.cuda.current_device())
         torch.cuda.set_device(self.device)
         self.batch, self.world, self.group = batch, world, process_group
@@ -49,7 +53,10 @@ class Trainer:
         # high priority: the library's side streams (weight / bias gradients) run at the default one, so
         # blocks of the critical path are scheduled first when both have work ready
         self.stream = torch.cuda.Stream(self.device, priority=-1) if self._own_stream else caller
-        check(lib.dcg_trainer_create(ctypes.byref(self._h), ctypes.byref(self.cfg), self.stream.cuda_stream))
+        self._dp = ctypes.c_void_p()
+        if world > 1 and comm == "abi":
+            self._dp = self._make_communicator(world, process_group)
+        check(lib.dcg_trainer_create_dp(ctypes.byref(self._h), ctypes.byref(self.cfg), self.stream.cuda_stream, self._dp))
         self._views = {}
         self.x = self.tensor("x").view(batch, 64, 64, 3)
         self.z = self.tensor("z").view(batch, 100)
@@ -58,6 +65,40 @@ class Trainer:
         self.d_grads, self.g_grads = self.tensor("d_grads"), self.tensor("g_grads")
         self._pipe = None   # staging of the end-to-end path, built on first use
         self._comm = None   # communication stream of the data-parallel step, built on first use
+
+    def _make_communicator(self, world, group):
+        """dcg_dp_init on every rank: rank 0 makes the NCCL id, torch.distributed broadcasts its bytes."""
+        import torch.distributed as dist
+        rank = dist.get_rank(group)
+        ident = (ctypes.c_ubyte * _lib.DP_ID_BYTES)()
+        if rank == 0:
+            check(lib.dcg_dp_unique_id(ident))
+        on_gpu = dist.get_backend(group) == "nccl"
+        carrier = torch.tensor(list(ident), dtype=torch.uint8, device=self.device if on_gpu else "cpu")
+        dist.broadcast(carrier, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        ident = (ctypes.c_ubyte * _lib.DP_ID_BYTES)(*carrier.cpu().tolist())
+        dp = ctypes.c_void_p()
+        check(lib.dcg_dp_init(ctypes.byref(dp), rank, world, ident))
+        return dp
+
+    def dp_info(self):
+        """(rank, world, NCCL version) of the communicator behind the C ABI, or None."""
+        if not self._dp:
+            return None
+        r, w, v = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        check(lib.dcg_dp_info(self._dp, ctypes.byref(r), ctypes.byref(w), ctypes.byref(v)))
+        return r.value, w.value, v.value
+
+    def allreduce(self, tensor):
+        """In-place sum of a device tensor over the ranks on the trainer's stream (communicator behind
+        the C ABI when there is one, else torch.distributed)."""
+        if self.world == 1:
+            return
+        with self._on_stream():
+            if self._dp:
+                check(lib.dcg_dp_allreduce(self._dp, tensor.data_ptr(), tensor.numel(), self.stream.cuda_stream))
+            else:
+                torch.distributed.all_reduce(tensor, group=self.group)
 
     # ---- device tensors ------------------------------------------------------
     def tensor(self, name):
@@ -90,6 +131,11 @@ class Trainer:
             check(lib.dcg_trainer_generate(self._h))
         return self.g_out
 
+    def d_fwd_bwd(self):
+        """Discriminator forward + backward on self.x against labels of ones (all layer gradients)."""
+        with self._on_stream():
+            check(lib.dcg_trainer_d_fwd_bwd(self._h))
+
     def d_backward(self):
         """G forward, D on fake and real, d_loss, D gradients (no update)."""
         with self._on_stream():
@@ -106,7 +152,7 @@ class Trainer:
 
     def _step(self):
         """Body of one iteration; runs with the trainer's stream current."""
-        if self.world == 1:
+        if self.world == 1 or self._dp:
             check(lib.dcg_trainer_step(self._h))   # the whole iteration, one CUDA graph once warmed up
             return
         # Data parallel: the discriminator's gradients are summed over ranks on a communication stream
@@ -206,6 +252,22 @@ class Trainer:
         CPU torch); returns (d_loss, g_loss) as Python floats read back from the device."""
         return self.result(self.submit_host(x_host, z_host))
 
+    # ---- checkpoints -----------------------------------------------------------------------------
+    def save(self, path, wait=False):
+        """Snapshot of variables, Adam moments and step counters; the file is written by a host thread
+        while training continues (wait=True, save_wait() or the next save / load joins it)."""
+        with self._on_stream():
+            check(lib.dcg_trainer_save(self._h, str(path).encode()))
+        if wait:
+            self.save_wait()
+
+    def save_wait(self):
+        check(lib.dcg_trainer_save_wait(self._h))
+
+    def load(self, path):
+        with self._on_stream():
+            check(lib.dcg_trainer_load(self._h, str(path).encode()))
+
     h2d_bytes_per_step = property(lambda self: self.batch * (64 * 64 * 3 + 100) * 4)
     d2h_bytes_per_step = property(lambda self: 8)
 
@@ -217,6 +279,10 @@ class Trainer:
             self._views.clear()
             lib.dcg_trainer_destroy(self._h)
             self._h = ctypes.c_void_p()
+        if getattr(self, "_dp", None):
+            torch.cuda.synchronize(self.device)
+            lib.dcg_dp_finalize(self._dp)
+            self._dp = ctypes.c_void_p()
 
     def __del__(self):
         try:

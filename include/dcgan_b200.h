@@ -332,6 +332,25 @@ int dcg_run_node(dcg_context* ctx, const dcg_node* node);
  * buffers flagged DCG_NODE_OUT_DEAD. */
 int dcg_run_nodes(dcg_context* ctx, const dcg_node* nodes, int count, int fuse);
 
+/* ---- data parallelism ------------------------------------------------------
+ * The path shards over the batch: one process per GPU, every rank trains its own images with a
+ * full replica of the 20 variables; the one exchange of an update is a sum of that network's
+ * contiguous gradient arena over the ranks (ncclAllReduce over NVLink / NVSwitch), then the replicated
+ * Adam step divides by the world size.  The reference has no multi-GPU code (its training loop is
+ * dcgan/main.cu:378-391 on one device); these entry points have no counterpart in it.
+ * NCCL is looked up at run time (libnccl.so.2), so the library loads without it.
+ *   dcg_dp_unique_id  rank 0 makes the 128-byte id; the caller hands it to every rank (any transport);
+ *   dcg_dp_init       collective: every rank calls it with its rank, on its own current device;
+ *   dcg_dp_allreduce  in-place sum over the ranks, enqueued on `stream` (no synchronisation);
+ *   dcg_dp_info       rank, world and the version of the NCCL library that was loaded. */
+#define DCG_DP_ID_BYTES 128
+typedef struct dcg_dp dcg_dp;
+int dcg_dp_unique_id(void* id_out);
+int dcg_dp_init(dcg_dp** out, int rank, int world, const void* unique_id);
+int dcg_dp_allreduce(dcg_dp* dp, float* buf, size_t count, dcg_stream_t stream);
+int dcg_dp_info(const dcg_dp* dp, int* rank, int* world, int* nccl_version);
+void dcg_dp_finalize(dcg_dp* dp);
+
 /* ---- DCGAN training step: the caller of the hot path ----------------------
  * Host-side counterpart of dcgan/main.cu:271-410: the generator / discriminator
  * of that file lowered to node lists (forward, autodiff gradients) and executed
@@ -354,6 +373,12 @@ typedef struct dcg_trainer_config {
 /* Allocates one device arena (parameters, Adam state, gradients, activations) and builds the
  * node lists.  The only allocating entry point besides dcg_context_create. */
 int dcg_trainer_create(dcg_trainer** out, const dcg_trainer_config* cfg, dcg_stream_t stream);
+/* The same for data-parallel training with the communicator behind the C ABI (cfg->world ranks; `dp`
+ * stays the caller's and must outlive the trainer): the arena comes from NCCL's own allocator where
+ * that exists (its in-switch reduction needs memory it mapped itself), the gradient arenas are
+ * registered with the communicator, and dcg_trainer_step runs the whole data-parallel iteration -
+ * node lists, the three gradient sums, the three Adam steps - as one CUDA graph. */
+int dcg_trainer_create_dp(dcg_trainer** out, const dcg_trainer_config* cfg, dcg_stream_t stream, dcg_dp* dp);
 void dcg_trainer_destroy(dcg_trainer* t);
 /* Device tensors by name: "x" [B,64,64,3] real images and "z" [B,100] noise (inputs the caller
  * fills), "g_out", "d_loss", "g_loss", "logits_fake", "logits_real", the contiguous per-network
@@ -368,6 +393,11 @@ void dcg_trainer_destroy(dcg_trainer* t);
 int dcg_trainer_tensor(dcg_trainer* t, const char* name, float** ptr, size_t* count);
 /* Generator forward only (z -> g_out): dcgan/main.cu:252-269. */
 int dcg_trainer_generate(dcg_trainer* t);
+/* Discriminator forward + backward on the real images "x" alone against labels of all ones: sigmoid
+ * cross-entropy, then the kernel, bias and input gradient of every layer (the image gradient lands
+ * in the generator-output gradient buffer).  Weight gradients go to "d_gradb0..9".  A measurement and
+ * test entry; it leaves parameters untouched. */
+int dcg_trainer_d_fwd_bwd(dcg_trainer* t);
 /* graph.run({d_opti, d_loss}) minus the update: G forward, D on fake and real, d_loss, D gradients. */
 int dcg_trainer_d_backward(dcg_trainer* t);
 /* Adam on the discriminator with gradients scaled by grad_scale (1/world after an all-reduce). */
@@ -379,8 +409,21 @@ int dcg_trainer_g_backward(dcg_trainer* t);
  * while the discriminator's gradients are still being all-reduced), part 1 everything after it. */
 int dcg_trainer_g_backward_part(dcg_trainer* t, int part);
 int dcg_trainer_g_apply(dcg_trainer* t, float grad_scale);
-/* One whole iteration on a single GPU: d_backward, d_apply, then twice g_backward, g_apply. */
+/* One whole iteration: d_backward, d_apply, then twice g_backward, g_apply; with a communicator
+ * (dcg_trainer_create_dp) each *_apply is preceded by the sum of that network's gradients over the
+ * ranks and scales by 1/world.  The third call onwards replays the iteration as one CUDA graph. */
 int dcg_trainer_step(dcg_trainer* t);
+/* Checkpoint / resume, the counterpart of ops::Graph::save_vars / load_vars (src/ops/graph.cu:326-361).
+ * dcg_trainer_save enqueues a device -> pinned-host snapshot behind the updates enqueued so far and
+ * returns; a host thread writes the file once the copy has landed, so training continues meanwhile
+ * (dcg_trainer_save_wait joins it and returns its status; the next save, a load and destroy wait too).
+ * File: raw tensor archive ("DCGT", u32 1, u32 count, per tensor u32 rank, extents, fp32 values) holding the
+ * generator's 10 variables, the discriminator's 10, Adam's first and second moments of both (which the
+ * reference does not save, src/api/adam-optimizer.cu:39-45) and the step counters [g_t, d_t].
+ * dcg_trainer_load also accepts an archive of the 20 variables alone. */
+int dcg_trainer_save(dcg_trainer* t, const char* path);
+int dcg_trainer_save_wait(dcg_trainer* t);
+int dcg_trainer_load(dcg_trainer* t, const char* path);
 /* The trainer's execution context (for dcg_context_profile_begin / _end around its phases). */
 dcg_context* dcg_trainer_context(dcg_trainer* t);
 /* Kernels launched by the last dcg_trainer_step. */
@@ -404,6 +447,10 @@ const char* dcg_last_error(void);
 void dcg_debug_set_wait_limit(long long sm_clocks);
 void dcg_debug_skip_stage(int stage);
 void dcg_debug_set_pairs(int mode);
+/*  dcg_debug_set_gather      1 / 0: input gradient of a layer with <= 4 input channels as ONE launch (the gather of
+ *                            the tap products fused into the GEMM's epilogue) or as GEMM + gather kernel; < 0
+ *                            follows the DCG_TC_GATHER environment variable (default on).  Same bits either way. */
+void dcg_debug_set_gather(int mode);
 /* Library version and the architecture the kernels were built for ("sm_100a"). */
 const char* dcg_build_info(void);
 /* Kernels launched by this library since it was loaded (all contexts, all threads). */

@@ -381,3 +381,32 @@ def test_cta_pairs_match_single_cta_tiles(pkg, dev, layer):
         assert (r - u).abs().max().item() <= TF32_TOL * scale, name
         assert (s1 - u).abs().max().item() <= 1e-4 * scale, name
         assert torch.equal(u, v), name
+
+
+@pytest.mark.parametrize("shape", [(3, 20, 12, 1, 3, 32, 1), (2, 16, 16, 4, 5, 96, 2), (5, 32, 32, 2, 4, 64, 2),
+                                   (2, 10, 14, 3, 5, 160, 2), (64, 64, 64, 3, 5, 64, 2), (3, 9, 7, 3, 5, 32, 2)])
+def test_fused_gather_equals_gemm_plus_gather(pkg, dev, shape):
+    """Input gradient of a layer with <= 4 input channels: the one-launch form (tiles of dy with a
+    halo, the tap products summed per output pixel inside the GEMM's epilogue) gives the same bits as
+    the GEMM that writes the tap-major products to scratch followed by the gather kernel - same
+    products, added in the same (kernel row, kernel column) order - with bias and tanh fused in."""
+    F, L = pkg.functional, pkg.lib
+    N, H, W, C, K, O, s = shape
+    Ho, Wo = (H + s - 1) // s, (W + s - 1) // s
+    g = torch.Generator(device="cpu").manual_seed(71)
+    dy = (torch.rand((N, Ho, Wo, O), generator=g) * 2 - 1).to(dev)
+    k = (torch.randn((K, K, C, O), generator=g) * 0.05).to(dev)
+    bias = torch.randn((C,), generator=g).to(dev)
+    outs = []
+    try:
+        for mode in (0, 1):
+            L.dcg_debug_set_gather(mode)
+            before = pkg.launches_total()
+            dx = F.conv2d_dx(dy, k, (H, W), (s, s), epilogue=F.make_epilogue(bias=bias, act=pkg.ACT_TANH))
+            torch.cuda.synchronize()
+            outs.append((dx, pkg.launches_total() - before))
+    finally:
+        L.dcg_debug_set_gather(-1)
+    assert L.dcg_device_status() == 0
+    assert torch.equal(outs[0][0], outs[1][0])
+    assert outs[1][1] == 2 and outs[0][1] == 3     # weight repack + GEMM (+ gather kernel)
