@@ -91,6 +91,7 @@ SIGNATURES = {
     "dcg_colsum_noalloc": (c_int, [_P, _P, c_size_t, c_size_t, _P]),
     "dcg_rowsum": (c_int, [_P, _P, c_size_t, c_size_t, _P]),
     "dcg_add": (c_int, [_P, _P, _P, c_size_t, _P]),
+    "dcg_u8_to_unit": (c_int, [_P, _P, c_size_t, _P]),
     "dcg_update": (c_int, [_P, _P, _P, c_size_t, _P]),
     "dcg_matmul": (c_int, [_P, _P, _P, _P, c_size_t, c_size_t, c_size_t, _P]),
     "dcg_matmul_tn": (c_int, [_P, _P, _P, c_size_t, c_size_t, c_size_t, _P]),
@@ -141,8 +142,6 @@ SIGNATURES = {
     "dcg_last_error": (ctypes.c_char_p, []),
     "dcg_debug_set_wait_limit": (None, [ctypes.c_longlong]),
     "dcg_debug_skip_stage": (None, [c_int]),
-    "dcg_debug_set_pairs": (None, [c_int]),
-    "dcg_debug_set_gather": (None, [c_int]),
     "dcg_build_info": (ctypes.c_char_p, []),
     "dcg_launches_total": (ctypes.c_uint64, []),
 }

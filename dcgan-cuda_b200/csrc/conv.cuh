@@ -30,11 +30,8 @@ int conv_tc_dk(const dcg_conv_desc& d, const float* x, const float* dy, float* d
 
 // Testing hooks of the tensor path.  wait_cycles: > 0 sets the limit of every barrier wait (SM clocks),
 // -1 restores the default, 0 leaves it; skip_stage: pipeline stage the producer leaves out (-1: none,
-// -2: leave as is); pairs: 1 / 0 force CTA pairs on / off, -1 follows the environment, -2 leaves as is.
-void conv_tc_set_hooks(long long wait_cycles, int skip_stage, int pairs);
-// 1 / 0: the input gradient of a narrow-channel layer as one launch (gather fused into the GEMM's epilogue) or as
-// GEMM + gather kernel; -1 follows the environment (DCG_TC_GATHER, default on).
-void conv_tc_set_gather(int mode);
+// -2: leave as is).
+void conv_tc_set_hooks(long long wait_cycles, int skip_stage);
 
 // Shape validation shared by the entry points: 0 or a negative dcg_status.
 int conv_check_desc(const dcg_conv_desc* d, const char* who);

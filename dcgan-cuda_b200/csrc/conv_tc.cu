@@ -52,7 +52,6 @@ constexpr int kEpi = 256;               // epilogue threads: warps 2..9, two per
 constexpr int kThreads = 64 + kEpi;
 constexpr int kMaxSmem = 227 * 1024;
 constexpr int kMaxCluster = 8;          // portable thread-block cluster size: the cap on K partitions
-constexpr int kPairDefault = 0;         // CTA pairs (cta_group::2) unless DCG_TC_PAIR says otherwise
 // Floats of shared memory the epilogue's transposition buffer takes for a 128 x bn tile (quads at a
 // pitch of BM + 1 sixteen-byte units); the row-offset table follows it.
 __host__ __device__ constexpr int kRedFloats(int bn) { return (bn / 4) * (BM + 1) * 4; }
@@ -101,15 +100,7 @@ struct Params {
     int m_tiles;                  // DK: 128-row tiles along the M channel axis
     int n_tiles;                  // BN-column tiles along the N channel axis
     int bn;                       // accumulator columns, multiple of 16, <= 256
-    int splits;                   // K partitions of a tile
-    int pair;                     // CTA pairs: two M tiles share every B tile through tcgen05 cta_group::2
-                                  //   (cluster = 2 * splits CTAs, rank = 2 * partition + half)
-    // FWD as the GEMM behind the input gradient of a narrow-channel layer, with the gather fused in:
-    // the tile is a TH x TW patch of dy of ONE image (halo included) whose origin may be negative, its
-    // accumulator columns are the tap products ycol[tap][4 channels], and the CTA sums, for each pixel of
-    // its g_bh x g_bw block of the OUTPUT image, the products that land on it (0: off)
-    int gather;
-    int g_H, g_W, g_C, g_KH, g_KW, g_sh, g_sw, g_pt, g_pl, g_bh, g_bw;
+    int splits;                   // K partitions of a tile = CTAs per cluster (<= 8)
     int skip_stage;               // test hook: the producer leaves this pipeline stage out (-1: never)
     long long wait_cycles;        // SM clocks after which a barrier wait gives up
     int kchunks;                  // 32-wide chunks along the contracted channel axis (FWD: C, DX: O)
@@ -199,66 +190,6 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, in
     return __all_sync(0xffffffffu, mbar_wait_slow(bar, parity, role, stage, limit));
 }
 
-// ---- CTA pairs (tcgen05 cta_group::2) -----------------------------------------------------------------
-// Two CTAs of a cluster whose ranks differ in the lowest bit work on one 256-row tile: each loads
-// its own 128 rows of A and its own HALF of the B tile into its own shared memory (plain TMA loads
-// on its own barriers - no multicast anywhere), and one tcgen05.mma.cta_group::2, issued by the
-// even CTA, multiplies both A halves with both B halves; every CTA ends up with its 128 rows of
-// the accumulator in its own TMEM.  Per pipeline stage a CTA thus fetches 16 KB + bn * 64 B instead
-// of 16 KB + bn * 128 B for the same tensor work, which is what the main loop is paced by.
-// The handshakes across the pair use mbarriers in the partner's shared memory, addressed through
-// mapa: the odd CTA tells the even one that its stage has landed (a plain remote arrive), the even
-// one tells the odd one that a stage has been read and that the accumulator is complete
-// (tcgen05.commit on the partner's barrier).
-__device__ __forceinline__ uint32_t cluster_ctarank()
-{
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank)
-{
-    uint32_t a;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_addr), "r"(rank));
-    return a;
-}
-
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr)
-{
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-
-// wait on a barrier that a thread of the partner CTA arrives on (acquire at cluster scope), bounded
-__device__ __noinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int role, int stage, long long limit)
-{
-    const long long t0 = clock64();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 64; ++i) {
-            uint32_t ok;
-            asm volatile(
-                "{\n\t.reg .pred p;\n\t"
-                "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-                "selp.u32 %0, 1, 0, p;\n\t}"
-                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-            if (ok) return true;
-        }
-        if (clock64() - t0 > limit) break;
-    }
-    if (atomicCAS(&g_tc_status[0], 0, 1) == 0) {
-        g_tc_status[1] = blockIdx.x;
-        g_tc_status[2] = role;
-        g_tc_status[3] = stage;
-    }
-    return false;
-}
-
-__device__ __forceinline__ bool mbar_wait_cluster_warp(uint32_t bar, uint32_t parity, int role, int stage, long long limit)
-{
-    return __all_sync(0xffffffffu, mbar_wait_cluster(bar, parity, role, stage, limit));
-}
-
 __device__ __forceinline__ bool elect_one()
 {
     uint32_t pred;
@@ -299,23 +230,6 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
 __device__ __forceinline__ void tcgen05_commit(uint32_t bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-// cta_group::2 forms: issued by one thread of the even CTA of a pair; the barrier operand is a
-// shared::cluster address and may name a barrier of either CTA of the pair.
-__device__ __forceinline__ void tcgen05_commit_pair(uint32_t cluster_bar)
-{
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
-}
-
-__device__ __forceinline__ void tcgen05_mma_tf32_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                                      uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
 __device__ __forceinline__ void tcgen05_mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
@@ -390,11 +304,8 @@ __device__ __forceinline__ uint32_t make_idesc(int a_mn_major, int b_mn_major, i
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------
-// PAIR: CTA pairs (cta_group::2).  A template flag rather than a run-time one: a kernel that contains
-// cta_group::2 instructions can only be launched with an even cluster size, so the single-CTA form
-// must not contain any.
-template <int MODE, bool X3, bool PAIR>
-__global__ void __launch_bounds__(kThreads, (X3 || PAIR) ? 1 : 2)
+template <int MODE, bool X3>
+__global__ void __launch_bounds__(kThreads, X3 ? 1 : 2)
 conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ Params p)
 {
@@ -402,7 +313,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 64) TC_TRACE(3072);
     TC_CTA_TRACE(0);
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const int b_stage_bytes = (PAIR ? p.bn / 2 : p.bn) * BK * 4;   // a pair CTA holds half of the B tile
+    const int b_stage_bytes = p.bn * BK * 4;
     const long long wait_limit = p.wait_cycles;
     const uint32_t a_base = smem_base;
     const uint32_t b_base = a_base + (uint32_t)p.stages * A_STAGE_BYTES;
@@ -415,7 +326,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t empty_bar = bar_base + 8u * p.stages;
     const uint32_t resid_bar = bar_base + 16u * p.stages;     // 3xTF32: residual tiles of the stage are written
     const uint32_t tmem_full_bar = bar_base + 24u * p.stages;
-    const uint32_t peer_full_bar = tmem_full_bar + 16u;           // pairs: the partner's tile of the stage has landed
     const uint32_t tmem_slot = tmem_full_bar + 8u;
     uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
@@ -427,7 +337,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_init(full_bar + 8u * s, 1);
             mbar_init(empty_bar + 8u * s, 1);
             mbar_init(resid_bar + 8u * s, kEpi);
-            if (PAIR) mbar_init(peer_full_bar + 8u * s, 1);
         }
         mbar_init(tmem_full_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -441,30 +350,20 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     int tmem_cols = 32;
     while (tmem_cols < (X3 ? 2 * p.bn : p.bn)) tmem_cols <<= 1;
     if (warp == 1) {
-        if (PAIR) {   // one warp of each CTA of the pair takes part
-            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(tmem_cols) : "memory");
-            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-        } else {
-            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(tmem_cols) : "memory");
-            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-        }
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
 
     // ---- decode this CTA's work item -------------------------------------------------------------
     // blockIdx.x = ((group * m_count + m) * n_tiles + n) * splits + split, where group is the parity
     // class (DX), the kernel tap (DK) or absent (FWD), and m a pixel tile (FWD/DX) or channel tile (DK).
-    // With CTA pairs the innermost index is the half of the 256-row tile (= parity of the cluster
-    // rank), then the partition; m then counts pairs of M tiles.
     int rem = blockIdx.x;
-    const int half = PAIR ? (rem & 1) : 0;
-    if (PAIR) rem >>= 1;
     const int split = rem % p.splits; rem /= p.splits;
     const int n_tile = rem % p.n_tiles; rem /= p.n_tiles;
     int m_count;
     if (MODE == MODE_DK) m_count = p.m_tiles;
     else m_count = p.tiles_w * p.tiles_h * p.tiles_n;
-    if (PAIR) m_count >>= 1;
-    const int m_tile = PAIR ? 2 * (rem % m_count) + half : rem % m_count;
+    const int m_tile = rem % m_count;
     const int group = rem / m_count;
 
     // pixel-tile origin (FWD/DX)
@@ -473,15 +372,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         j0 = (m_tile % p.tiles_w) * p.TW;
         i0 = ((m_tile / p.tiles_w) % p.tiles_h) * p.TH;
         n0 = (m_tile / (p.tiles_w * p.tiles_h)) * p.TN;
-    }
-    int g_h0 = 0, g_w0 = 0;   // gather: origin of this CTA's block of output pixels
-    if (MODE == MODE_FWD && p.gather) {
-        g_w0 = (m_tile % p.tiles_w) * p.g_bw;
-        g_h0 = ((m_tile / p.tiles_w) % p.tiles_h) * p.g_bh;
-        // first dy row / column any output pixel of the block reads: ceil((h0 + pad - (K - 1)) / s)
-        const int ah = g_h0 + p.g_pt - (p.g_KH - 1), aw = g_w0 + p.g_pl - (p.g_KW - 1);
-        i0 = ah >= 0 ? (ah + p.g_sh - 1) / p.g_sh : -((-ah) / p.g_sh);
-        j0 = aw >= 0 ? (aw + p.g_sw - 1) / p.g_sw : -((-aw) / p.g_sw);
     }
     // DX: parity class and its taps; DK: the kernel tap
     int ph = 0, pw = 0, rh = 0, rw = 0, eh = 0, ew = 0, taps_h = 1, taps_w = 1, tap_di = 0, tap_dj = 0;
@@ -506,8 +396,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    // pairs: the partner's barriers must be initialised before anything arrives on them remotely
-    if (PAIR) cluster_sync_all();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = *tmem_slot_ptr;
     // Programmatic dependent launch: everything above (barriers, TMEM, descriptor prefetch) may run
@@ -581,15 +469,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         if (it < 128) TC_TRACE(256 + it);
                         tma_load_4d(a_dst, &map_a, fb, chunk * BK, p.sw * j0 + dj - p.pl, p.sh * i0 + di - p.pt, n0);
                         if (it < 128) TC_TRACE(512 + it);
-                        // B: bn / 32 chunks of 32 output channels; a pair CTA takes its half of them
-                        tma_load_4d(b_dst, &map_b, fb, 0, chunk * BK, tap,
-                                    PAIR ? n_tile * (p.bn / 32) + half * (p.bn / 64) : n_tile * (p.bn / 32));
+                        tma_load_4d(b_dst, &map_b, fb, 0, chunk * BK, tap, n_tile * (p.bn / 32));
                         if (it < 128) TC_TRACE(768 + it);
                     } else if (MODE == MODE_DX) {
                         // (di, dj) count the taps of this parity class: kernel tap (rh + sh*di, rw + sw*dj)
                         tma_load_4d(a_dst, &map_a, fb, chunk * BK, j0 + ew - dj, i0 + eh - di, n0);
-                        tma_load_4d(b_dst, &map_b, fb, chunk * BK, n_tile * p.bn + (PAIR ? half * (p.bn / 2) : 0),
-                                    rw + p.sw * dj, rh + p.sh * di);
+                        tma_load_4d(b_dst, &map_b, fb, chunk * BK, n_tile * p.bn, rw + p.sw * dj, rh + p.sh * di);
                     } else {
                         // (tap, di, dj) count the 32-pixel tiles along (n, h, w)
                         const int pj = dj * p.TW, pi = di * p.TH, pn = tap * p.TN;
@@ -622,7 +507,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         {
             const int a_mn = (MODE == MODE_DK) ? 1 : 0;
             const int b_mn = (MODE == MODE_DX) ? 0 : 1;
-            const uint32_t idesc = make_idesc(a_mn, b_mn, p.bn, PAIR ? 2 * BM : BM);
+            const uint32_t idesc = make_idesc(a_mn, b_mn, p.bn, BM);
             // K-major tile: rows of 128 B, 8-row groups 1024 B apart (stride offset); one MMA (K = 8)
             // consumes 32 B of each row.
             // MN-major tile: [32-channel chunk][k row][128 B]: chunks 4096 B apart (leading offset), the
@@ -639,41 +524,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t a_stage16 = A_STAGE_BYTES >> 4, b_stage16 = (uint32_t)b_stage_bytes >> 4;
             int s = 0;
             uint32_t phase = 0;
-            if (PAIR && half == 1) {
-                // ===== odd CTA of a pair: no MMAs of its own; tells the even CTA when a stage has landed =====
-                const uint32_t partner_peer_full = map_to_cta(peer_full_bar, cluster_ctarank() ^ 1u);
-                for (int it = 0; it < nq; ++it) {
-                    if (!mbar_wait_warp(full_bar + 8u * s, phase, 5, it, wait_limit)) break;
-                    if (elect_one()) mbar_arrive_remote(partner_peer_full + 8u * s);
-                    if (++s == p.stages) { s = 0; phase ^= 1u; }
-                }
-            } else if (PAIR) {
-                // ===== even CTA of a pair: one MMA over both CTAs' tiles per K step =====
-                const uint32_t partner = cluster_ctarank() ^ 1u;
-                const uint32_t partner_empty = map_to_cta(empty_bar, partner);
-                const uint32_t partner_tmem_full = map_to_cta(tmem_full_bar, partner);
-                for (int it = 0; it < nq; ++it) {
-                    if (!mbar_wait_warp(full_bar + 8u * s, phase, 1, it, wait_limit)) break;
-                    if (!mbar_wait_cluster_warp(peer_full_bar + 8u * s, phase, 6, it, wait_limit)) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    if (elect_one()) {
-                        const uint64_t adesc = adesc0 + (uint64_t)(s * a_stage16);
-                        const uint64_t bdesc = bdesc0 + (uint64_t)(s * b_stage16);
-#pragma unroll
-                        for (int kk = 0; kk < BK / 8; ++kk)
-                            tcgen05_mma_tf32_pair(tmem_d, adesc + (uint64_t)(kk * (a_step >> 4)), bdesc + (uint64_t)(kk * (b_step >> 4)),
-                                                  idesc, (it > 0 || kk > 0) ? 1u : 0u);
-                        // the stage is free in BOTH CTAs once these MMAs have read it
-                        tcgen05_commit_pair(empty_bar + 8u * s);
-                        tcgen05_commit_pair(partner_empty + 8u * s);
-                    }
-                    if (++s == p.stages) { s = 0; phase ^= 1u; }
-                }
-                if (elect_one()) {   // accumulator complete (or abandoned), in both CTAs
-                    tcgen05_commit_pair(tmem_full_bar);
-                    tcgen05_commit_pair(partner_tmem_full);
-                }
-            } else {
+            {
             for (int it = 0; it < nq; ++it) {
                 if (!mbar_wait_warp(full_bar + 8u * s, phase, 1, it, wait_limit)) break;
                 if (X3 && !mbar_wait_warp(resid_bar + 8u * s, phase, 3, it, wait_limit)) break;
@@ -798,11 +649,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int QPO = (qpr + S - 1) / S;        //   quads per share
     const int QS = BM + 1;                    // shared-memory quad pitch in 16-byte units (odd: lanes = quads hit distinct banks)
     const int CL = (p.bn + S - 1) / S;        // scalar path: columns per share
-    // scratch slot = blockIdx.x; the partitions of this CTA's tile are pstride slots apart (with CTA
-    // pairs the two halves of a 256-row tile interleave)
-    const int pstride = PAIR ? 2 : 1;
     float* my_scratch = p.scratch + (size_t)blockIdx.x * BM * p.bn;
-    const float* tile_scratch = p.scratch + (size_t)(blockIdx.x - pstride * part) * BM * p.bn;
+    const float* tile_scratch = p.scratch + (size_t)(blockIdx.x - part) * BM * p.bn;
     if (threadIdx.x == 64) TC_TRACE(3000);
     if (warp >= 2) {
         const int quad = warp & 3;
@@ -858,36 +706,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 64) TC_TRACE(3002);
     TC_CTA_TRACE(4);
 
-    if (MODE == MODE_FWD && p.gather) {
-        // ===== fused gather: the accumulator tile sits in shared memory as [tap][tile pixel] float4s
-        // (4 channels per tap); every output pixel of this CTA's block adds the products of the taps
-        // whose parity matches it - in (kernel row, kernel column) order - and goes through the fused
-        // chain.  dy pixels outside the image were zero-filled by TMA, so their products are zero.
-        if (warp >= 2) {
-            const int tid_e = threadIdx.x - 64;
-            const float4* red4 = reinterpret_cast<const float4*>(red);
-            const int block = p.g_bh * p.g_bw;
-            for (int idx = tid_e; idx < block; idx += kEpi) {
-                const int h = g_h0 + idx / p.g_bw, w = g_w0 + idx % p.g_bw;
-                if (h >= p.g_H || w >= p.g_W || n0 >= p.N) continue;
-                float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                for (int di = (h + p.g_pt) % p.g_sh; di < p.g_KH; di += p.g_sh) {
-                    const int i = (h + p.g_pt - di) / p.g_sh - i0;     // exact division (matching parity)
-                    for (int dj = (w + p.g_pl) % p.g_sw; dj < p.g_KW; dj += p.g_sw) {
-                        const int j = (w + p.g_pl - dj) / p.g_sw - j0;
-                        const float4 v = red4[(di * p.g_KW + dj) * QS + i * p.TW + j];
-                        acc[0] = __fadd_rn(acc[0], v.x); acc[1] = __fadd_rn(acc[1], v.y);
-                        acc[2] = __fadd_rn(acc[2], v.z); acc[3] = __fadd_rn(acc[3], v.w);
-                    }
-                }
-                const size_t pix = ((size_t)n0 * p.g_H + h) * p.g_W + w;
-                for (int c = 0; c < p.g_C; ++c) {
-                    const size_t o = pix * p.g_C + c;
-                    p.out[o] = epilogue_apply(p.ep, acc[c], o, c);
-                }
-            }
-        }
-    } else if (warp >= 2 && finish_here) {
+    if (warp >= 2 && finish_here) {
         // ===== this partition's share: sum in partition order, fused chain, stores =====
         const int tid_e = threadIdx.x - 64;
         const EpilogueArgs& e = p.ep;
@@ -930,7 +749,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     for (int sidx = 1; sidx < S; ++sidx) {   // two partitions' loads in flight; the adds keep partition order
                         float4 v[4];
 #pragma unroll
-                        for (int u = 0; u < 4; ++u) v[u] = __ldcg(src[u] + (size_t)sidx * pstride * BM * qpr);
+                        for (int u = 0; u < 4; ++u) v[u] = __ldcg(src[u] + (size_t)sidx * BM * qpr);
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
                             acc[u].x = __fadd_rn(acc[u].x, v[u].x); acc[u].y = __fadd_rn(acc[u].y, v[u].y);
@@ -1022,7 +841,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         float v[4];
 #pragma unroll
                         for (int u = 0; u < 4; ++u)
-                            v[u] = __ldcg(tile_scratch + ((size_t)sidx * pstride * p.bn + (cols[u] < 0 ? 0 : cols[u])) * BM + my_row);
+                            v[u] = __ldcg(tile_scratch + ((size_t)sidx * p.bn + (cols[u] < 0 ? 0 : cols[u])) * BM + my_row);
 #pragma unroll
                         for (int u = 0; u < 4; ++u) acc[u] = __fadd_rn(acc[u], v[u]);
                     }
@@ -1050,14 +869,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // ---- teardown: everyone is done with TMEM before warp 1 releases it --------------------------
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (PAIR) {
-        // both CTAs of a pair are done with TMEM (and with each other's barriers) before either frees it
-        cluster_sync_all();
-        if (warp == 1) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
-        }
-    } else if (warp == 1) {
+    if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
     }
@@ -1362,39 +1174,10 @@ int choose_splits(int tiles, int min_stages_per_tile, int ctas_per_sm = 1)
     return s < 1 ? 1 : s;
 }
 
-// CTA pairs (cta_group::2): on unless switched off (DCG_TC_PAIR=0 in the environment, or the
-// testing hook dcg_debug_set_pairs).  -1 = follow the environment.
-std::atomic<int> g_pair_override{-1};
-bool pairs_enabled()
-{
-    const int o = g_pair_override.load();
-    if (o >= 0) return o != 0;
-    static const int env = [] { const char* v = getenv("DCG_TC_PAIR"); return v ? atoi(v) : kPairDefault; }();
-    return env != 0;
-}
-
-// Turns a plan with `tiles` single tiles (m_count of them along M per group and N tile) into a plan
-// of CTA pairs where that is possible: an even number of M tiles, a B tile that halves into whole
-// 32-channel chunks (MN-major) or 8-row groups (K-major), no 3xTF32.  The K partitions of a pair
-// tile and its two halves share one cluster, so at most kMaxCluster / 2 partitions.
-void maybe_pair(Plan& pl, int tiles, int m_count, int b_half_granule)
-{
-    Params& p = pl.p;
-    if (!pairs_enabled() || p.x3 || p.narrow || p.ext_finish) return;
-    if (m_count < 2 || (m_count & 1) || p.bn % (2 * b_half_granule) != 0) return;
-    // Only grids that are resident all at once with one CTA per SM.  With more CTAs than SMs the
-    // single-CTA form keeps two CTAs per SM; pair kernels in that regime (two pair halves sharing an
-    // SM, several waves) ran into their wait limits on B200 and are not used.
-    int splits = p.splits > kMaxCluster / 2 ? kMaxCluster / 2 : p.splits;
-    if (tiles * splits > sm_count()) return;
-    p.pair = 1;
-    p.splits = splits;
-}
-
 void finish_plan(Plan& pl)
 {
     Params& p = pl.p;
-    const int b_stage = (p.pair ? p.bn / 2 : p.bn) * BK * 4;           // a pair CTA holds half of the B tile
+    const int b_stage = p.bn * BK * 4;
     const int per_stage = (A_STAGE_BYTES + b_stage) * (p.x3 ? 2 : 1);   // 3xTF32: operand + residual tiles
     // two CTAs per SM when the grid has more CTAs than SMs, else one deep pipeline
     const int budget = (pl.grid > sm_count() && p.bn <= 128 && !p.x3) ? (kMaxSmem / 2 - 2048) : (kMaxSmem - 2048);
@@ -1410,7 +1193,7 @@ void finish_plan(Plan& pl)
     static const int debug = env_int("DCG_TC_DEBUG");
     p.debug = debug;
 #endif
-    pl.smem = (size_t)stages * per_stage + 1024 /*alignment slack*/ + 32 * stages + 32;
+    pl.smem = (size_t)stages * per_stage + 1024 /*alignment slack*/ + 24 * stages + 32;
     p.skip_stage = -1;
     p.wait_cycles = kWaitCycles;
     pl.partial_bytes = p.splits > 1 ? (size_t)pl.grid * BM * p.bn * sizeof(float) : 0;
@@ -1464,7 +1247,6 @@ bool plan_fwd(const dcg_conv_desc& d, Plan& pl)
         pl.k4_bytes = (size_t)d.kh * 32 * d.o * sizeof(float);
     }
     p.splits = choose_splits(tiles, narrow ? d.kh : d.kh * d.kw * p.kchunks);
-    maybe_pair(pl, tiles, p.tiles_w * p.tiles_h * p.tiles_n, 32);   // B: whole 32-channel chunks per half
     pl.grid = tiles * p.splits;
     finish_plan(pl);
     return true;
@@ -1481,71 +1263,9 @@ dcg_conv_desc dx_gemm_desc(const dcg_conv_desc& d, int Jp)
 
 bool plan_fwd(const dcg_conv_desc& d, Plan& pl);
 
-// Fused gather (the default for the input gradient of a narrow-channel layer; DCG_TC_GATHER=0 or the
-// testing hook switch back to GEMM + separate gather kernel).  -1 = follow the environment.
-std::atomic<int> g_gather_override{-1};
-bool gather_enabled()
-{
-    const int o = g_gather_override.load();
-    if (o >= 0) return o != 0;
-    static const int env = [] { const char* v = getenv("DCG_TC_GATHER"); return v ? atoi(v) : 1; }();
-    return env != 0;
-}
-
-// Largest block extent (a multiple of the stride, at most `limit` rounded up to one) such that the
-// dy rows any block of that extent reads fit into `tile` rows; 0 if even one stride does not fit.
-int gather_block_extent(int extent, int k, int s, int pad, int tile, int limit)
-{
-    for (int b = (limit + s - 1) / s * s; b >= s; b -= s) {
-        bool ok = true;
-        for (int h0 = 0; h0 < extent && ok; h0 += b) {
-            const int a = h0 + pad - (k - 1);
-            const int lo = a >= 0 ? (a + s - 1) / s : -((-a) / s);
-            const int last = (h0 + b < extent ? h0 + b : extent) - 1;
-            const int hi = (last + pad) / s;
-            ok = hi - lo + 1 <= tile;
-        }
-        if (ok) return b;
-    }
-    return 0;
-}
-
-// Input gradient of a narrow-channel layer as ONE launch: the GEMM of dy against all taps on tiles
-// of 8 x 16 dy pixels (halo included) with the gather in its epilogue.  Nothing but the output is
-// written: the tap-major GEMM result never exists in memory.
-bool plan_dx_gather(const dcg_conv_desc& d, Plan& pl)
-{
-    if (!gather_enabled() || t_plan_x3) return false;
-    const int Jp = (d.kh * d.kw * 4 + 31) / 32 * 32;   // four accumulator columns per tap
-    if (Jp > 128) return false;                          // one N tile holds every tap
-    if (!plan_fwd(dx_gemm_desc(d, Jp), pl)) return false;
-    Params& p = pl.p;
-    if (p.narrow || p.n_tiles != 1) return false;
-    p.TW = 16; p.TH = 8; p.TN = 1;
-    const int bh = gather_block_extent(d.h, d.kh, d.stride_h, d.pad_top, p.TH, d.h);
-    const int bw = gather_block_extent(d.w, d.kw, d.stride_w, d.pad_left, p.TW, d.w);
-    if (bh <= 0 || bw <= 0) return false;
-    p.gather = 1;
-    p.g_H = d.h; p.g_W = d.w; p.g_C = d.c; p.g_KH = d.kh; p.g_KW = d.kw;
-    p.g_sh = d.stride_h; p.g_sw = d.stride_w; p.g_pt = d.pad_top; p.g_pl = d.pad_left;
-    p.g_bh = bh; p.g_bw = bw;
-    p.tiles_w = (d.w + bw - 1) / bw; p.tiles_h = (d.h + bh - 1) / bh; p.tiles_n = d.n;
-    p.splits = 1; p.pair = 0;
-    p.o_store = d.kh * d.kw * 4;   // accumulator columns beyond the last tap are padding
-    pl.grid = p.tiles_w * p.tiles_h * p.tiles_n;
-    pl.Jp = Jp;
-    pl.k2_bytes = (size_t)d.o * Jp * sizeof(float);
-    pl.ycol_bytes = 0;
-    finish_plan(pl);
-    pl.ws_bytes = pl.k2_off() + align_up(pl.k2_bytes, 256);
-    return true;
-}
-
 bool plan_dx(const dcg_conv_desc& d, Plan& pl)
 {
     if (d.c <= 4 && d.o % 32 == 0 && d.stride_h <= d.kh && d.stride_w <= d.kw) {
-        if (plan_dx_gather(d, pl)) return true;
-        pl = Plan{};
         const int Jp = (d.kh * d.kw * 4 + 31) / 32 * 32;   // four columns per tap
         pl.Jp = Jp;
         pl.k2_bytes = (size_t)d.o * Jp * sizeof(float);
@@ -1574,7 +1294,6 @@ bool plan_dx(const dcg_conv_desc& d, Plan& pl)
     const int tiles = classes * p.tiles_w * p.tiles_h * p.tiles_n * p.n_tiles;
     const int min_taps = (d.kh / d.stride_h) * (d.kw / d.stride_w);
     p.splits = choose_splits(tiles, (min_taps < 1 ? 1 : min_taps) * p.kchunks);
-    maybe_pair(pl, tiles, p.tiles_w * p.tiles_h * p.tiles_n, 8);    // B: K-major rows, whole 8-row swizzle groups per half
     pl.grid = tiles * p.splits;
     finish_plan(pl);
     return true;
@@ -1661,19 +1380,17 @@ int launch_grid(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, i
         attr[na].val.programmaticStreamSerializationAllowed = 1;
         ++na;
     }
-    const int cluster = (p.pair ? 2 : 1) * (p.ext_finish ? 1 : p.splits);
-    if (cluster > 1) {
+    if (p.splits > 1 && !p.ext_finish) {
         attr[na].id = cudaLaunchAttributeClusterDimension;
-        attr[na].val.clusterDim.x = (unsigned)cluster;   // blockIdx.x = tile * cluster + rank: one cluster per (pair) tile
+        attr[na].val.clusterDim.x = (unsigned)p.splits;   // blockIdx.x = tile * splits + split: one cluster per tile
         attr[na].val.clusterDim.y = 1;
         attr[na].val.clusterDim.z = 1;
         ++na;
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    const cudaError_t err = p.x3 ? cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE, true, false>, ma, mb, p)
-                          : p.pair ? cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE, false, true>, ma, mb, p)
-                                   : cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE, false, false>, ma, mb, p);
+    const cudaError_t err = p.x3 ? cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE, true>, ma, mb, p)
+                                 : cudaLaunchKernelEx(&cfg, conv_tc_kernel<MODE, false>, ma, mb, p);
     if (err != cudaSuccess) return fail(DCG_ERR_CUDA, "conv_tc_kernel launch: %s", cudaGetErrorString(err));
     count_launch();
     return DCG_OK;
@@ -1686,11 +1403,9 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, Plan& pl, float* out, c
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(conv_tc_kernel<MODE, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+        attr_err = cudaFuncSetAttribute(conv_tc_kernel<MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
         if (attr_err == cudaSuccess)
-            attr_err = cudaFuncSetAttribute(conv_tc_kernel<MODE, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
-        if (attr_err == cudaSuccess && MODE != MODE_DK)
-            attr_err = cudaFuncSetAttribute(conv_tc_kernel<MODE, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+            attr_err = cudaFuncSetAttribute(conv_tc_kernel<MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
     });
     if (attr_err != cudaSuccess)
         return fail(DCG_ERR_CUDA, "cudaFuncSetAttribute(conv_tc_kernel): %s", cudaGetErrorString(attr_err));
@@ -1762,15 +1477,15 @@ int map_window(CUtensorMap* map, const float* xp, const dcg_conv_desc& d, const 
 // ---- prepared calls: plan + tensor maps, cached ------------------------------------------------------
 // Planning a convolution and encoding its two tensor maps costs the host ~10 us.  A training step
 // or the reference's Graph::run issues the same convolutions on the same buffers over and over, so
-// the result is kept per (device, operator, shape, operand addresses, scratch address, precision and
-// pair setting) in a small table; a hit leaves only the launch.
+// the result is kept per (device, operator, shape, operand addresses, scratch address, precision)
+// in a small table; a hit leaves only the launch.
 struct Prepared {
     Plan pl;
     CUtensorMap ma, mb;
 };
 
 struct CacheKey {
-    int dev, kind, x3, pairs;   // pairs: bit 0 CTA pairs, bit 1 fused gather (the switches a plan depends on)
+    int dev, kind, x3;
     dcg_conv_desc d;
     const void *a, *b, *ws;
     size_t ws_bytes;
@@ -1788,7 +1503,7 @@ size_t g_cache_next = 0;
 
 bool same_key(const CacheKey& u, const CacheKey& v)
 {
-    return u.dev == v.dev && u.kind == v.kind && u.x3 == v.x3 && u.pairs == v.pairs && u.a == v.a && u.b == v.b &&
+    return u.dev == v.dev && u.kind == v.kind && u.x3 == v.x3 && u.a == v.a && u.b == v.b &&
            u.ws == v.ws && u.ws_bytes == v.ws_bytes && std::memcmp(&u.d, &v.d, sizeof(dcg_conv_desc)) == 0;
 }
 
@@ -1814,10 +1529,10 @@ int build_fwd(const dcg_conv_desc& d, const float* x, const float* k, void* ws, 
         return encode_map(&pr.mb, k4, 4, dims, true, strides, box, es);
     }
     if ((st = map_act_4d(&pr.ma, x, d.n, d.h, d.w, d.c, p.TW, p.TH, p.TN, d.stride_w, d.stride_h))) return st;
-    // k [tap][c][o] as (o%32, c, tap, o/32), box (32, 32, 1, bn/32); a pair CTA loads half the chunks
+    // k [tap][c][o] as (o%32, c, tap, o/32), box (32, 32, 1, bn/32)
     const cuuint64_t dims[4] = {32, (cuuint64_t)d.c, (cuuint64_t)(d.kh * d.kw), (cuuint64_t)(d.o / 32)};
     const cuuint64_t strides[3] = {(cuuint64_t)d.o * 4, (cuuint64_t)d.c * d.o * 4, 128};
-    const cuuint32_t box[4] = {32, 32, 1, (cuuint32_t)(p.pair ? p.bn / 64 : p.bn / 32)};
+    const cuuint32_t box[4] = {32, 32, 1, (cuuint32_t)(p.bn / 32)};
     const cuuint32_t es[4] = {1, 1, 1, 1};
     return encode_map(&pr.mb, k, 4, dims, true, strides, box, es);
 }
@@ -1829,7 +1544,7 @@ int build_dx(const dcg_conv_desc& d, const float* dy, const float* k, void* ws, 
     const Params& p = pl.p;
     int st = map_act_4d(&pr.ma, dy, d.n, d.ho, d.wo, d.o, p.TW, p.TH, p.TN, 1, 1);
     if (st) return st;
-    if (pl.ycol_bytes || p.gather) {   // narrow-channel layer: GEMM over all taps, then (or fused with) the gather
+    if (pl.ycol_bytes) {   // narrow-channel layer: GEMM over all taps, then gather
         if (!ws || ws_bytes < pl.ws_bytes)
             return fail(DCG_ERR_WORKSPACE, "conv dx (tensor path, narrow input): workspace %zu < %zu bytes", ws_bytes, pl.ws_bytes);
         const float* k2 = reinterpret_cast<const float*>(static_cast<uint8_t*>(ws) + pl.k2_off());
@@ -1841,10 +1556,10 @@ int build_dx(const dcg_conv_desc& d, const float* dy, const float* k, void* ws, 
         const cuuint32_t es[4] = {1, 1, 1, 1};
         return encode_map(&pr.mb, k2, 4, dims, true, strides, box, es);
     }
-    // k [kh][kw][c][o] as (o, c, kw, kh), box (32 o, bn c, 1, 1); a pair CTA loads half the rows
+    // k [kh][kw][c][o] as (o, c, kw, kh), box (32 o, bn c, 1, 1)
     const cuuint64_t dims[4] = {(cuuint64_t)d.o, (cuuint64_t)d.c, (cuuint64_t)d.kw, (cuuint64_t)d.kh};
     const cuuint64_t strides[3] = {(cuuint64_t)d.o * 4, (cuuint64_t)d.c * d.o * 4, (cuuint64_t)d.kw * d.c * d.o * 4};
-    const cuuint32_t box[4] = {32, (cuuint32_t)(p.pair ? p.bn / 2 : p.bn), 1, 1};
+    const cuuint32_t box[4] = {32, (cuuint32_t)p.bn, 1, 1};
     const cuuint32_t es[4] = {1, 1, 1, 1};
     return encode_map(&pr.mb, k, 4, dims, false, strides, box, es);
 }
@@ -1880,7 +1595,7 @@ int prepared_call(int kind, const dcg_conv_desc& d, const void* a, const void* b
     CacheKey key;
     std::memset(&key, 0, sizeof(key));
     if (cudaGetDevice(&key.dev) != cudaSuccess) key.dev = -1;
-    key.kind = kind; key.x3 = t_plan_x3; key.pairs = (pairs_enabled() ? 1 : 0) | (gather_enabled() ? 2 : 0);
+    key.kind = kind; key.x3 = t_plan_x3;
     key.d = d; key.a = a; key.b = b; key.ws = ws; key.ws_bytes = ws_bytes;
     {
         std::lock_guard<std::mutex> lock(g_cache_mutex);
@@ -1943,12 +1658,6 @@ int conv_tc_dx(const dcg_conv_desc& d, const float* dy, const float* k, float* d
     int st = prepared_call(kConvDx, d, dy, k, ws, ws_bytes, pr);
     if (st) return st;
     Plan& pl = pr.pl;
-    if (pl.p.gather) {   // narrow-channel layer, one launch: GEMM over all taps with the gather in its epilogue
-        float* k2 = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + pl.k2_off());
-        launch_pdl(repack_k2_kernel, (d.o * pl.Jp + 255) / 256, 256, 0, stream, k, k2, d.kh * d.kw, d.c, pl.Jp, d.o);
-        DCG_LAUNCH_CHECK("repack_k2_kernel");
-        return launch<MODE_FWD>(pr.ma, pr.mb, pl, dx, ep, d.c, ws, ws_bytes, stream);
-    }
     if (pl.ycol_bytes) {   // narrow-channel layer: GEMM over all taps, then gather
         uint8_t* base = static_cast<uint8_t*>(ws);
         float* k2 = reinterpret_cast<float*>(base + pl.k2_off());
@@ -1986,15 +1695,12 @@ int conv_tc_dk(const dcg_conv_desc& d, const float* x, const float* dy, float* d
     return launch<MODE_DK>(pr.ma, pr.mb, pr.pl, dk, none, d.o, ws, ws_bytes, stream);
 }
 
-// wait_cycles: > 0 sets the limit, -1 restores the default, 0 leaves it; skip_stage / pairs: -2 leaves it.
-void conv_tc_set_gather(int mode) { g_gather_override.store(mode < 0 ? -1 : (mode != 0)); }
-
-void conv_tc_set_hooks(long long wait_cycles, int skip_stage, int pairs)
+// wait_cycles: > 0 sets the limit, -1 restores the default, 0 leaves it; skip_stage: -2 leaves it.
+void conv_tc_set_hooks(long long wait_cycles, int skip_stage)
 {
     if (wait_cycles > 0) g_wait_cycles.store(wait_cycles);
     else if (wait_cycles < 0) g_wait_cycles.store(default_wait_cycles());
     if (skip_stage != -2) g_test_skip_stage.store(skip_stage);
-    if (pairs != -2) g_pair_override.store(pairs);
 }
 
 // Reads (and clears) the device status word of the tensor-path kernels.  Synchronises the device.
@@ -2020,14 +1726,10 @@ extern "C" int dcg_device_status(void) { return dcg::conv_tc_device_status(nullp
 
 extern "C" void dcg_debug_set_wait_limit(long long sm_clocks)
 {
-    dcg::conv_tc_set_hooks(sm_clocks > 0 ? sm_clocks : -1, -2, -2);
+    dcg::conv_tc_set_hooks(sm_clocks > 0 ? sm_clocks : -1, -2);
 }
 
-extern "C" void dcg_debug_skip_stage(int stage) { dcg::conv_tc_set_hooks(0, stage < 0 ? -1 : stage, -2); }
-
-extern "C" void dcg_debug_set_pairs(int mode) { dcg::conv_tc_set_hooks(0, -2, mode < 0 ? -1 : (mode != 0)); }
-
-extern "C" void dcg_debug_set_gather(int mode) { dcg::conv_tc_set_gather(mode); }
+extern "C" void dcg_debug_skip_stage(int stage) { dcg::conv_tc_set_hooks(0, stage < 0 ? -1 : stage); }
 
 #ifdef DCG_TC_TRACING
 // Tuning aids of -DDCG_TC_TRACING builds, not part of the public header: copy the timelines recorded

@@ -542,6 +542,46 @@ extern "C" int dcg_add(const float* a, const float* b, float* out, size_t n, dcg
     return DCG_OK;
 }
 
+// ---- image decode: bytes -> [-1, 1] ---------------------------------------------------------
+// The reference scales every pixel on the host, per step (src/datasets/celeba.cu:29):
+//     img[j] = dbl_t(pixs[j]) / 127.5 - 1.;        (float -> double arithmetic -> float)
+// Doing it on the device lets the input pipeline copy one byte per value instead of four.  The
+// double-precision expression is kept, so the result is the reference's bit for bit.
+namespace dcg { namespace {
+__global__ void __launch_bounds__(kThreads) u8_to_unit_kernel(const unsigned char* __restrict__ in, float* __restrict__ out, size_t n)
+{
+    pdl_enter();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const size_t n16 = n / 16;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(in) + i);
+        const unsigned w[4] = {raw.x, raw.y, raw.z, raw.w};
+        float4* dst = reinterpret_cast<float4*>(out) + 4 * i;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            float4 v;
+            v.x = (float)((double)(float)(w[q] & 0xffu) / 127.5 - 1.);
+            v.y = (float)((double)(float)((w[q] >> 8) & 0xffu) / 127.5 - 1.);
+            v.z = (float)((double)(float)((w[q] >> 16) & 0xffu) / 127.5 - 1.);
+            v.w = (float)((double)(float)(w[q] >> 24) / 127.5 - 1.);
+            dst[q] = v;
+        }
+    }
+    for (size_t i = n16 * 16 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        out[i] = (float)((double)(float)in[i] / 127.5 - 1.);
+}
+} }
+
+extern "C" int dcg_u8_to_unit(const unsigned char* in, float* out, size_t n, dcg_stream_t stream)
+{
+    DCG_CHECK_ARG(in && out, "dcg_u8_to_unit: null pointer");
+    DCG_CHECK_ARG(aligned16(in) && aligned16(out), "dcg_u8_to_unit: buffers must be 16-byte aligned");
+    if (n == 0) return DCG_OK;
+    launch_pdl(u8_to_unit_kernel, stream_grid((n + 15) / 16), kThreads, 0, as_stream(stream), in, out, n);
+    DCG_LAUNCH_CHECK("u8_to_unit_kernel");
+    return DCG_OK;
+}
+
 extern "C" int dcg_update(const float* dv, float* out, const float* coeff, size_t n,
                           dcg_stream_t stream)
 {

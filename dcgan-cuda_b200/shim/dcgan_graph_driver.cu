@@ -9,9 +9,9 @@
 //   dcgan_graph_driver gen   BATCH ITERS OUT [leaky|relu] [SEED]   generator forward only
 //   dcgan_graph_driver train BATCH ITERS OUT [leaky|relu] [SEED]   ITERS x (1 D update + 2 G updates)
 //
-// OUT receives a tensor archive: gen -> [g_out]; train -> [d_loss per iteration, g_loss per
-// iteration, the 10 generator variables (k0,b0,..,k3,b3,dense w,dense b), the 10 discriminator
-// variables].  One JSON line with the wall-clock milliseconds of every Graph::run group goes to stdout.
+// OUT receives a tensor archive: gen -> [g_out]; train -> [d_loss per iteration, g_loss of the
+// second G run per iteration, the 10 generator variables (k0,b0,..,k3,b3,dense w,dense b), the 10
+// discriminator variables, g_loss of the first G run per iteration].  One JSON line with the wall-clock milliseconds of every Graph::run group goes to stdout.
 #include <algorithm>
 #include <chrono>
 #include <cmath>
@@ -209,7 +209,7 @@ int main(int argc, char** argv)
         AdamOptimizer g_adam(0.0002, 0.5), d_adam(0.0002, 0.5);
         auto g_opti = g_adam.minimize(g_loss, g_vars);
         auto d_opti = d_adam.minimize(d_loss, d_vars);
-        tocha::Tensor dl = tocha::Tensor::f32(iters), gl = tocha::Tensor::f32(iters);
+        tocha::Tensor dl = tocha::Tensor::f32(iters), gl = tocha::Tensor::f32(iters), gl_first = tocha::Tensor::f32(iters);
         for (int it = 0; it < iters; ++it) {
             dbl_t d_loss_val = 0, g_loss_val = 0;
             const double t0 = now_ms();
@@ -220,10 +220,12 @@ int main(int argc, char** argv)
                        {z, {z_h.data(), ops::Shape({B, kZ})}},
                        {x, {x_h.data(), ops::Shape({B, 64, 64, 3})}}},
                       {nullptr, &d_loss_val});
-            for (int k = 0; k < 2; ++k)
+            for (int k = 0; k < 2; ++k) {
                 graph.run({g_opti, g_loss},
                           {{logits1, {ones.data(), ops::Shape({B, 1})}}, {z, {z_h.data(), ops::Shape({B, kZ})}}},
                           {nullptr, &g_loss_val});
+                if (k == 0) reinterpret_cast<dbl_t*>(gl_first.data)[it] = g_loss_val;
+            }
             ms.push_back(now_ms() - t0);
             reinterpret_cast<dbl_t*>(dl.data)[it] = d_loss_val;
             reinterpret_cast<dbl_t*>(gl.data)[it] = g_loss_val;
@@ -232,6 +234,7 @@ int main(int argc, char** argv)
         out.add(gl);
         for (auto v : g_vars) add_var(out, v);
         for (auto v : d_vars) add_var(out, v);
+        out.add(gl_first);
     }
     out.save(out_path);
 

@@ -194,6 +194,8 @@ class Trainer:
                 "xs": [torch.empty((B, 64, 64, 3), device=dev) for _ in range(2)],
                 "zs": [torch.empty((B, 100), device=dev) for _ in range(2)],
                 "hx": [torch.empty((B, 64, 64, 3)).pin_memory() for _ in range(2)],
+                "xs8": [torch.empty((B, 64, 64, 3), dtype=torch.uint8, device=dev) for _ in range(2)],
+                "hx8": [torch.empty((B, 64, 64, 3), dtype=torch.uint8).pin_memory() for _ in range(2)],
                 "hz": [torch.empty((B, 100)).pin_memory() for _ in range(2)],
                 "copied": [torch.cuda.Event() for _ in range(2)],    # slot's host -> device copy done
                 "consumed": [torch.cuda.Event() for _ in range(2)],  # slot read by its iteration
@@ -208,7 +210,9 @@ class Trainer:
         copy of x_host [B,64,64,3] and z_host [B,100] (HOST arrays; pinned torch tensors are copied
         from directly, anything else is staged through pinned memory first) runs on a copy stream
         and overlaps the iteration submitted before; the losses are read back into pinned memory.
-        At most _RING iterations may be outstanding."""
+        x_host may also hold uint8 pixel values: the bytes are copied as they are (a quarter of the
+        traffic) and scaled to [-1, 1] on the device, bit for bit what celeba::load computes on the
+        host (src/datasets/celeba.cu:29).  At most _RING iterations may be outstanding."""
         p = self._pipeline()
         n = p["n"]
         p["n"] = n + 1
@@ -218,19 +222,27 @@ class Trainer:
         if n >= 2:
             p["consumed"][slot].synchronize()   # the slot's previous iteration has taken its inputs
         xh, zh = torch.as_tensor(x_host), torch.as_tensor(z_host)
-        if not (xh.is_pinned() and xh.dtype == torch.float32 and xh.is_contiguous()):
+        as_bytes = xh.dtype == torch.uint8
+        if as_bytes:
+            if not (xh.is_pinned() and xh.is_contiguous()):
+                p["hx8"][slot].copy_(xh.reshape(p["hx8"][slot].shape))
+                xh = p["hx8"][slot]
+        elif not (xh.is_pinned() and xh.dtype == torch.float32 and xh.is_contiguous()):
             p["hx"][slot].copy_(xh.reshape(p["hx"][slot].shape))
             xh = p["hx"][slot]
         if not (zh.is_pinned() and zh.dtype == torch.float32 and zh.is_contiguous()):
             p["hz"][slot].copy_(zh.reshape(p["hz"][slot].shape))
             zh = p["hz"][slot]
         with torch.cuda.stream(p["copy"]):
-            p["xs"][slot].copy_(xh.reshape(p["xs"][slot].shape), non_blocking=True)
+            (p["xs8"] if as_bytes else p["xs"])[slot].copy_(xh.reshape(p["xs"][slot].shape), non_blocking=True)
             p["zs"][slot].copy_(zh.reshape(p["zs"][slot].shape), non_blocking=True)
             p["copied"][slot].record()
         with self._on_stream():
             self.stream.wait_event(p["copied"][slot])
-            self.x.copy_(p["xs"][slot], non_blocking=True)   # device -> device, a few microseconds
+            if as_bytes:   # decode on the device, straight into the trainer's input tensor
+                check(lib.dcg_u8_to_unit(p["xs8"][slot].data_ptr(), self.x.data_ptr(), self.x.numel(), self.stream.cuda_stream))
+            else:
+                self.x.copy_(p["xs"][slot], non_blocking=True)   # device -> device, a few microseconds
             self.z.copy_(p["zs"][slot], non_blocking=True)
             p["consumed"][slot].record()
             self._step()
@@ -269,6 +281,7 @@ class Trainer:
             check(lib.dcg_trainer_load(self._h, str(path).encode()))
 
     h2d_bytes_per_step = property(lambda self: self.batch * (64 * 64 * 3 + 100) * 4)
+    h2d_bytes_per_step_u8 = property(lambda self: self.batch * (64 * 64 * 3 + 100 * 4))
     d2h_bytes_per_step = property(lambda self: 8)
 
     def launches_per_step(self):

@@ -159,6 +159,11 @@ int dcg_rowsum(const float* a, float* out, size_t rows, size_t cols, dcg_stream_
 /* out = a + b.  Replaces gpu::kernel_add (src/gpu/sum.cu:206-214,251-257). */
 int dcg_add(const float* a, const float* b, float* out, size_t n, dcg_stream_t stream);
 
+/* Image decode on the device: out[i] = (float)((double)in[i] / 127.5 - 1.), the scaling of pixel
+ * bytes to [-1, 1] that celeba::load does on the host for every batch (src/datasets/celeba.cu:16-34),
+ * bit for bit.  Both buffers 16-byte aligned. */
+int dcg_u8_to_unit(const unsigned char* in, float* out, size_t n, dcg_stream_t stream);
+
 /* out += coeff[0] * dv, coeff a DEVICE scalar.
  * Replaces gpu::kernel_update (src/gpu/update.cu:13-21,58-63). */
 int dcg_update(const float* dv, float* out, const float* coeff, size_t n, dcg_stream_t stream);
@@ -441,16 +446,9 @@ const char* dcg_last_error(void);
  *  dcg_debug_set_wait_limit  limit of every bounded barrier wait in SM clocks (<= 0 restores ~1 s);
  *  dcg_debug_skip_stage      the TMA producer leaves pipeline stage `stage` of every tile out (< 0: never), so
  *                            that a consumer's wait runs into the limit: the kernel then records the failure,
- *                            still terminates, and dcg_device_status() returns DCG_ERR_DEVICE;
- *  dcg_debug_set_pairs       1 / 0 force CTA pairs (tcgen05 cta_group::2 tiles of 256 rows) on / off for the
- *                            shapes that allow them, < 0 follows the DCG_TC_PAIR environment variable. */
+ *                            still terminates, and dcg_device_status() returns DCG_ERR_DEVICE. */
 void dcg_debug_set_wait_limit(long long sm_clocks);
 void dcg_debug_skip_stage(int stage);
-void dcg_debug_set_pairs(int mode);
-/*  dcg_debug_set_gather      1 / 0: input gradient of a layer with <= 4 input channels as ONE launch (the gather of
- *                            the tap products fused into the GEMM's epilogue) or as GEMM + gather kernel; < 0
- *                            follows the DCG_TC_GATHER environment variable (default on).  Same bits either way. */
-void dcg_debug_set_gather(int mode);
 /* Library version and the architecture the kernels were built for ("sm_100a"). */
 const char* dcg_build_info(void);
 /* Kernels launched by this library since it was loaded (all contexts, all threads). */

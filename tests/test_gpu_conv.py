@@ -329,7 +329,6 @@ def test_bounded_wait_runs_out_and_the_context_survives(pkg, dev):
     xd, kd = torch.from_numpy(x).to(dev), torch.from_numpy(k).to(dev)
     assert L.dcg_device_status() == 0
     try:
-        L.dcg_debug_set_pairs(0)
         L.dcg_debug_set_wait_limit(2_000_000)   # ~1 ms of SM clocks
         L.dcg_debug_skip_stage(3)
         F.conv2d_fwd(xd, kd, precision=pkg.PREC_TF32)
@@ -337,7 +336,6 @@ def test_bounded_wait_runs_out_and_the_context_survives(pkg, dev):
     finally:
         L.dcg_debug_skip_stage(-1)
         L.dcg_debug_set_wait_limit(0)
-        L.dcg_debug_set_pairs(-1)
     assert L.dcg_device_status() == pkg._lib.ERR_DEVICE
     assert b"gave up waiting" in L.dcg_last_error()
     assert L.dcg_device_status() == 0           # reading clears the word
@@ -347,66 +345,3 @@ def test_bounded_wait_runs_out_and_the_context_survives(pkg, dev):
     y32 = F.conv2d_fwd(xd, kd, precision=pkg.PREC_FP32)   # bit-equal to the oracle (test_conv_fwd_dx_dk)
     torch.cuda.synchronize()
     assert (y - y32).abs().max().item() <= TF32_TOL * y32.abs().max().item()
-
-
-@pytest.mark.parametrize("layer", [(64, 32, 64, 128), (64, 16, 128, 256), (64, 8, 256, 512), (128, 16, 128, 256),
-                                   (6, 16, 128, 256), (2, 32, 64, 128)])
-def test_cta_pairs_match_single_cta_tiles(pkg, dev, layer):
-    """CTA pairs (one tcgen05.mma.cta_group::2 over two CTAs' A halves and B halves) compute the same
-    tiles as single CTAs: forward and input gradient, with and without K partitions, against the
-    fp32 path (1e-2 * max|ref|) and against the single-CTA tensor path (same operand rounding, the K
-    partitions may be cut differently: 1e-4 * max), and deterministic."""
-    F, L = pkg.functional, pkg.lib
-    B, H, C, O = layer
-    g = torch.Generator(device="cpu").manual_seed(61)
-    x = (torch.rand((B, H, H, C), generator=g) * 2 - 1).to(dev)
-    k = (torch.randn((5, 5, C, O), generator=g) * 0.02).to(dev)
-    dy = (torch.rand((B, H // 2, H // 2, O), generator=g) * 2 - 1).to(dev)
-    bias = torch.randn((O,), generator=g).to(dev)
-    ref = (F.conv2d_fwd(x, k, precision=pkg.PREC_FP32) + bias, F.conv2d_dx(dy, k, (H, H), precision=pkg.PREC_FP32))
-    run = lambda: (F.conv2d_fwd(x, k, epilogue=F.make_epilogue(bias=bias)), F.conv2d_dx(dy, k, (H, H)))
-    try:
-        L.dcg_debug_set_pairs(0)
-        single = run()
-        L.dcg_debug_set_pairs(1)
-        L.dcg_debug_set_wait_limit(40_000_000)   # a handshake that never completes costs ~20 ms, not seconds
-        a, b = run(), run()
-        torch.cuda.synchronize()
-    finally:
-        L.dcg_debug_set_pairs(-1)
-        L.dcg_debug_set_wait_limit(0)
-    assert L.dcg_device_status() == 0, L.dcg_last_error()
-    for name, r, s1, u, v in zip(("fwd+bias", "dx"), ref, single, a, b):
-        scale = r.abs().max().item()
-        assert (r - u).abs().max().item() <= TF32_TOL * scale, name
-        assert (s1 - u).abs().max().item() <= 1e-4 * scale, name
-        assert torch.equal(u, v), name
-
-
-@pytest.mark.parametrize("shape", [(3, 20, 12, 1, 3, 32, 1), (2, 16, 16, 4, 5, 96, 2), (5, 32, 32, 2, 4, 64, 2),
-                                   (2, 10, 14, 3, 5, 160, 2), (64, 64, 64, 3, 5, 64, 2), (3, 9, 7, 3, 5, 32, 2)])
-def test_fused_gather_equals_gemm_plus_gather(pkg, dev, shape):
-    """Input gradient of a layer with <= 4 input channels: the one-launch form (tiles of dy with a
-    halo, the tap products summed per output pixel inside the GEMM's epilogue) gives the same bits as
-    the GEMM that writes the tap-major products to scratch followed by the gather kernel - same
-    products, added in the same (kernel row, kernel column) order - with bias and tanh fused in."""
-    F, L = pkg.functional, pkg.lib
-    N, H, W, C, K, O, s = shape
-    Ho, Wo = (H + s - 1) // s, (W + s - 1) // s
-    g = torch.Generator(device="cpu").manual_seed(71)
-    dy = (torch.rand((N, Ho, Wo, O), generator=g) * 2 - 1).to(dev)
-    k = (torch.randn((K, K, C, O), generator=g) * 0.05).to(dev)
-    bias = torch.randn((C,), generator=g).to(dev)
-    outs = []
-    try:
-        for mode in (0, 1):
-            L.dcg_debug_set_gather(mode)
-            before = pkg.launches_total()
-            dx = F.conv2d_dx(dy, k, (H, W), (s, s), epilogue=F.make_epilogue(bias=bias, act=pkg.ACT_TANH))
-            torch.cuda.synchronize()
-            outs.append((dx, pkg.launches_total() - before))
-    finally:
-        L.dcg_debug_set_gather(-1)
-    assert L.dcg_device_status() == 0
-    assert torch.equal(outs[0][0], outs[1][0])
-    assert outs[1][1] == 2 and outs[0][1] == 3     # weight repack + GEMM (+ gather kernel)

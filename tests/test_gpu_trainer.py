@@ -282,3 +282,52 @@ def test_discriminator_forward_backward_matches_cpu_model(pkg, dev, orc):
         for i in range(10):
             assert err(tr.tensor("d_gradb%d" % i).cpu().numpy(), gr[i].reshape(-1)) <= tol, i
         tr.close()
+
+
+def test_pipelined_submit_equals_blocking_steps(pkg, dev):
+    """submit_host / result with several iterations in flight (the host -> device copies of iteration
+    i+1 overlap the compute of iteration i, losses are collected with a lag) gives the same losses and
+    parameters as blocking step_host calls on the same host batches."""
+    B = 4
+    g = torch.Generator(device="cpu").manual_seed(81)
+    xs = [(torch.rand((B, 64, 64, 3), generator=g) * 2 - 1).pin_memory() for _ in range(7)]
+    zs = [(torch.rand((B, 100), generator=g) * 2 - 1).numpy() for _ in range(7)]   # pinned and pageable sources
+    a = pkg.Trainer(batch=B, precision=pkg.PREC_TF32, seed=77)
+    la = [a.step_host(x, z) for x, z in zip(xs, zs)]
+    b = pkg.Trainer(batch=B, precision=pkg.PREC_TF32, seed=77)
+    tickets, lb = [], []
+    for x, z in zip(xs, zs):
+        tickets.append(b.submit_host(x, z))
+        if len(tickets) > 3:
+            lb.append(b.result(tickets.pop(0)))
+    lb += [b.result(t) for t in tickets]
+    torch.cuda.synchronize()
+    assert la == lb
+    assert torch.equal(a.tensor("d_params"), b.tensor("d_params")) and torch.equal(a.tensor("g_params"), b.tensor("g_params"))
+    a.close()
+    b.close()
+
+
+def test_uint8_images_are_decoded_on_the_device_like_the_reference(pkg, dev):
+    """celeba::load scales bytes to [-1, 1] on the host: img = float(p) / 127.5 - 1. in double, stored
+    as float (src/datasets/celeba.cu:29).  submit_host with uint8 images copies the bytes and runs that
+    expression on the device: all 256 values bit-equal, and a step fed with bytes equals a step fed
+    with the host-scaled floats."""
+    import ctypes
+    vals = torch.arange(256, dtype=torch.uint8).repeat(4)            # 1024 values, 16-byte multiples
+    want = torch.from_numpy((vals.numpy().astype(np.float32).astype(np.float64) / 127.5 - 1.).astype(np.float32))
+    src, dst = vals.to(dev), torch.empty(vals.numel(), device=dev)
+    pkg._lib.check(pkg.lib.dcg_u8_to_unit(src.data_ptr(), dst.data_ptr(), src.numel(), torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert torch.equal(dst.cpu(), want)
+    B = 4
+    g = torch.Generator(device="cpu").manual_seed(91)
+    px = torch.randint(0, 256, (B, 64, 64, 3), generator=g, dtype=torch.uint8)
+    z = (torch.rand((B, 100), generator=g) * 2 - 1).numpy()
+    xf = torch.from_numpy((px.numpy().astype(np.float32).astype(np.float64) / 127.5 - 1.).astype(np.float32))
+    a = pkg.Trainer(batch=B, precision=pkg.PREC_TF32, seed=77)
+    b = pkg.Trainer(batch=B, precision=pkg.PREC_TF32, seed=77)
+    assert a.step_host(px, z) == b.step_host(xf, z)
+    assert torch.equal(a.tensor("g_params"), b.tensor("g_params"))
+    a.close()
+    b.close()

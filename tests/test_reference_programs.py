@@ -199,11 +199,20 @@ def test_generator_forward_through_reference_graph(dev, tmp_path):
 @pytest.mark.gpu
 def test_training_iteration_through_reference_graph(dev, tmp_path):
     """One full iteration of dcgan/main.cu:378-391 (D update, two G updates, Adam) at batch 1 driven by
-    the reference's Graph::run, autodiff and AdamOptimizer: RT_MODE=CPU against RT_MODE=GPU.  After
-    one Adam step every parameter has moved by about lr in the direction of its gradient's sign, so
-    the fp32 path is compared on losses (1e-5) and on the parameters (a sign flip of a near-zero
-    gradient moves a weight by 2 lr: the bound is 2.5 lr = 5e-4 absolute and 99.9 % of the entries
-    within 1e-6); the TF32 path on the losses (1e-2 relative)."""
+    the reference's Graph::run, autodiff and AdamOptimizer: RT_MODE=CPU against RT_MODE=GPU.
+
+    What is comparable: everything up to and including the first G run's loss - d_loss, the
+    discriminator's Adam update, the generator / discriminator forward passes after it.  The
+    generator's own gradients are not: the reference's CPU code evaluates conv2d_transpose_input_grad /
+    conv2d_transpose_kernel_grad with zero padding (src/cpu/ops.hxx:808-902), which is the adjoint of
+    its conv2d_transpose only without padding, while its GPU handlers - and this library - derive the
+    padding from the sizes (src/gpu/conv2d.cu:229-236,281-288).  For the 5x5 SAME generator layers the
+    reference's two modes therefore disagree with each other after the first generator update, and
+    the second G run's loss and the generator's variables are only reported.
+
+    fp32 path: losses to 1e-5; after one Adam step every discriminator weight has moved by about lr in
+    the direction of its gradient's sign, so a sign flip of a near-zero gradient moves a weight by
+    2 lr = 4e-4: the bound is 5e-4 absolute and 99.9 % of the entries within 1e-6.  TF32: losses 1e-2."""
     progs = _prebuilt()
     if "dcgan_graph_driver" not in progs:
         pytest.skip("reference programs were not built")
@@ -215,12 +224,16 @@ def test_training_iteration_through_reference_graph(dev, tmp_path):
         json.loads(line.strip().splitlines()[-1])
         outs[tag] = load_archive(str(out))
     ref = outs["cpu"]
-    assert len(ref) == 22
+    assert len(ref) == 23
+    report = {tag: {"d_loss": float(outs[tag][0][0]), "g_loss_first": float(outs[tag][22][0]), "g_loss_second": float(outs[tag][1][0]),
+                    "param_maxdiff": [float(np.abs(g - r).max()) for r, g in zip(ref[2:22], outs[tag][2:22])]}
+              for tag in outs}
+    print("training iteration through the reference graph:", json.dumps(report))
     for tag, loss_tol in (("fp32", 1e-5), ("tf32", 1e-2)):
         got = outs[tag]
-        for i in (0, 1):
-            assert abs(float(got[i][0]) - float(ref[i][0])) <= loss_tol * max(1.0, abs(float(ref[i][0]))), (tag, i)
-    for r, g in zip(ref[2:], outs["fp32"][2:]):
+        for i in (0, 22):
+            assert abs(float(got[i][0]) - float(ref[i][0])) <= loss_tol * max(1.0, abs(float(ref[i][0]))), (tag, i, report)
+    for r, g in zip(ref[12:22], outs["fp32"][12:22]):   # the discriminator's 10 variables
         diff = np.abs(g - r)
-        assert float(diff.max()) <= 5e-4
-        assert float((diff <= 1e-6).mean()) >= 0.999
+        assert float(diff.max()) <= 5e-4, report
+        assert float((diff <= 1e-6).mean()) >= 0.999, report
