@@ -304,7 +304,7 @@ def run_ours(args, rank, local_rank, world):
     assert world == args.gpus, "launch with torchrun --nproc-per-node equal to --gpus"
 
     precision = {"tf32": pkg.PREC_TF32, "3xtf32": pkg.PREC_3XTF32, "fp32": pkg.PREC_FP32}[args.precision]
-    trainer = pkg.Trainer(batch=BATCH, precision=precision, fuse=True, seed=234, world=world)
+    trainer = pkg.Trainer(batch=BATCH, precision=precision, fuse=True, seed=234, world=world, comm=args.comm)
     batches = synthetic_batches(rank, 4)
     trainer.x.copy_(batches[0][0])
     trainer.z.copy_(batches[0][1])
@@ -410,13 +410,15 @@ def run_ours(args, rank, local_rank, world):
             us[name] = 1e3 * max_over_ranks(a0.elapsed_time(a1)) / 20
         dp_extra["allreduce_us"] = us   # back to back, outside the timed region: an upper bound on what a step exposes
         dp_extra["allreduce_bytes"] = {"d": trainer.d_grads.numel() * 4, "g": trainer.g_grads.numel() * 4}
-        dp_extra["comm"] = "nccl behind the C ABI (dcg_dp_*), version %s" % (trainer.dp_info() or (0, 0, "?"))[2]
+        info = trainer.dp_info()
+        dp_extra["comm"] = ("nccl behind the C ABI (dcg_dp_*), version %s; whole iteration = one CUDA graph" % info[2]) if info \
+            else "torch.distributed all_reduce between the library's phases"
 
     # ---- BASELINE configs[0] and configs[1] at batch 64 (device-timed, inputs resident) ---------------
-    def timed(fn, reps):
+    def timed(fn, reps):   # rank 0 only: no collective in here
         for _ in range(3):
             fn()
-        barrier()
+        torch.cuda.synchronize()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
         for _ in range(reps):
@@ -553,7 +555,10 @@ def run_sweep(args):
     tf32_peak = peaks["bf16_tflops"] / 2.0
     flush = torch.empty(256 * 2 ** 20 // 4, device=dev)
     rows = []
-    for B in args.sweep_batches:
+    precs = {"tf32": pkg.PREC_TF32, "3xtf32": pkg.PREC_3XTF32, "fp32": pkg.PREC_FP32}
+    for prec_name in args.sweep_precisions:
+      prec = precs[prec_name]
+      for B in args.sweep_batches:
         for name, H, C, O in (("D0/G3", 64, 3, 64), ("D1/G2", 32, 64, 128), ("D2/G1", 16, 128, 256),
                               ("D3/G0", 8, 256, 512)):
             if args.sweep_layers and name.split("/")[0] not in args.sweep_layers:
@@ -563,8 +568,15 @@ def run_sweep(args):
             dy = torch.rand(B, H // 2, H // 2, O, device=dev) * 2 - 1
             y, dx, dk = torch.empty_like(dy), torch.empty_like(x), torch.empty_like(k)
             flops = 2.0 * B * (H // 2) ** 2 * 25 * C * O
-            ops = (("fwd", lambda: F.conv2d_fwd(x, k, out=y)), ("dx", lambda: F.conv2d_dx(dy, k, (H, H), out=dx)),
-                   ("dk", lambda: F.conv2d_dk(x, dy, (5, 5), out=dk)))
+            # operand sets to rotate through for the back-to-back timing: together larger than L2
+            n_sets = max(2, min(16, -(-(256 * 2 ** 20) // ((x.numel() + dy.numel()) * 4))))
+            xs, dys = [x] + [x.clone() for _ in range(n_sets - 1)], [dy] + [dy.clone() for _ in range(n_sets - 1)]
+            b2b = {"fwd": lambda i: F.conv2d_fwd(xs[i], k, out=y, precision=prec),
+                   "dx": lambda i: F.conv2d_dx(dys[i], k, (H, H), out=dx, precision=prec),
+                   "dk": lambda i: F.conv2d_dk(xs[i], dys[i], (5, 5), out=dk, precision=prec)}
+            ops = (("fwd", lambda: F.conv2d_fwd(x, k, out=y, precision=prec)),
+                   ("dx", lambda: F.conv2d_dx(dy, k, (H, H), out=dx, precision=prec)),
+                   ("dk", lambda: F.conv2d_dk(x, dy, (5, 5), out=dk, precision=prec)))
             for op, fn in ops:
                 if args.sweep_ops and op not in args.sweep_ops:
                     continue
@@ -580,14 +592,30 @@ def run_sweep(args):
                     torch.cuda.synchronize()
                     times.append(s.elapsed_time(t))
                 med = statistics.median(times)
-                tflops = flops / (med * 1e-3) / 1e12
-                rows.append({"layer": name, "op": op, "batch": B, "us": med * 1e3, "tflops": tflops,
-                             "frac_tf32_peak": tflops / tf32_peak})
-                if int(os.environ.get("DCG_TC_DEBUG", "0") or 0) & 8:
+                # back to back: n_calls launches between two events, operands rotating through the sets (so they
+                # come from HBM, not L2), which takes the launch latency of an isolated call out of the figure
+                n_calls = max(16, n_sets)
+                reps = []
+                for _ in range(5):
+                    s, t = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize()
+                    s.record()
+                    for i in range(n_calls):
+                        b2b[op](i % n_sets)
+                    t.record()
+                    torch.cuda.synchronize()
+                    reps.append(s.elapsed_time(t) / n_calls)
+                bb = statistics.median(reps)
+                tflops = flops / (bb * 1e-3) / 1e12
+                rows.append({"precision": prec_name, "layer": name, "op": op, "batch": B, "us_isolated": med * 1e3,
+                             "us": bb * 1e3, "tflops": tflops, "frac_tf32_peak": tflops / tf32_peak})
+                if int(os.environ.get("DCG_TC_DEBUG", "0") or 0) & 8 and hasattr(pkg.lib, "dcg_debug_cta_trace"):
                     rows[-1]["cta_timeline_us"] = cta_timeline(pkg)
     pkg._lib.check(pkg.lib.dcg_device_status())
     print(json.dumps({"sweep": rows, "tf32_peak_tflops": tf32_peak, "peak_source": peaks["_source"],
-                      "timing": "median of %d, CUDA events, 256 MB L2 flush before each" % args.sweep_iters}))
+                      "timing": "us: back to back - 16+ launches between two CUDA events, operands rotating through sets "
+                                "that together exceed L2, median of 5; us_isolated: one launch between two events, median of "
+                                "%d, 256 MB L2 flush before each (includes the launch latency)" % args.sweep_iters}))
 
 
 def main():
@@ -597,6 +625,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--precision", choices=["tf32", "3xtf32", "fp32"], default="tf32")
+    ap.add_argument("--comm", choices=["abi", "torch"], default="abi",
+                    help="N > 1: communicator behind the C ABI (default) or torch.distributed collectives")
+    ap.add_argument("--sweep-precisions", nargs="+", default=["tf32"], choices=["tf32", "3xtf32", "fp32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra-configs", action="store_true", help="skip the configs[0] / configs[1] timings")
     ap.add_argument("--cpu-seconds", type=float, default=20.0)
