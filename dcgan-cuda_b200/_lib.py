@@ -70,7 +70,7 @@ class ProfileRow(ctypes.Structure):
 class TrainerConfig(ctypes.Structure):
     _fields_ = [("batch", c_int), ("world", c_int), ("precision", c_int), ("fuse", c_int),
                 ("g_leaky", c_int), ("lr", c_float), ("beta1", c_float), ("beta2", c_float),
-                ("eps", c_float), ("seed", ctypes.c_uint64)]
+                ("eps", c_float), ("seed", ctypes.c_uint64), ("share_g_forward", c_int)]
 
 
 DP_ID_BYTES = 128   # DCG_DP_ID_BYTES
@@ -136,6 +136,7 @@ SIGNATURES = {
     "dcg_trainer_context": (_P, [_P]),
     "dcg_context_profile_begin": (c_int, [_P]),
     "dcg_context_profile_end": (c_int, [_P, ctypes.POINTER(ProfileRow), c_int, ctypes.POINTER(c_int)]),
+    "dcg_trainer_step_mode": (c_int, [_P]),
     "dcg_trainer_step_launches": (ctypes.c_uint64, [_P]),
     "dcg_trainer_arena_bytes": (c_size_t, [_P]),
     "dcg_device_status": (c_int, []),

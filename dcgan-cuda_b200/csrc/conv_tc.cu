@@ -101,6 +101,13 @@ struct Params {
     int n_tiles;                  // BN-column tiles along the N channel axis
     int bn;                       // accumulator columns, multiple of 16, <= 256
     int splits;                   // K partitions of a tile = CTAs per cluster (<= 8)
+    // DX with operand re-use across taps ("halo"): per 32-channel K chunk ONE window of dy - the
+    // 8 x TH x TN pixel tile plus the rows / columns its taps reach, [h][n][16 w][32 c] - is loaded and
+    // every tap of the parity class multiplies a shifted view of it (shared-memory descriptor start
+    // address moved by whole pixels), instead of one 16 KB tile per tap.  Only B streams per tap.
+    int halo;                     // 0: off
+    int halo_groups;              // windows in flight
+    int halo_group_bytes;         // 16 * TN * (TH + max row taps - 1) * 128, a multiple of 1024
     int skip_stage;               // test hook: the producer leaves this pipeline stage out (-1: never)
     long long wait_cycles;        // SM clocks after which a barrier wait gives up
     int kchunks;                  // 32-wide chunks along the contracted channel axis (FWD: C, DX: O)
@@ -296,6 +303,13 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_b
     return d;
 }
 
+// A K-major, 128-byte-swizzled tile whose first row does not sit on a 1024-byte boundary: the
+// swizzle phase of that row ((address >> 7) & 7) goes into the descriptor's base-offset field.
+__device__ __forceinline__ uint64_t with_base_offset(uint64_t desc, uint32_t phase)
+{
+    return desc | ((uint64_t)(phase & 7u) << 49);
+}
+
 // Instruction descriptor: fp32 accumulator, TF32 operands, operand majors, N and M.
 __device__ __forceinline__ uint32_t make_idesc(int a_mn_major, int b_mn_major, int n, int m)
 {
@@ -316,7 +330,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int b_stage_bytes = p.bn * BK * 4;
     const long long wait_limit = p.wait_cycles;
     const uint32_t a_base = smem_base;
-    const uint32_t b_base = a_base + (uint32_t)p.stages * A_STAGE_BYTES;
+    const bool halo = MODE == MODE_DX && !X3 && p.halo;
+    const uint32_t b_base = a_base + (halo ? (uint32_t)(p.halo_groups * p.halo_group_bytes) : (uint32_t)p.stages * A_STAGE_BYTES);
     // 3xTF32: residual tiles (operand minus its TF32 part) of every stage follow the operand tiles
     const uint32_t as_base = b_base + (uint32_t)p.stages * b_stage_bytes;
     const uint32_t bs_base = as_base + (uint32_t)p.stages * A_STAGE_BYTES;
@@ -327,6 +342,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t resid_bar = bar_base + 16u * p.stages;     // 3xTF32: residual tiles of the stage are written
     const uint32_t tmem_full_bar = bar_base + 24u * p.stages;
     const uint32_t tmem_slot = tmem_full_bar + 8u;
+    const uint32_t gfull_bar = tmem_full_bar + 16u;               // halo: window g has landed / has been read
+    const uint32_t gempty_bar = gfull_bar + 8u * 4u;
     uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
@@ -338,6 +355,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_init(empty_bar + 8u * s, 1);
             mbar_init(resid_bar + 8u * s, kEpi);
         }
+        if (halo)
+            for (int g = 0; g < p.halo_groups; ++g) {
+                mbar_init(gfull_bar + 8u * g, 1);
+                mbar_init(gempty_bar + 8u * g, 1);
+            }
         mbar_init(tmem_full_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
@@ -390,8 +412,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (MODE == MODE_FWD) total_stages = p.narrow ? p.KH : p.KH * p.KW * p.kchunks;
     else if (MODE == MODE_DX) total_stages = taps_h * taps_w * p.kchunks;
     else total_stages = p.tiles_w * p.tiles_h * p.tiles_n;
-    const int q0 = (int)((long long)total_stages * split / p.splits);
-    const int q1 = (int)((long long)total_stages * (split + 1) / p.splits);
+    int q0 = (int)((long long)total_stages * split / p.splits);
+    int q1 = (int)((long long)total_stages * (split + 1) / p.splits);
+    if (halo) {   // partitions own whole K chunks (a window is loaded once per chunk); stages run chunk-major
+        const int ntaps = taps_h * taps_w;
+        q0 = (p.kchunks * split / p.splits) * ntaps;
+        q1 = (p.kchunks * (split + 1) / p.splits) * ntaps;
+    }
     const int nq = q1 - q0;
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -433,7 +460,37 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // One thread issues every load.  All position bookkeeping is incremental: an integer division
         // costs this lone thread ~100 cycles, and the loop has to turn around in well under the 256
         // cycles the tensor core needs per stage.
-        {
+        if (halo) {
+            const int ntaps = taps_h * taps_w;
+            int s = 0, g = 0, t = 0, di = 0, dj = 0;
+            int chunk = ntaps > 0 ? q0 / ntaps : 0;
+            uint32_t phase = 0, gphase = 0;
+            for (int it = 0; it < nq; ++it) {
+                if (t == 0) {   // a new K chunk: its window of dy, once
+                    if (!mbar_wait_warp(gempty_bar + 8u * g, gphase ^ 1u, 6, it, wait_limit)) break;
+                    if (elect_one()) {
+                        const uint32_t gb = gfull_bar + 8u * g;
+                        mbar_expect_tx(gb, (uint32_t)p.halo_group_bytes);
+                        // map (c, w, n, h): the window starts where the tap that reaches furthest back reads
+                        tma_load_4d(a_base + (uint32_t)(g * p.halo_group_bytes), &map_a, gb, chunk * BK,
+                                    j0 + ew - (taps_w - 1), n0, i0 + eh - (taps_h - 1));
+                    }
+                }
+                if (!mbar_wait_warp(empty_bar + 8u * s, phase ^ 1u, 0, it, wait_limit)) break;
+                if (it != p.skip_stage && elect_one()) {
+                    const uint32_t fb = full_bar + 8u * s;
+                    mbar_expect_tx(fb, (uint32_t)b_stage_bytes);
+                    tma_load_4d(b_base + (uint32_t)s * b_stage_bytes, &map_b, fb, chunk * BK, n_tile * p.bn, rw + p.sw * dj,
+                                rh + p.sh * di);
+                }
+                if (++dj == taps_w) { dj = 0; ++di; }
+                if (++t == ntaps) {
+                    t = 0; di = 0; dj = 0; ++chunk;
+                    if (++g == p.halo_groups) { g = 0; gphase ^= 1u; }
+                }
+                if (++s == p.stages) { s = 0; phase ^= 1u; }
+            }
+        } else {
             const uint32_t tx_bytes = (uint32_t)(A_STAGE_BYTES + b_stage_bytes);
             int s = 0;
             uint32_t phase = 0;
@@ -524,7 +581,38 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t a_stage16 = A_STAGE_BYTES >> 4, b_stage16 = (uint32_t)b_stage_bytes >> 4;
             int s = 0;
             uint32_t phase = 0;
-            {
+            if (halo) {
+                // one window per K chunk; tap (a, b) of the class reads it shifted by whole pixels:
+                // accumulator row (th, tn, tw) <-> window pixel (taps_h-1-a + th, tn, taps_w-1-b + tw), rows of
+                // 128 B, 8 consecutive w = one swizzle group, groups 16 pixels = 2048 B apart
+                const int ntaps = taps_h * taps_w;
+                int g = 0, t = 0, a = 0, b = 0;
+                uint32_t gphase = 0;
+                for (int it = 0; it < nq; ++it) {
+                    if (t == 0 && !mbar_wait_warp(gfull_bar + 8u * g, gphase, 7, it, wait_limit)) break;
+                    if (!mbar_wait_warp(full_bar + 8u * s, phase, 1, it, wait_limit)) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    if (elect_one()) {
+                        const uint32_t r0 = (uint32_t)((taps_h - 1 - a) * p.TN * 16 + (taps_w - 1 - b));
+                        const uint32_t a_addr = a_base + (uint32_t)(g * p.halo_group_bytes) + r0 * 128u;
+                        const uint64_t adesc = with_base_offset(make_smem_desc(a_addr, 16u, 2048u, kLayoutSw128), r0);
+                        const uint64_t bdesc = bdesc0 + (uint64_t)(s * b_stage16);
+#pragma unroll
+                        for (int kk = 0; kk < BK / 8; ++kk)
+                            tcgen05_mma_tf32(tmem_d, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * (b_step >> 4)), idesc,
+                                             (it > 0 || kk > 0) ? 1u : 0u);
+                        tcgen05_commit(empty_bar + 8u * s);
+                        if (t == ntaps - 1) tcgen05_commit(gempty_bar + 8u * g);   // the window may be overwritten
+                    }
+                    if (++b == taps_w) { b = 0; ++a; }
+                    if (++t == ntaps) {
+                        t = 0; a = 0; b = 0;
+                        if (++g == p.halo_groups) { g = 0; gphase ^= 1u; }
+                    }
+                    if (++s == p.stages) { s = 0; phase ^= 1u; }
+                }
+                if (elect_one()) tcgen05_commit(tmem_full_bar);
+            } else {
             for (int it = 0; it < nq; ++it) {
                 if (!mbar_wait_warp(full_bar + 8u * s, phase, 1, it, wait_limit)) break;
                 if (X3 && !mbar_wait_warp(resid_bar + 8u * s, phase, 3, it, wait_limit)) break;
@@ -578,7 +666,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             row_off = (((unsigned long long)n * p.Ho + i) * p.Wo + j) * p.O + ch0;
             if (p.planes) row_off = (((unsigned long long)n * p.Ho + i) * p.Wo + j) * 4ull;
         } else if (MODE == MODE_DX) {
-            const int tw = row % p.TW, th = (row / p.TW) % p.TH, tn = row / (p.TW * p.TH);
+            int tw = row % p.TW, th = (row / p.TW) % p.TH, tn = row / (p.TW * p.TH);
+            if (halo) { tn = (row / p.TW) % p.TN; th = row / (p.TW * p.TN); }   // windows are laid out [h][n][w]
             const int n = n0 + tn, h = p.sh * (i0 + th) + ph, w = p.sw * (j0 + tw) + pw;
             row_valid = n < p.N && h < p.H && w < p.W;
             row_off = (((unsigned long long)n * p.H + h) * p.W + w) * p.C + ch0;
@@ -993,11 +1082,15 @@ repack_k2_kernel(const float* __restrict__ k, float* __restrict__ k2, int taps, 
 
 // ycol is stored tap-major, [tap][pixel of dy][4 channels]: the threads of a warp walk adjacent
 // pixels, so their 16-byte reads of one tap's plane are contiguous.  One thread per output pixel.
+// KH_, KW_, S_ > 0 fix kernel extent and stride at compile time (the DCGAN layers: 5, 5, 2): the tap
+// loops unroll, the divisions turn into shifts and all loads of a pixel are in flight together.
+template <int KH_, int KW_, int S_>
 __global__ void __launch_bounds__(256)
 col2im_kernel(const float4* __restrict__ ycol, float* __restrict__ out, int N, int H, int W, int C, int Ho, int Wo,
-              int KH, int KW, int sh, int sw, int pt, int pl, const EpilogueArgs ep)
+              int KHr, int KWr, int shr, int swr, int pt, int pl, const EpilogueArgs ep)
 {
     pdl_enter();
+    const int KH = KH_ > 0 ? KH_ : KHr, KW = KW_ > 0 ? KW_ : KWr, sh = S_ > 0 ? S_ : shr, sw = S_ > 0 ? S_ : swr;
     const size_t total = (size_t)N * H * W;
     const size_t pixels = (size_t)N * Ho * Wo;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -1006,17 +1099,48 @@ col2im_kernel(const float4* __restrict__ ycol, float* __restrict__ out, int N, i
         const int h = (int)((pix / W) % H);
         const int n = (int)(pix / ((size_t)W * H));
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int di = (h + pt) % sh; di < KH; di += sh) {      // taps whose row parity matches
-            if (h + pt - di < 0) break;
-            const int i = (h + pt - di) / sh;
-            if (i >= Ho) continue;
-            for (int dj = (w + pl) % sw; dj < KW; dj += sw) {
-                if (w + pl - dj < 0) break;
-                const int j = (w + pl - dj) / sw;
-                if (j >= Wo) continue;
-                const float4 v = __ldg(ycol + (size_t)(di * KW + dj) * pixels + ((size_t)n * Ho + i) * Wo + j);
-                acc[0] = __fadd_rn(acc[0], v.x); acc[1] = __fadd_rn(acc[1], v.y);
-                acc[2] = __fadd_rn(acc[2], v.z); acc[3] = __fadd_rn(acc[3], v.w);
+        const int di0 = (h + pt) % sh, dj0 = (w + pl) % sw;
+        const float4* img = ycol + (size_t)n * Ho * Wo;
+        if constexpr (KH_ > 0) {
+            // all candidate taps of this pixel's parity class, loads first (zero where the tap falls outside)
+            constexpr int SS = S_ > 0 ? S_ : 1;
+            constexpr int TH = (KH_ + SS - 1) / SS, TW = (KW_ + SS - 1) / SS;
+            float4 v[TH * TW];
+#pragma unroll
+            for (int a = 0; a < TH; ++a) {
+                const int di = di0 + a * S_;
+                const int hh = h + pt - di;
+                const int i = hh / S_;
+                const bool row_ok = di < KH_ && hh >= 0 && i < Ho;
+#pragma unroll
+                for (int b = 0; b < TW; ++b) {
+                    const int dj = dj0 + b * S_;
+                    const int ww = w + pl - dj;
+                    const int j = ww / S_;
+                    const bool ok = row_ok && dj < KW_ && ww >= 0 && j < Wo;
+                    v[a * TW + b] = ok ? __ldg(img + (size_t)(di * KW_ + dj) * pixels + (size_t)i * Wo + j)
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+            // same order as the run-time form: kernel rows ascending, columns ascending (absent taps add +0)
+#pragma unroll
+            for (int q = 0; q < TH * TW; ++q) {
+                acc[0] = __fadd_rn(acc[0], v[q].x); acc[1] = __fadd_rn(acc[1], v[q].y);
+                acc[2] = __fadd_rn(acc[2], v[q].z); acc[3] = __fadd_rn(acc[3], v[q].w);
+            }
+        } else {
+            for (int di = di0; di < KH; di += sh) {      // taps whose row parity matches
+                if (h + pt - di < 0) break;
+                const int i = (h + pt - di) / sh;
+                if (i >= Ho) continue;
+                for (int dj = dj0; dj < KW; dj += sw) {
+                    if (w + pl - dj < 0) break;
+                    const int j = (w + pl - dj) / sw;
+                    if (j >= Wo) continue;
+                    const float4 v = __ldg(img + (size_t)(di * KW + dj) * pixels + (size_t)i * Wo + j);
+                    acc[0] = __fadd_rn(acc[0], v.x); acc[1] = __fadd_rn(acc[1], v.y);
+                    acc[2] = __fadd_rn(acc[2], v.z); acc[3] = __fadd_rn(acc[3], v.w);
+                }
             }
         }
         for (int c = 0; c < C; ++c) {
@@ -1193,7 +1317,7 @@ void finish_plan(Plan& pl)
     static const int debug = env_int("DCG_TC_DEBUG");
     p.debug = debug;
 #endif
-    pl.smem = (size_t)stages * per_stage + 1024 /*alignment slack*/ + 24 * stages + 32;
+    pl.smem = (size_t)stages * per_stage + 1024 /*alignment slack*/ + 24 * stages + 96;
     p.skip_stage = -1;
     p.wait_cycles = kWaitCycles;
     pl.partial_bytes = p.splits > 1 ? (size_t)pl.grid * BM * p.bn * sizeof(float) : 0;
@@ -1263,6 +1387,55 @@ dcg_conv_desc dx_gemm_desc(const dcg_conv_desc& d, int Jp)
 
 bool plan_fwd(const dcg_conv_desc& d, Plan& pl);
 
+// Operand re-use across taps for the input gradient (DCG_TC_HALO=0 switches it off): turns a
+// finished DX plan into the windowed form where the class-subsampled image is at least 8 pixels
+// wide.  Tile = 8 wide x TH high x TN images (TH * TN = 16), window = 16 wide x (TH + row taps - 1)
+// high per image and 32-channel chunk; two windows in flight, the rest of the shared memory is
+// the B ring.  K partitions own whole chunks.
+void plan_dx_halo(const dcg_conv_desc& d, Plan& pl)
+{
+    static const int enabled = [] { const char* v = getenv("DCG_TC_HALO"); return v ? atoi(v) : 1; }();
+    Params& p = pl.p;
+    if (!enabled || p.x3 || d.stride_h != d.stride_w) return;
+    const int s = d.stride_h;
+    const int ha = (d.h + s - 1) / s, wa = (d.w + s - 1) / s;
+    const int taps_h = (d.kh + s - 1) / s, taps_w = (d.kw + s - 1) / s;   // of the class with the most taps
+    if (wa < 8 || taps_w > 9 || taps_h * taps_w < 2) return;
+    int th = pow2_ceil(ha);
+    if (th > 16) th = 16;
+    const int tn = 16 / th;
+    const int group_bytes = 16 * tn * (th + taps_h - 1) * 128;
+    const int b_stage = p.bn * BK * 4;
+    const int tiles_w = (wa + 7) / 8, tiles_h = (ha + th - 1) / th, tiles_n = (d.n + tn - 1) / tn;
+    const int classes = s * s;
+    const int tiles = classes * tiles_w * tiles_h * tiles_n * p.n_tiles;
+    const int min_taps = (d.kh / s) * (d.kw / s);
+    int splits = choose_splits(tiles, (min_taps < 1 ? 1 : min_taps) * p.kchunks);
+    if (splits > p.kchunks) splits = p.kchunks;
+    const int grid = tiles * splits;
+    const int groups = 2;
+    int budget = (grid > sm_count() && p.bn <= 128) ? (kMaxSmem / 2 - 2048) : (kMaxSmem - 2048);
+    int stages = (budget - groups * group_bytes) / b_stage;
+    if (stages < 3) {   // no room beside a second CTA: one CTA per SM
+        budget = kMaxSmem - 2048;
+        stages = (budget - groups * group_bytes) / b_stage;
+    }
+    if (stages > 8) stages = 8;
+    if (stages < 3) return;
+    if ((size_t)groups * group_bytes + (size_t)stages * b_stage < (size_t)kRedFloats(p.bn) * 4 + BM * 8) return;
+    p.halo = 1;
+    p.halo_groups = groups;
+    p.halo_group_bytes = group_bytes;
+    p.TW = 8; p.TH = th; p.TN = tn;
+    p.tiles_w = tiles_w; p.tiles_h = tiles_h; p.tiles_n = tiles_n;
+    p.splits = splits;
+    p.stages = stages;
+    pl.grid = grid;
+    pl.smem = (size_t)groups * group_bytes + (size_t)stages * b_stage + 1024 + 24 * stages + 96;
+    pl.partial_bytes = splits > 1 ? (size_t)grid * BM * p.bn * sizeof(float) : 0;
+    pl.ws_bytes = pl.partial_bytes;
+}
+
 bool plan_dx(const dcg_conv_desc& d, Plan& pl)
 {
     if (d.c <= 4 && d.o % 32 == 0 && d.stride_h <= d.kh && d.stride_w <= d.kw) {
@@ -1296,6 +1469,7 @@ bool plan_dx(const dcg_conv_desc& d, Plan& pl)
     p.splits = choose_splits(tiles, (min_taps < 1 ? 1 : min_taps) * p.kchunks);
     pl.grid = tiles * p.splits;
     finish_plan(pl);
+    plan_dx_halo(d, pl);
     return true;
 }
 
@@ -1542,7 +1716,18 @@ int build_dx(const dcg_conv_desc& d, const float* dy, const float* k, void* ws, 
     Plan& pl = pr.pl;
     if (!plan_dx(d, pl)) return fail(DCG_ERR_UNSUPPORTED, "conv dx: shape not supported by the tensor path");
     const Params& p = pl.p;
-    int st = map_act_4d(&pr.ma, dy, d.n, d.ho, d.wo, d.o, p.TW, p.TH, p.TN, 1, 1);
+    int st;
+    if (p.halo) {
+        // dy [n, ho, wo, o] as (o, w, n, h) - images before rows, so that a window lands as [h][n][w][32 c] -
+        // with a (32, 16, TN, window rows) box
+        const cuuint64_t dims[4] = {(cuuint64_t)d.o, (cuuint64_t)d.wo, (cuuint64_t)d.n, (cuuint64_t)d.ho};
+        const cuuint64_t strides[3] = {(cuuint64_t)d.o * 4, (cuuint64_t)d.ho * d.wo * d.o * 4, (cuuint64_t)d.wo * d.o * 4};
+        const cuuint32_t box[4] = {32, 16, (cuuint32_t)p.TN, (cuuint32_t)(p.halo_group_bytes / (16 * p.TN * 128))};
+        const cuuint32_t es[4] = {1, 1, 1, 1};
+        st = encode_map(&pr.ma, dy, 4, dims, false, strides, box, es);
+    } else {
+        st = map_act_4d(&pr.ma, dy, d.n, d.ho, d.wo, d.o, p.TW, p.TH, p.TN, 1, 1);
+    }
     if (st) return st;
     if (pl.ycol_bytes) {   // narrow-channel layer: GEMM over all taps, then gather
         if (!ws || ws_bytes < pl.ws_bytes)
@@ -1671,9 +1856,12 @@ int conv_tc_dx(const dcg_conv_desc& d, const float* dy, const float* k, float* d
         size_t blocks = (total + 255) / 256;
         const size_t cap = (size_t)sm_count() * 16;
         if (blocks > cap) blocks = cap;
-        launch_pdl(col2im_kernel, (unsigned)blocks, 256, 0, stream, reinterpret_cast<const float4*>(ycol), dx, d.n, d.h, d.w, d.c,
-                                                            d.ho, d.wo, d.kh, d.kw, d.stride_h, d.stride_w, d.pad_top,
-                                                            d.pad_left, ep);
+        if (d.kh == 5 && d.kw == 5 && d.stride_h == 2 && d.stride_w == 2)
+            launch_pdl(col2im_kernel<5, 5, 2>, (unsigned)blocks, 256, 0, stream, reinterpret_cast<const float4*>(ycol), dx, d.n, d.h,
+                       d.w, d.c, d.ho, d.wo, d.kh, d.kw, d.stride_h, d.stride_w, d.pad_top, d.pad_left, ep);
+        else
+            launch_pdl(col2im_kernel<0, 0, 0>, (unsigned)blocks, 256, 0, stream, reinterpret_cast<const float4*>(ycol), dx, d.n, d.h,
+                       d.w, d.c, d.ho, d.wo, d.kh, d.kw, d.stride_h, d.stride_w, d.pad_top, d.pad_left, ep);
         DCG_LAUNCH_CHECK("col2im_kernel");
         return DCG_OK;
     }

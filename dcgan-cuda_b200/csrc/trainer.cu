@@ -602,7 +602,10 @@ int enqueue_step(dcg_trainer* t, const float* lr_dev)
     if ((st = dcg_run_nodes(t->ctx, t->d_nodes.data(), (int)t->d_nodes.size(), t->cfg.fuse))) return st;
     if ((st = apply_adam(t, t->d_param, t->d_grad, d_second, t->d_m, t->d_v, &t->d_t, 1.f, lr_dev))) return st;
     for (int rep = 0; rep < 2; ++rep) {
-        if ((st = dcg_run_nodes(t->ctx, t->g_nodes.data(), (int)t->g_nodes.size(), t->cfg.fuse))) return st;
+        // share_g_forward: the first G run re-uses the generator activations the D run just computed
+        // (the generator's parameters have not changed in between) instead of recomputing them
+        const int first = (rep == 0 && t->cfg.share_g_forward) ? (int)t->g_forward_nodes : 0;
+        if ((st = dcg_run_nodes(t->ctx, t->g_nodes.data() + first, (int)t->g_nodes.size() - first, t->cfg.fuse))) return st;
         if ((st = apply_adam(t, t->g_param, t->g_grad, nullptr, t->g_m, t->g_v, &t->g_t, 1.f,
                              lr_dev ? lr_dev + 1 + rep : nullptr)))
             return st;
@@ -646,7 +649,9 @@ int step_as_one_graph(dcg_trainer* t)
             cudaGetLastError();
             g.exec = nullptr;
             g.failed = true;
-            if (getenv("DCG_TRAINER_VERBOSE")) fprintf(stderr, "dcg_trainer: whole-step graph capture failed; using per-list graphs\n");
+            if (getenv("DCG_TRAINER_VERBOSE"))
+                fprintf(stderr, "dcg_trainer: whole-step graph capture failed (list status %d: %s); running %s\n", st,
+                        st ? dcg_last_error() : "capture / instantiate", t->dp ? "eagerly" : "per-list graphs");
             // the step counters already advanced: finish this iteration eagerly with the same step sizes
             return (st = enqueue_step(t, t->lr_dev.p)) ? st : 1;
         }
@@ -819,6 +824,8 @@ extern "C" int dcg_trainer_step(dcg_trainer* t)
         if (t->dp) {
             st = enqueue_step(t, nullptr);   // eager, collectives included
             if (st) return st;
+        } else if (t->cfg.share_g_forward) {
+            if ((st = enqueue_step(t, nullptr))) return st;   // eager; the per-list graphs have no shared form
         } else {
             if ((st = dcg_trainer_d_backward(t))) return st;
             if ((st = dcg_trainer_d_apply(t, 1.f))) return st;
@@ -1024,5 +1031,12 @@ extern "C" int dcg_trainer_tensor(dcg_trainer* t, const char* name, float** ptr,
 extern "C" dcg_context* dcg_trainer_context(dcg_trainer* t) { return t ? t->ctx : nullptr; }
 
 extern "C" uint64_t dcg_trainer_step_launches(const dcg_trainer* t) { return t ? t->last_step_launches : 0; }
+
+extern "C" int dcg_trainer_step_mode(const dcg_trainer* t)
+{
+    if (!t) return -1;
+    if (t->step_graph.exec) return 2;
+    return t->step_graph.failed ? 0 : 1;
+}
 
 extern "C" size_t dcg_trainer_arena_bytes(const dcg_trainer* t) { return t ? t->arena_bytes : 0; }

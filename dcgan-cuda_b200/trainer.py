@@ -38,12 +38,13 @@ class _CudaView:
 
 class Trainer:
     def __init__(self, batch=64, precision=_lib.PREC_TF32, fuse=True, g_leaky=False, lr=2e-4, beta1=0.5,
-                 beta2=0.999, eps=1e-8, seed=234, world=1, device=None, process_group=None, comm="abi"):
+                 beta2=0.999, eps=1e-8, seed=234, world=1, device=None, process_group=None, comm="abi",
+                 share_g_forward=False):
         self.device = torch.device(device if device is not None else "cuda:%d" % torch.cuda.current_device())
         torch.cuda.set_device(self.device)
         self.batch, self.world, self.group = batch, world, process_group
         self.cfg = TrainerConfig(batch, world, precision, 1 if fuse else 0, 1 if g_leaky else 0, lr, beta1,
-                                 beta2, eps, seed)
+                                 beta2, eps, seed, 1 if share_g_forward else 0)
         self._h = ctypes.c_void_p()
         # The trainer replays its node lists as CUDA graphs, which cannot be captured on the legacy
         # default stream: when that is the caller's current stream the trainer works on a stream of its
@@ -283,6 +284,10 @@ class Trainer:
     h2d_bytes_per_step = property(lambda self: self.batch * (64 * 64 * 3 + 100) * 4)
     h2d_bytes_per_step_u8 = property(lambda self: self.batch * (64 * 64 * 3 + 100 * 4))
     d2h_bytes_per_step = property(lambda self: 8)
+
+    def step_mode(self):
+        """'graph' once the whole iteration replays as one CUDA graph, 'warmup' before, 'eager' if capturing it failed."""
+        return {2: "graph", 1: "warmup", 0: "eager"}.get(int(lib.dcg_trainer_step_mode(self._h)), "unknown")
 
     def launches_per_step(self):
         return int(lib.dcg_trainer_step_launches(self._h))

@@ -373,6 +373,9 @@ typedef struct dcg_trainer_config {
     int g_leaky;         /* generator activation: 0 = relu (dcgan/main.cu:69,97), 1 = leaky-relu(0.2) */
     float lr, beta1, beta2, eps; /* Adam (dcgan/main.cu:35-36, src/api/adam-optimizer.hh:11-14) */
     uint64_t seed;       /* weights ~ N(0, 0.02) from the xorshift generator, biases 0 */
+    int share_g_forward; /* dcg_trainer_step only, single GPU: 1 = the first G run of an iteration re-uses the generator
+                            forward pass of the D run (same generator parameters, so the same numbers) instead of
+                            recomputing it as dcgan/main.cu:378-391 does; 0 = recompute (the benchmarked workload) */
 } dcg_trainer_config;
 
 /* Allocates one device arena (parameters, Adam state, gradients, activations) and builds the
@@ -431,6 +434,9 @@ int dcg_trainer_save_wait(dcg_trainer* t);
 int dcg_trainer_load(dcg_trainer* t, const char* path);
 /* The trainer's execution context (for dcg_context_profile_begin / _end around its phases). */
 dcg_context* dcg_trainer_context(dcg_trainer* t);
+/* How dcg_trainer_step runs: 2 = the whole iteration replays as one CUDA graph, 1 = still warming up
+ * (eager / per-list graphs), 0 = capturing the iteration failed and it stays eager. */
+int dcg_trainer_step_mode(const dcg_trainer* t);
 /* Kernels launched by the last dcg_trainer_step. */
 uint64_t dcg_trainer_step_launches(const dcg_trainer* t);
 size_t dcg_trainer_arena_bytes(const dcg_trainer* t);

@@ -331,3 +331,23 @@ def test_uint8_images_are_decoded_on_the_device_like_the_reference(pkg, dev):
     assert torch.equal(a.tensor("g_params"), b.tensor("g_params"))
     a.close()
     b.close()
+
+
+def test_shared_generator_forward_gives_the_same_numbers(pkg, dev):
+    """share_g_forward: the first G run of an iteration re-uses the generator activations of the D run
+    (the generator's parameters are unchanged in between).  Same losses and parameters, bit for bit,
+    as the recomputing form, before and after the iteration replays as a CUDA graph; fewer launches."""
+    B = 4
+    g = torch.Generator(device="cpu").manual_seed(33)
+    xs = [(torch.rand((B, 64, 64, 3), generator=g) * 2 - 1).numpy() for _ in range(5)]
+    zs = [(torch.rand((B, 100), generator=g) * 2 - 1).numpy() for _ in range(5)]
+    out = []
+    for share in (False, True):
+        tr = pkg.Trainer(batch=B, precision=pkg.PREC_TF32, seed=77, share_g_forward=share)
+        losses = [tr.step_host(x, z) for x, z in zip(xs, zs)]
+        torch.cuda.synchronize()
+        out.append((losses, tr.tensor("d_params").clone(), tr.tensor("g_params").clone(), tr.launches_per_step()))
+        tr.close()
+    assert out[0][0] == out[1][0]
+    assert torch.equal(out[0][1], out[1][1]) and torch.equal(out[0][2], out[1][2])
+    assert out[1][3] < out[0][3]
