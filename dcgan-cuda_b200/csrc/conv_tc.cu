@@ -101,13 +101,6 @@ struct Params {
     int n_tiles;                  // BN-column tiles along the N channel axis
     int bn;                       // accumulator columns, multiple of 16, <= 256
     int splits;                   // K partitions of a tile = CTAs per cluster (<= 8)
-    // DX with operand re-use across taps ("halo"): per 32-channel K chunk ONE window of dy - the
-    // 8 x TH x TN pixel tile plus the rows / columns its taps reach, [h][n][16 w][32 c] - is loaded and
-    // every tap of the parity class multiplies a shifted view of it (shared-memory descriptor start
-    // address moved by whole pixels), instead of one 16 KB tile per tap.  Only B streams per tap.
-    int halo;                     // 0: off
-    int halo_groups;              // windows in flight
-    int halo_group_bytes;         // 16 * TN * (TH + max row taps - 1) * 128, a multiple of 1024
     int skip_stage;               // test hook: the producer leaves this pipeline stage out (-1: never)
     long long wait_cycles;        // SM clocks after which a barrier wait gives up
     int kchunks;                  // 32-wide chunks along the contracted channel axis (FWD: C, DX: O)
@@ -303,13 +296,6 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_b
     return d;
 }
 
-// A K-major, 128-byte-swizzled tile whose first row does not sit on a 1024-byte boundary: the
-// swizzle phase of that row ((address >> 7) & 7) goes into the descriptor's base-offset field.
-__device__ __forceinline__ uint64_t with_base_offset(uint64_t desc, uint32_t phase)
-{
-    return desc | ((uint64_t)(phase & 7u) << 49);
-}
-
 // Instruction descriptor: fp32 accumulator, TF32 operands, operand majors, N and M.
 __device__ __forceinline__ uint32_t make_idesc(int a_mn_major, int b_mn_major, int n, int m)
 {
@@ -330,8 +316,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int b_stage_bytes = p.bn * BK * 4;
     const long long wait_limit = p.wait_cycles;
     const uint32_t a_base = smem_base;
-    const bool halo = MODE == MODE_DX && !X3 && p.halo;
-    const uint32_t b_base = a_base + (halo ? (uint32_t)(p.halo_groups * p.halo_group_bytes) : (uint32_t)p.stages * A_STAGE_BYTES);
+    const uint32_t b_base = a_base + (uint32_t)p.stages * A_STAGE_BYTES;
     // 3xTF32: residual tiles (operand minus its TF32 part) of every stage follow the operand tiles
     const uint32_t as_base = b_base + (uint32_t)p.stages * b_stage_bytes;
     const uint32_t bs_base = as_base + (uint32_t)p.stages * A_STAGE_BYTES;
@@ -342,8 +327,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t resid_bar = bar_base + 16u * p.stages;     // 3xTF32: residual tiles of the stage are written
     const uint32_t tmem_full_bar = bar_base + 24u * p.stages;
     const uint32_t tmem_slot = tmem_full_bar + 8u;
-    const uint32_t gfull_bar = tmem_full_bar + 16u;               // halo: window g has landed / has been read
-    const uint32_t gempty_bar = gfull_bar + 8u * 4u;
     uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
@@ -355,11 +338,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_init(empty_bar + 8u * s, 1);
             mbar_init(resid_bar + 8u * s, kEpi);
         }
-        if (halo)
-            for (int g = 0; g < p.halo_groups; ++g) {
-                mbar_init(gfull_bar + 8u * g, 1);
-                mbar_init(gempty_bar + 8u * g, 1);
-            }
         mbar_init(tmem_full_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
@@ -412,13 +390,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (MODE == MODE_FWD) total_stages = p.narrow ? p.KH : p.KH * p.KW * p.kchunks;
     else if (MODE == MODE_DX) total_stages = taps_h * taps_w * p.kchunks;
     else total_stages = p.tiles_w * p.tiles_h * p.tiles_n;
-    int q0 = (int)((long long)total_stages * split / p.splits);
-    int q1 = (int)((long long)total_stages * (split + 1) / p.splits);
-    if (halo) {   // partitions own whole K chunks (a window is loaded once per chunk); stages run chunk-major
-        const int ntaps = taps_h * taps_w;
-        q0 = (p.kchunks * split / p.splits) * ntaps;
-        q1 = (p.kchunks * (split + 1) / p.splits) * ntaps;
-    }
+    const int q0 = (int)((long long)total_stages * split / p.splits);
+    const int q1 = (int)((long long)total_stages * (split + 1) / p.splits);
     const int nq = q1 - q0;
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -460,37 +433,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // One thread issues every load.  All position bookkeeping is incremental: an integer division
         // costs this lone thread ~100 cycles, and the loop has to turn around in well under the 256
         // cycles the tensor core needs per stage.
-        if (halo) {
-            const int ntaps = taps_h * taps_w;
-            int s = 0, g = 0, t = 0, di = 0, dj = 0;
-            int chunk = ntaps > 0 ? q0 / ntaps : 0;
-            uint32_t phase = 0, gphase = 0;
-            for (int it = 0; it < nq; ++it) {
-                if (t == 0) {   // a new K chunk: its window of dy, once
-                    if (!mbar_wait_warp(gempty_bar + 8u * g, gphase ^ 1u, 6, it, wait_limit)) break;
-                    if (elect_one()) {
-                        const uint32_t gb = gfull_bar + 8u * g;
-                        mbar_expect_tx(gb, (uint32_t)p.halo_group_bytes);
-                        // map (c, w, n, h): the window starts where the tap that reaches furthest back reads
-                        tma_load_4d(a_base + (uint32_t)(g * p.halo_group_bytes), &map_a, gb, chunk * BK,
-                                    j0 + ew - (taps_w - 1), n0, i0 + eh - (taps_h - 1));
-                    }
-                }
-                if (!mbar_wait_warp(empty_bar + 8u * s, phase ^ 1u, 0, it, wait_limit)) break;
-                if (it != p.skip_stage && elect_one()) {
-                    const uint32_t fb = full_bar + 8u * s;
-                    mbar_expect_tx(fb, (uint32_t)b_stage_bytes);
-                    tma_load_4d(b_base + (uint32_t)s * b_stage_bytes, &map_b, fb, chunk * BK, n_tile * p.bn, rw + p.sw * dj,
-                                rh + p.sh * di);
-                }
-                if (++dj == taps_w) { dj = 0; ++di; }
-                if (++t == ntaps) {
-                    t = 0; di = 0; dj = 0; ++chunk;
-                    if (++g == p.halo_groups) { g = 0; gphase ^= 1u; }
-                }
-                if (++s == p.stages) { s = 0; phase ^= 1u; }
-            }
-        } else {
+        {
             const uint32_t tx_bytes = (uint32_t)(A_STAGE_BYTES + b_stage_bytes);
             int s = 0;
             uint32_t phase = 0;
@@ -581,38 +524,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t a_stage16 = A_STAGE_BYTES >> 4, b_stage16 = (uint32_t)b_stage_bytes >> 4;
             int s = 0;
             uint32_t phase = 0;
-            if (halo) {
-                // one window per K chunk; tap (a, b) of the class reads it shifted by whole pixels:
-                // accumulator row (th, tn, tw) <-> window pixel (taps_h-1-a + th, tn, taps_w-1-b + tw), rows of
-                // 128 B, 8 consecutive w = one swizzle group, groups 16 pixels = 2048 B apart
-                const int ntaps = taps_h * taps_w;
-                int g = 0, t = 0, a = 0, b = 0;
-                uint32_t gphase = 0;
-                for (int it = 0; it < nq; ++it) {
-                    if (t == 0 && !mbar_wait_warp(gfull_bar + 8u * g, gphase, 7, it, wait_limit)) break;
-                    if (!mbar_wait_warp(full_bar + 8u * s, phase, 1, it, wait_limit)) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    if (elect_one()) {
-                        const uint32_t r0 = (uint32_t)((taps_h - 1 - a) * p.TN * 16 + (taps_w - 1 - b));
-                        const uint32_t a_addr = a_base + (uint32_t)(g * p.halo_group_bytes) + r0 * 128u;
-                        const uint64_t adesc = with_base_offset(make_smem_desc(a_addr, 16u, 2048u, kLayoutSw128), r0);
-                        const uint64_t bdesc = bdesc0 + (uint64_t)(s * b_stage16);
-#pragma unroll
-                        for (int kk = 0; kk < BK / 8; ++kk)
-                            tcgen05_mma_tf32(tmem_d, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * (b_step >> 4)), idesc,
-                                             (it > 0 || kk > 0) ? 1u : 0u);
-                        tcgen05_commit(empty_bar + 8u * s);
-                        if (t == ntaps - 1) tcgen05_commit(gempty_bar + 8u * g);   // the window may be overwritten
-                    }
-                    if (++b == taps_w) { b = 0; ++a; }
-                    if (++t == ntaps) {
-                        t = 0; a = 0; b = 0;
-                        if (++g == p.halo_groups) { g = 0; gphase ^= 1u; }
-                    }
-                    if (++s == p.stages) { s = 0; phase ^= 1u; }
-                }
-                if (elect_one()) tcgen05_commit(tmem_full_bar);
-            } else {
+            {
             for (int it = 0; it < nq; ++it) {
                 if (!mbar_wait_warp(full_bar + 8u * s, phase, 1, it, wait_limit)) break;
                 if (X3 && !mbar_wait_warp(resid_bar + 8u * s, phase, 3, it, wait_limit)) break;
@@ -666,8 +578,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             row_off = (((unsigned long long)n * p.Ho + i) * p.Wo + j) * p.O + ch0;
             if (p.planes) row_off = (((unsigned long long)n * p.Ho + i) * p.Wo + j) * 4ull;
         } else if (MODE == MODE_DX) {
-            int tw = row % p.TW, th = (row / p.TW) % p.TH, tn = row / (p.TW * p.TH);
-            if (halo) { tn = (row / p.TW) % p.TN; th = row / (p.TW * p.TN); }   // windows are laid out [h][n][w]
+            const int tw = row % p.TW, th = (row / p.TW) % p.TH, tn = row / (p.TW * p.TH);
             const int n = n0 + tn, h = p.sh * (i0 + th) + ph, w = p.sw * (j0 + tw) + pw;
             row_valid = n < p.N && h < p.H && w < p.W;
             row_off = (((unsigned long long)n * p.H + h) * p.W + w) * p.C + ch0;
@@ -1317,7 +1228,7 @@ void finish_plan(Plan& pl)
     static const int debug = env_int("DCG_TC_DEBUG");
     p.debug = debug;
 #endif
-    pl.smem = (size_t)stages * per_stage + 1024 /*alignment slack*/ + 24 * stages + 96;
+    pl.smem = (size_t)stages * per_stage + 1024 /*alignment slack*/ + 24 * stages + 32;
     p.skip_stage = -1;
     p.wait_cycles = kWaitCycles;
     pl.partial_bytes = p.splits > 1 ? (size_t)pl.grid * BM * p.bn * sizeof(float) : 0;
@@ -1387,55 +1298,6 @@ dcg_conv_desc dx_gemm_desc(const dcg_conv_desc& d, int Jp)
 
 bool plan_fwd(const dcg_conv_desc& d, Plan& pl);
 
-// Operand re-use across taps for the input gradient (DCG_TC_HALO=0 switches it off): turns a
-// finished DX plan into the windowed form where the class-subsampled image is at least 8 pixels
-// wide.  Tile = 8 wide x TH high x TN images (TH * TN = 16), window = 16 wide x (TH + row taps - 1)
-// high per image and 32-channel chunk; two windows in flight, the rest of the shared memory is
-// the B ring.  K partitions own whole chunks.
-void plan_dx_halo(const dcg_conv_desc& d, Plan& pl)
-{
-    static const int enabled = [] { const char* v = getenv("DCG_TC_HALO"); return v ? atoi(v) : 1; }();
-    Params& p = pl.p;
-    if (!enabled || p.x3 || d.stride_h != d.stride_w) return;
-    const int s = d.stride_h;
-    const int ha = (d.h + s - 1) / s, wa = (d.w + s - 1) / s;
-    const int taps_h = (d.kh + s - 1) / s, taps_w = (d.kw + s - 1) / s;   // of the class with the most taps
-    if (wa < 8 || taps_w > 9 || taps_h * taps_w < 2) return;
-    int th = pow2_ceil(ha);
-    if (th > 16) th = 16;
-    const int tn = 16 / th;
-    const int group_bytes = 16 * tn * (th + taps_h - 1) * 128;
-    const int b_stage = p.bn * BK * 4;
-    const int tiles_w = (wa + 7) / 8, tiles_h = (ha + th - 1) / th, tiles_n = (d.n + tn - 1) / tn;
-    const int classes = s * s;
-    const int tiles = classes * tiles_w * tiles_h * tiles_n * p.n_tiles;
-    const int min_taps = (d.kh / s) * (d.kw / s);
-    int splits = choose_splits(tiles, (min_taps < 1 ? 1 : min_taps) * p.kchunks);
-    if (splits > p.kchunks) splits = p.kchunks;
-    const int grid = tiles * splits;
-    const int groups = 2;
-    int budget = (grid > sm_count() && p.bn <= 128) ? (kMaxSmem / 2 - 2048) : (kMaxSmem - 2048);
-    int stages = (budget - groups * group_bytes) / b_stage;
-    if (stages < 3) {   // no room beside a second CTA: one CTA per SM
-        budget = kMaxSmem - 2048;
-        stages = (budget - groups * group_bytes) / b_stage;
-    }
-    if (stages > 8) stages = 8;
-    if (stages < 3) return;
-    if ((size_t)groups * group_bytes + (size_t)stages * b_stage < (size_t)kRedFloats(p.bn) * 4 + BM * 8) return;
-    p.halo = 1;
-    p.halo_groups = groups;
-    p.halo_group_bytes = group_bytes;
-    p.TW = 8; p.TH = th; p.TN = tn;
-    p.tiles_w = tiles_w; p.tiles_h = tiles_h; p.tiles_n = tiles_n;
-    p.splits = splits;
-    p.stages = stages;
-    pl.grid = grid;
-    pl.smem = (size_t)groups * group_bytes + (size_t)stages * b_stage + 1024 + 24 * stages + 96;
-    pl.partial_bytes = splits > 1 ? (size_t)grid * BM * p.bn * sizeof(float) : 0;
-    pl.ws_bytes = pl.partial_bytes;
-}
-
 bool plan_dx(const dcg_conv_desc& d, Plan& pl)
 {
     if (d.c <= 4 && d.o % 32 == 0 && d.stride_h <= d.kh && d.stride_w <= d.kw) {
@@ -1469,7 +1331,6 @@ bool plan_dx(const dcg_conv_desc& d, Plan& pl)
     p.splits = choose_splits(tiles, (min_taps < 1 ? 1 : min_taps) * p.kchunks);
     pl.grid = tiles * p.splits;
     finish_plan(pl);
-    plan_dx_halo(d, pl);
     return true;
 }
 
@@ -1716,18 +1577,7 @@ int build_dx(const dcg_conv_desc& d, const float* dy, const float* k, void* ws, 
     Plan& pl = pr.pl;
     if (!plan_dx(d, pl)) return fail(DCG_ERR_UNSUPPORTED, "conv dx: shape not supported by the tensor path");
     const Params& p = pl.p;
-    int st;
-    if (p.halo) {
-        // dy [n, ho, wo, o] as (o, w, n, h) - images before rows, so that a window lands as [h][n][w][32 c] -
-        // with a (32, 16, TN, window rows) box
-        const cuuint64_t dims[4] = {(cuuint64_t)d.o, (cuuint64_t)d.wo, (cuuint64_t)d.n, (cuuint64_t)d.ho};
-        const cuuint64_t strides[3] = {(cuuint64_t)d.o * 4, (cuuint64_t)d.ho * d.wo * d.o * 4, (cuuint64_t)d.wo * d.o * 4};
-        const cuuint32_t box[4] = {32, 16, (cuuint32_t)p.TN, (cuuint32_t)(p.halo_group_bytes / (16 * p.TN * 128))};
-        const cuuint32_t es[4] = {1, 1, 1, 1};
-        st = encode_map(&pr.ma, dy, 4, dims, false, strides, box, es);
-    } else {
-        st = map_act_4d(&pr.ma, dy, d.n, d.ho, d.wo, d.o, p.TW, p.TH, p.TN, 1, 1);
-    }
+    int st = map_act_4d(&pr.ma, dy, d.n, d.ho, d.wo, d.o, p.TW, p.TH, p.TN, 1, 1);
     if (st) return st;
     if (pl.ycol_bytes) {   // narrow-channel layer: GEMM over all taps, then gather
         if (!ws || ws_bytes < pl.ws_bytes)
@@ -1905,7 +1755,7 @@ int conv_tc_device_status(int* detail /* [4] */)
         return fail(DCG_ERR_DEVICE, "tensor-path kernel gave up waiting: code %d block %d role %d stage %d",
                     h[0], h[1], h[2], h[3]);
     }
-    return DCG_OK;
+    return dp_status_check();
 }
 
 }  // namespace dcg
