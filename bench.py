@@ -427,8 +427,11 @@ def run_ours(args, rank, local_rank, world):
         dp_extra["allreduce_us"] = us   # back to back, outside the timed region: an upper bound on what a step exposes
         dp_extra["allreduce_bytes"] = {"d": trainer.d_grads.numel() * 4, "g": trainer.g_grads.numel() * 4}
         info = trainer.dp_info()
-        dp_extra["comm"] = ("nccl behind the C ABI (dcg_dp_*), version %s; whole iteration = one CUDA graph" % info[2]) if info \
+        dp_extra["comm"] = ("communicator behind the C ABI (dcg_dp_*, NCCL %s); update = %s; whole iteration = one CUDA graph"
+                            % (info[2], {"fused": "one kernel over peer memory (gradient sum + Adam + parameter broadcast)",
+                                         "nccl": "ncclAllReduce + replicated Adam"}.get(trainer.dp_mode(), "?"))) if info \
             else "torch.distributed all_reduce between the library's phases"
+        dp_extra["dp_mode"] = trainer.dp_mode()
 
     # ---- BASELINE configs[0] and configs[1] at batch 64 (device-timed, inputs resident) ---------------
     def timed(fn, reps):   # rank 0 only: no collective in here

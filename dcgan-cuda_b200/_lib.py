@@ -136,6 +136,7 @@ SIGNATURES = {
     "dcg_trainer_context": (_P, [_P]),
     "dcg_context_profile_begin": (c_int, [_P]),
     "dcg_context_profile_end": (c_int, [_P, ctypes.POINTER(ProfileRow), c_int, ctypes.POINTER(c_int)]),
+    "dcg_trainer_dp_mode": (c_int, [_P]),
     "dcg_trainer_step_mode": (c_int, [_P]),
     "dcg_trainer_step_launches": (ctypes.c_uint64, [_P]),
     "dcg_trainer_arena_bytes": (c_size_t, [_P]),

@@ -92,6 +92,9 @@ size_t colsum_partial_bytes_max(size_t rows, size_t cols);
 // Clears the ticket words of every live context (after a kernel reported an error, a launch may
 // have left some of them counted up).  Synchronises the device.
 void contexts_reset_tickets();
+// Status word of the fused data-parallel update (dp_adam.cu): DCG_OK, or DCG_ERR_DEVICE after a wait for
+// a peer ran out.  Reads and clears; the caller has synchronised the device.
+int dp_status_check();
 
 // Number of SMs of the current device (cached per device id).
 int sm_count();

@@ -26,6 +26,7 @@ struct NcclApi {
     ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
     ncclResult_t (*GroupStart)() = nullptr;
@@ -51,6 +52,7 @@ NcclApi& api()
         a.GetUniqueId = reinterpret_cast<decltype(a.GetUniqueId)>(sym("ncclGetUniqueId"));
         a.CommInitRank = reinterpret_cast<decltype(a.CommInitRank)>(sym("ncclCommInitRank"));
         a.AllReduce = reinterpret_cast<decltype(a.AllReduce)>(sym("ncclAllReduce"));
+        a.AllGather = reinterpret_cast<decltype(a.AllGather)>(sym("ncclAllGather"));
         a.CommDestroy = reinterpret_cast<decltype(a.CommDestroy)>(sym("ncclCommDestroy"));
         a.GetErrorString = reinterpret_cast<decltype(a.GetErrorString)>(sym("ncclGetErrorString"));
         a.GroupStart = reinterpret_cast<decltype(a.GroupStart)>(sym("ncclGroupStart"));
@@ -109,6 +111,77 @@ void dp_register(dcg_dp* dp, void* buf, size_t bytes)
 }
 
 int dp_world(const dcg_dp* dp) { return dp ? dp->world : 1; }
+int dp_rank(const dcg_dp* dp) { return dp ? dp->rank : 0; }
+
+// Maps every rank's copy of a cudaMalloc'ed buffer into this process: each rank exports an IPC handle
+// of `local_base`, the handles travel through the communicator (an all-gather of 64-byte records),
+// and the peers' buffers are opened with peer access enabled.  bases[r] is rank r's buffer as seen
+// from this GPU (bases[rank] = local_base).  Collective.  Every rank learns whether ALL succeeded:
+// returns DCG_OK only then (the caller falls back to NCCL collectives otherwise), and on failure
+// whatever this rank had opened is closed again.
+int dp_map_peers(dcg_dp* dp, void* local_base, void** bases /* [world] */)
+{
+    NcclApi& a = api();
+    DCG_CHECK_ARG(dp && dp->comm && a.ok && a.AllGather, "dcg_dp: no communicator");
+    const int W = dp->world;
+    DCG_CHECK_ARG(W <= 8, "dcg_dp: peer mapping supports up to 8 ranks");
+    struct Record { cudaIpcMemHandle_t handle; int ok; int pad[3]; };
+    Record mine;
+    std::memset(&mine, 0, sizeof(mine));
+    mine.ok = cudaIpcGetMemHandle(&mine.handle, local_base) == cudaSuccess ? 1 : 0;
+    if (!mine.ok) cudaGetLastError();
+    Record *d_send = nullptr, *d_recv = nullptr;
+    Record all[8];
+    cudaStream_t s = nullptr;
+    bool ok = cudaMalloc(&d_send, sizeof(Record)) == cudaSuccess && cudaMalloc(&d_recv, sizeof(Record) * W) == cudaSuccess &&
+              cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) == cudaSuccess;
+    auto gather = [&](const Record& r) {   // collective: every rank must call it the same number of times
+        if (!ok) return false;
+        if (cudaMemcpyAsync(d_send, &r, sizeof(Record), cudaMemcpyHostToDevice, s) != cudaSuccess) return false;
+        if (a.AllGather(d_send, d_recv, sizeof(Record), ncclChar, dp->comm, s) != ncclSuccess) return false;
+        if (cudaMemcpyAsync(all, d_recv, sizeof(Record) * W, cudaMemcpyDeviceToHost, s) != cudaSuccess) return false;
+        return cudaStreamSynchronize(s) == cudaSuccess;
+    };
+    bool fine = gather(mine);
+    for (int r = 0; fine && r < W; ++r) fine = all[r].ok != 0;
+    int opened = 0;
+    for (int r = 0; r < W; ++r) bases[r] = nullptr;
+    if (fine) {
+        for (int r = 0; r < W; ++r) {
+            if (r == dp->rank) { bases[r] = local_base; continue; }
+            if (cudaIpcOpenMemHandle(&bases[r], all[r].handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+                cudaGetLastError();
+                bases[r] = nullptr;
+                fine = false;
+                break;
+            }
+            ++opened;
+        }
+    }
+    // second round: did every rank manage to open every peer?
+    Record verdict;
+    std::memset(&verdict, 0, sizeof(verdict));
+    verdict.ok = fine ? 1 : 0;
+    bool all_fine = gather(verdict);
+    for (int r = 0; all_fine && r < W; ++r) all_fine = all[r].ok != 0;
+    if (!all_fine) {
+        for (int r = 0; r < W; ++r)
+            if (r != dp->rank && bases[r]) { cudaIpcCloseMemHandle(bases[r]); bases[r] = nullptr; }
+        (void)opened;
+    }
+    if (d_send) cudaFree(d_send);
+    if (d_recv) cudaFree(d_recv);
+    if (s) cudaStreamDestroy(s);
+    cudaGetLastError();
+    return all_fine ? DCG_OK : fail(DCG_ERR_UNSUPPORTED, "dcg_dp: the ranks could not map each other's memory");
+}
+
+void dp_unmap_peers(dcg_dp* dp, void** bases)
+{
+    if (!dp) return;
+    for (int r = 0; r < dp->world && r < 8; ++r)
+        if (r != dp->rank && bases[r]) { cudaIpcCloseMemHandle(bases[r]); bases[r] = nullptr; }
+}
 
 // Several in-place sums as one NCCL group (one launch).
 int dp_allreduce_group(dcg_dp* dp, float* const* bufs, const size_t* counts, int n, cudaStream_t stream)

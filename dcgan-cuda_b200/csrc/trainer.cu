@@ -27,6 +27,14 @@ void* dp_mem_alloc(size_t bytes);
 void dp_mem_free(void* p);
 void dp_register(dcg_dp* dp, void* buf, size_t bytes);
 int dp_world(const dcg_dp* dp);
+int dp_rank(const dcg_dp* dp);
+int dp_map_peers(dcg_dp* dp, void* local_base, void** bases);
+void dp_unmap_peers(dcg_dp* dp, void** bases);
+// dp_adam.cu: gradient sum over the ranks + Adam + parameter broadcast as one kernel over peer memory
+int dp_reduce_adam_launch(int rank, int world, float* const* grads, float* const* params, float* m, float* v,
+                          unsigned* const* ready, unsigned* const* done, unsigned* epoch, unsigned* ticket, size_t n_floats,
+                          float lr_t, float a1, float b1, float a2, float b2, float eps, float scale, const float* lr_t_dev,
+                          cudaStream_t stream);
 int dp_allreduce_group(dcg_dp* dp, float* const* bufs, const size_t* counts, int n, cudaStream_t stream);
 }  // namespace dcg
 
@@ -79,6 +87,11 @@ struct dcg_trainer {
     dcg_dp* dp = nullptr;
     cudaStream_t comm_stream = nullptr;
     cudaEvent_t ev_grads = nullptr, ev_summed = nullptr;
+    // Fused update (dp_adam.cu): every rank's arena mapped into this process, and per network the
+    // flag words the peers write (in the arena, so that they are mapped along with it).
+    bool fused_update = false;
+    void* peer_arena[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    Tensor sync_words[2];   // [0] discriminator, [1] generator: ready[8] | done[8] | epoch | ticket
 
     // parameters / gradients / Adam moments: index 0..9 = (k0,b0,...,k3,b3,dense w,dense b)
     Tensor g_param[10], g_grad[10], g_m[10], g_v[10];
@@ -193,6 +206,8 @@ void layout(dcg_trainer* t, Alloc& a)
     t->z = a.get((size_t)B * kZ);
     t->ones = a.get(B); t->zeros = a.get(B);
     t->lr_dev = a.get(4);
+    t->sync_words[0] = a.get(32);
+    t->sync_words[1] = a.get(32);
     t->d_loss = a.get(1); t->d1_loss = a.get(1); t->d2_loss = a.get(1); t->g_loss = a.get(1);
     t->g0z = a.get((size_t)B * 8192); t->g0a = a.get((size_t)B * 8192);
     for (int i = 0; i < kLayers; ++i) {
@@ -560,6 +575,34 @@ int sum_over_ranks(dcg_trainer* t, Tensor& grads, cudaStream_t stream)
     return dcg::dp_allreduce_group(t->dp, bufs, counts, 1, stream);
 }
 
+// One network's data-parallel update as a single kernel: sum of the ranks' gradients + Adam on this rank's
+// slice + broadcast of the slice's new parameters (dp_adam.cu).  net: 0 discriminator, 1 generator.
+int fused_update(dcg_trainer* t, int net, float* step, float scale, const float* lr_dev, cudaStream_t stream)
+{
+    const int W = t->cfg.world, R = dcg::dp_rank(t->dp);
+    Tensor& params = net == 0 ? t->d_params_all : t->g_params_all;
+    Tensor& grads = net == 0 ? t->d_grads_all : t->g_grads_all;
+    Tensor* m = net == 0 ? t->d_m : t->g_m;
+    Tensor* v = net == 0 ? t->d_v : t->g_v;
+    float *g_ptr[8], *p_ptr[8];
+    unsigned *ready[8], *done[8];
+    for (int r = 0; r < W; ++r) {   // same layout on every rank: a peer's tensor sits at the same offset in its arena
+        uint8_t* base = static_cast<uint8_t*>(t->peer_arena[r]);
+        g_ptr[r] = reinterpret_cast<float*>(base + (reinterpret_cast<uint8_t*>(grads.p) - t->arena));
+        p_ptr[r] = reinterpret_cast<float*>(base + (reinterpret_cast<uint8_t*>(params.p) - t->arena));
+        unsigned* words = reinterpret_cast<unsigned*>(base + (reinterpret_cast<uint8_t*>(t->sync_words[net].p) - t->arena));
+        ready[r] = words;
+        done[r] = words + 8;
+    }
+    unsigned* mine = reinterpret_cast<unsigned*>(t->sync_words[net].p);
+    const float lr_t = lr_dev ? 0.f : dcg_adam_lr_t(step, t->cfg.lr, t->cfg.beta1, t->cfg.beta2);
+    dcg::ProfScope scope(t->ctx, "dp_reduce_adam", 0.0);
+    // m / v of a network are contiguous like its parameters: the arrays start at m[0] / v[0]
+    return dcg::dp_reduce_adam_launch(R, W, g_ptr, p_ptr, m[0].p, v[0].p, ready, done, mine + 16, mine + 17, params.n, lr_t,
+                                      t->cfg.beta1, 1.f - t->cfg.beta1, t->cfg.beta2, 1.f - t->cfg.beta2, t->cfg.eps, scale,
+                                      lr_dev, stream);
+}
+
 // The data-parallel iteration (world > 1, communicator attached): the same three runs, each followed
 // by ONE sum of that network's gradient arena over the ranks and the replicated Adam step, which
 // divides by the world size.  The discriminator's sum runs on the communication stream under the
@@ -577,18 +620,27 @@ int enqueue_step_dp(dcg_trainer* t, const float* lr_dev)
             if ((st = dcg_add(t->d_grad[i].p, t->d_grad2[i].p, t->d_grad[i].p, t->d_grad[i].n, t->stream))) return st;
     DCG_CUDA(cudaEventRecord(t->ev_grads, t->stream));
     DCG_CUDA(cudaStreamWaitEvent(t->comm_stream, t->ev_grads, 0));
-    if ((st = sum_over_ranks(t, t->d_grads_all, t->comm_stream))) return st;
+    if (t->fused_update) {   // sum + Adam + broadcast in one kernel, under the generator's forward pass
+        if ((st = fused_update(t, 0, &t->d_t, scale, lr_dev, t->comm_stream))) return st;
+    } else if ((st = sum_over_ranks(t, t->d_grads_all, t->comm_stream))) {
+        return st;
+    }
     DCG_CUDA(cudaEventRecord(t->ev_summed, t->comm_stream));
     if ((st = dcg_run_nodes(t->ctx, t->g_nodes.data(), fwd, t->cfg.fuse))) return st;
     DCG_CUDA(cudaStreamWaitEvent(t->stream, t->ev_summed, 0));
-    if ((st = apply_adam(t, t->d_param, t->d_grad, nullptr, t->d_m, t->d_v, &t->d_t, scale, lr_dev))) return st;
+    if (!t->fused_update &&
+        (st = apply_adam(t, t->d_param, t->d_grad, nullptr, t->d_m, t->d_v, &t->d_t, scale, lr_dev)))
+        return st;
     if ((st = dcg_run_nodes(t->ctx, t->g_nodes.data() + fwd, all - fwd, t->cfg.fuse))) return st;
     for (int rep = 0; rep < 2; ++rep) {
         if (rep == 1 && (st = dcg_run_nodes(t->ctx, t->g_nodes.data(), all, t->cfg.fuse))) return st;
-        if ((st = sum_over_ranks(t, t->g_grads_all, t->stream))) return st;
-        if ((st = apply_adam(t, t->g_param, t->g_grad, nullptr, t->g_m, t->g_v, &t->g_t, scale,
-                             lr_dev ? lr_dev + 1 + rep : nullptr)))
-            return st;
+        const float* lr = lr_dev ? lr_dev + 1 + rep : nullptr;
+        if (t->fused_update) {
+            if ((st = fused_update(t, 1, &t->g_t, scale, lr, t->stream))) return st;
+        } else {
+            if ((st = sum_over_ranks(t, t->g_grads_all, t->stream))) return st;
+            if ((st = apply_adam(t, t->g_param, t->g_grad, nullptr, t->g_m, t->g_v, &t->g_t, scale, lr))) return st;
+        }
     }
     return DCG_OK;
 }
@@ -690,7 +742,15 @@ extern "C" int dcg_trainer_create_dp(dcg_trainer** out, const dcg_trainer_config
     Alloc dry{t, true};
     layout(t, dry);
     t->arena_bytes = dcg::align_up(dry.off, 256) + 256;
-    if (t->dp) {   // memory NCCL allocated itself is eligible for its in-switch reduction of user buffers
+    // Data parallel: by default the update is the fused kernel over peer memory (dp_adam.cu), which
+    // needs a cudaMalloc'ed arena (CUDA IPC); DCG_DP_FUSED=0 keeps NCCL all-reduce + replicated Adam,
+    // with the arena from NCCL's own allocator (eligible for its in-switch reduction of user buffers).
+    bool want_fused = false;
+    if (t->dp) {
+        const char* f = getenv("DCG_DP_FUSED");
+        want_fused = !(f && atoi(f) == 0) && cfg->world <= 8;
+    }
+    if (t->dp && !want_fused) {
         t->arena = static_cast<uint8_t*>(dcg::dp_mem_alloc(t->arena_bytes));
         t->arena_from_nccl = t->arena != nullptr;
     }
@@ -728,7 +788,12 @@ extern "C" int dcg_trainer_create_dp(dcg_trainer** out, const dcg_trainer_config
     cudaMemcpyAsync(t->ones.p, one.data(), one.size() * sizeof(float), cudaMemcpyHostToDevice, t->stream);
     cudaStreamSynchronize(t->stream);
     build_lists(t);
-    if (t->dp) {   // the two buffers the communicator reduces every iteration
+    if (t->dp && want_fused) {
+        // collective: every rank maps every other rank's arena; all ranks agree on the outcome
+        cudaStreamSynchronize(t->stream);   // the arena (flag words included) is zeroed before anyone may write to it
+        t->fused_update = dcg::dp_map_peers(t->dp, t->arena, t->peer_arena) == DCG_OK;
+    }
+    if (t->dp && !t->fused_update) {   // the two buffers the communicator reduces every iteration
         dcg::dp_register(t->dp, t->d_grads_all.p, t->d_grads_all.n * sizeof(float));
         dcg::dp_register(t->dp, t->g_grads_all.p, t->g_grads_all.n * sizeof(float));
     }
@@ -747,6 +812,16 @@ extern "C" void dcg_trainer_destroy(dcg_trainer* t)
                                       &t->step_graph})
         if (g->exec) cudaGraphExecDestroy(g->exec);
     if (t->ctx) dcg_context_destroy(t->ctx);
+    if (t->fused_update) {
+        // COLLECTIVE: an exported arena must not be freed while a peer still has it mapped, so every rank
+        // closes its mappings, then the ranks meet (a one-float all-reduce), then the arenas go
+        cudaDeviceSynchronize();
+        dcg::dp_unmap_peers(t->dp, t->peer_arena);
+        float* token[1] = {t->lr_dev.p + 3};
+        const size_t one[1] = {1};
+        if (dcg::dp_allreduce_group(t->dp, token, one, 1, t->stream) == DCG_OK) cudaStreamSynchronize(t->stream);
+        cudaGetLastError();
+    }
     if (t->arena) {
         if (t->arena_from_nccl) dcg::dp_mem_free(t->arena);
         else cudaFree(t->arena);
@@ -929,6 +1004,31 @@ extern "C" int dcg_trainer_save(dcg_trainer* t, const char* path)
         t->snap_floats = total;
         DCG_CUDA(cudaEventCreateWithFlags(&t->ev_snap, cudaEventDisableTiming));
     }
+    if (t->fused_update) {
+        // The moments of a parameter slice only live on the rank that owns it.  COLLECTIVE in this mode:
+        // every rank calls save after the same iteration; between two barriers each rank copies the
+        // other owners' slices of m and v out of their arenas, so that the file holds complete state.
+        const int W = t->cfg.world, R = dcg::dp_rank(t->dp);
+        float* token[1] = {t->lr_dev.p + 3};
+        const size_t one[1] = {1};
+        if ((st = dcg::dp_allreduce_group(t->dp, token, one, 1, t->stream))) return st;   // everybody's updates are done
+        for (int net = 0; net < 2; ++net) {
+            const Tensor& params = net == 0 ? t->d_params_all : t->g_params_all;
+            Tensor* mv[2] = {net == 0 ? t->d_m : t->g_m, net == 0 ? t->d_v : t->g_v};
+            const size_t n4 = (params.n + 3) / 4, chunk = (n4 + W - 1) / W;
+            for (int r = 0; r < W; ++r) {
+                if (r == R) continue;
+                const size_t lo = chunk * r, hi = lo + chunk < n4 ? lo + chunk : n4;
+                if (hi <= lo) continue;
+                for (int q = 0; q < 2; ++q) {
+                    uint8_t* mine = reinterpret_cast<uint8_t*>(mv[q][0].p) + lo * 16;
+                    const uint8_t* theirs = static_cast<uint8_t*>(t->peer_arena[r]) + (mine - t->arena);
+                    DCG_CUDA(cudaMemcpyAsync(mine, theirs, (hi - lo) * 16, cudaMemcpyDefault, t->stream));
+                }
+            }
+        }
+        if ((st = dcg::dp_allreduce_group(t->dp, token, one, 1, t->stream))) return st;   // nobody moves on while a peer still reads
+    }
     size_t off = 0;
     for (const CkptTensor& c : lay) {   // stream-ordered behind the updates enqueued so far
         DCG_CUDA(cudaMemcpyAsync(t->snap + off, c.t.p, c.t.n * sizeof(float), cudaMemcpyDeviceToHost, t->stream));
@@ -1031,6 +1131,12 @@ extern "C" int dcg_trainer_tensor(dcg_trainer* t, const char* name, float** ptr,
 extern "C" dcg_context* dcg_trainer_context(dcg_trainer* t) { return t ? t->ctx : nullptr; }
 
 extern "C" uint64_t dcg_trainer_step_launches(const dcg_trainer* t) { return t ? t->last_step_launches : 0; }
+
+extern "C" int dcg_trainer_dp_mode(const dcg_trainer* t)
+{
+    if (!t || !t->dp) return 0;
+    return t->fused_update ? 2 : 1;
+}
 
 extern "C" int dcg_trainer_step_mode(const dcg_trainer* t)
 {

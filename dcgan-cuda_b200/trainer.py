@@ -289,10 +289,15 @@ class Trainer:
         """'graph' once the whole iteration replays as one CUDA graph, 'warmup' before, 'eager' if capturing it failed."""
         return {2: "graph", 1: "warmup", 0: "eager"}.get(int(lib.dcg_trainer_step_mode(self._h)), "unknown")
 
+    def dp_mode(self):
+        """'fused' (sum + Adam + broadcast as one kernel over peer memory), 'nccl' (all-reduce + replicated Adam) or 'none'."""
+        return {2: "fused", 1: "nccl", 0: "none"}.get(int(lib.dcg_trainer_dp_mode(self._h)), "unknown")
+
     def launches_per_step(self):
         return int(lib.dcg_trainer_step_launches(self._h))
 
     def close(self):
+        """Releases the trainer.  Data parallel: collective - every rank calls it."""
         if self._h:
             self._views.clear()
             lib.dcg_trainer_destroy(self._h)
@@ -303,7 +308,10 @@ class Trainer:
             self._dp = ctypes.c_void_p()
 
     def __del__(self):
+        # A data-parallel trainer is torn down collectively (close() on every rank): never from the
+        # garbage collector, where the ranks would not meet.  Process exit releases it anyway.
         try:
-            self.close()
+            if not getattr(self, "_dp", None):
+                self.close()
         except Exception:
             pass

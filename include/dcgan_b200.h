@@ -434,6 +434,11 @@ int dcg_trainer_save_wait(dcg_trainer* t);
 int dcg_trainer_load(dcg_trainer* t, const char* path);
 /* The trainer's execution context (for dcg_context_profile_begin / _end around its phases). */
 dcg_context* dcg_trainer_context(dcg_trainer* t);
+/* How a data-parallel trainer exchanges gradients: 0 = no communicator, 1 = NCCL all-reduce + replicated Adam,
+ * 2 = the fused kernel over peer memory (every rank sums its 1/W slice of all ranks' gradients over NVLink,
+ * applies Adam to it and writes the new parameters of the slice to every rank; the default where the ranks
+ * can map each other's memory, DCG_DP_FUSED=0 selects 1). */
+int dcg_trainer_dp_mode(const dcg_trainer* t);
 /* How dcg_trainer_step runs: 2 = the whole iteration replays as one CUDA graph, 1 = still warming up
  * (eager / per-list graphs), 0 = capturing the iteration failed and it stays eager. */
 int dcg_trainer_step_mode(const dcg_trainer* t);

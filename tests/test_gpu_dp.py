@@ -5,11 +5,13 @@ process on a mismatch:
   * fp32 path: the rank gradients of the D run, summed over ranks through the communicator behind
     the C ABI (dcg_dp_allreduce) and divided by 2, equal a single-GPU D run on the concatenated
     batch (2e-5 * max) - the average of per-shard mean gradients is the global-batch gradient;
-  * TF32 path, 3 whole iterations (dcg_trainer_step: lists, the three gradient sums and Adam steps,
-    replayed as one CUDA graph from the third on): parameters are bit-identical on both ranks, and
-    differ from the initial ones;
-  * the same with the collectives issued by torch.distributed between the library's phases.
-No peer-memory kernels are involved: plain NCCL.
+  * fp32 path, one whole iteration with the fused update (gradient sum + Adam + parameter broadcast as
+    one kernel over peer memory, plain peer loads / stores, no multimem): the parameters agree with a
+    single-GPU iteration on the concatenated batch up to Adam sign flips of rounding-level gradients;
+  * TF32 path, 4 whole iterations (dcg_trainer_step, replayed as one CUDA graph from the third on):
+    parameters are bit-identical on both ranks and differ from the initial ones - with the fused
+    update, with NCCL all-reduce + replicated Adam behind the C ABI, and with the collectives issued
+    by torch.distributed between the library's phases.
 """
 import os
 import subprocess
@@ -58,9 +60,35 @@ def _worker():
         err = (got - ref).abs().max().item()
         assert err <= 2e-5 * ref.abs().max().item(), ("averaged gradients", err, ref.abs().max().item())
 
+    # ---- one whole iteration, fused update (sum + Adam + broadcast as one kernel over peer memory), fp32 path,
+    # against a single GPU on the concatenated batch: Adam's first steps move every weight by about lr in the
+    # direction of its gradient's sign, so the two agree except where a gradient at rounding level changes sign ----
+    tr = pkg.Trainer(batch=B, precision=pkg.PREC_FP32, seed=234, world=world)
+    assert tr.dp_mode() == "fused", tr.dp_mode()
+    tr.x.copy_(xs)
+    tr.z.copy_(zs)
+    tr.step()
+    torch.cuda.synchronize()
+    assert pkg.lib.dcg_device_status() == 0, pkg.lib.dcg_last_error()
+    got = torch.cat([tr.tensor("d_params"), tr.tensor("g_params")]).cpu()
+    tr.close()
+    if rank == 0:
+        one = pkg.Trainer(batch=world * B, precision=pkg.PREC_FP32, seed=234, world=1)
+        one.x.copy_(x_all)
+        one.z.copy_(z_all)
+        one.step()
+        torch.cuda.synchronize()
+        ref = torch.cat([one.tensor("d_params"), one.tensor("g_params")]).cpu()
+        one.close()
+        diff = (got - ref).abs()
+        assert diff.max().item() <= 1.3e-3, diff.max().item()          # at most a few flipped steps of lr = 2e-4
+        assert (diff <= 1e-6).float().mean().item() >= 0.99, (diff <= 1e-6).float().mean().item()
+
     # ---- replicas stay bit-identical over whole iterations ----
-    for comm in ("abi", "torch"):
+    for comm, fused in (("abi", "1"), ("abi", "0"), ("torch", "1")):
+        os.environ["DCG_DP_FUSED"] = fused
         tr = pkg.Trainer(batch=B, precision=pkg.PREC_TF32, seed=234, world=world, comm=comm)
+        assert tr.dp_mode() == {("abi", "1"): "fused", ("abi", "0"): "nccl", ("torch", "1"): "none"}[(comm, fused)]
         start = torch.cat([tr.tensor("d_params"), tr.tensor("g_params")]).clone()
         tr.x.copy_(xs)
         tr.z.copy_(zs)
@@ -72,7 +100,7 @@ def _worker():
         both = [torch.empty_like(mine) for _ in range(world)]
         dist.all_gather(both, mine)
         for other in both[1:]:
-            assert torch.equal(both[0], other), "replicas differ (%s)" % comm
+            assert torch.equal(both[0], other), "replicas differ (%s, fused %s)" % (comm, fused)
         assert not torch.equal(mine, start)
         assert torch.isfinite(mine).all()
         tr.close()
