@@ -144,6 +144,8 @@ SIGNATURES = {
     "dcg_last_error": (ctypes.c_char_p, []),
     "dcg_debug_set_wait_limit": (None, [ctypes.c_longlong]),
     "dcg_debug_skip_stage": (None, [c_int]),
+    "dcg_debug_set_dx_mode": (None, [c_int]),
+    "dcg_debug_fused_dx_launches": (ctypes.c_uint64, []),
     "dcg_build_info": (ctypes.c_char_p, []),
     "dcg_launches_total": (ctypes.c_uint64, []),
 }

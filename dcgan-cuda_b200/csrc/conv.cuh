@@ -32,6 +32,10 @@ int conv_tc_dk(const dcg_conv_desc& d, const float* x, const float* dy, float* d
 // -1 restores the default, 0 leaves it; skip_stage: pipeline stage the producer leaves out (-1: none,
 // -2: leave as is).
 void conv_tc_set_hooks(long long wait_cycles, int skip_stage);
+// Input gradient with the parity classes of a tile in one CTA: 0 never, 1 where it pays (default), 2 wherever
+// the shape allows, anything else: back to the default.
+void conv_tc_set_dx_mode(int mode);
+unsigned long long conv_tc_fused_dx_launches();   // launches of the class-fused kernel so far
 
 // Shape validation shared by the entry points: 0 or a negative dcg_status.
 int conv_check_desc(const dcg_conv_desc* d, const char* who);

@@ -875,6 +875,291 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+// ---- DX with all parity classes of a pixel tile in one CTA -------------------------------------------
+// The parity classes of the input gradient (pix mod stride) read the SAME windows of dy, only paired
+// with different kernel taps: class (ph, pw), tap (di, dj) reads dy at pixel offset
+// ((ph + pad - di) / s, (pw + pad - dj) / s) of the class grid.  For a 5x5 kernel at stride 2 the 25
+// (class, tap) pairs share 9 distinct windows.  conv_tc_kernel<DX> runs every class as a tile of its
+// own and so fetches a dy tile from L2 once per tap; with a narrow N tile (64 input channels: A 16 KB
+// against B 8 KB per stage) that fetch is two thirds of what the SM has to take in, and taking
+// operands in is what bounds the main loop.  This kernel gives one CTA the 128 pixels of ALL classes:
+// one accumulator per class (classes x bn <= 512 TMEM columns), each window fetched once and
+// multiplied against the weight tiles of every pair that reads it - 9 x 16 KB + 25 x 8 KB per 32
+// output channels instead of 25 x 24 KB.  A pipeline stage is one window plus the weight tiles of up to
+// `pb` pairs that read it (a window with more pairs takes several stages and is fetched again for
+// each).  The windows are ordered so that the classes complete one after the other; the epilogue
+// of a finished class (through a transposition buffer of its own, not the stage ring) runs under
+// the main loop of the rest.  No K partitions: the planner only picks this kernel when the tiles
+// alone fill the GPU.
+//
+// The accumulators of the classes sit side by side in TMEM, and the weight tiles of a stage are stacked
+// in shared memory in the same order, so pairs whose classes are neighbours there are ONE MMA with
+// N = count x bn columns.  That matters for narrow tiles: an N = 64 MMA takes as long as an N = 128
+// one (measured: the MMA-only time of the 64-channel layer is 1.8 x that of its N = 128 forward), so
+// the 25 N = 64 products of a channel chunk become 4 of N = 256, 4 of N = 128 and 1 of N = 64.
+struct CfWin {
+    signed char sy, sx;        // window: dy pixel (i + sy, j + sx) for class pixel (i, j)
+    unsigned char n;           // pairs of this stage, in TMEM order
+    unsigned char last;        // bit j: pair j is the last contribution to its class (in the last channel chunk)
+    unsigned char fresh;       // bit j: pair j is the first contribution to its class (in the first channel chunk)
+    unsigned char cls[4], kh[4], kw[4];
+    unsigned char slot[4];     // TMEM position of the pair's accumulator (columns slot * bn ...)
+    unsigned char glen[4];     // pair j starts an MMA over glen[j] adjacent accumulators (0: it belongs to an earlier one)
+};
+struct CfTable {
+    int nwin, ncls;            // stages per channel chunk, parity classes
+    int slot_bytes;            // stage size: A tile + pb weight tiles
+    int order[4];              // classes in the order in which they complete
+    int slot_of_class[4];      // TMEM position of every class
+    CfWin win[32];
+};
+constexpr int kCfHalf = 64;                // accumulator columns the epilogue moves at a time
+__host__ __device__ constexpr int kCfRedBytes() { return kRedFloats(kCfHalf) * 4 + BM * 8; }
+
+// The fused chain over four 16-byte items at once: every optional step is tested once and its loads
+// (bias, gate) are in flight together.  goff < 0 marks an item that is not stored.
+__device__ __forceinline__ void cf_chain_store4(const EpilogueArgs& e, float* out, float4 (&acc)[4], const long long (&goff)[4],
+                                                const int (&ch)[4])
+{
+    if (e.raw_out) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (goff[u] >= 0) *reinterpret_cast<float4*>(e.raw_out + goff[u]) = acc[u];
+    }
+    if (e.bias) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float4 bv = __ldg(reinterpret_cast<const float4*>(e.bias + ch[u]));
+            acc[u].x = __fadd_rn(acc[u].x, bv.x); acc[u].y = __fadd_rn(acc[u].y, bv.y);
+            acc[u].z = __fadd_rn(acc[u].z, bv.z); acc[u].w = __fadd_rn(acc[u].w, bv.w);
+        }
+    }
+    if (e.pre_act) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (goff[u] >= 0) *reinterpret_cast<float4*>(e.pre_act + goff[u]) = acc[u];
+    }
+    if (e.act != DCG_ACT_NONE) {
+        const int act = e.act;
+        const float alpha = e.alpha;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            acc[u].x = act_apply(acc[u].x, act, alpha); acc[u].y = act_apply(acc[u].y, act, alpha);
+            acc[u].z = act_apply(acc[u].z, act, alpha); acc[u].w = act_apply(acc[u].w, act, alpha);
+        }
+    }
+    if (e.gate) {
+        float4 g[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            g[u] = goff[u] >= 0 ? __ldg(reinterpret_cast<const float4*>(e.gate + goff[u])) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const int gact = e.gate_act;
+        const float galpha = e.gate_alpha;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            acc[u].x = act_grad_apply(g[u].x, acc[u].x, gact, galpha);
+            acc[u].y = act_grad_apply(g[u].y, acc[u].y, gact, galpha);
+            acc[u].z = act_grad_apply(g[u].z, acc[u].z, gact, galpha);
+            acc[u].w = act_grad_apply(g[u].w, acc[u].w, gact, galpha);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+        if (goff[u] >= 0) *reinterpret_cast<float4*>(out + goff[u]) = acc[u];
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+conv_dxf_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const __grid_constant__ Params p, const __grid_constant__ CfTable t)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem0 = smem_u32(smem_raw);
+    const uint32_t ring = (smem0 + 1023u) & ~1023u;
+    const long long wait_limit = p.wait_cycles;
+    const uint32_t slot_bytes = (uint32_t)t.slot_bytes;
+    const uint32_t red_base = ring + (uint32_t)p.stages * slot_bytes;
+    const uint32_t bar_base = red_base + (uint32_t)kCfRedBytes();
+    const uint32_t full_bar = bar_base;
+    const uint32_t empty_bar = bar_base + 8u * p.stages;
+    const uint32_t cls_bar = bar_base + 16u * p.stages;     // accumulator of class c complete
+    const uint32_t tmem_slot = cls_bar + 32u;
+    uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem0));
+    float* red = reinterpret_cast<float*>(smem_raw + (red_base - smem0));
+    long long* s_rowoff = reinterpret_cast<long long*>(red + kRedFloats(kCfHalf));
+
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
+    const int ncls = t.ncls, nwin = t.nwin;
+    const uint32_t b_bytes = (uint32_t)p.bn * BK * 4;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(full_bar + 8u * s, 1);
+            mbar_init(empty_bar + 8u * s, 1);
+        }
+        for (int c = 0; c < 4; ++c) mbar_init(cls_bar + 8u * c, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    }
+    int tmem_cols = 32;
+    while (tmem_cols < ncls * p.bn) tmem_cols <<= 1;
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // blockIdx.x = pixel tile * n_tiles + channel tile
+    const int n_tile = blockIdx.x % p.n_tiles, m_tile = blockIdx.x / p.n_tiles;
+    const int j0 = (m_tile % p.tiles_w) * p.TW;
+    const int i0 = ((m_tile / p.tiles_w) % p.tiles_h) * p.TH;
+    const int n0 = (m_tile / (p.tiles_w * p.tiles_h)) * p.TN;
+    const int ch0 = n_tile * p.bn;
+    const int ncols_valid = min(p.bn, p.C - ch0);
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = *tmem_slot_ptr;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    if (warp == 0) {
+        // ===== TMA producer: for every table entry, for every channel chunk: the window, then its weight tiles =====
+        int s = 0, it = 0;
+        uint32_t phase = 0;
+        bool alive = true;
+        for (int w = 0; w < nwin && alive; ++w) {
+            const CfWin& wn = t.win[w];
+            const int sy = wn.sy, sx = wn.sx, np = wn.n;
+            for (int chunk = 0; chunk < p.kchunks; ++chunk, ++it) {
+                if (!mbar_wait_warp(empty_bar + 8u * s, phase ^ 1u, 0, it, wait_limit)) { alive = false; break; }
+                if (elect_one()) {
+                    const uint32_t fb = full_bar + 8u * s;
+                    const uint32_t dst = ring + (uint32_t)s * slot_bytes;
+                    mbar_expect_tx(fb, (uint32_t)A_STAGE_BYTES + (uint32_t)np * b_bytes);
+                    tma_load_4d(dst, &map_a, fb, chunk * BK, j0 + sx, i0 + sy, n0);
+                    for (int j = 0; j < np; ++j)
+                        tma_load_4d(dst + (uint32_t)A_STAGE_BYTES + (uint32_t)j * b_bytes, &map_b, fb, chunk * BK, ch0,
+                                    (int)wn.kw[j], (int)wn.kh[j]);
+                }
+                if (++s == p.stages) { s = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        // ===== MMA issuer =====
+        const uint64_t desc0 = make_smem_desc(ring, 16u, 1024u, kLayoutSw128);   // K-major, 128-byte rows, 8-row groups 1024 B apart
+        const uint32_t slot16 = slot_bytes >> 4, b16 = b_bytes >> 4;
+        int s = 0, it = 0;
+        uint32_t phase = 0, done = 0;
+        bool alive = true;
+        for (int w = 0; w < nwin && alive; ++w) {
+            const CfWin& wn = t.win[w];
+            const int np = wn.n;
+            const uint32_t last = wn.last, fresh = wn.fresh;
+            for (int chunk = 0; chunk < p.kchunks; ++chunk, ++it) {
+                if (!mbar_wait_warp(full_bar + 8u * s, phase, 1, it, wait_limit)) { alive = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const bool final_chunk = chunk == p.kchunks - 1;
+                if (elect_one()) {
+                    const uint64_t adesc = desc0 + (uint64_t)((uint32_t)s * slot16);
+                    for (int j = 0; j < np; ++j) {
+                        const int cnt = wn.glen[j];
+                        if (cnt > 0) {   // one MMA per K step over the cnt adjacent accumulators that start here
+                            const uint32_t idesc = make_idesc(0, 0, cnt * p.bn, BM);
+                            const uint64_t bdesc = adesc + (uint64_t)((uint32_t)(A_STAGE_BYTES >> 4) + (uint32_t)j * b16);
+                            const uint32_t acc = tmem_d + (uint32_t)(wn.slot[j] * p.bn);
+                            const bool overwrite = chunk == 0 && ((fresh >> j) & 1u);
+#pragma unroll
+                            for (int kk = 0; kk < BK / 8; ++kk)
+                                tcgen05_mma_tf32(acc, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc,
+                                                 (overwrite && kk == 0) ? 0u : 1u);
+                        }
+                    }
+                    if (final_chunk)
+                        for (int j = 0; j < np; ++j)
+                            if ((last >> j) & 1u) tcgen05_commit(cls_bar + 8u * wn.cls[j]);
+                    tcgen05_commit(empty_bar + 8u * s);
+                }
+                if (final_chunk)
+                    for (int j = 0; j < np; ++j)
+                        if ((last >> j) & 1u) done |= 1u << wn.cls[j];
+                if (++s == p.stages) { s = 0; phase ^= 1u; }
+            }
+        }
+        // a pipeline that gave up still releases the epilogue (which stores nothing then)
+        if (elect_one())
+            for (int c = 0; c < ncls; ++c)
+                if (!((done >> c) & 1u)) tcgen05_commit(cls_bar + 8u * c);
+    } else {
+        // ===== epilogue: classes in completion order, 64 accumulator columns at a time =====
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        const int tid_e = threadIdx.x - 64;
+        const int tw = row % p.TW, th = (row / p.TW) % p.TH, tn = row / (p.TW * p.TH);
+        const EpilogueArgs& e = p.ep;
+        constexpr int QS = BM + 1;
+        for (int ci = 0; ci < ncls; ++ci) {
+            const int cls = t.order[ci];
+            const int ph = cls / p.sw, pw = cls % p.sw;
+            bool ok = mbar_wait(cls_bar + 8u * cls, 0, 2, cls, wait_limit);
+            ok = __all_sync(0xffffffffu, ok);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (warp < 6) {
+                const int n = n0 + tn, h = p.sh * (i0 + th) + ph, w = p.sw * (j0 + tw) + pw;
+                const bool valid = ok && n < p.N && h < p.H && w < p.W;
+                s_rowoff[row] = valid ? (long long)((((unsigned long long)n * p.H + h) * p.W + w) * p.C + ch0) : -1;
+            }
+            for (int half0 = 0; half0 < p.bn; half0 += kCfHalf) {
+                const int hcols = min(kCfHalf, p.bn - half0);
+                // TMEM -> transposition buffer: thread = row, the two warps of a lane quadrant take one 32-column slab each
+                const int c0 = half0 + ((warp - 2) >> 2) * 32;
+                if (c0 < half0 + hcols) {
+                    uint32_t r[32];
+                    const uint32_t taddr = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)(t.slot_of_class[cls] * p.bn + c0);
+                    const bool full = half0 + hcols - c0 >= 32;
+                    if (full) tmem_ld_32x32b_x32(taddr, r);
+                    else tmem_ld_32x32b_x16(taddr, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    float4* d4 = reinterpret_cast<float4*>(red) + ((c0 - half0) >> 2) * QS + row;
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        if (q < 4 || full)
+                            d4[q * QS] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                     __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(kEpi) : "memory");
+                // fused chain and stores: consecutive lanes take consecutive 16-byte column quads of a row
+                const int hq = hcols >> 2;
+                const float4* red4 = reinterpret_cast<const float4*>(red);
+                const int items = BM * hq;   // = kEpi * hq / 2: every thread has hq / 2 items, taken four at a time
+                for (int base = tid_e; base < items; base += 4 * kEpi) {
+                    float4 acc[4];
+                    long long goff[4];
+                    int ch[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int idx = base + u * kEpi;
+                        const bool in = idx < items;
+                        const int rr = in ? idx / hq : 0, q = in ? idx - rr * hq : 0;
+                        const int col = half0 + (q << 2);
+                        const long long ro = in ? s_rowoff[rr] : -1;
+                        acc[u] = red4[q * QS + rr];
+                        goff[u] = (ro < 0 || col >= ncols_valid) ? -1 : ro + col;
+                        ch[u] = ch0 + (col < ncols_valid ? col : 0);
+                    }
+                    cf_chain_store4(e, p.out, acc, goff, ch);
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(kEpi) : "memory");
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
+    }
+}
+
 // ---- narrow-channel DK: add the partitions' partial tiles -----------------------------------------
 // partial[m tile][partition][col][row] (col = 32 * kernel row + window slot, row = output channel).
 // Block = 32 rows x 8 lanes of one column: lane l adds partitions l, l+8, ... (all loads in
@@ -1334,6 +1619,153 @@ bool plan_dx(const dcg_conv_desc& d, Plan& pl)
     return true;
 }
 
+// When the input gradient fuses its parity classes (conv_dxf_kernel): 0 never, 1 where one CTA per tile fills the
+// GPU (default), 2 wherever the shape allows.  DCG_TC_DXF sets the default, dcg_debug_set_dx_mode overrides it.
+std::atomic<int> g_dxf_mode{-1};
+std::atomic<unsigned long long> g_dxf_launches{0};
+int dxf_mode()
+{
+    static const int from_env = [] { const char* v = getenv("DCG_TC_DXF"); return v ? atoi(v) : 1; }();
+    const int m = g_dxf_mode.load();
+    return m >= 0 ? m : from_env;
+}
+
+// The class-fused input gradient (conv_dxf_kernel): windows of dy, the (class, tap) pairs that read each, and
+// the order of both.
+bool plan_dxf(const dcg_conv_desc& d, Plan& pl, CfTable& t)
+{
+    const int mode = dxf_mode();
+    if (mode == 0 || t_plan_x3) return false;
+    if (d.c <= 4 || d.c % 4 != 0 || d.o % 4 != 0) return false;
+    if (d.stride_h > d.kh || d.stride_w > d.kw) return false;
+    const int ncls = d.stride_h * d.stride_w;
+    if (ncls < 2 || ncls > 4) return false;
+    Params& p = pl.p;
+    base_params(p, d);
+    const int ha = (d.h + d.stride_h - 1) / d.stride_h, wa = (d.w + d.stride_w - 1) / d.stride_w;
+    pixel_tile(BM, wa, ha, p.TW, p.TH, p.TN);
+    p.tiles_w = (wa + p.TW - 1) / p.TW; p.tiles_h = (ha + p.TH - 1) / p.TH; p.tiles_n = (d.n + p.TN - 1) / p.TN;
+    int bn = (d.c + 15) / 16 * 16;
+    if (bn > 128) bn = 128;
+    if (ncls * bn > 512) return false;
+    p.bn = bn;
+    p.n_tiles = (d.c + bn - 1) / bn;
+    p.kchunks = (d.o + BK - 1) / BK;
+    const int tiles = p.tiles_w * p.tiles_h * p.tiles_n * p.n_tiles;
+    // one CTA per tile, no K partitions: only where the tiles alone fill (most of) the GPU
+    if (mode != 2 && tiles * 4 < sm_count() * 3) return false;
+    // every (class, tap) pair with the window it reads
+    struct Pair { int sy, sx, cls, kh, kw; };
+    std::vector<Pair> pairs;
+    for (int ph = 0; ph < d.stride_h; ++ph)
+        for (int pw = 0; pw < d.stride_w; ++pw) {
+            const int rh = (ph + d.pad_top) % d.stride_h, eh = (ph + d.pad_top) / d.stride_h;
+            const int rw = (pw + d.pad_left) % d.stride_w, ew = (pw + d.pad_left) / d.stride_w;
+            for (int a = 0; rh + d.stride_h * a < d.kh; ++a)
+                for (int b = 0; rw + d.stride_w * b < d.kw; ++b)
+                    pairs.push_back({eh - a, ew - b, ph * d.stride_w + pw, rh + d.stride_h * a, rw + d.stride_w * b});
+        }
+    // classes in the order "fewest windows still to fetch first"; the windows follow that order
+    t = CfTable{};
+    t.ncls = ncls;
+    std::vector<std::pair<int, int>> wins;   // scheduled windows
+    auto scheduled = [&](int sy, int sx) {
+        for (auto& w : wins) if (w.first == sy && w.second == sx) return true;
+        return false;
+    };
+    bool finished[4] = {false, false, false, false};
+    for (int ci = 0; ci < ncls; ++ci) {
+        int best = -1, best_need = 1 << 30;
+        for (int c = 0; c < ncls; ++c) {
+            if (finished[c]) continue;
+            std::vector<std::pair<int, int>> need;
+            for (auto& q : pairs)
+                if (q.cls == c && !scheduled(q.sy, q.sx)) {
+                    bool seen = false;
+                    for (auto& n : need) seen |= n.first == q.sy && n.second == q.sx;
+                    if (!seen) need.push_back({q.sy, q.sx});
+                }
+            if ((int)need.size() < best_need) { best_need = (int)need.size(); best = c; }
+        }
+        if (best < 0) return false;
+        bool any = false;
+        for (auto& q : pairs)
+            if (q.cls == best) {
+                any = true;
+                if (!scheduled(q.sy, q.sx)) wins.push_back({q.sy, q.sx});
+            }
+        if (!any) return false;   // a class without taps
+        finished[best] = true;
+        t.order[ci] = best;
+    }
+    // stages: a window with its pairs, at most pb per stage (the stage ring holds about 48 KB per stage)
+    const int b_tile = bn * BK * 4;
+    int pb = (48 * 1024 - A_STAGE_BYTES) / b_tile;
+    if (pb > 4) pb = 4;
+    if (pb < 1) pb = 1;
+    // TMEM order of the classes: for 2 x 2 classes the cyclic order (0,0) (0,1) (1,1) (1,0), in which the classes
+    // of one row / one column parity are neighbours, so that the pairs of a window merge into wide MMAs
+    for (int c = 0; c < ncls; ++c) t.slot_of_class[c] = c;
+    if (d.stride_h == 2 && d.stride_w == 2) { t.slot_of_class[2] = 3; t.slot_of_class[3] = 2; }
+    int last_stage[4] = {-1, -1, -1, -1}, last_pair[4] = {0, 0, 0, 0};
+    bool started[4] = {false, false, false, false};
+    int ns = 0;
+    for (size_t w = 0; w < wins.size(); ++w) {
+        if (wins[w].first < -128 || wins[w].first > 127 || wins[w].second < -128 || wins[w].second > 127) return false;
+        // the pairs of this window in TMEM order
+        std::vector<Pair> mine;
+        for (auto& q : pairs)
+            if (q.sy == wins[w].first && q.sx == wins[w].second) mine.push_back(q);
+        for (size_t a = 0; a < mine.size(); ++a)
+            for (size_t b = a + 1; b < mine.size(); ++b)
+                if (t.slot_of_class[mine[b].cls] < t.slot_of_class[mine[a].cls]) std::swap(mine[a], mine[b]);
+        for (size_t first = 0; first < mine.size(); first += pb) {
+            if (ns == 32) return false;
+            CfWin& cw = t.win[ns];
+            cw.sy = (signed char)wins[w].first; cw.sx = (signed char)wins[w].second;
+            const size_t end = std::min(mine.size(), first + (size_t)pb);
+            int group_start = -1;
+            for (size_t a = first; a < end; ++a) {
+                const Pair& q = mine[a];
+                const int j = cw.n;
+                const int slot = t.slot_of_class[q.cls];
+                const bool fresh = !started[q.cls];
+                cw.cls[j] = (unsigned char)q.cls; cw.kh[j] = (unsigned char)q.kh; cw.kw[j] = (unsigned char)q.kw;
+                cw.slot[j] = (unsigned char)slot;
+                if (fresh) cw.fresh |= (unsigned char)(1u << j);
+                // joins the running MMA if its accumulator follows directly, starts the same way and N stays <= 256
+                const bool join = group_start >= 0 && cw.slot[j - 1] + 1 == slot &&
+                                  (((cw.fresh >> group_start) & 1u) != 0) == fresh &&
+                                  (cw.glen[group_start] + 1) * bn <= 256;
+                if (join) ++cw.glen[group_start];
+                else { group_start = j; cw.glen[j] = 1; }
+                last_stage[q.cls] = ns; last_pair[q.cls] = j;
+                ++cw.n;
+            }
+            for (int j = 0; j < cw.n; ++j) started[cw.cls[j]] = true;
+            ++ns;
+        }
+    }
+    t.nwin = ns;
+    for (int c = 0; c < ncls; ++c) {
+        if (last_stage[c] < 0) return false;
+        t.win[last_stage[c]].last |= (unsigned char)(1u << last_pair[c]);
+    }
+    t.slot_bytes = A_STAGE_BYTES + pb * b_tile;
+    p.splits = 1;
+    pl.grid = tiles;
+    int stages = (kMaxSmem - 1024 - kCfRedBytes() - 256) / t.slot_bytes;
+    if (stages > 8) stages = 8;
+    if (stages < 3) return false;
+    p.stages = stages;
+    pl.smem = (size_t)stages * t.slot_bytes + 1024 + kCfRedBytes() + 16 * stages + 64;
+    p.skip_stage = -1;
+    p.wait_cycles = kWaitCycles;
+    pl.partial_bytes = 0;
+    pl.ws_bytes = 0;
+    return true;
+}
+
 bool plan_dk(const dcg_conv_desc& d, Plan& pl)
 {
     const bool narrow = narrow_ok(d);
@@ -1466,6 +1898,9 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, Plan& pl, float* out, c
     return DCG_OK;
 }
 
+struct Prepared;
+int launch_dxf(Prepared& pr, float* out, const EpilogueArgs& ep, cudaStream_t stream);
+
 // Narrow-channel layers: builds the padded 4-channel image (and, for FWD, the repacked weights) in
 // the caller's scratch and returns their addresses.
 int narrow_prepare(const dcg_conv_desc& d, const Plan& pl, const float* x, const float* k, void* ws, size_t ws_bytes,
@@ -1517,7 +1952,45 @@ int map_window(CUtensorMap* map, const float* xp, const dcg_conv_desc& d, const 
 struct Prepared {
     Plan pl;
     CUtensorMap ma, mb;
+    bool dxf = false;   // input gradient with the parity classes fused (conv_dxf_kernel); cf is its table
+    CfTable cf;
 };
+
+int launch_dxf(Prepared& pr, float* out, const EpilogueArgs& ep, cudaStream_t stream)
+{
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(conv_dxf_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    });
+    if (attr_err != cudaSuccess)
+        return fail(DCG_ERR_CUDA, "cudaFuncSetAttribute(conv_dxf_kernel): %s", cudaGetErrorString(attr_err));
+    Params& p = pr.pl.p;
+    p.out = out;
+    p.ep = ep;
+    p.scratch = nullptr;
+    p.wait_cycles = g_wait_cycles.load();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)pr.pl.grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = pr.pl.smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    int na = 0;
+    static const int no_pdl = env_int("DCG_TC_NO_PDL");
+    if (!no_pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, conv_dxf_kernel, pr.ma, pr.mb, p, pr.cf);
+    if (err != cudaSuccess) return fail(DCG_ERR_CUDA, "conv_dxf_kernel launch: %s", cudaGetErrorString(err));
+    count_launch();
+    g_dxf_launches.fetch_add(1);
+    return DCG_OK;
+}
 
 struct CacheKey {
     int dev, kind, x3;
@@ -1575,7 +2048,11 @@ int build_fwd(const dcg_conv_desc& d, const float* x, const float* k, void* ws, 
 int build_dx(const dcg_conv_desc& d, const float* dy, const float* k, void* ws, size_t ws_bytes, Prepared& pr)
 {
     Plan& pl = pr.pl;
-    if (!plan_dx(d, pl)) return fail(DCG_ERR_UNSUPPORTED, "conv dx: shape not supported by the tensor path");
+    pr.dxf = plan_dxf(d, pl, pr.cf);
+    if (!pr.dxf) {
+        pl = Plan{};
+        if (!plan_dx(d, pl)) return fail(DCG_ERR_UNSUPPORTED, "conv dx: shape not supported by the tensor path");
+    }
     const Params& p = pl.p;
     int st = map_act_4d(&pr.ma, dy, d.n, d.ho, d.wo, d.o, p.TW, p.TH, p.TN, 1, 1);
     if (st) return st;
@@ -1630,7 +2107,7 @@ int prepared_call(int kind, const dcg_conv_desc& d, const void* a, const void* b
     CacheKey key;
     std::memset(&key, 0, sizeof(key));
     if (cudaGetDevice(&key.dev) != cudaSuccess) key.dev = -1;
-    key.kind = kind; key.x3 = t_plan_x3;
+    key.kind = kind; key.x3 = t_plan_x3 | (dxf_mode() << 1);   // the plan depends on both
     key.d = d; key.a = a; key.b = b; key.ws = ws; key.ws_bytes = ws_bytes;
     {
         std::lock_guard<std::mutex> lock(g_cache_mutex);
@@ -1715,6 +2192,7 @@ int conv_tc_dx(const dcg_conv_desc& d, const float* dy, const float* k, float* d
         DCG_LAUNCH_CHECK("col2im_kernel");
         return DCG_OK;
     }
+    if (pr.dxf) return launch_dxf(pr, dx, ep, stream);
     return launch<MODE_DX>(pr.ma, pr.mb, pl, dx, ep, d.c, ws, ws_bytes, stream);
 }
 
@@ -1732,6 +2210,9 @@ int conv_tc_dk(const dcg_conv_desc& d, const float* x, const float* dy, float* d
     const EpilogueArgs none{};
     return launch<MODE_DK>(pr.ma, pr.mb, pr.pl, dk, none, d.o, ws, ws_bytes, stream);
 }
+
+void conv_tc_set_dx_mode(int mode) { g_dxf_mode.store(mode < 0 || mode > 2 ? -1 : mode); }
+unsigned long long conv_tc_fused_dx_launches() { return g_dxf_launches.load(); }
 
 // wait_cycles: > 0 sets the limit, -1 restores the default, 0 leaves it; skip_stage: -2 leaves it.
 void conv_tc_set_hooks(long long wait_cycles, int skip_stage)
@@ -1768,6 +2249,9 @@ extern "C" void dcg_debug_set_wait_limit(long long sm_clocks)
 }
 
 extern "C" void dcg_debug_skip_stage(int stage) { dcg::conv_tc_set_hooks(0, stage < 0 ? -1 : stage); }
+
+extern "C" void dcg_debug_set_dx_mode(int mode) { dcg::conv_tc_set_dx_mode(mode); }
+extern "C" uint64_t dcg_debug_fused_dx_launches(void) { return dcg::conv_tc_fused_dx_launches(); }
 
 #ifdef DCG_TC_TRACING
 // Tuning aids of -DDCG_TC_TRACING builds, not part of the public header: copy the timelines recorded

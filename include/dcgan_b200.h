@@ -457,9 +457,15 @@ const char* dcg_last_error(void);
  *  dcg_debug_set_wait_limit  limit of every bounded barrier wait in SM clocks (<= 0 restores ~1 s);
  *  dcg_debug_skip_stage      the TMA producer leaves pipeline stage `stage` of every tile out (< 0: never), so
  *                            that a consumer's wait runs into the limit: the kernel then records the failure,
- *                            still terminates, and dcg_device_status() returns DCG_ERR_DEVICE. */
+ *                            still terminates, and dcg_device_status() returns DCG_ERR_DEVICE;
+ *  dcg_debug_set_dx_mode     which input-gradient kernel the tensor path plans: 0 = one tile per parity class,
+ *                            1 = the parity classes of a tile fused in one CTA where one CTA per tile fills the
+ *                            GPU (default), 2 = fused wherever the shape allows, < 0 = back to the default;
+ *  dcg_debug_fused_dx_launches  how often the fused kernel has been launched (tests check which kernel ran). */
 void dcg_debug_set_wait_limit(long long sm_clocks);
 void dcg_debug_skip_stage(int stage);
+void dcg_debug_set_dx_mode(int mode);
+uint64_t dcg_debug_fused_dx_launches(void);   /* launches of the class-fused input-gradient kernel so far */
 /* Library version and the architecture the kernels were built for ("sm_100a"). */
 const char* dcg_build_info(void);
 /* Kernels launched by this library since it was loaded (all contexts, all threads). */

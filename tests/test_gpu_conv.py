@@ -66,6 +66,61 @@ def test_conv_fwd_dx_dk(pkg, dev, orc, shape, prec_name):
     _check(dk, orc.conv2d_kernel_grad(dy, x, s, pad), prec, pkg, "dk")
 
 
+# stride 2 (four parity classes), more than 4 input channels in multiples of 4: the shapes the class-fused input
+# gradient takes - tiles narrower and wider than 64 columns, a ragged channel chunk (40 = 32 + 8), two channel
+# tiles (256 = 2 x 128), odd extents (a class with fewer rows / columns), 3x3 and 4x4 kernels
+FUSED_DX_SHAPES = [
+    (2, 16, 16, 32, 5, 64, 2), (2, 12, 20, 36, 5, 40, 2), (2, 32, 32, 64, 5, 128, 2), (2, 16, 16, 128, 5, 256, 2),
+    (2, 8, 8, 256, 5, 512, 2), (1, 7, 9, 8, 5, 12, 2), (2, 9, 9, 8, 3, 8, 2), (3, 32, 32, 8, 4, 64, 2),
+]
+
+
+@pytest.mark.parametrize("shape", FUSED_DX_SHAPES)
+def test_dx_with_parity_classes_fused(pkg, dev, orc, shape):
+    """The input gradient that gives one CTA all parity classes of a pixel tile (planned by default only where
+    one CTA per tile fills the GPU; forced here) against the reference's CPU code: plain, gated by the previous
+    layer's activation with the raw gradient kept, and as a generator layer (bias, pre-activation, activation)."""
+    F, L = pkg.functional, pkg.lib
+    N, H, W, C, K, O, s = shape
+    k = seeded((K, K, C, O), 235) * np.float32(0.1)
+    y_shape = orc.conv2d(seeded((N, H, W, C), 234), k, (s, s)).shape
+    dy = seeded(y_shape, 236)
+    z = seeded((N, H, W, C), 237)
+    b = seeded((C,), 238)
+    dx_ref = orc.conv2d_input_grad(dy, k, s, (H, W))
+    kd, dyd, zd, bd = (torch.from_numpy(a).to(dev) for a in (k, dy, z, b))
+    before = L.dcg_debug_fused_dx_launches()
+    try:
+        L.dcg_debug_set_dx_mode(2)
+        dx = F.conv2d_dx(dyd, kd, (H, W), (s, s), precision=pkg.PREC_TF32)
+        raw = torch.empty(dx_ref.shape, device=dev)
+        gated = F.conv2d_dx(dyd, kd, (H, W), (s, s), precision=pkg.PREC_TF32,
+                            epilogue=F.make_epilogue(gate=zd, gate_act=pkg.ACT_LEAKY, gate_alpha=0.2, raw_out=raw))
+        pre = torch.empty(dx_ref.shape, device=dev)
+        act = F.conv2d_dx(dyd, kd, (H, W), (s, s), precision=pkg.PREC_TF32,
+                          epilogue=F.make_epilogue(bias=bd, act=pkg.ACT_RELU, pre_act=pre))
+        torch.cuda.synchronize()
+    finally:
+        L.dcg_debug_set_dx_mode(-1)
+    assert L.dcg_device_status() == 0, L.dcg_last_error()
+    assert L.dcg_debug_fused_dx_launches() - before == 3, "the fused kernel did not take this shape"
+    _check(dx, dx_ref, pkg.PREC_TF32, pkg, "dx")
+    _check(raw, dx_ref, pkg.PREC_TF32, pkg, "raw dx")
+    _check(gated, orc.leaky_relu_grad(z, dx_ref, 0.2), pkg.PREC_TF32, pkg, "gated dx")
+    pre_ref = orc.mvrow_add(dx_ref.reshape(-1, C), b).reshape(dx_ref.shape)
+    _check(pre, pre_ref, pkg.PREC_TF32, pkg, "pre-activation")
+    _check(act, orc.vect_relu(pre_ref), pkg.PREC_TF32, pkg, "activation")
+    # and the same call planned the other way gives the same numbers up to TF32 summation order
+    L.dcg_debug_set_dx_mode(0)
+    try:
+        dx0 = F.conv2d_dx(dyd, kd, (H, W), (s, s), precision=pkg.PREC_TF32)
+        torch.cuda.synchronize()
+    finally:
+        L.dcg_debug_set_dx_mode(-1)
+    assert L.dcg_debug_fused_dx_launches() - before == 3
+    _check(dx0, dx_ref, pkg.PREC_TF32, pkg, "dx, one tile per class")
+
+
 @pytest.mark.parametrize("prec_name", ["fp32", "tf32"])
 def test_golden_reference_cases(pkg, dev, golden, prec_name):
     """The reference's own unit-test tensors (tests/test_conv2d*.cu) through the C ABI."""
