@@ -5,6 +5,9 @@ modification time under csrc/build/, then one link step.  No GPU is needed:
 nvcc cross-compiles.
 
 Run: ``python dcgan-cuda_b200/build.py [--force] [--verbose]``
+
+``DCG_BUILD_FLAGS`` (environment) adds nvcc flags, e.g. ``-DDCG_TC_TRACING`` for the build with the
+convolution kernel's timeline and loads-only / MMAs-only switches (``DCG_TC_DEBUG``); use --force with it.
 """
 import concurrent.futures
 import glob
@@ -21,7 +24,7 @@ LIB = os.path.join(HERE, "libdcgan_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 CFLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall",
-          "-I", os.path.join(ROOT, "include"), "-I", CSRC]
+          "-I", os.path.join(ROOT, "include"), "-I", CSRC] + os.environ.get("DCG_BUILD_FLAGS", "").split()
 
 
 def _deps():

@@ -66,12 +66,14 @@ def test_conv_fwd_dx_dk(pkg, dev, orc, shape, prec_name):
     _check(dk, orc.conv2d_kernel_grad(dy, x, s, pad), prec, pkg, "dk")
 
 
-# stride 2 (four parity classes), more than 4 input channels in multiples of 4: the shapes the class-fused input
-# gradient takes - tiles narrower and wider than 64 columns, a ragged channel chunk (40 = 32 + 8), two channel
+# stride 2 (four parity classes): the shapes the class-fused input gradient takes - tiles narrower and wider than
+# 64 columns, a ragged channel chunk (40 = 32 + 8), two channel
 # tiles (256 = 2 x 128), odd extents (a class with fewer rows / columns), 3x3 and 4x4 kernels
 FUSED_DX_SHAPES = [
     (2, 16, 16, 32, 5, 64, 2), (2, 12, 20, 36, 5, 40, 2), (2, 32, 32, 64, 5, 128, 2), (2, 16, 16, 128, 5, 256, 2),
     (2, 8, 8, 256, 5, 512, 2), (1, 7, 9, 8, 5, 12, 2), (2, 9, 9, 8, 3, 8, 2), (3, 32, 32, 8, 4, 64, 2),
+    # channel counts that rule out 16-byte stores (element-wise epilogue)
+    (2, 16, 16, 6, 5, 32, 2), (2, 10, 14, 9, 5, 160, 2),
 ]
 
 

@@ -193,8 +193,10 @@ def test_batch64_tensor_path_vs_fp32_path(pkg, dev):
     streams, K-partition clusters at the shapes bench.py times) on the TF32 tensor path against the
     fp32 CUDA-core path on identical parameters and inputs; the fp32 path is itself pinned to the
     CPU oracle at batch 2 (test_gradients_match_cpu_model).  Losses to 1e-4; every gradient by
-    relative L2 (kink flips of single pre-activations average out over 64 images, so the bound is far
-    tighter than the 1e-1 of the batch-2 check); the test prints what it measured."""
+    relative L2 within 1e-1.  Measured: discriminator conv weights 0.016-0.032, its dense weight 0.0033,
+    dense bias 2e-4; generator weights 0.012-0.018, its last conv weight 0.048, last bias 0.015 - TF32
+    rounding moves single pre-activations across a leaky-relu / relu kink, a finite step per flip that
+    no operator-level bound covers.  The test prints what it measured."""
     B = 64
     g = torch.Generator().manual_seed(17)
     x = torch.rand((B, 64, 64, 3), generator=g) * 2 - 1
