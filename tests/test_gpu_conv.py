@@ -123,6 +123,42 @@ def test_dx_with_parity_classes_fused(pkg, dev, orc, shape):
     _check(dx0, dx_ref, pkg.PREC_TF32, pkg, "dx, one tile per class")
 
 
+@pytest.mark.parametrize("shape", [(40, 64, 64, 3, 5, 64, 2), (40, 60, 52, 3, 5, 64, 2), (37, 64, 64, 4, 5, 32, 2)])
+def test_three_channel_layers_with_persistent_ctas(pkg, dev, orc, shape):
+    """More tiles than SMs: the forward of a <= 4-channel layer and the GEMM of its input gradient run as
+    persistent CTAs that walk several tiles each (weights resident, accumulator double-buffered).  Forward with
+    the whole fused chain, input gradient with bias + tanh (a generator's last layer), against the CPU code;
+    tile counts that do and do not divide by the grid, output extents that do not fill the pixel tiles."""
+    F = pkg.functional
+    N, H, W, C, K, O, s = shape
+    x = seeded((N, H, W, C), 234)
+    k = seeded((K, K, C, O), 235) * np.float32(0.1)
+    b = seeded((O,), 303)
+    raw_ref = orc.conv2d(x, k, (s, s))
+    z_ref = orc.mvrow_add(raw_ref, b)
+    xd, kd, bd = (torch.from_numpy(a).to(dev) for a in (x, k, b))
+    raw = torch.empty(raw_ref.shape, device=dev)
+    z = torch.empty(raw_ref.shape, device=dev)
+    y = F.conv2d_fwd(xd, kd, (s, s), precision=pkg.PREC_TF32,
+                     epilogue=F.make_epilogue(bias=bd, act=pkg.ACT_LEAKY, alpha=0.2, pre_act=z, raw_out=raw))
+    torch.cuda.synchronize()
+    assert pkg.lib.dcg_device_status() == 0, pkg.lib.dcg_last_error()
+    _check(raw, raw_ref, pkg.PREC_TF32, pkg, "raw")
+    _check(z, z_ref, pkg.PREC_TF32, pkg, "pre-activation")
+    _check(y, orc.vect_relu_leaky(z_ref, 0.2), pkg.PREC_TF32, pkg, "activation")
+    dy = seeded(raw_ref.shape, 236)
+    bc = seeded((C,), 304)
+    dyd, bcd = torch.from_numpy(dy).to(dev), torch.from_numpy(bc).to(dev)
+    dx_ref = orc.conv2d_input_grad(dy, k, s, (H, W))
+    dx = F.conv2d_dx(dyd, kd, (H, W), (s, s), precision=pkg.PREC_TF32)
+    t = F.conv2d_dx(dyd, kd, (H, W), (s, s), precision=pkg.PREC_TF32, epilogue=F.make_epilogue(bias=bcd, act=pkg.ACT_TANH))
+    torch.cuda.synchronize()
+    assert pkg.lib.dcg_device_status() == 0, pkg.lib.dcg_last_error()
+    _check(dx, dx_ref, pkg.PREC_TF32, pkg, "dx")
+    np.testing.assert_allclose(t.cpu().numpy(), orc.vect_tanh(orc.mvrow_add(dx_ref, bc)), rtol=0,
+                               atol=TF32_TOL * max(np.abs(dx_ref).max(), 1.0))
+
+
 @pytest.mark.parametrize("prec_name", ["fp32", "tf32"])
 def test_golden_reference_cases(pkg, dev, golden, prec_name):
     """The reference's own unit-test tensors (tests/test_conv2d*.cu) through the C ABI."""
