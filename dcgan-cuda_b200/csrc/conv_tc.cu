@@ -109,6 +109,7 @@ struct Params {
     int ext_finish;               // the K partitions only write partials; a second kernel adds them (narrow DK)
     int planes;                   // FWD: 16-byte column quad q of output pixel r goes to out[(q * pixels + r) * 4]
     int o_store;                  // FWD: output columns >= o_store are padding and never stored (0: store all O)
+    int b_direct;                 // short-K GEMM: B is read from k itself, K-major (row = 4 * tap + channel, 32 o per row)
     int x3;                       // 3xTF32: every operand tile gets a residual tile, three MMAs per K step
     unsigned long long plane_stride;  // planes: elements between two quads' planes (4 * pixels)
     int debug;                    // DCG_TC_TRACING builds only: 1 = no MMA, 2 = no TMA, 4 / 8 = record timelines
@@ -216,6 +217,14 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
         " [%0], [%1, {%3, %4, %5, %6}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 
 __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
@@ -1255,6 +1264,7 @@ conv_fwd_short_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             mbar_expect_tx(b_bar, (uint32_t)ksteps * b_bytes);
             for (int q = 0; q < ksteps; ++q) {
                 if (NARROW) tma_load_4d(b_res + (uint32_t)q * b_bytes, &map_b, b_bar, 0, 0, q, 0);
+                else if (p.b_direct) tma_load_3d(b_res + (uint32_t)q * b_bytes, &map_b, b_bar, q * BK, 0, 0);
                 else tma_load_4d(b_res + (uint32_t)q * b_bytes, &map_b, b_bar, 0, q * BK, 0, 0);
             }
         }
@@ -1279,9 +1289,14 @@ conv_fwd_short_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         }
     } else if (warp == 1) {
         // ===== MMA issuer: A K-major, B MN-major (chunks of 32 columns 4096 B apart, 4-row groups 512 B apart) =====
-        const uint32_t idesc = make_idesc(0, 1, p.bn, BM);
+        // B: MN-major (chunks of 32 columns 4096 B apart, 4-row groups 512 B apart, 8 k rows per MMA = 1024 B), or -
+        // read from k directly - K-major like A (128-byte rows, 32 bytes per MMA)
+        const bool bk = !NARROW && p.b_direct;
+        const uint32_t idesc = make_idesc(0, bk ? 0 : 1, p.bn, BM);
         const uint64_t adesc0 = make_smem_desc(ring, 16u, 1024u, kLayoutSw128);
-        const uint64_t bdesc0 = make_smem_desc(b_res, 4096u, 512u, kLayoutSw128Base32);
+        const uint64_t bdesc0 = bk ? make_smem_desc(b_res, 16u, 1024u, kLayoutSw128)
+                                   : make_smem_desc(b_res, 4096u, 512u, kLayoutSw128Base32);
+        const uint32_t b_kstep = bk ? 2u : 64u;
         int s = 0, it = 0, n = 0;
         uint32_t phase = 0;
         bool alive = mbar_wait_warp(b_bar, 0, 1, -1, wait_limit);
@@ -1298,7 +1313,7 @@ conv_fwd_short_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     const uint64_t bdesc = bdesc0 + (uint64_t)((uint32_t)q * (b_bytes >> 4));
 #pragma unroll
                     for (int kk = 0; kk < BK / 8; ++kk)
-                        tcgen05_mma_tf32(tmem_d + (uint32_t)(buf * p.bn), adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 64), idesc,
+                        tcgen05_mma_tf32(tmem_d + (uint32_t)(buf * p.bn), adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * b_kstep), idesc,
                                          (q > 0 || kk > 0) ? 1u : 0u);
                     tcgen05_commit(empty_bar + 8u * s);
                 }
@@ -2365,6 +2380,16 @@ int build_dx(const dcg_conv_desc& d, const float* dy, const float* k, void* ws, 
     if (pl.ycol_bytes) {   // narrow-channel layer: GEMM over all taps, then gather
         if (!ws || ws_bytes < pl.ws_bytes)
             return fail(DCG_ERR_WORKSPACE, "conv dx (tensor path, narrow input): workspace %zu < %zu bytes", ws_bytes, pl.ws_bytes);
+        if (short_ok(pl) && d.c <= 4 && d.kh * d.kw <= 32 && p.bn == 128) {
+            // persistent GEMM: B straight from k [tap][c][o] as (o, c, tap) with a (32 o, 4 c, 32 taps) box - rows
+            // 4 * tap + c of 32 contiguous o, K-major; channel 3 and the taps beyond the last are zero-filled
+            pl.p.b_direct = 1;
+            const cuuint64_t dims[3] = {(cuuint64_t)d.o, (cuuint64_t)d.c, (cuuint64_t)(d.kh * d.kw)};
+            const cuuint64_t strides[2] = {(cuuint64_t)d.o * 4, (cuuint64_t)d.c * d.o * 4};
+            const cuuint32_t box[3] = {32, 4, 32};
+            const cuuint32_t es[3] = {1, 1, 1};
+            return encode_map(&pr.mb, k, 3, dims, false, strides, box, es);
+        }
         const float* k2 = reinterpret_cast<const float*>(static_cast<uint8_t*>(ws) + pl.k2_off());
         const int Jp = pl.Jp;
         // k2 [o][Jp] as (j%32, o, 1, j/32), box (32, 32, 1, bn/32): the FWD kernel's weight view with one tap
@@ -2482,8 +2507,10 @@ int conv_tc_dx(const dcg_conv_desc& d, const float* dy, const float* k, float* d
         float* k2 = reinterpret_cast<float*>(base + pl.k2_off());
         float* ycol = reinterpret_cast<float*>(base + pl.ycol_off());
         const int Jp = pl.Jp;
-        launch_pdl(repack_k2_kernel, (d.o * Jp + 255) / 256, 256, 0, stream, k, k2, d.kh * d.kw, d.c, Jp, d.o);
-        DCG_LAUNCH_CHECK("repack_k2_kernel");
+        if (!pl.p.b_direct) {   // the transposed weights k2 [o][Jp]; the persistent GEMM reads k itself
+            launch_pdl(repack_k2_kernel, (d.o * Jp + 255) / 256, 256, 0, stream, k, k2, d.kh * d.kw, d.c, Jp, d.o);
+            DCG_LAUNCH_CHECK("repack_k2_kernel");
+        }
         const EpilogueArgs none{};
         if (short_ok(pl)) st = launch_short(pr, false, ycol, none, stream);
         else st = launch<MODE_FWD>(pr.ma, pr.mb, pl, ycol, none, Jp, ws, ws_bytes, stream);
