@@ -454,6 +454,42 @@ extern "C" uint64_t dcg_context_launch_count(const dcg_context* ctx)
     return ctx ? launches_total() - ctx->launches_base : 0;
 }
 
+namespace {
+// On the tensor path a wide dense layer (the generator's 100 -> 8192 projection) is a 1x1 convolution over
+// a 1x1 image: x [m,1,1,n], k [1,1,n,p], bias in the epilogue; K that is not a multiple of 32 is zero-filled by
+// TMA.  With act_out the activation node that follows is part of the same launch (nd->out1 still receives the
+// pre-activation).  Returns 1 if the shape or the precision keeps the node off the tensor path.
+int run_dense_on_tensor_path(dcg_context* ctx, const dcg_node* nd, int act, float alpha, float* act_out)
+{
+    const size_t m = nd->len1, n = nd->len2, pp = nd->len3;
+    if (!(ctx->precision != DCG_PREC_FP32 && pp >= 1024 && pp % 32 == 0 && n % 4 == 0 && n >= 32 && m >= 32 &&
+          m <= 65536 && n <= 65536 && pp <= 65536 &&
+          ((reinterpret_cast<uintptr_t>(nd->in1) | reinterpret_cast<uintptr_t>(nd->in2) |
+            reinterpret_cast<uintptr_t>(nd->in3) | reinterpret_cast<uintptr_t>(nd->out1) |
+            reinterpret_cast<uintptr_t>(act_out)) & 15u) == 0))
+        return 1;
+    dcg_conv_desc d{};
+    d.n = (int)m; d.h = 1; d.w = 1; d.c = (int)n; d.kh = 1; d.kw = 1; d.o = (int)pp; d.ho = 1; d.wo = 1;
+    d.stride_h = 1; d.stride_w = 1; d.pad_top = 0; d.pad_left = 0;
+    const bool x3 = ctx->precision == DCG_PREC_3XTF32;
+    if (!conv_tc_supported(d, kConvFwd, x3)) return 1;
+    int st = ensure_workspace(ctx, conv_tc_workspace(d, kConvFwd, x3));
+    if (st) return st;
+    dcg_epilogue ep{};
+    ep.bias = nd->in3;
+    ep.act = DCG_ACT_NONE;
+    float* out = nd->out1;
+    if (act_out) {
+        ep.act = act;
+        ep.alpha = alpha;
+        ep.pre_act = nd->out1;
+        out = act_out;
+    }
+    ProfScope scope(act_out ? ctx : nullptr, "mat_mul_add", 0.0);   // the fused form does not pass through dcg_run_node
+    return dcg_conv2d_fwd(&d, nd->in1, nd->in2, out, &ep, ctx->precision, ctx->ws, ctx->ws_bytes, ctx->stream);
+}
+}  // namespace
+
 extern "C" int dcg_run_node(dcg_context* ctx, const dcg_node* nd)
 {
     DCG_CHECK_ARG(ctx && nd, "dcg_run_node: null argument");
@@ -487,28 +523,9 @@ extern "C" int dcg_run_node(dcg_context* ctx, const dcg_node* nd)
     case DCG_OP_SIGMOID_GRAD:  // src/gpu/sigmoid.cu:138-146
         return dcg_act_grad(nd->in1, nd->in2, nd->out1, nd->len1, DCG_ACT_SIGMOID, 0.f, s);
     case DCG_OP_MAT_MUL_ADD: {  // src/gpu/matmul.cu:121-137
-        // On the tensor path a wide dense layer (the generator's 100 -> 8192 projection) is a 1x1
-        // convolution over a 1x1 image: x [m,1,1,n], k [1,1,n,p], bias in the epilogue.  K that is
-        // not a multiple of 32 is zero-filled by TMA.
-        const size_t m = nd->len1, n = nd->len2, pp = nd->len3;
-        if (ctx->precision != DCG_PREC_FP32 && pp >= 1024 && pp % 32 == 0 && n % 4 == 0 && n >= 32 && m >= 32 &&
-            m <= 65536 && n <= 65536 && pp <= 65536 &&
-            ((reinterpret_cast<uintptr_t>(nd->in1) | reinterpret_cast<uintptr_t>(nd->in2) |
-              reinterpret_cast<uintptr_t>(nd->in3) | reinterpret_cast<uintptr_t>(nd->out1)) & 15u) == 0) {
-            dcg_conv_desc d{};
-            d.n = (int)m; d.h = 1; d.w = 1; d.c = (int)n; d.kh = 1; d.kw = 1; d.o = (int)pp; d.ho = 1; d.wo = 1;
-            d.stride_h = 1; d.stride_w = 1; d.pad_top = 0; d.pad_left = 0;
-            const bool x3 = ctx->precision == DCG_PREC_3XTF32;
-            if (conv_tc_supported(d, kConvFwd, x3)) {
-                int st = ensure_workspace(ctx, conv_tc_workspace(d, kConvFwd, x3));
-                if (st) return st;
-                dcg_epilogue ep{};
-                ep.bias = nd->in3;
-                ep.act = DCG_ACT_NONE;
-                return dcg_conv2d_fwd(&d, nd->in1, nd->in2, nd->out1, &ep, ctx->precision, ctx->ws, ctx->ws_bytes, s);
-            }
-        }
-        return dcg_matmul(nd->in1, nd->in2, nd->in3, nd->out1, m, n, pp, s);
+        const int st = run_dense_on_tensor_path(ctx, nd, DCG_ACT_NONE, 0.f, nullptr);
+        if (st != 1) return st;
+        return dcg_matmul(nd->in1, nd->in2, nd->in3, nd->out1, nd->len1, nd->len2, nd->len3, s);
     }
     case DCG_OP_TMAT_MAT_MUL:  // src/gpu/matmul.cu:139-153
         return dcg_matmul_tn(nd->in1, nd->in2, nd->out1, nd->len1, nd->len2, nd->len3, s);
@@ -570,6 +587,12 @@ extern "C" int dcg_run_node(dcg_context* ctx, const dcg_node* nd)
         return fail(DCG_ERR_INVALID, "dcg_run_node: unknown node type %d", nd->type);
     }
 }
+
+namespace dcg {
+int sigmoid_xent_with_grad(const float* y, const float* logits, float* loss, float* grad, size_t n, cudaStream_t stream);
+int matmul_nt_gated(const float* a, const float* b, float* out, size_t m, size_t n, size_t p, const float* gate,
+                    float* gated_out, int gate_act, float gate_alpha, cudaStream_t stream);
+}  // namespace dcg
 
 namespace {
 
@@ -661,6 +684,37 @@ int run_nodes_impl(dcg_context* ctx, const dcg_node* nodes, int count, int fuse)
             if (used < 0) return used;
             i += used;
             continue;
+        }
+        if (i + 1 < count && !(nodes[i + 1].flags & DCG_NODE_SIDE)) {
+            const dcg_node& a = nodes[i];
+            const dcg_node& b = nodes[i + 1];
+            // dense layer + activation (tensor path only)
+            const int act = act_of_node(b.type);
+            if (a.type == DCG_OP_MAT_MUL_ADD && act >= 0 && b.in1 == a.out1 && b.len1 == a.len1 * a.len3 && b.out1 != a.out1) {
+                const int st = run_dense_on_tensor_path(ctx, &a, act, b.type == DCG_OP_RELU_LEAKY ? b.alpha_leaky : 0.f, b.out1);
+                if (st < 0) return st;
+                if (st == 0) { i += 2; continue; }
+            }
+            // loss + its gradient on the same labels and logits
+            if (a.type == DCG_OP_SIGMOID_CROSS_ENTROPY && b.type == DCG_OP_SIGMOID_CROSS_ENTROPY_GRAD && a.in1 == b.in1 &&
+                a.in2 == b.in2 && a.len1 == b.len1 && a.len1 <= 65536 && a.out1 != b.out1) {
+                ProfScope scope(ctx, "sigmoid_xent_with_grad", 0.0);
+                const int st = dcg::sigmoid_xent_with_grad(a.in1, a.in2, a.out1, b.out1, a.len1, ctx->stream);
+                if (st) return st;
+                i += 2;
+                continue;
+            }
+            // x W^T + the activation gradient that gates it (the discriminator head's input gradient)
+            const int gact = grad_act_of_node(b.type);
+            if (a.type == DCG_OP_MAT_TMAT_MUL && gact >= 0 && b.in2 == a.out1 && b.in1 != a.out1 && b.out1 != a.out1 &&
+                b.len1 == a.len1 * a.len3) {
+                ProfScope scope(ctx, "mat_tmat_mul_gated", 0.0);
+                const int st = dcg::matmul_nt_gated(a.in1, a.in2, a.out1, a.len1, a.len2, a.len3, b.in1, b.out1, gact,
+                                                    b.type == DCG_OP_LEAKY_RELU_GRAD ? b.cons1 : 0.f, ctx->stream);
+                if (st) return st;
+                i += 2;
+                continue;
+            }
         }
         AdamTriple first;
         if (match_adam_triple(nodes, i, count, first)) {

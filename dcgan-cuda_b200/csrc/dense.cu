@@ -31,7 +31,8 @@ template <bool TA, bool TB>
 __global__ void __launch_bounds__(TPB)
 gemm_tiled_kernel(const float* __restrict__ a, const float* __restrict__ b,
                   const float* __restrict__ bias, float* __restrict__ out,
-                  size_t m, size_t n, size_t p)
+                  size_t m, size_t n, size_t p, const float* __restrict__ gate, float* __restrict__ gated_out,
+                  int gate_act, float gate_alpha)
 {
     pdl_enter();
     __shared__ float As[KT][TILE + 1];  // [k][row]
@@ -83,6 +84,8 @@ gemm_tiled_kernel(const float* __restrict__ a, const float* __restrict__ b,
             float v = acc[i][j];
             if (bias) v = __fadd_rn(v, __ldg(bias + c));
             out[r * p + c] = v;
+            // the activation gradient that follows the product in a backward list, same expression as act_grad_kernel
+            if (gate) gated_out[r * p + c] = act_grad_apply(__ldg(gate + r * p + c), v, gate_act, gate_alpha);
         }
     }
 }
@@ -234,10 +237,11 @@ inline bool wide_shape(size_t m, size_t n, size_t p) { return n <= 256 && p >= 5
 
 template <bool TA, bool TB>
 int launch_tiled(const float* a, const float* b, const float* bias, float* out, size_t m, size_t n,
-                 size_t p, cudaStream_t stream, const char* name)
+                 size_t p, cudaStream_t stream, const char* name, const float* gate = nullptr, float* gated_out = nullptr,
+                 int gate_act = 0, float gate_alpha = 0.f)
 {
     const dim3 grid((unsigned)((p + TILE - 1) / TILE), (unsigned)((m + TILE - 1) / TILE));
-    launch_pdl(gemm_tiled_kernel<TA, TB>, grid, TPB, 0, stream, a, b, bias, out, m, n, p);
+    launch_pdl(gemm_tiled_kernel<TA, TB>, grid, TPB, 0, stream, a, b, bias, out, m, n, p, gate, gated_out, gate_act, gate_alpha);
     DCG_LAUNCH_CHECK(name);
     return DCG_OK;
 }
@@ -272,6 +276,17 @@ extern "C" int dcg_matmul_tn(const float* a, const float* b, float* out, size_t 
     }
     return launch_tiled<true, false>(a, b, nullptr, out, m, n, p, as_stream(stream), "gemm_tiled_kernel<tn>");
 }
+
+namespace dcg {
+// dcg_matmul_nt followed by dcg_act_grad(gate, out) -> gated_out as one launch (node fusion of the backend).
+int matmul_nt_gated(const float* a, const float* b, float* out, size_t m, size_t n, size_t p, const float* gate,
+                    float* gated_out, int gate_act, float gate_alpha, cudaStream_t stream)
+{
+    DCG_CHECK_ARG(a && b && out && gate && gated_out && m > 0 && n > 0 && p > 0, "matmul_nt_gated: bad arguments");
+    return launch_tiled<false, true>(a, b, nullptr, out, m, n, p, stream, "gemm_tiled_kernel<nt>", gate, gated_out, gate_act,
+                                     gate_alpha);
+}
+}  // namespace dcg
 
 extern "C" int dcg_matmul_nt(const float* a, const float* b, float* out, size_t m, size_t n,
                              size_t p, dcg_stream_t stream)

@@ -379,6 +379,24 @@ sigmoid_xent_grad_kernel(const float* __restrict__ y, const float* __restrict__ 
         out[i] = (act_apply(__ldg(x + i), DCG_ACT_SIGMOID, 0.f) - __ldg(y + i)) / (float)n;
 }
 
+// Loss and its gradient in one launch (the two nodes are neighbours in a training list): the same
+// expressions as the two kernels above, element for element, so the results are bit-identical.
+__global__ void __launch_bounds__(512)
+sigmoid_xent_both_kernel(const float* __restrict__ y, const float* __restrict__ x, float* __restrict__ loss,
+                         float* __restrict__ grad, size_t n)
+{
+    pdl_enter();
+    __shared__ float red[32];
+    float s = 0.f;
+    for (size_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const float xi = __ldg(x + i), yi = __ldg(y + i);
+        s += xi >= 0.f ? xi - xi * yi + logf(1.f + expf(-xi)) : -xi * yi + logf(1.f + expf(xi));
+        grad[i] = (act_apply(xi, DCG_ACT_SIGMOID, 0.f) - yi) / (float)n;
+    }
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) loss[0] = s / (float)n;
+}
+
 __global__ void __launch_bounds__(512)
 mse_kernel(const float* __restrict__ y, const float* __restrict__ y_hat, float* __restrict__ out,
            size_t n)
@@ -722,6 +740,17 @@ extern "C" int dcg_sigmoid_xent(const float* y, const float* logits, float* out,
     DCG_LAUNCH_CHECK("sigmoid_xent_kernel");
     return DCG_OK;
 }
+
+namespace dcg {
+// dcg_sigmoid_xent and dcg_sigmoid_xent_grad as one launch (node fusion of the backend); n small enough for one block.
+int sigmoid_xent_with_grad(const float* y, const float* logits, float* loss, float* grad, size_t n, cudaStream_t stream)
+{
+    DCG_CHECK_ARG(y && logits && loss && grad && n > 0, "sigmoid_xent_with_grad: bad arguments");
+    launch_pdl(sigmoid_xent_both_kernel, 1, 512, 0, stream, y, logits, loss, grad, n);
+    DCG_LAUNCH_CHECK("sigmoid_xent_both_kernel");
+    return DCG_OK;
+}
+}  // namespace dcg
 
 extern "C" int dcg_sigmoid_xent_grad(const float* y, const float* logits, float* out, size_t n,
                                      dcg_stream_t stream)

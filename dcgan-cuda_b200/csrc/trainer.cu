@@ -461,11 +461,12 @@ void build_lists(dcg_trainer* t)
         build_discriminator(t, D, t->g_out.p, 0, B);
         build_discriminator(t, D, t->x.p, 1, B);
     }
+    // each loss next to its gradient: the pair is one launch when the list runs fused
     D.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY, t->zeros.p, t->logits[0].p, t->d1_loss.p, B));
-    D.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY, t->ones.p, t->logits[1].p, t->d2_loss.p, B));
-    D.push_back(n_binary(DCG_OP_ADD, t->d1_loss.p, t->d2_loss.p, t->d_loss.p, 1));
     D.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY_GRAD, t->zeros.p, t->logits[0].p, t->dlogits[0].p, B));
+    D.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY, t->ones.p, t->logits[1].p, t->d2_loss.p, B));
     D.push_back(n_binary(DCG_OP_SIGMOID_CROSS_ENTROPY_GRAD, t->ones.p, t->logits[1].p, t->dlogits[1].p, B));
+    D.push_back(n_binary(DCG_OP_ADD, t->d1_loss.p, t->d2_loss.p, t->d_loss.p, 1));
     if (t->batched_d) {
         // dlogits = [fake | real], each half already divided by its own B: the 2B-row backward pass
         // sums both gradient paths (the Add of src/ops/graph.cu:302-309) inside its reductions
