@@ -196,6 +196,45 @@ def test_adam_triples_fuse_into_one_launch(pkg, dev, orc):
         assert np.array_equal(host[True][i], p)
 
 
+@pytest.mark.parametrize("prec_name", ["fp32", "tf32"])
+def test_small_neighbours_fuse_into_one_launch(pkg, dev, prec_name):
+    """Pairs of neighbouring nodes that run as one launch when fusion is on: dense layer + activation (tensor path:
+    one 1x1-convolution launch with the activation in its epilogue), sigmoid cross-entropy + its gradient, x W^T + the
+    activation gradient that gates it.  Every output of the unfused list is still written and is bit-identical."""
+    N = pkg.nodes
+    prec = pkg.PREC_FP32 if prec_name == "fp32" else pkg.PREC_TF32
+    B = 64
+    z, w, b = _t(seeded((B, 100), 1), dev), _t(seeded((100, 8192), 2) * np.float32(0.05), dev), _t(seeded((8192,), 3), dev)
+    labels, logits = torch.ones((B, 1), device=dev), _t(seeded((B, 1), 4), dev)
+    wh, gate = _t(seeded((8192, 1), 5), dev), _t(seeded((B, 8192), 6), dev)
+    results = {}
+    for fuse in (False, True):
+        pre, act = torch.empty((B, 8192), device=dev), torch.empty((B, 8192), device=dev)
+        loss, dl = torch.empty((1,), device=dev), torch.empty((B, 1), device=dev)
+        dda, ddz = torch.empty((B, 8192), device=dev), torch.empty((B, 8192), device=dev)
+        nodes = [
+            N.op_mat_mul_add(z, w, b, pre, B, 100, 8192),
+            N.op_relu_leaky(pre, act, pre.numel(), 0.2),
+            N.op_sigmoid_cross_entropy(labels, logits, loss, B),
+            N.op_sigmoid_cross_entropy_grad(labels, logits, dl, B),
+            N.op_mat_tmat_mul(dl, wh, dda, B, 1, 8192),
+            N.op_leaky_relu_grad(gate, dda, ddz, 0.2, dda.numel()),
+        ]
+        ctx = pkg.Context(prec)
+        ctx.run(nodes, fuse=fuse)      # first run may allocate scratch
+        before = ctx.launch_count()
+        ctx.run(nodes, fuse=fuse)
+        torch.cuda.synchronize()
+        launches = ctx.launch_count() - before
+        results[fuse] = ([t.cpu().numpy() for t in (pre, act, loss, dl, dda, ddz)], launches)
+        ctx.close()
+    for a, c in zip(results[False][0], results[True][0]):
+        assert np.array_equal(a, c)
+    # fp32: the dense layer stays on the CUDA-core kernel (no fused form), the other two pairs fuse
+    assert results[False][1] == 6
+    assert results[True][1] == (4 if prec_name == "fp32" else 3)
+
+
 def test_reshape_is_an_alias_and_unknown_nodes_fail(pkg, dev):
     """Reshape lowers to no instruction at all (src/ops/reshape.cu:20-44): the consumer reads the
     producer's buffer, so it is bit-exact by construction.  Unknown node types are errors."""
