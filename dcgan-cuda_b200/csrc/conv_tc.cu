@@ -1725,9 +1725,9 @@ int tile_width(int n_ch) { return n_ch >= 128 ? 128 : n_ch; }
 // K partitions of a tile.  Measured on every DCGAN layer at batch 64 (per-CTA timelines, partition
 // counts 1..8 forced): the shortest launch is the one with about ONE CTA per SM - a deeper pipeline
 // per CTA and half the partial-tile traffic beat a second resident CTA (e.g. the 256 -> 512 forward
-// layer: 18.5 us with 4 partitions = 128 CTAs against 22.3 us with 8 = 256).  The exception is the
-// kernel gradient with the channel roles swapped (its finish phase walks columns one by one and
-// gains from more, smaller shares): two CTAs per SM there.
+// layer: 18.5 us with 4 partitions = 128 CTAs against 22.3 us with 8 = 256; the 64 -> 128 kernel gradient with
+// the channel roles swapped: 25.0 us with 25 taps x 5 = 125 CTAs against 27.0 us with 25 x 8 = 200, 39.8 us
+// against 46.7 us over 128 images).
 int choose_splits(int tiles, int min_stages_per_tile, int ctas_per_sm = 1)
 {
     static const int forced = env_int("DCG_TC_SPLITS");
@@ -2064,7 +2064,7 @@ bool plan_dk(const dcg_conv_desc& d, Plan& pl)
     p.bn = tile_width(n_ch);
     p.n_tiles = (n_ch + p.bn - 1) / p.bn;
     const int tiles = d.kh * d.kw * p.m_tiles * p.n_tiles;
-    p.splits = choose_splits(tiles, p.tiles_w * p.tiles_h * p.tiles_n, p.swap ? 2 : 1);
+    p.splits = choose_splits(tiles, p.tiles_w * p.tiles_h * p.tiles_n);
     pl.grid = tiles * p.splits;
     finish_plan(pl);
     return true;
