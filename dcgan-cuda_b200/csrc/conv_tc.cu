@@ -705,7 +705,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (q < 16 || full) d1[q * BM] = __uint_as_float(r[q]);
             }
         }
-        if (multi) __threadfence();   // the partial is visible device-wide before this CTA arrives
+        // no fence here: every thread's partial stores are ordered before its own arrival at the cluster barrier
+        // (barrier.cluster.arrive.release / wait.acquire), and before the finish kernel by the kernel boundary
     }
     if (threadIdx.x == 64) TC_TRACE(3001);
     TC_CTA_TRACE(3);
