@@ -31,6 +31,11 @@
 //
 // Every wait is bounded: a barrier that does not complete within ~1 s makes the waiting role
 // record an error code in a device status word and leave; TMEM is always released.
+//
+// Two specialisations of the same machinery live further down in this file: conv_dxf_kernel (input
+// gradient with all parity classes of a pixel tile in one CTA, their accumulators merged into wide
+// MMAs) and conv_fwd_short_kernel (the two short-K launches of the 3-channel layers as persistent
+// CTAs with resident weights and a double-buffered accumulator).
 #include <cuda.h>
 
 #include <atomic>

@@ -72,7 +72,9 @@ DEFAULT_PROGRAMS = {
 
 
 def default_reference():
-    return os.environ.get("DCGAN_REFERENCE_DIR", "/root/reference")
+    """The reference checkout: DCGAN_REFERENCE_DIR, else a directory `reference` next to this repository."""
+    repo = os.path.dirname(os.path.dirname(HERE))
+    return os.environ.get("DCGAN_REFERENCE_DIR") or os.path.join(os.path.dirname(repo), "reference")
 
 
 def _run(cmd):

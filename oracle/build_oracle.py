@@ -21,7 +21,8 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_DIR = os.environ.get("DCGAN_REFERENCE_DIR", "/root/reference")
+# the reference checkout: DCGAN_REFERENCE_DIR, else a directory `reference` next to this repository
+REF_DIR = os.environ.get("DCGAN_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 PORT_LIB = os.path.join(HERE, "liboracle.so")
 REF_OUT_DIR = os.path.join(HERE, "_ref")
 REF_LIB = os.path.join(REF_OUT_DIR, "libdcgan_ref_cpu.so")
