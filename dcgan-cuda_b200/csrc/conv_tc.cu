@@ -1423,6 +1423,235 @@ conv_fwd_short_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     }
 }
 
+// ---- input gradient of a <= 4-channel layer: GEMM and gather in one persistent kernel -----------------
+// dx[n, h, w, c] = sum over the taps of matching parity of ycol[tap][n, i, j][c], where ycol = dy x k^T is
+// the plain GEMM of every dy pixel against all taps (N = 4 columns per tap).  Written to memory, ycol is
+// 100 floats per dy pixel - 26 MB at batch 64 for a 3 MB result - and the gather is a second launch.
+// Here a CTA owns 2R output rows of one image: it runs the GEMM for the R + 2 dy rows that contribute to
+// them (two 128-pixel M tiles = 8 rows of 32 pixels, so the rows at the seams are computed twice), parks
+// the products in shared memory as [tap][dy pixel][4] and gathers its own output pixels from there, fused
+// chain included.  Nothing but dy, the weights and dx touches memory, and it is one launch.  Persistent:
+// a CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...; the weights stay resident (read from k
+// itself, K-major rows 4 * tap + c), the dy tiles of the next tile stream in and its MMAs run while this
+// tile is being gathered (one TMEM accumulator per M tile, handed back as soon as it is in shared memory).
+struct Dx3Args {
+    int R;            // dy rows owned per tile (2R output rows)
+    int lo;           // first dy row a tile needs, relative to its first owned row (<= 0)
+    int tiles_per_img, tiles;
+};
+constexpr int kDx3Rows = 8;                               // dy rows per tile (two M tiles of 4 rows x 32 pixels)
+constexpr int kDx3Stages = 4;
+constexpr int kDx3Epi = 512;                              // epilogue threads: 16 warps, four per TMEM lane quadrant (one 32-column slab each)
+constexpr int kDx3Threads = 64 + kDx3Epi;
+constexpr int kDx3YcolBytes = 32 * kDx3Rows * 32 * 16;    // up to 32 taps x 256 dy pixels x 4 floats
+
+template <int KH_, int KW_>   // 5, 5: tap loops unrolled, all loads of a pixel in flight; 0, 0: any kernel size
+__global__ void __launch_bounds__(kDx3Threads, 1)
+conv_dx3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const __grid_constant__ Params p, const __grid_constant__ Dx3Args g)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem0 = smem_u32(smem_raw);
+    const uint32_t b_res = (smem0 + 1023u) & ~1023u;
+    const long long wait_limit = p.wait_cycles;
+    const int ksteps = p.kchunks;
+    const uint32_t b_bytes = 128u * BK * 4;                       // 128 rows (4 * tap + c) x 32 output channels
+    const uint32_t ring = b_res + (uint32_t)ksteps * b_bytes;
+    const uint32_t ycol_base = ring + (uint32_t)kDx3Stages * A_STAGE_BYTES;
+    const int ntaps = p.KH * p.KW;
+    const uint32_t bar_base = ycol_base + (uint32_t)ntaps * (kDx3Rows * 32 * 16);
+    const uint32_t full_bar = bar_base;                           // [kDx3Stages]
+    const uint32_t empty_bar = bar_base + 8u * kDx3Stages;        // [kDx3Stages]
+    const uint32_t b_bar = bar_base + 16u * kDx3Stages;
+    const uint32_t acc_full = b_bar + 8u;                         // [2] one per M tile
+    const uint32_t acc_empty = acc_full + 16u;                    // [2]
+    const uint32_t tmem_slot = acc_empty + 16u;
+    uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem0));
+    const float4* ycol = reinterpret_cast<const float4*>(smem_raw + (ycol_base - smem0));
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kDx3Stages; ++s) {
+            mbar_init(full_bar + 8u * s, 1);
+            mbar_init(empty_bar + 8u * s, 1);
+        }
+        mbar_init(b_bar, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full + 8u * b, 1);
+            mbar_init(acc_empty + 8u * b, kDx3Epi / 32);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    }
+    constexpr int tmem_cols = 256;
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = *tmem_slot_ptr;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    if (warp == 0) {
+        // ===== producer: the weights once; per tile two M tiles (4 dy rows x 32 pixels each) x the channel chunks =====
+        if (elect_one()) {
+            mbar_expect_tx(b_bar, (uint32_t)ksteps * b_bytes);
+            for (int q = 0; q < ksteps; ++q) tma_load_3d(b_res + (uint32_t)q * b_bytes, &map_b, b_bar, q * BK, 0, 0);
+        }
+        int s = 0, it = 0;
+        uint32_t phase = 0;
+        bool alive = true;
+        for (int tile = blockIdx.x; tile < g.tiles && alive; tile += gridDim.x) {
+            const int n = tile / g.tiles_per_img, t = tile - n * g.tiles_per_img;
+            const int i_base = g.R * t + g.lo;
+            for (int mt = 0; mt < 2 && alive; ++mt)
+                for (int q = 0; q < ksteps; ++q, ++it) {
+                    if (!mbar_wait_warp(empty_bar + 8u * s, phase ^ 1u, 0, it, wait_limit)) { alive = false; break; }
+                    if (elect_one()) {
+                        const uint32_t fb = full_bar + 8u * s;
+                        mbar_expect_tx(fb, (uint32_t)A_STAGE_BYTES);
+                        tma_load_4d(ring + (uint32_t)s * A_STAGE_BYTES, &map_a, fb, q * BK, 0, i_base + 4 * mt, n);
+                    }
+                    if (++s == kDx3Stages) { s = 0; phase ^= 1u; }
+                }
+        }
+    } else if (warp == 1) {
+        // ===== MMA issuer: both operands K-major =====
+        const uint32_t idesc = make_idesc(0, 0, 128, BM);
+        const uint64_t adesc0 = make_smem_desc(ring, 16u, 1024u, kLayoutSw128);
+        const uint64_t bdesc0 = make_smem_desc(b_res, 16u, 1024u, kLayoutSw128);
+        int s = 0, it = 0, n = 0;
+        uint32_t phase = 0;
+        bool alive = mbar_wait_warp(b_bar, 0, 1, -1, wait_limit);
+        for (int tile = blockIdx.x; tile < g.tiles && alive; tile += gridDim.x, ++n) {
+            for (int mt = 0; mt < 2 && alive; ++mt) {
+                // the epilogue has copied this accumulator's previous tile to shared memory (first tile: passes at once)
+                if (!mbar_wait_warp(acc_empty + 8u * mt, ((uint32_t)n & 1u) ^ 1u, 1, it, wait_limit)) { alive = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int q = 0; q < ksteps; ++q, ++it) {
+                    if (!mbar_wait_warp(full_bar + 8u * s, phase, 1, it, wait_limit)) { alive = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    if (elect_one()) {
+                        const uint64_t adesc = adesc0 + (uint64_t)((uint32_t)s * (A_STAGE_BYTES >> 4));
+                        const uint64_t bdesc = bdesc0 + (uint64_t)((uint32_t)q * (b_bytes >> 4));
+#pragma unroll
+                        for (int kk = 0; kk < BK / 8; ++kk)
+                            tcgen05_mma_tf32(tmem_d + (uint32_t)(mt * 128), adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc,
+                                             (q > 0 || kk > 0) ? 1u : 0u);
+                        tcgen05_commit(empty_bar + 8u * s);
+                    }
+                    if (++s == kDx3Stages) { s = 0; phase ^= 1u; }
+                }
+                if (elect_one()) tcgen05_commit(acc_full + 8u * mt);   // complete, or abandoned
+            }
+        }
+    } else {
+        // ===== epilogue: accumulators -> shared memory [tap][dy pixel][4], then gather the tile's own output pixels =====
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;                // dy pixel of the M tile: 32 * (row of the tile) + column
+        const int slab = (warp - 2) >> 2;                // the four warps of a lane quadrant take one 32-column slab each
+        const int tid_e = threadIdx.x - 64;
+        const EpilogueArgs& e = p.ep;
+        const int W = p.W, own = 2 * g.R * W;            // output pixels a tile owns
+        int n_it = 0;
+        for (int tile = blockIdx.x; tile < g.tiles; tile += gridDim.x, ++n_it) {
+            const int n = tile / g.tiles_per_img, t = tile - n * g.tiles_per_img;
+            const int i_base = g.R * t + g.lo;
+            bool ok = true;
+            for (int mt = 0; mt < 2; ++mt) {
+                bool got = mbar_wait(acc_full + 8u * mt, (uint32_t)n_it & 1u, 2, n_it, wait_limit);
+                got = __all_sync(0xffffffffu, got);
+                ok = ok && got;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                {
+                    const int c0 = slab * 32;
+                    if (c0 < 4 * ntaps) {
+                        uint32_t r[32];
+                        tmem_ld_32x32b_x32(tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)(mt * 128 + c0), r);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            const int tap = (c0 >> 2) + q;
+                            if (tap < ntaps) {
+                                const uint32_t addr = ycol_base + (uint32_t)(((tap * kDx3Rows * 32) + mt * 128 + row) * 16);
+                                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(__uint_as_float(r[4 * q])),
+                                             "f"(__uint_as_float(r[4 * q + 1])), "f"(__uint_as_float(r[4 * q + 2])),
+                                             "f"(__uint_as_float(r[4 * q + 3])) : "memory");
+                            }
+                        }
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty + 8u * mt) : "memory");
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kDx3Epi) : "memory");
+            // gather: consecutive threads take consecutive output pixels of the tile's 2R rows
+            for (int px = tid_e; px < own; px += kDx3Epi) {
+                const int hl = px / W, w = px - hl * W;
+                const int h = 2 * g.R * t + hl;
+                if (h >= p.H || !ok) continue;
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                const int di0 = (h + p.pt) & 1, dj0 = (w + p.pl) & 1;   // kernel rows / columns of matching parity, ascending
+                if constexpr (KH_ > 0) {
+                    constexpr int TH = (KH_ + 1) / 2, TW = (KW_ + 1) / 2;
+                    float4 v[TH * TW];
+#pragma unroll
+                    for (int a = 0; a < TH; ++a) {
+                        const int di = di0 + 2 * a;
+                        const int hh = h + p.pt - di;
+                        const int i = hh >> 1;
+                        const bool row_ok = di < KH_ && hh >= 0 && i < p.Ho;
+#pragma unroll
+                        for (int b = 0; b < TW; ++b) {
+                            const int dj = dj0 + 2 * b;
+                            const int ww = w + p.pl - dj;
+                            const int j = ww >> 1;
+                            const bool in = row_ok && dj < KW_ && ww >= 0 && j < p.Wo;
+                            v[a * TW + b] = in ? ycol[((di * KW_ + dj) * kDx3Rows + (i - i_base)) * 32 + j]
+                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                    }
+#pragma unroll
+                    for (int q = 0; q < TH * TW; ++q) {
+                        acc[0] = __fadd_rn(acc[0], v[q].x); acc[1] = __fadd_rn(acc[1], v[q].y);
+                        acc[2] = __fadd_rn(acc[2], v[q].z); acc[3] = __fadd_rn(acc[3], v[q].w);
+                    }
+                } else {
+                    for (int di = di0; di < p.KH; di += 2) {
+                        const int i = (h + p.pt - di) >> 1;
+                        if (h + p.pt - di < 0 || i >= p.Ho) continue;
+                        const int rl = i - i_base;
+                        for (int dj = dj0; dj < p.KW; dj += 2) {
+                            const int j = (w + p.pl - dj) >> 1;
+                            if (w + p.pl - dj < 0 || j >= p.Wo) continue;
+                            const float4 v = ycol[((di * p.KW + dj) * kDx3Rows + rl) * 32 + j];
+                            acc[0] = __fadd_rn(acc[0], v.x); acc[1] = __fadd_rn(acc[1], v.y);
+                            acc[2] = __fadd_rn(acc[2], v.z); acc[3] = __fadd_rn(acc[3], v.w);
+                        }
+                    }
+                }
+                const size_t pix = ((size_t)n * p.H + h) * W + w;
+                for (int c = 0; c < p.C; ++c) {
+                    const size_t idx = pix * p.C + c;
+                    p.out[idx] = epilogue_apply(e, acc[c], idx, c);
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kDx3Epi) : "memory");   // the products are consumed: the next tile may overwrite them
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
+    }
+}
+
 // ---- narrow-channel DK: add the partitions' partial tiles -----------------------------------------
 // partial[m tile][partition][col][row] (col = 32 * kernel row + window slot, row = output channel).
 // Block = 32 rows x 8 lanes of one column: lane l adds partitions l, l+8, ... (all loads in
@@ -2168,6 +2397,7 @@ struct Prepared;
 int launch_dxf(Prepared& pr, float* out, const EpilogueArgs& ep, cudaStream_t stream);
 bool short_ok(const Plan& pl);
 int launch_short(Prepared& pr, bool narrow, float* out, const EpilogueArgs& ep, cudaStream_t stream);
+int launch_dx3(Prepared& pr, float* out, const EpilogueArgs& ep, cudaStream_t stream);
 
 // Narrow-channel layers: builds the padded 4-channel image (and, for FWD, the repacked weights) in
 // the caller's scratch and returns their addresses.
@@ -2222,6 +2452,8 @@ struct Prepared {
     CUtensorMap ma, mb;
     bool dxf = false;   // input gradient with the parity classes fused (conv_dxf_kernel); cf is its table
     CfTable cf;
+    bool dx3 = false;   // input gradient of a <= 4-channel layer as one GEMM + gather kernel (conv_dx3_kernel)
+    Dx3Args dx3_args;
 };
 
 int launch_dxf(Prepared& pr, float* out, const EpilogueArgs& ep, cudaStream_t stream)
@@ -2319,6 +2551,86 @@ int launch_short(Prepared& pr, bool narrow, float* out, const EpilogueArgs& ep, 
     return DCG_OK;
 }
 
+// GEMM + gather in one kernel for the input gradient of a <= 4-channel layer (conv_dx3_kernel): stride 2, at most
+// 32 taps, dy rows of at most 32 pixels and at most 64 channels (the resident weights and the products of a tile
+// share the CTA's shared memory).  DCG_TC_DX3=0 switches it off.
+bool plan_dx3(const dcg_conv_desc& d, Plan& pl, Dx3Args& g)
+{
+    static const int off = [] { const char* v = getenv("DCG_TC_DX3"); return v && atoi(v) == 0 ? 1 : 0; }();
+    if (off || t_plan_x3) return false;
+    if (d.c > 4 || d.stride_h != 2 || d.stride_w != 2 || d.kh * d.kw > 32 || d.kh < 2 || d.kw < 2) return false;
+    if (d.o % 32 != 0 || d.o > 64 || d.wo > 32 || d.pad_top >= d.kh || d.pad_left >= d.kw) return false;
+    // the most output rows (2R) whose contributing dy rows fit the 8 rows of a tile
+    int R = 0, lo = 0;
+    for (int r = kDx3Rows; r >= 1 && R == 0; --r) {
+        int mn = 1 << 30, mx = -(1 << 30);
+        for (int hl = 0; hl < 2 * r; ++hl)
+            for (int di = (hl + d.pad_top) & 1; di < d.kh; di += 2) {
+                const int v = hl + d.pad_top - di;
+                const int i = v >= 0 ? v / 2 : -((-v + 1) / 2);   // floor
+                if (i < mn) mn = i;
+                if (i > mx) mx = i;
+            }
+        if (mx - mn + 1 <= kDx3Rows) { R = r; lo = mn; }
+    }
+    if (R == 0) return false;
+    Params& p = pl.p;
+    base_params(p, d);
+    p.kchunks = d.o / BK;
+    p.bn = 128;
+    p.splits = 1;
+    p.skip_stage = -1;
+    p.wait_cycles = kWaitCycles;
+    g.R = R;
+    g.lo = lo;
+    g.tiles_per_img = (d.h + 2 * R - 1) / (2 * R);
+    g.tiles = d.n * g.tiles_per_img;
+    pl.grid = g.tiles < sm_count() ? g.tiles : sm_count();
+    pl.smem = 1024 + (size_t)p.kchunks * 128 * BK * 4 + (size_t)kDx3Stages * A_STAGE_BYTES +
+              (size_t)d.kh * d.kw * kDx3Rows * 32 * 16 + 16 * kDx3Stages + 64;
+    pl.ws_bytes = 0;
+    return pl.smem <= (size_t)kMaxSmem;
+}
+
+int launch_dx3(Prepared& pr, float* out, const EpilogueArgs& ep, cudaStream_t stream)
+{
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(conv_dx3_kernel<5, 5>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+        if (attr_err == cudaSuccess)
+            attr_err = cudaFuncSetAttribute(conv_dx3_kernel<0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    });
+    if (attr_err != cudaSuccess)
+        return fail(DCG_ERR_CUDA, "cudaFuncSetAttribute(conv_dx3_kernel): %s", cudaGetErrorString(attr_err));
+    Params& p = pr.pl.p;
+    p.out = out;
+    p.ep = ep;
+    p.scratch = nullptr;
+    p.wait_cycles = g_wait_cycles.load();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)pr.pl.grid);
+    cfg.blockDim = dim3(kDx3Threads);
+    cfg.dynamicSmemBytes = pr.pl.smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    int na = 0;
+    static const int no_pdl = env_int("DCG_TC_NO_PDL");
+    if (!no_pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    const cudaError_t err = (p.KH == 5 && p.KW == 5)
+                                ? cudaLaunchKernelEx(&cfg, conv_dx3_kernel<5, 5>, pr.ma, pr.mb, p, pr.dx3_args)
+                                : cudaLaunchKernelEx(&cfg, conv_dx3_kernel<0, 0>, pr.ma, pr.mb, p, pr.dx3_args);
+    if (err != cudaSuccess) return fail(DCG_ERR_CUDA, "conv_dx3_kernel launch: %s", cudaGetErrorString(err));
+    count_launch();
+    return DCG_OK;
+}
+
 struct CacheKey {
     int dev, kind, x3;
     dcg_conv_desc d;
@@ -2375,6 +2687,19 @@ int build_fwd(const dcg_conv_desc& d, const float* x, const float* k, void* ws, 
 int build_dx(const dcg_conv_desc& d, const float* dy, const float* k, void* ws, size_t ws_bytes, Prepared& pr)
 {
     Plan& pl = pr.pl;
+    pr.dx3 = plan_dx3(d, pl, pr.dx3_args);
+    if (pr.dx3) {
+        // dy [n, ho, wo, o] in boxes of (32 o, 32 pixels, 4 rows, 1 image); k [tap][c][o] as (o, c, tap) in boxes of
+        // (32 o, 4 c, 32 taps): rows 4 * tap + c, K-major, channel 3 and the taps beyond the last zero-filled
+        int st = map_act_4d(&pr.ma, dy, d.n, d.ho, d.wo, d.o, 32, 4, 1, 1, 1);
+        if (st) return st;
+        const cuuint64_t dims[3] = {(cuuint64_t)d.o, (cuuint64_t)d.c, (cuuint64_t)(d.kh * d.kw)};
+        const cuuint64_t strides[2] = {(cuuint64_t)d.o * 4, (cuuint64_t)d.c * d.o * 4};
+        const cuuint32_t box[3] = {32, 4, 32};
+        const cuuint32_t es[3] = {1, 1, 1};
+        return encode_map(&pr.mb, k, 3, dims, false, strides, box, es);
+    }
+    pl = Plan{};
     pr.dxf = plan_dxf(d, pl, pr.cf);
     if (!pr.dxf) {
         pl = Plan{};
@@ -2508,6 +2833,7 @@ int conv_tc_dx(const dcg_conv_desc& d, const float* dy, const float* k, float* d
     int st = prepared_call(kConvDx, d, dy, k, ws, ws_bytes, pr);
     if (st) return st;
     Plan& pl = pr.pl;
+    if (pr.dx3) return launch_dx3(pr, dx, ep, stream);
     if (pl.ycol_bytes) {   // narrow-channel layer: GEMM over all taps, then gather
         uint8_t* base = static_cast<uint8_t*>(ws);
         float* k2 = reinterpret_cast<float*>(base + pl.k2_off());
