@@ -480,7 +480,7 @@ def run_ours(args, rank, local_rank, world):
     tf32_peak = peaks["bf16_tflops"] / 2.0
     achieved = conv_flops / (conv_ms * 1e-3) / 1e12 if conv_ms > 0 else 0.0
     roofline = {
-        "kernel": "conv_tc_kernel and its two specialisations conv_dxf_kernel / conv_fwd_short_kernel (tcgen05 implicit-GEMM "
+        "kernel": "conv_tc_kernel and its specialisations conv_dxf_kernel / conv_fwd_short_kernel / conv_dx3_kernel (tcgen05 implicit-GEMM "
                   "conv: fwd, dx, dk launch groups of the step, each timed over %s back-to-back launches)"
                   % os.environ.get("DCG_PROFILE_REPEAT", "1"),
         "bound": "tensor", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
