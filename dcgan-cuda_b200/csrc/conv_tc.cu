@@ -32,10 +32,16 @@
 // Every wait is bounded: a barrier that does not complete within ~1 s makes the waiting role
 // record an error code in a device status word and leave; TMEM is always released.
 //
-// Two specialisations of the same machinery live further down in this file: conv_dxf_kernel (input
-// gradient with all parity classes of a pixel tile in one CTA, their accumulators merged into wide
-// MMAs) and conv_fwd_short_kernel (the two short-K launches of the 3-channel layers as persistent
-// CTAs with resident weights and a double-buffered accumulator).
+// This file is the host side (tensor maps, planning, the plan cache, launches, entry points); the
+// device code of this translation unit sits in the headers it includes:
+//   conv_tc_common.cuh   constants, kernel parameters, PTX wrappers, descriptors
+//   conv_tc_kernel.cuh   conv_tc_kernel<MODE, X3>, the general kernel described above
+//   conv_tc_dxf.cuh      conv_dxf_kernel: input gradient with all parity classes of a pixel tile in one
+//                        CTA, their accumulators merged into wide MMAs
+//   conv_tc_short.cuh    conv_fwd_short_kernel: the short-K forward GEMMs of the 3-channel layers as
+//                        persistent CTAs with resident weights and a double-buffered accumulator
+//   conv_tc_dx3.cuh      conv_dx3_kernel: input gradient of a 3-channel layer, GEMM + gather in one kernel
+//   conv_tc_narrow.cuh   repack, partition-finish and gather helpers of the 3-channel layers
 #include <cuda.h>
 
 #include <atomic>
@@ -47,1796 +53,15 @@
 #include "common.cuh"
 #include "conv.cuh"
 
+#include "conv_tc_common.cuh"
+#include "conv_tc_kernel.cuh"
+#include "conv_tc_dxf.cuh"
+#include "conv_tc_short.cuh"
+#include "conv_tc_dx3.cuh"
+#include "conv_tc_narrow.cuh"
+
 namespace dcg {
 namespace {
-
-constexpr int BM = 128;                 // accumulator rows (TMEM lanes)
-constexpr int BK = 32;                  // K elements per pipeline stage (one 128-byte swizzle row)
-constexpr int A_STAGE_BYTES = BM * BK * 4;
-constexpr int kEpi = 256;               // epilogue threads: warps 2..9, two per TMEM lane quadrant
-constexpr int kThreads = 64 + kEpi;
-constexpr int kMaxSmem = 227 * 1024;
-constexpr int kMaxCluster = 8;          // portable thread-block cluster size: the cap on K partitions
-// Floats of shared memory the epilogue's transposition buffer takes for a 128 x bn tile (quads at a
-// pitch of BM + 1 sixteen-byte units); the row-offset table follows it.
-__host__ __device__ constexpr int kRedFloats(int bn) { return (bn / 4) * (BM + 1) * 4; }
-constexpr long long kWaitCycles = 2000000000LL;  // default wait limit: ~1 s at 2 GHz
-
-enum Mode { MODE_FWD = 0, MODE_DX = 1, MODE_DK = 2 };
-
-// Error word: [0] code (0 = ok), [1] blockIdx, [2] role, [3] stage.  Read by dcg_device_status().
-__device__ int g_tc_status[4];
-
-// Tuning aids, compiled in only with -DDCG_TC_TRACING (the default build has none of it): clock
-// stamps of CTA 0's pipeline and a per-CTA phase timeline, read back through dcg_debug_trace /
-// dcg_debug_cta_trace; Params::debug bit 0 drops the MMAs, bit 1 the loads (results are garbage).
-#ifdef DCG_TC_TRACING
-// [0..1023] TMA issue of stage i, [1024..2047] stage i seen full by the MMA thread, [2048..3071] MMAs
-// of stage i issued, [3072] kernel entry, [3073] setup done, [3074] accumulator ready, [3075] stores done.
-__device__ long long g_tc_trace[3080];
-#define TC_TRACE(slot)                                                         \
-    do {                                                                       \
-        if ((p.debug & 4) && blockIdx.x == 0 && (slot) < 3080) g_tc_trace[(slot)] = clock64(); \
-    } while (0)
-// global-timer stamps (ns) of thread 64 of the first 1024 CTAs at [0] kernel entry, [1] setup done,
-// [2] accumulator ready, [3] tile handed over, [4] partitions met, [5] end; [6] = SM id.
-__device__ unsigned long long g_tc_cta_trace[1024][8];
-__device__ __forceinline__ unsigned long long global_ns()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-#define TC_CTA_TRACE(slot)                                                                         \
-    do {                                                                                           \
-        if ((p.debug & 8) && threadIdx.x == 64 && blockIdx.x < 1024) g_tc_cta_trace[blockIdx.x][(slot)] = global_ns(); \
-    } while (0)
-#define TC_DEBUG_BIT(bit) (p.debug & (bit))
-#else
-#define TC_TRACE(slot) do { } while (0)
-#define TC_CTA_TRACE(slot) do { } while (0)
-#define TC_DEBUG_BIT(bit) false
-#endif
-
-struct Params {
-    int N, H, W, C, KH, KW, O, Ho, Wo, sh, sw, pt, pl;
-    int TW, TH, TN;               // pixel-tile extents (FWD/DX: the 128 rows; DK: the 32-pixel K step)
-    int tiles_w, tiles_h, tiles_n;  // pixel tiles along each axis
-    int m_tiles;                  // DK: 128-row tiles along the M channel axis
-    int n_tiles;                  // BN-column tiles along the N channel axis
-    int bn;                       // accumulator columns, multiple of 16, <= 256
-    int splits;                   // K partitions of a tile = CTAs per cluster (<= 8)
-    int skip_stage;               // test hook: the producer leaves this pipeline stage out (-1: never)
-    long long wait_cycles;        // SM clocks after which a barrier wait gives up
-    int kchunks;                  // 32-wide chunks along the contracted channel axis (FWD: C, DX: O)
-    int swap;                     // DK: M axis is o (A from dy, B from x)
-    int narrow;                   // FWD/DK with <= 4 input channels: x is read through the window map
-    int ext_finish;               // the K partitions only write partials; a second kernel adds them (narrow DK)
-    int planes;                   // FWD: 16-byte column quad q of output pixel r goes to out[(q * pixels + r) * 4]
-    int o_store;                  // FWD: output columns >= o_store are padding and never stored (0: store all O)
-    int b_direct;                 // short-K GEMM: B is read from k itself, K-major (row = 4 * tap + channel, 32 o per row)
-    int x3;                       // 3xTF32: every operand tile gets a residual tile, three MMAs per K step
-    unsigned long long plane_stride;  // planes: elements between two quads' planes (4 * pixels)
-    int debug;                    // DCG_TC_TRACING builds only: 1 = no MMA, 2 = no TMA, 4 / 8 = record timelines
-    int stages;                   // pipeline depth
-    float* out;                   // the output tensor
-    float* scratch;               // splits > 1: partial tiles, [CTA][128 x bn], quad- or column-major
-    EpilogueArgs ep;
-};
-
-// ---- PTX wrappers ----------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p)
-{
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-
-// Bounded wait, slow path.  Returns false (after recording the failure) if the phase never completes.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int role, int stage, long long limit)
-{
-    const long long t0 = clock64();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 64; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (clock64() - t0 > limit) break;
-    }
-    if (atomicCAS(&g_tc_status[0], 0, 1) == 0) {
-        g_tc_status[1] = blockIdx.x;
-        g_tc_status[2] = role;
-        g_tc_status[3] = stage;
-    }
-    return false;
-}
-
-// Bounded wait: a non-blocking probe first (the common case in a running pipeline), then the
-// suspending, time-limited loop.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int role, int stage, long long limit)
-{
-    if (mbar_test_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, role, stage, limit);
-}
-
-// Warp-uniform form for loops that a whole warp walks in lockstep (one elected lane issues): the
-// vote makes the outcome uniform by construction, which keeps the loop state in uniform registers.
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int role, int stage, long long limit)
-{
-    if (__all_sync(0xffffffffu, mbar_test_wait(bar, parity))) return true;
-    return __all_sync(0xffffffffu, mbar_wait_slow(bar, parity, role, stage, limit));
-}
-
-__device__ __forceinline__ bool elect_one()
-{
-    uint32_t pred;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "elect.sync _|p, 0xffffffff;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(pred));
-    return pred != 0;
-}
-
-// ---- thread-block cluster barrier -----------------------------------------------------------------
-// The barrier is a hardware one (no time limit can be attached); every thread of every CTA of the
-// cluster reaches both of its uses on every path, error paths included.
-__device__ __forceinline__ void cluster_sync_all()
-{
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int c0, int c1, int c2, int c3)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
-        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
-        " [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
-
-__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int c0, int c1, int c2, int c3, int c4)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes"
-        " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
-}
-
-__device__ __forceinline__ void tcgen05_commit(uint32_t bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tcgen05_mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                                 uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t* r)
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t* r)
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr) : "memory");
-}
-
-// 3xTF32: what the TF32 part of a value (its top 19 bits, which is what the tensor core reads) leaves over.
-// The residual is itself rounded to nearest TF32 here (the tensor core would truncate it, and a
-// truncation error always points the same way, so it would add up over a long reduction).
-__device__ __forceinline__ float tf32_residual_1(float v)
-{
-    const float r = __fsub_rn(v, __uint_as_float(__float_as_uint(v) & 0xFFFFE000u));
-    return __uint_as_float((__float_as_uint(r) + 0x1000u) & 0xFFFFE000u);
-}
-__device__ __forceinline__ float4 tf32_residual(float4 v)
-{
-    return make_float4(tf32_residual_1(v.x), tf32_residual_1(v.y), tf32_residual_1(v.z), tf32_residual_1(v.w));
-}
-
-// Shared-memory operand descriptor (tcgen05): start address, leading / stride byte offsets in
-// 16-byte units, version 1, swizzle layout.  Layout 2 = 128-byte swizzle of 16-byte chunks (what
-// K-major tiles use); layout 1 = 128-byte swizzle of 32-byte chunks, the only swizzled layout the
-// tensor core accepts for MN-major 32-bit (TF32) operands.
-constexpr uint32_t kLayoutSw128 = 2, kLayoutSw128Base32 = 1;
-
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
-                                                   uint32_t layout)
-{
-    uint64_t d = 0;
-    d |= (uint64_t)((addr >> 4) & 0x3FFF);
-    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
-    d |= (uint64_t)1 << 46;  // descriptor version
-    d |= (uint64_t)layout << 61;
-    return d;
-}
-
-// Instruction descriptor: fp32 accumulator, TF32 operands, operand majors, N and M.
-__device__ __forceinline__ uint32_t make_idesc(int a_mn_major, int b_mn_major, int n, int m)
-{
-    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)a_mn_major << 15) |
-           ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-// ---- the kernel ---------------------------------------------------------------------------------
-template <int MODE, bool X3>
-__global__ void __launch_bounds__(kThreads, X3 ? 1 : 2)
-conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const __grid_constant__ Params p)
-{
-    extern __shared__ uint8_t smem_raw[];
-    if (threadIdx.x == 64) TC_TRACE(3072);
-    TC_CTA_TRACE(0);
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const int b_stage_bytes = p.bn * BK * 4;
-    const long long wait_limit = p.wait_cycles;
-    const uint32_t a_base = smem_base;
-    const uint32_t b_base = a_base + (uint32_t)p.stages * A_STAGE_BYTES;
-    // 3xTF32: residual tiles (operand minus its TF32 part) of every stage follow the operand tiles
-    const uint32_t as_base = b_base + (uint32_t)p.stages * b_stage_bytes;
-    const uint32_t bs_base = as_base + (uint32_t)p.stages * A_STAGE_BYTES;
-    const uint32_t bar_base = X3 ? bs_base + (uint32_t)p.stages * b_stage_bytes : as_base;
-    // barriers: full[stages], empty[stages], tmem_full; then the TMEM base address word
-    const uint32_t full_bar = bar_base;
-    const uint32_t empty_bar = bar_base + 8u * p.stages;
-    const uint32_t resid_bar = bar_base + 16u * p.stages;     // 3xTF32: residual tiles of the stage are written
-    const uint32_t tmem_full_bar = bar_base + 24u * p.stages;
-    const uint32_t tmem_slot = tmem_full_bar + 8u;
-    uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
-
-    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
-
-    // ---- one-time setup (first: thread 0 and warp 1 are busy with it while everyone decodes) ---------
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < p.stages; ++s) {
-            mbar_init(full_bar + 8u * s, 1);
-            mbar_init(empty_bar + 8u * s, 1);
-            mbar_init(resid_bar + 8u * s, kEpi);
-        }
-        mbar_init(tmem_full_bar, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
-    }
-    // 3xTF32 keeps the two small cross terms in an accumulator of their own (columns bn .. 2*bn): the
-    // tensor core rounds its accumulator toward zero at every step, an error that grows with the
-    // number of steps and with the accumulator's size, so the long chain of large terms is kept as
-    // short as in the plain TF32 kernel and the small terms round among themselves
-    int tmem_cols = 32;
-    while (tmem_cols < (X3 ? 2 * p.bn : p.bn)) tmem_cols <<= 1;
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(tmem_cols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-
-    // ---- decode this CTA's work item -------------------------------------------------------------
-    // blockIdx.x = ((group * m_count + m) * n_tiles + n) * splits + split, where group is the parity
-    // class (DX), the kernel tap (DK) or absent (FWD), and m a pixel tile (FWD/DX) or channel tile (DK).
-    int rem = blockIdx.x;
-    const int split = rem % p.splits; rem /= p.splits;
-    const int n_tile = rem % p.n_tiles; rem /= p.n_tiles;
-    int m_count;
-    if (MODE == MODE_DK) m_count = p.m_tiles;
-    else m_count = p.tiles_w * p.tiles_h * p.tiles_n;
-    const int m_tile = rem % m_count;
-    const int group = rem / m_count;
-
-    // pixel-tile origin (FWD/DX)
-    int j0 = 0, i0 = 0, n0 = 0;
-    if (MODE != MODE_DK) {
-        j0 = (m_tile % p.tiles_w) * p.TW;
-        i0 = ((m_tile / p.tiles_w) % p.tiles_h) * p.TH;
-        n0 = (m_tile / (p.tiles_w * p.tiles_h)) * p.TN;
-    }
-    // DX: parity class and its taps; DK: the kernel tap
-    int ph = 0, pw = 0, rh = 0, rw = 0, eh = 0, ew = 0, taps_h = 1, taps_w = 1, tap_di = 0, tap_dj = 0;
-    if (MODE == MODE_DX) {
-        ph = group / p.sw; pw = group % p.sw;
-        rh = (ph + p.pt) % p.sh; rw = (pw + p.pl) % p.sw;
-        eh = (ph + p.pt) / p.sh; ew = (pw + p.pl) / p.sw;
-        taps_h = rh < p.KH ? (p.KH - rh + p.sh - 1) / p.sh : 0;
-        taps_w = rw < p.KW ? (p.KW - rw + p.sw - 1) / p.sw : 0;
-    } else if (MODE == MODE_DK) {
-        if (p.narrow) { tap_di = 0; tap_dj = 0; }   // one tile holds every tap: 32 window slots per kernel row
-        else { tap_di = group / p.KW; tap_dj = group % p.KW; }
-    }
-    // K-stage range of this split
-    int total_stages;
-    if (MODE == MODE_FWD) total_stages = p.narrow ? p.KH : p.KH * p.KW * p.kchunks;
-    else if (MODE == MODE_DX) total_stages = taps_h * taps_w * p.kchunks;
-    else total_stages = p.tiles_w * p.tiles_h * p.tiles_n;
-    const int q0 = (int)((long long)total_stages * split / p.splits);
-    const int q1 = (int)((long long)total_stages * (split + 1) / p.splits);
-    const int nq = q1 - q0;
-
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_d = *tmem_slot_ptr;
-    // Programmatic dependent launch: everything above (barriers, TMEM, descriptor prefetch) may run
-    // while the previous kernel of the stream is still draining; from here on its results are needed.
-    // The next kernel's CTAs may in turn be set up as soon as every CTA of this grid has got here.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    if (threadIdx.x == 64) TC_TRACE(3073);
-    TC_CTA_TRACE(1);
-#ifdef DCG_TC_TRACING
-    if ((p.debug & 8) && threadIdx.x == 64 && blockIdx.x < 1024) {
-        unsigned smid;
-        asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
-        g_tc_cta_trace[blockIdx.x][6] = smid;
-    }
-#endif
-
-    // ---- epilogue geometry (uniform over the CTA) ---------------------------------------------------
-    const int ch0 = n_tile * p.bn;    // channel index of accumulator column 0 (bias axis) unless DK
-    int ncols_valid;                  // valid columns in this N tile
-    long long col_stride = 1;         // element stride between accumulator columns in the output
-    if (MODE == MODE_FWD) ncols_valid = min(p.bn, (p.o_store ? p.o_store : p.O) - ch0);
-    else if (MODE == MODE_DX) ncols_valid = min(p.bn, p.C - ch0);
-    else if (p.narrow) { ncols_valid = 32 * p.KH; col_stride = p.O; }
-    else if (!p.swap) ncols_valid = min(p.bn, p.O - ch0);
-    else { ncols_valid = min(p.bn, p.C - ch0); col_stride = p.O; }
-    // Row-contiguous outputs whose channel count allows 16-byte stores take the vector path.
-    const int ch_total = (MODE == MODE_DX) ? p.C : p.O;
-    const bool vec = col_stride == 1 && (ch_total & 3) == 0 && (ncols_valid & 3) == 0;
-    float* red = reinterpret_cast<float*>(smem_raw + (a_base - smem_u32(smem_raw)));
-    long long* s_rowoff = reinterpret_cast<long long*>(red + kRedFloats(p.bn));
-
-    if (warp == 0) {
-        // ===== TMA producer =====
-        // One thread issues every load.  All position bookkeeping is incremental: an integer division
-        // costs this lone thread ~100 cycles, and the loop has to turn around in well under the 256
-        // cycles the tensor core needs per stage.
-        {
-            const uint32_t tx_bytes = (uint32_t)(A_STAGE_BYTES + b_stage_bytes);
-            int s = 0;
-            uint32_t phase = 0;
-            // counters of stage q0: FWD (chunk, tap, di, dj); DX (chunk, -, th, tw); DK (-, tile_n, tile_h, tile_w)
-            int chunk = 0, tap = 0, di = 0, dj = 0;
-            if (MODE == MODE_FWD && !p.narrow) {
-                tap = q0 / p.kchunks; chunk = q0 % p.kchunks; di = tap / p.KW; dj = tap % p.KW;
-            } else if (MODE == MODE_DX) {
-                const int t = q0 / p.kchunks;
-                chunk = q0 % p.kchunks; di = t / taps_w; dj = t % taps_w;
-            } else if (MODE == MODE_DK) {
-                dj = q0 % p.tiles_w; di = (q0 / p.tiles_w) % p.tiles_h; tap = q0 / (p.tiles_w * p.tiles_h);
-            }
-            const int wrap_dj = (MODE == MODE_FWD) ? p.KW : taps_w;
-            for (int it = 0; it < nq; ++it) {
-                if (!mbar_wait_warp(empty_bar + 8u * s, phase ^ 1u, 0, it, wait_limit)) break;
-                const uint32_t fb = full_bar + 8u * s;
-                if (it != p.skip_stage && elect_one()) {
-                TC_TRACE(it);
-                if (TC_DEBUG_BIT(2)) {   // timing experiment: no loads, the stage is declared full at once
-                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(fb) : "memory");
-                } else {
-                    mbar_expect_tx(fb, tx_bytes);
-                    const uint32_t a_dst = a_base + (uint32_t)s * A_STAGE_BYTES;
-                    const uint32_t b_dst = b_base + (uint32_t)s * b_stage_bytes;
-                    if (MODE == MODE_FWD && p.narrow) {
-                        // stage = kernel row: 128 output pixels x the 32-float window (8 pixels x 4
-                        // channels) that starts at padded column s*j of padded row s*i + row
-                        const int q = q0 + it;
-                        tma_load_5d(a_dst, &map_a, fb, 0, j0, i0, n0, q);
-                        tma_load_4d(b_dst, &map_b, fb, 0, 0, q, n_tile * (p.bn / 32));
-                    } else if (MODE == MODE_FWD) {
-                        if (it < 128) TC_TRACE(256 + it);
-                        tma_load_4d(a_dst, &map_a, fb, chunk * BK, p.sw * j0 + dj - p.pl, p.sh * i0 + di - p.pt, n0);
-                        if (it < 128) TC_TRACE(512 + it);
-                        tma_load_4d(b_dst, &map_b, fb, 0, chunk * BK, tap, n_tile * (p.bn / 32));
-                        if (it < 128) TC_TRACE(768 + it);
-                    } else if (MODE == MODE_DX) {
-                        // (di, dj) count the taps of this parity class: kernel tap (rh + sh*di, rw + sw*dj)
-                        tma_load_4d(a_dst, &map_a, fb, chunk * BK, j0 + ew - dj, i0 + eh - di, n0);
-                        tma_load_4d(b_dst, &map_b, fb, chunk * BK, n_tile * p.bn, rw + p.sw * dj, rh + p.sh * di);
-                    } else {
-                        // (tap, di, dj) count the 32-pixel tiles along (n, h, w)
-                        const int pj = dj * p.TW, pi = di * p.TH, pn = tap * p.TN;
-                        const int xw = p.sw * pj + tap_dj - p.pl, xh = p.sh * pi + tap_di - p.pt;
-                        if (p.narrow) {  // A: dy (rows o), B: the KH 32-float windows of 32 output pixels
-                            tma_load_5d(a_dst, &map_a, fb, 0, pj, pi, pn, m_tile * (BM / 32));
-                            tma_load_5d(b_dst, &map_b, fb, 0, pj, pi, pn, 0);   // box covers all KH kernel rows
-                        } else if (!p.swap) {   // A: x (rows c), B: dy (cols o)
-                            tma_load_5d(a_dst, &map_a, fb, 0, xw, xh, pn, m_tile * (BM / 32));
-                            tma_load_5d(b_dst, &map_b, fb, 0, pj, pi, pn, n_tile * (p.bn / 32));
-                        } else {         // A: dy (rows o), B: x (cols c)
-                            tma_load_5d(a_dst, &map_a, fb, 0, pj, pi, pn, m_tile * (BM / 32));
-                            tma_load_5d(b_dst, &map_b, fb, 0, xw, xh, pn, n_tile * (p.bn / 32));
-                        }
-                    }
-                }
-                }
-                // advance to the next stage
-                if (MODE == MODE_DK) {
-                    if (++dj == p.tiles_w) { dj = 0; if (++di == p.tiles_h) { di = 0; ++tap; } }
-                } else if (++chunk == p.kchunks) {
-                    chunk = 0; ++tap;
-                    if (++dj == wrap_dj) { dj = 0; ++di; }
-                }
-                if (++s == p.stages) { s = 0; phase ^= 1u; }
-            }
-        }
-    } else if (warp == 1) {
-        // ===== MMA issuer =====
-        {
-            const int a_mn = (MODE == MODE_DK) ? 1 : 0;
-            const int b_mn = (MODE == MODE_DX) ? 0 : 1;
-            const uint32_t idesc = make_idesc(a_mn, b_mn, p.bn, BM);
-            // K-major tile: rows of 128 B, 8-row groups 1024 B apart (stride offset); one MMA (K = 8)
-            // consumes 32 B of each row.
-            // MN-major tile: [32-channel chunk][k row][128 B]: chunks 4096 B apart (leading offset), the
-            // 32-byte-chunk swizzle repeats every 4 k rows, so 4-row groups are 512 B apart (stride
-            // offset); one MMA consumes 8 k rows = 1024 B.
-            const uint32_t a_lbo = a_mn ? 4096u : 16u, b_lbo = b_mn ? 4096u : 16u;
-            const uint32_t a_sbo = a_mn ? 512u : 1024u, b_sbo = b_mn ? 512u : 1024u;
-            const uint32_t a_lay = a_mn ? kLayoutSw128Base32 : kLayoutSw128;
-            const uint32_t b_lay = b_mn ? kLayoutSw128Base32 : kLayoutSw128;
-            const uint32_t a_step = a_mn ? 1024u : 32u, b_step = b_mn ? 1024u : 32u;
-            // descriptors of stage 0; a stage further on only changes the 14-bit start-address field
-            const uint64_t adesc0 = make_smem_desc(a_base, a_lbo, a_sbo, a_lay);
-            const uint64_t bdesc0 = make_smem_desc(b_base, b_lbo, b_sbo, b_lay);
-            const uint32_t a_stage16 = A_STAGE_BYTES >> 4, b_stage16 = (uint32_t)b_stage_bytes >> 4;
-            int s = 0;
-            uint32_t phase = 0;
-            {
-            for (int it = 0; it < nq; ++it) {
-                if (!mbar_wait_warp(full_bar + 8u * s, phase, 1, it, wait_limit)) break;
-                if (X3 && !mbar_wait_warp(resid_bar + 8u * s, phase, 3, it, wait_limit)) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (elect_one()) {
-                TC_TRACE(1024 + it);
-                if (TC_DEBUG_BIT(1)) {   // timing experiment: no MMA, the stage is released at once
-                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_bar + 8u * s) : "memory");
-                } else {
-                    const uint64_t adesc = adesc0 + (uint64_t)(s * a_stage16);
-                    const uint64_t bdesc = bdesc0 + (uint64_t)(s * b_stage16);
-                    if (X3) {
-                        // a*b ~ a_hi*b_lo + a_lo*b_hi + a_hi*b_hi, the small terms first; the tensor core
-                        // reads the TF32 part (top 19 bits) of whatever fp32 word it is given
-                        const uint64_t ares = adesc + (uint64_t)((as_base - a_base) >> 4);
-                        const uint64_t bres = bdesc + (uint64_t)((bs_base - b_base) >> 4);
-#pragma unroll
-                        for (int kk = 0; kk < BK / 8; ++kk) {
-                            const uint64_t ka = (uint64_t)(kk * (a_step >> 4)), kb = (uint64_t)(kk * (b_step >> 4));
-                            const uint32_t first = (it > 0 || kk > 0) ? 1u : 0u;
-                            tcgen05_mma_tf32(tmem_d + (uint32_t)p.bn, adesc + ka, bres + kb, idesc, first);
-                            tcgen05_mma_tf32(tmem_d + (uint32_t)p.bn, ares + ka, bdesc + kb, idesc, 1u);
-                            tcgen05_mma_tf32(tmem_d, adesc + ka, bdesc + kb, idesc, first);
-                        }
-                    } else {
-#pragma unroll
-                        for (int kk = 0; kk < BK / 8; ++kk)
-                            tcgen05_mma_tf32(tmem_d, adesc + (uint64_t)(kk * (a_step >> 4)), bdesc + (uint64_t)(kk * (b_step >> 4)),
-                                             idesc, (it > 0 || kk > 0) ? 1u : 0u);
-                    }
-                    tcgen05_commit(empty_bar + 8u * s);  // frees the stage once these MMAs have read it
-                }
-                TC_TRACE(2048 + it);
-                }
-                if (++s == p.stages) { s = 0; phase ^= 1u; }
-            }
-            if (elect_one()) tcgen05_commit(tmem_full_bar);   // accumulator complete (or abandoned)
-            }
-        }
-    } else {
-        // ===== epilogue, part 1 (warps 2..5; TMEM lane quadrant = warp % 4; thread = accumulator row) =====
-        const int quad = warp & 3;
-        const int row = quad * 32 + lane;
-        // where does this accumulator row go?  (worked out while the main loop is still running)
-        bool row_valid = false;
-        unsigned long long row_off = 0;   // element offset of column 0 of this row
-        if (MODE == MODE_FWD) {
-            const int tw = row % p.TW, th = (row / p.TW) % p.TH, tn = row / (p.TW * p.TH);
-            const int n = n0 + tn, i = i0 + th, j = j0 + tw;
-            row_valid = n < p.N && i < p.Ho && j < p.Wo;
-            row_off = (((unsigned long long)n * p.Ho + i) * p.Wo + j) * p.O + ch0;
-            if (p.planes) row_off = (((unsigned long long)n * p.Ho + i) * p.Wo + j) * 4ull;
-        } else if (MODE == MODE_DX) {
-            const int tw = row % p.TW, th = (row / p.TW) % p.TH, tn = row / (p.TW * p.TH);
-            const int n = n0 + tn, h = p.sh * (i0 + th) + ph, w = p.sw * (j0 + tw) + pw;
-            row_valid = n < p.N && h < p.H && w < p.W;
-            row_off = (((unsigned long long)n * p.H + h) * p.W + w) * p.C + ch0;
-        } else {
-            const unsigned long long tap_off = (unsigned long long)group * p.C * p.O;
-            if (p.narrow) {  // rows o, columns = 32 * kernel row + window slot (kernel column dj = slot / 4, channel = slot % 4)
-                const int o = m_tile * BM + row;
-                row_valid = o < p.O;
-                row_off = o;
-            } else if (!p.swap) {   // rows c, columns o
-                const int c = m_tile * BM + row;
-                row_valid = c < p.C;
-                row_off = tap_off + (unsigned long long)c * p.O + ch0;
-            } else {         // rows o, columns c
-                const int o = m_tile * BM + row;
-                row_valid = o < p.O;
-                row_off = tap_off + (unsigned long long)ch0 * p.O + o;
-            }
-        }
-        if (X3) {
-            // ===== 3xTF32: these four warps turn every landed stage into its residual tiles =====
-            // residual = value - (value with the low 13 mantissa bits cleared); element-wise on the raw
-            // bytes of the stage, so the swizzled layout carries over unchanged
-            const int tid_r = threadIdx.x - 64;
-            int s = 0;
-            uint32_t phase = 0;
-            const int a_q = A_STAGE_BYTES / 16, b_q = b_stage_bytes / 16;   // 16-byte words per tile
-            for (int it = 0; it < nq; ++it) {
-                if (!mbar_wait(full_bar + 8u * s, phase, 4, it, wait_limit)) break;
-                const float4* asrc = reinterpret_cast<const float4*>(smem_raw + (a_base + (uint32_t)s * A_STAGE_BYTES - smem_u32(smem_raw)));
-                float4* adst = reinterpret_cast<float4*>(smem_raw + (as_base + (uint32_t)s * A_STAGE_BYTES - smem_u32(smem_raw)));
-                const float4* bsrc = reinterpret_cast<const float4*>(smem_raw + (b_base + (uint32_t)s * b_stage_bytes - smem_u32(smem_raw)));
-                float4* bdst = reinterpret_cast<float4*>(smem_raw + (bs_base + (uint32_t)s * b_stage_bytes - smem_u32(smem_raw)));
-#pragma unroll 4
-                for (int i = tid_r; i < a_q; i += kEpi) adst[i] = tf32_residual(asrc[i]);
-#pragma unroll 4
-                for (int i = tid_r; i < b_q; i += kEpi) bdst[i] = tf32_residual(bsrc[i]);
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor core reads
-                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(resid_bar + 8u * s) : "memory");
-                if (++s == p.stages) { s = 0; phase ^= 1u; }
-            }
-        }
-        bool ok = mbar_wait(tmem_full_bar, 0, 2, 0, wait_limit);
-        ok = __all_sync(0xffffffffu, ok);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (threadIdx.x == 64) TC_TRACE(3074);
-        TC_CTA_TRACE(2);
-        if (!ok || nq <= 0) row_valid = false;   // nothing trustworthy to store
-        // The pipeline stages are idle from here on (every MMA that read them has completed).
-        s_rowoff[row] = row_valid ? (long long)row_off : -1;
-    }
-
-    // ===== the K partitions of a tile meet =====
-    // The S partitions of one tile form a thread-block cluster, which guarantees that they run at the
-    // same time and gives them a hardware barrier.  Each partition writes its partial accumulator
-    // to scratch (it stays in L2), the cluster meets, and partition j then finishes a 1/S share of
-    // the tile: it adds the S partials in partition order - so the result does not depend on timing -
-    // applies the fused chain and writes the final tensor.  (Handing the partials over through
-    // distributed shared memory instead was measured at under 10 bytes per clock and SM.)
-    // Partials are stored quad-major, [CTA][16-byte column quad][row]: lanes are consecutive rows, so
-    // both the partial stores and the loads of the second phase move 512 contiguous bytes per warp.
-    // Without partitions the same layout in shared memory (quad pitch QS) is the transposition buffer
-    // between "thread = row" (TMEM) and "warp = row segment" (coalesced global stores).
-    const int S = p.splits, part = split;
-    const bool multi = S > 1;
-    const bool finish_here = !p.ext_finish;   // else: partials only, a second kernel adds them
-    const int qpr = p.bn >> 2;                // vector path: 16-byte column quads per row,
-    const int QPO = (qpr + S - 1) / S;        //   quads per share
-    const int QS = BM + 1;                    // shared-memory quad pitch in 16-byte units (odd: lanes = quads hit distinct banks)
-    const int CL = (p.bn + S - 1) / S;        // scalar path: columns per share
-    float* my_scratch = p.scratch + (size_t)blockIdx.x * BM * p.bn;
-    const float* tile_scratch = p.scratch + (size_t)(blockIdx.x - part) * BM * p.bn;
-    if (threadIdx.x == 64) TC_TRACE(3000);
-    if (warp >= 2) {
-        const int quad = warp & 3;
-        const int row = quad * 32 + lane;
-        // the two warps of a lane quadrant (2..5 and 6..9) take alternate 32-column slabs
-        for (int c0 = ((warp - 2) >> 2) * 32; c0 < p.bn; c0 += 64) {
-            uint32_t r[32];
-            const uint32_t taddr = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0;
-            const bool full = p.bn - c0 >= 32;   // bn is a multiple of 16: the last slab has 32 or 16 columns
-            if (full) tmem_ld_32x32b_x32(taddr, r);
-            else tmem_ld_32x32b_x16(taddr, r);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (X3) {   // add the accumulator of the small terms
-                uint32_t r2[32];
-                if (full) tmem_ld_32x32b_x32(taddr + (uint32_t)p.bn, r2);
-                else tmem_ld_32x32b_x16(taddr + (uint32_t)p.bn, r2);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int q = 0; q < 32; ++q)
-                    if (q < 16 || full) r[q] = __float_as_uint(__fadd_rn(__uint_as_float(r[q]), __uint_as_float(r2[q])));
-            }
-            if (vec) {
-                if (multi) {
-                    float4* d4 = reinterpret_cast<float4*>(my_scratch) + (size_t)(c0 >> 2) * BM + row;
-#pragma unroll
-                    for (int q = 0; q < 8; ++q)
-                        if (q < 4 || full)
-                            __stcg(d4 + q * BM, make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                                            __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3])));
-                } else {
-                    float4* d4 = reinterpret_cast<float4*>(red) + (c0 >> 2) * QS + row;
-#pragma unroll
-                    for (int q = 0; q < 8; ++q)
-                        if (q < 4 || full)
-                            d4[q * QS] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                                     __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-                }
-            } else {
-                // column-major [column][row], in scratch or in shared memory
-                float* d1 = (multi ? my_scratch : red) + (size_t)c0 * BM + row;
-#pragma unroll
-                for (int q = 0; q < 32; ++q)
-                    if (q < 16 || full) d1[q * BM] = __uint_as_float(r[q]);
-            }
-        }
-        // no fence here: every thread's partial stores are ordered before its own arrival at the cluster barrier
-        // (barrier.cluster.arrive.release / wait.acquire), and before the finish kernel by the kernel boundary
-    }
-    if (threadIdx.x == 64) TC_TRACE(3001);
-    TC_CTA_TRACE(3);
-    __syncwarp();
-    if (multi && finish_here) cluster_sync_all();
-    else if (warp >= 2) asm volatile("bar.sync 1, %0;" ::"n"(kEpi) : "memory");
-    if (threadIdx.x == 64) TC_TRACE(3002);
-    TC_CTA_TRACE(4);
-
-    if (warp >= 2 && finish_here) {
-        // ===== this partition's share: sum in partition order, fused chain, stores =====
-        const int tid_e = threadIdx.x - 64;
-        const EpilogueArgs& e = p.ep;
-        if (vec) {
-            const bool fused = e.raw_out || e.bias || e.pre_act || e.gate || e.act != DCG_ACT_NONE;
-            // multi: thread = row, items = the quads of this share.  single: item = (row, quad) with
-            // consecutive lanes on consecutive quads, so a warp stores whole 128-byte row segments.
-            const int Qm = min(QPO, qpr - part * QPO);
-            const bool by_row = multi || p.planes;               // thread = row (else: lanes walk the quads of a row)
-            // by_row: the two threads of a row (tid_e and tid_e + 128) take alternate quads
-            const int my_row = tid_e & (BM - 1), my_half = tid_e >> 7;
-            const int row_quads = multi ? Qm : qpr;              // by_row: quads of this row's share
-            const int per_thread = by_row ? (row_quads > my_half ? (row_quads - my_half + 1) / 2 : 0)
-                                          : qpr / 2;            // single: 128 * qpr items over 256 threads (qpr is even)
-            const int quad0 = ch0 >> 2;                          // planes: global index of this tile's first quad
-            const int step_r = kEpi / qpr, step_q = kEpi % qpr;  // single: how (row, quad) moves when the item index grows by kEpi
-            int rr = tid_e / qpr, q = tid_e % qpr;
-            const long long my_ro = s_rowoff[my_row];
-            const float4* red4 = reinterpret_cast<const float4*>(red);
-            const float4* ts4 = reinterpret_cast<const float4*>(tile_scratch);
-            for (int base = 0; base < per_thread; base += 4) {
-                float4 acc[4];
-                long long goff[4];
-                int cq[4];
-                if (by_row) {
-                    const float4* src[4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const bool in = base + u < per_thread;
-                        const int qd = part * QPO + (in ? my_half + 2 * (base + u) : 0);
-                        cq[u] = qd << 2;
-                        goff[u] = (!in || my_ro < 0 || cq[u] >= ncols_valid) ? -1
-                                  : p.planes ? my_ro + (long long)((unsigned long long)(quad0 + qd) * p.plane_stride)
-                                             : my_ro + cq[u];
-                        src[u] = (multi ? ts4 + (size_t)qd * BM : red4 + qd * QS) + my_row;
-                    }
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) acc[u] = multi ? __ldcg(src[u]) : *src[u];
-#pragma unroll 2
-                    for (int sidx = 1; sidx < S; ++sidx) {   // two partitions' loads in flight; the adds keep partition order
-                        float4 v[4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) v[u] = __ldcg(src[u] + (size_t)sidx * BM * qpr);
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            acc[u].x = __fadd_rn(acc[u].x, v[u].x); acc[u].y = __fadd_rn(acc[u].y, v[u].y);
-                            acc[u].z = __fadd_rn(acc[u].z, v[u].z); acc[u].w = __fadd_rn(acc[u].w, v[u].w);
-                        }
-                    }
-                } else {
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const bool in = base + u < per_thread;
-                        cq[u] = q << 2;
-                        const long long ro = in ? s_rowoff[rr] : -1;
-                        goff[u] = (ro < 0 || cq[u] >= ncols_valid) ? -1 : ro + cq[u];
-                        acc[u] = red4[in ? q * QS + rr : 0];
-                        rr += step_r; q += step_q;
-                        if (q >= qpr) { q -= qpr; ++rr; }
-                    }
-                }
-                if (fused) {
-                    // each optional step of the chain runs over the four items at once, so its
-                    // test is paid once and the loads of a step are in flight together
-                    if (e.raw_out) {
-#pragma unroll
-                        for (int u = 0; u < 4; ++u)
-                            if (goff[u] >= 0) *reinterpret_cast<float4*>(e.raw_out + goff[u]) = acc[u];
-                    }
-                    if (e.bias) {
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const float4 bv = __ldg(reinterpret_cast<const float4*>(e.bias + ch0 + cq[u]));
-                            acc[u].x = __fadd_rn(acc[u].x, bv.x); acc[u].y = __fadd_rn(acc[u].y, bv.y);
-                            acc[u].z = __fadd_rn(acc[u].z, bv.z); acc[u].w = __fadd_rn(acc[u].w, bv.w);
-                        }
-                    }
-                    if (e.pre_act) {
-#pragma unroll
-                        for (int u = 0; u < 4; ++u)
-                            if (goff[u] >= 0) *reinterpret_cast<float4*>(e.pre_act + goff[u]) = acc[u];
-                    }
-                    if (e.act != DCG_ACT_NONE) {
-                        const int act = e.act;
-                        const float alpha = e.alpha;
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            acc[u].x = act_apply(acc[u].x, act, alpha); acc[u].y = act_apply(acc[u].y, act, alpha);
-                            acc[u].z = act_apply(acc[u].z, act, alpha); acc[u].w = act_apply(acc[u].w, act, alpha);
-                        }
-                    }
-                    if (e.gate) {
-                        float4 gg[4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u)
-                            gg[u] = goff[u] >= 0 ? __ldg(reinterpret_cast<const float4*>(e.gate + goff[u]))
-                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
-                        const int gact = e.gate_act;
-                        const float galpha = e.gate_alpha;
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            acc[u].x = act_grad_apply(gg[u].x, acc[u].x, gact, galpha);
-                            acc[u].y = act_grad_apply(gg[u].y, acc[u].y, gact, galpha);
-                            acc[u].z = act_grad_apply(gg[u].z, acc[u].z, gact, galpha);
-                            acc[u].w = act_grad_apply(gg[u].w, acc[u].w, gact, galpha);
-                        }
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (goff[u] >= 0) *reinterpret_cast<float4*>(p.out + goff[u]) = acc[u];
-            }
-        } else {
-            // thread = row; share = every S-th column.  Used where consecutive ROWS are adjacent in
-            // memory (DK with the channel roles swapped, narrow-channel DK) and for channel counts
-            // that rule out 16-byte stores.
-            const int my_row = tid_e & (BM - 1), my_half = tid_e >> 7;   // the two threads of a row take alternate columns
-            const long long ro = s_rowoff[my_row];
-            for (int cl0 = 0; 2 * cl0 + my_half < CL; cl0 += 4) {   // four columns at a time: their loads are in flight together
-                float acc[4];
-                int cols[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int cl = 2 * (cl0 + u) + my_half;
-                    const int col = cl * S + part;
-                    cols[u] = (cl < CL && col < ncols_valid) ? col : -1;
-                    const int cc = cols[u] < 0 ? 0 : cols[u];
-                    acc[u] = multi ? __ldcg(tile_scratch + (size_t)cc * BM + my_row) : red[cc * BM + my_row];
-                }
-                if (multi) {
-                    for (int sidx = 1; sidx < S; ++sidx) {
-                        float v[4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u)
-                            v[u] = __ldcg(tile_scratch + ((size_t)sidx * p.bn + (cols[u] < 0 ? 0 : cols[u])) * BM + my_row);
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) acc[u] = __fadd_rn(acc[u], v[u]);
-                    }
-                }
-                if (ro < 0) continue;
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int col = cols[u];
-                    if (col < 0) continue;
-                    unsigned long long id = (unsigned long long)ro + (unsigned long long)col * col_stride;
-                    if (MODE == MODE_DK && p.narrow) {
-                        const int di = col >> 5, dj = (col & 31) >> 2, c = col & 3;   // slot = 4*dj + channel
-                        if (dj >= p.KW || c >= p.C) continue;                          // padding slots
-                        id = (unsigned long long)ro + (unsigned long long)((di * p.KW + dj) * p.C + c) * p.O;
-                    }
-                    // the fused chain only exists for FWD/DX; DK stores raw sums
-                    p.out[id] = (MODE == MODE_DK) ? acc[u] : epilogue_apply(e, acc[u], id, ch0 + col);
-                }
-            }
-        }
-    }
-
-    if (threadIdx.x == 64) TC_TRACE(3075);
-    TC_CTA_TRACE(5);
-    // ---- teardown: everyone is done with TMEM before warp 1 releases it --------------------------
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 1) {
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
-    }
-}
-
-// ---- DX with all parity classes of a pixel tile in one CTA -------------------------------------------
-// The parity classes of the input gradient (pix mod stride) read the SAME windows of dy, only paired
-// with different kernel taps: class (ph, pw), tap (di, dj) reads dy at pixel offset
-// ((ph + pad - di) / s, (pw + pad - dj) / s) of the class grid.  For a 5x5 kernel at stride 2 the 25
-// (class, tap) pairs share 9 distinct windows.  conv_tc_kernel<DX> runs every class as a tile of its
-// own and so fetches a dy tile from L2 once per tap; with a narrow N tile (64 input channels: A 16 KB
-// against B 8 KB per stage) that fetch is two thirds of what the SM has to take in, and taking
-// operands in is what bounds the main loop.  This kernel gives one CTA the 128 pixels of ALL classes:
-// one accumulator per class (classes x bn <= 512 TMEM columns), each window fetched once and
-// multiplied against the weight tiles of every pair that reads it - 9 x 16 KB + 25 x 8 KB per 32
-// output channels instead of 25 x 24 KB.  A pipeline stage is one window plus the weight tiles of up to
-// `pb` pairs that read it (a window with more pairs takes several stages and is fetched again for
-// each).  The windows are ordered so that the classes complete one after the other; the epilogue
-// of a finished class (through a transposition buffer of its own, not the stage ring) runs under
-// the main loop of the rest.  No K partitions: the planner only picks this kernel when the tiles
-// alone fill the GPU.
-//
-// The accumulators of the classes sit side by side in TMEM, and the weight tiles of a stage are stacked
-// in shared memory in the same order, so pairs whose classes are neighbours there are ONE MMA with
-// N = count x bn columns.  That matters for narrow tiles: an N = 64 MMA takes as long as an N = 128
-// one (measured: the MMA-only time of the 64-channel layer is 1.8 x that of its N = 128 forward), so
-// the 25 N = 64 products of a channel chunk become 4 of N = 256, 4 of N = 128 and 1 of N = 64.
-struct CfWin {
-    signed char sy, sx;        // window: dy pixel (i + sy, j + sx) for class pixel (i, j)
-    unsigned char n;           // pairs of this stage, in TMEM order
-    unsigned char last;        // bit j: pair j is the last contribution to its class (in the last channel chunk)
-    unsigned char fresh;       // bit j: pair j is the first contribution to its class (in the first channel chunk)
-    unsigned char cls[4], kh[4], kw[4];
-    unsigned char slot[4];     // TMEM position of the pair's accumulator (columns slot * bn ...)
-    unsigned char glen[4];     // pair j starts an MMA over glen[j] adjacent accumulators (0: it belongs to an earlier one)
-};
-struct CfTable {
-    int nwin, ncls;            // stages per channel chunk, parity classes
-    int slot_bytes;            // stage size: A tile + pb weight tiles
-    int order[4];              // classes in the order in which they complete
-    int slot_of_class[4];      // TMEM position of every class
-    CfWin win[32];
-};
-constexpr int kCfHalf = 64;                // accumulator columns the epilogue moves at a time
-__host__ __device__ constexpr int kCfRedBytes() { return kRedFloats(kCfHalf) * 4 + BM * 8; }
-
-// The fused chain over four 16-byte items at once: every optional step is tested once and its loads
-// (bias, gate) are in flight together.  goff < 0 marks an item that is not stored.
-__device__ __forceinline__ void cf_chain_store4(const EpilogueArgs& e, float* out, float4 (&acc)[4], const long long (&goff)[4],
-                                                const int (&ch)[4])
-{
-    if (e.raw_out) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-            if (goff[u] >= 0) *reinterpret_cast<float4*>(e.raw_out + goff[u]) = acc[u];
-    }
-    if (e.bias) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const float4 bv = __ldg(reinterpret_cast<const float4*>(e.bias + ch[u]));
-            acc[u].x = __fadd_rn(acc[u].x, bv.x); acc[u].y = __fadd_rn(acc[u].y, bv.y);
-            acc[u].z = __fadd_rn(acc[u].z, bv.z); acc[u].w = __fadd_rn(acc[u].w, bv.w);
-        }
-    }
-    if (e.pre_act) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-            if (goff[u] >= 0) *reinterpret_cast<float4*>(e.pre_act + goff[u]) = acc[u];
-    }
-    if (e.act != DCG_ACT_NONE) {
-        const int act = e.act;
-        const float alpha = e.alpha;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            acc[u].x = act_apply(acc[u].x, act, alpha); acc[u].y = act_apply(acc[u].y, act, alpha);
-            acc[u].z = act_apply(acc[u].z, act, alpha); acc[u].w = act_apply(acc[u].w, act, alpha);
-        }
-    }
-    if (e.gate) {
-        float4 g[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-            g[u] = goff[u] >= 0 ? __ldg(reinterpret_cast<const float4*>(e.gate + goff[u])) : make_float4(0.f, 0.f, 0.f, 0.f);
-        const int gact = e.gate_act;
-        const float galpha = e.gate_alpha;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            acc[u].x = act_grad_apply(g[u].x, acc[u].x, gact, galpha);
-            acc[u].y = act_grad_apply(g[u].y, acc[u].y, gact, galpha);
-            acc[u].z = act_grad_apply(g[u].z, acc[u].z, gact, galpha);
-            acc[u].w = act_grad_apply(g[u].w, acc[u].w, gact, galpha);
-        }
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u)
-        if (goff[u] >= 0) *reinterpret_cast<float4*>(out + goff[u]) = acc[u];
-}
-
-__global__ void __launch_bounds__(kThreads, 1)
-conv_dxf_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                const __grid_constant__ Params p, const __grid_constant__ CfTable t)
-{
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t smem0 = smem_u32(smem_raw);
-    const uint32_t ring = (smem0 + 1023u) & ~1023u;
-    const long long wait_limit = p.wait_cycles;
-    const uint32_t slot_bytes = (uint32_t)t.slot_bytes;
-    const uint32_t red_base = ring + (uint32_t)p.stages * slot_bytes;
-    const uint32_t bar_base = red_base + (uint32_t)kCfRedBytes();
-    const uint32_t full_bar = bar_base;
-    const uint32_t empty_bar = bar_base + 8u * p.stages;
-    const uint32_t cls_bar = bar_base + 16u * p.stages;     // accumulator of class c complete
-    const uint32_t tmem_slot = cls_bar + 32u;
-    uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem0));
-    float* red = reinterpret_cast<float*>(smem_raw + (red_base - smem0));
-    long long* s_rowoff = reinterpret_cast<long long*>(red + kRedFloats(kCfHalf));
-
-    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
-    const int ncls = t.ncls, nwin = t.nwin;
-    const uint32_t b_bytes = (uint32_t)p.bn * BK * 4;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < p.stages; ++s) {
-            mbar_init(full_bar + 8u * s, 1);
-            mbar_init(empty_bar + 8u * s, 1);
-        }
-        for (int c = 0; c < 4; ++c) mbar_init(cls_bar + 8u * c, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
-    }
-    int tmem_cols = 32;
-    while (tmem_cols < ncls * p.bn) tmem_cols <<= 1;
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(tmem_cols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    // blockIdx.x = pixel tile * n_tiles + channel tile
-    const int n_tile = blockIdx.x % p.n_tiles, m_tile = blockIdx.x / p.n_tiles;
-    const int j0 = (m_tile % p.tiles_w) * p.TW;
-    const int i0 = ((m_tile / p.tiles_w) % p.tiles_h) * p.TH;
-    const int n0 = (m_tile / (p.tiles_w * p.tiles_h)) * p.TN;
-    const int ch0 = n_tile * p.bn;
-    const int ncols_valid = min(p.bn, p.C - ch0);
-
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_d = *tmem_slot_ptr;
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-
-    if (warp == 0) {
-        // ===== TMA producer: for every table entry, for every channel chunk: the window, then its weight tiles =====
-        int s = 0, it = 0;
-        uint32_t phase = 0;
-        bool alive = true;
-        for (int w = 0; w < nwin && alive; ++w) {
-            const CfWin& wn = t.win[w];
-            const int sy = wn.sy, sx = wn.sx, np = wn.n;
-            for (int chunk = 0; chunk < p.kchunks; ++chunk, ++it) {
-                if (!mbar_wait_warp(empty_bar + 8u * s, phase ^ 1u, 0, it, wait_limit)) { alive = false; break; }
-                if (elect_one()) {
-                    const uint32_t fb = full_bar + 8u * s;
-                    const uint32_t dst = ring + (uint32_t)s * slot_bytes;
-                    mbar_expect_tx(fb, (uint32_t)A_STAGE_BYTES + (uint32_t)np * b_bytes);
-                    tma_load_4d(dst, &map_a, fb, chunk * BK, j0 + sx, i0 + sy, n0);
-                    for (int j = 0; j < np; ++j)
-                        tma_load_4d(dst + (uint32_t)A_STAGE_BYTES + (uint32_t)j * b_bytes, &map_b, fb, chunk * BK, ch0,
-                                    (int)wn.kw[j], (int)wn.kh[j]);
-                }
-                if (++s == p.stages) { s = 0; phase ^= 1u; }
-            }
-        }
-    } else if (warp == 1) {
-        // ===== MMA issuer =====
-        const uint64_t desc0 = make_smem_desc(ring, 16u, 1024u, kLayoutSw128);   // K-major, 128-byte rows, 8-row groups 1024 B apart
-        const uint32_t slot16 = slot_bytes >> 4, b16 = b_bytes >> 4;
-        int s = 0, it = 0;
-        uint32_t phase = 0, done = 0;
-        bool alive = true;
-        for (int w = 0; w < nwin && alive; ++w) {
-            const CfWin& wn = t.win[w];
-            const int np = wn.n;
-            const uint32_t last = wn.last, fresh = wn.fresh;
-            for (int chunk = 0; chunk < p.kchunks; ++chunk, ++it) {
-                if (!mbar_wait_warp(full_bar + 8u * s, phase, 1, it, wait_limit)) { alive = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const bool final_chunk = chunk == p.kchunks - 1;
-                if (elect_one()) {
-                    const uint64_t adesc = desc0 + (uint64_t)((uint32_t)s * slot16);
-                    for (int j = 0; j < np; ++j) {
-                        const int cnt = wn.glen[j];
-                        if (cnt > 0) {   // one MMA per K step over the cnt adjacent accumulators that start here
-                            const uint32_t idesc = make_idesc(0, 0, cnt * p.bn, BM);
-                            const uint64_t bdesc = adesc + (uint64_t)((uint32_t)(A_STAGE_BYTES >> 4) + (uint32_t)j * b16);
-                            const uint32_t acc = tmem_d + (uint32_t)(wn.slot[j] * p.bn);
-                            const bool overwrite = chunk == 0 && ((fresh >> j) & 1u);
-#pragma unroll
-                            for (int kk = 0; kk < BK / 8; ++kk)
-                                tcgen05_mma_tf32(acc, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc,
-                                                 (overwrite && kk == 0) ? 0u : 1u);
-                        }
-                    }
-                    if (final_chunk)
-                        for (int j = 0; j < np; ++j)
-                            if ((last >> j) & 1u) tcgen05_commit(cls_bar + 8u * wn.cls[j]);
-                    tcgen05_commit(empty_bar + 8u * s);
-                }
-                if (final_chunk)
-                    for (int j = 0; j < np; ++j)
-                        if ((last >> j) & 1u) done |= 1u << wn.cls[j];
-                if (++s == p.stages) { s = 0; phase ^= 1u; }
-            }
-        }
-        // a pipeline that gave up still releases the epilogue (which stores nothing then)
-        if (elect_one())
-            for (int c = 0; c < ncls; ++c)
-                if (!((done >> c) & 1u)) tcgen05_commit(cls_bar + 8u * c);
-    } else {
-        // ===== epilogue: classes in completion order, 64 accumulator columns at a time =====
-        const int quad = warp & 3;
-        const int row = quad * 32 + lane;
-        const int tid_e = threadIdx.x - 64;
-        const int tw = row % p.TW, th = (row / p.TW) % p.TH, tn = row / (p.TW * p.TH);
-        const EpilogueArgs& e = p.ep;
-        constexpr int QS = BM + 1;
-        // 16-byte stores need whole column quads in every row; else (3 input channels) element by element
-        const bool vec = (p.C & 3) == 0 && (ncols_valid & 3) == 0;
-        for (int ci = 0; ci < ncls; ++ci) {
-            const int cls = t.order[ci];
-            const int ph = cls / p.sw, pw = cls % p.sw;
-            bool ok = mbar_wait(cls_bar + 8u * cls, 0, 2, cls, wait_limit);
-            ok = __all_sync(0xffffffffu, ok);
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (warp < 6) {
-                const int n = n0 + tn, h = p.sh * (i0 + th) + ph, w = p.sw * (j0 + tw) + pw;
-                const bool valid = ok && n < p.N && h < p.H && w < p.W;
-                s_rowoff[row] = valid ? (long long)((((unsigned long long)n * p.H + h) * p.W + w) * p.C + ch0) : -1;
-            }
-            for (int half0 = 0; half0 < p.bn; half0 += kCfHalf) {
-                const int hcols = min(kCfHalf, p.bn - half0);
-                // TMEM -> transposition buffer: thread = row, the two warps of a lane quadrant take one 32-column slab each
-                const int c0 = half0 + ((warp - 2) >> 2) * 32;
-                if (c0 < half0 + hcols) {
-                    uint32_t r[32];
-                    const uint32_t taddr = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)(t.slot_of_class[cls] * p.bn + c0);
-                    const bool full = half0 + hcols - c0 >= 32;
-                    if (full) tmem_ld_32x32b_x32(taddr, r);
-                    else tmem_ld_32x32b_x16(taddr, r);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (vec) {
-                        float4* d4 = reinterpret_cast<float4*>(red) + ((c0 - half0) >> 2) * QS + row;
-#pragma unroll
-                        for (int q = 0; q < 8; ++q)
-                            if (q < 4 || full)
-                                d4[q * QS] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                                         __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-                    } else {   // column-major [column][row]; only the valid columns are ever read back
-                        float* d1 = red + (c0 - half0) * BM + row;
-                        const int nv = ncols_valid - c0;
-#pragma unroll
-                        for (int q = 0; q < 32; ++q)
-                            if ((q < 16 || full) && q < nv) d1[q * BM] = __uint_as_float(r[q]);
-                    }
-                }
-                asm volatile("bar.sync 1, %0;" ::"n"(kEpi) : "memory");
-                // fused chain and stores: consecutive lanes take consecutive 16-byte column quads of a row
-                const int hq = hcols >> 2;
-                const float4* red4 = reinterpret_cast<const float4*>(red);
-                if (!vec) {   // consecutive lanes take the consecutive valid columns of a row
-                    const int hv = min(hcols, ncols_valid - half0);
-                    for (int idx = tid_e; idx < BM * hv; idx += kEpi) {
-                        const int rr = idx / hv, c = idx - rr * hv;
-                        const long long ro = s_rowoff[rr];
-                        if (ro < 0) continue;
-                        const unsigned long long id = (unsigned long long)ro + (unsigned long long)(half0 + c);
-                        p.out[id] = epilogue_apply(e, red[c * BM + rr], id, ch0 + half0 + c);
-                    }
-                }
-                const int items = vec ? BM * hq : 0;   // = kEpi * hq / 2: every thread has hq / 2 items, taken four at a time
-                for (int base = tid_e; base < items; base += 4 * kEpi) {
-                    float4 acc[4];
-                    long long goff[4];
-                    int ch[4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const int idx = base + u * kEpi;
-                        const bool in = idx < items;
-                        const int rr = in ? idx / hq : 0, q = in ? idx - rr * hq : 0;
-                        const int col = half0 + (q << 2);
-                        const long long ro = in ? s_rowoff[rr] : -1;
-                        acc[u] = red4[q * QS + rr];
-                        goff[u] = (ro < 0 || col >= ncols_valid) ? -1 : ro + col;
-                        ch[u] = ch0 + (col < ncols_valid ? col : 0);
-                    }
-                    cf_chain_store4(e, p.out, acc, goff, ch);
-                }
-                asm volatile("bar.sync 1, %0;" ::"n"(kEpi) : "memory");
-            }
-        }
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 1) {
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
-    }
-}
-
-// ---- short-K forward GEMMs as persistent CTAs ---------------------------------------------------------
-// The two tensor-core launches of the 3-channel layers have almost no K: the forward contracts five
-// 32-float row windows per tile (A through the overlapping-window map, B = k4), the GEMM of the input
-// gradient two 32-channel chunks (a 1x1 convolution of dy against all taps, result in quad planes).
-// With one tile per CTA such a CTA spends its life on set-up, pipeline fill and epilogue (2-5 stages
-// of work against ~3 us of fixed cost) and fetches the same weights again for every tile.  Here a
-// CTA (two per SM) walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...: the weights are loaded once and stay
-// in shared memory, the A tiles of the next tiles stream through a ring while the tensor core works
-// on this one, and the accumulator is double-buffered in TMEM so that the epilogue of tile i
-// runs under the MMAs of tile i + 1.  The GEMM's result goes out straight from registers (thread = pixel
-// row, and in the quad-plane layout consecutive pixels are consecutive 16-byte words); the forward's NHWC
-// rows go through a small per-warp patch of shared memory (32 rows x 16 columns) so that every store
-// instruction covers whole 64-byte row pieces.
-constexpr int kShortMaxStages = 4;         // A ring depth (16 KB each): 4 for the GEMM, 3 next to the forward's patches
-constexpr int kShortMaxB = 40 * 1024;      // resident weights
-constexpr int kPatchPitch = 20;            // floats per patch row (16 columns + 4: keeps 16-byte alignment)
-constexpr int kPatchBytes = 32 * kPatchPitch * 4;
-
-template <bool NARROW>
-__global__ void __launch_bounds__(kThreads, 2)
-conv_fwd_short_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                      const __grid_constant__ Params p, const int tiles, const int ksteps)
-{
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t smem0 = smem_u32(smem_raw);
-    const uint32_t b_res = (smem0 + 1023u) & ~1023u;
-    const long long wait_limit = p.wait_cycles;
-    const uint32_t b_bytes = (uint32_t)p.bn * BK * 4;
-    const uint32_t ring = b_res + (uint32_t)ksteps * b_bytes;
-    const int kShortStages = p.stages;
-    const uint32_t patch_base = ring + (uint32_t)kShortStages * A_STAGE_BYTES;   // NARROW: one patch per epilogue warp
-    const uint32_t bar_base = patch_base + (NARROW ? (uint32_t)(kEpi / 32) * kPatchBytes : 0u);
-    const uint32_t full_bar = bar_base;                          // [kShortMaxStages]
-    const uint32_t empty_bar = bar_base + 8u * kShortMaxStages;  // [kShortMaxStages]
-    const uint32_t b_bar = bar_base + 16u * kShortMaxStages;     // weights have landed
-    const uint32_t acc_full = b_bar + 8u;                        // [2] accumulator buffer complete
-    const uint32_t acc_empty = acc_full + 16u;                   // [2] accumulator buffer drained (8 epilogue warps)
-    const uint32_t tmem_slot = acc_empty + 16u;
-    uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem0));
-    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kShortStages; ++s) {
-            mbar_init(full_bar + 8u * s, 1);
-            mbar_init(empty_bar + 8u * s, 1);
-        }
-        mbar_init(b_bar, 1);
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(acc_full + 8u * b, 1);
-            mbar_init(acc_empty + 8u * b, kEpi / 32);
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
-    }
-    int tmem_cols = 32;
-    while (tmem_cols < 2 * p.bn) tmem_cols <<= 1;
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(tmem_cols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_d = *tmem_slot_ptr;
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const int per_image = p.tiles_w * p.tiles_h;
-
-    if (warp == 0) {
-        // ===== producer: the weights once, then the A tiles of every tile of this CTA =====
-        if (elect_one()) {
-            mbar_expect_tx(b_bar, (uint32_t)ksteps * b_bytes);
-            for (int q = 0; q < ksteps; ++q) {
-                if (NARROW) tma_load_4d(b_res + (uint32_t)q * b_bytes, &map_b, b_bar, 0, 0, q, 0);
-                else if (p.b_direct) tma_load_3d(b_res + (uint32_t)q * b_bytes, &map_b, b_bar, q * BK, 0, 0);
-                else tma_load_4d(b_res + (uint32_t)q * b_bytes, &map_b, b_bar, 0, q * BK, 0, 0);
-            }
-        }
-        int s = 0, it = 0;
-        uint32_t phase = 0;
-        bool alive = true;
-        for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x) {
-            const int j0 = (tile % p.tiles_w) * p.TW;
-            const int i0 = ((tile / p.tiles_w) % p.tiles_h) * p.TH;
-            const int n0 = (tile / per_image) * p.TN;
-            for (int q = 0; q < ksteps; ++q, ++it) {
-                if (!mbar_wait_warp(empty_bar + 8u * s, phase ^ 1u, 0, it, wait_limit)) { alive = false; break; }
-                if (elect_one()) {
-                    const uint32_t fb = full_bar + 8u * s;
-                    const uint32_t dst = ring + (uint32_t)s * A_STAGE_BYTES;
-                    mbar_expect_tx(fb, (uint32_t)A_STAGE_BYTES);
-                    if (NARROW) tma_load_5d(dst, &map_a, fb, 0, j0, i0, n0, q);
-                    else tma_load_4d(dst, &map_a, fb, q * BK, j0, i0, n0);
-                }
-                if (++s == kShortStages) { s = 0; phase ^= 1u; }
-            }
-        }
-    } else if (warp == 1) {
-        // ===== MMA issuer: A K-major, B MN-major (chunks of 32 columns 4096 B apart, 4-row groups 512 B apart) =====
-        // B: MN-major (chunks of 32 columns 4096 B apart, 4-row groups 512 B apart, 8 k rows per MMA = 1024 B), or -
-        // read from k directly - K-major like A (128-byte rows, 32 bytes per MMA)
-        const bool bk = !NARROW && p.b_direct;
-        const uint32_t idesc = make_idesc(0, bk ? 0 : 1, p.bn, BM);
-        const uint64_t adesc0 = make_smem_desc(ring, 16u, 1024u, kLayoutSw128);
-        const uint64_t bdesc0 = bk ? make_smem_desc(b_res, 16u, 1024u, kLayoutSw128)
-                                   : make_smem_desc(b_res, 4096u, 512u, kLayoutSw128Base32);
-        const uint32_t b_kstep = bk ? 2u : 64u;
-        int s = 0, it = 0, n = 0;
-        uint32_t phase = 0;
-        bool alive = mbar_wait_warp(b_bar, 0, 1, -1, wait_limit);
-        for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x, ++n) {
-            const int buf = n & 1;
-            // the epilogue has drained this buffer's previous tile (first use: passes at once)
-            if (!mbar_wait_warp(acc_empty + 8u * buf, ((uint32_t)(n >> 1) & 1u) ^ 1u, 1, it, wait_limit)) { alive = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            for (int q = 0; q < ksteps; ++q, ++it) {
-                if (!mbar_wait_warp(full_bar + 8u * s, phase, 1, it, wait_limit)) { alive = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (elect_one()) {
-                    const uint64_t adesc = adesc0 + (uint64_t)((uint32_t)s * (A_STAGE_BYTES >> 4));
-                    const uint64_t bdesc = bdesc0 + (uint64_t)((uint32_t)q * (b_bytes >> 4));
-#pragma unroll
-                    for (int kk = 0; kk < BK / 8; ++kk)
-                        tcgen05_mma_tf32(tmem_d + (uint32_t)(buf * p.bn), adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * b_kstep), idesc,
-                                         (q > 0 || kk > 0) ? 1u : 0u);
-                    tcgen05_commit(empty_bar + 8u * s);
-                }
-                if (++s == kShortStages) { s = 0; phase ^= 1u; }
-            }
-            if (elect_one()) tcgen05_commit(acc_full + 8u * buf);   // complete, or abandoned
-        }
-    } else {
-        // ===== epilogue: thread = accumulator row; the two warps of a lane quadrant take alternate 32-column slabs =====
-        const int quad = warp & 3;
-        const int row = quad * 32 + lane;
-        const int tw = row % p.TW, th = (row / p.TW) % p.TH, tn = row / (p.TW * p.TH);
-        const EpilogueArgs& e = p.ep;
-        const int ncols = p.o_store ? p.o_store : p.O;
-        int n = 0;
-        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++n) {
-            const int buf = n & 1;
-            const int j = (tile % p.tiles_w) * p.TW + tw;
-            const int i = ((tile / p.tiles_w) % p.tiles_h) * p.TH + th;
-            const int img = (tile / per_image) * p.TN + tn;
-            bool ok = mbar_wait(acc_full + 8u * buf, (uint32_t)(n >> 1) & 1u, 2, n, wait_limit);
-            ok = __all_sync(0xffffffffu, ok);
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const bool valid = ok && img < p.N && i < p.Ho && j < p.Wo;
-            const unsigned long long pix = ((unsigned long long)img * p.Ho + i) * p.Wo + j;
-            const int first = (warp - 2) >> 2, nslabs = (p.bn + 31) >> 5;
-            for (int sl = first; sl < nslabs; sl += 2) {
-                const int c0 = sl * 32;
-                uint32_t r[32];
-                const uint32_t taddr = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * p.bn + c0);
-                const bool full = p.bn - c0 >= 32;
-                if (full) tmem_ld_32x32b_x32(taddr, r);
-                else tmem_ld_32x32b_x16(taddr, r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (sl + 2 >= nslabs) {   // this warp's last read of the buffer: hand it back to the MMA warp
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty + 8u * buf) : "memory");
-                }
-                if (NARROW) {
-                    // 16 columns at a time through this warp's patch: written by rows (lane = row), read back with four
-                    // lanes per row, so that a store instruction covers eight 64-byte row pieces
-                    float* patch = reinterpret_cast<float*>(smem_raw + (patch_base - smem0)) + (warp - 2) * (kPatchBytes / 4);
-                    const long long my_off = valid ? (long long)(pix * (unsigned long long)p.O) : -1;
-#pragma unroll
-                    for (int hs = 0; hs < 2; ++hs) {
-                        if (hs == 1 && !full) break;
-                        __syncwarp();
-#pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4)
-                            *reinterpret_cast<float4*>(patch + lane * kPatchPitch + 4 * q4) =
-                                make_float4(__uint_as_float(r[16 * hs + 4 * q4]), __uint_as_float(r[16 * hs + 4 * q4 + 1]),
-                                            __uint_as_float(r[16 * hs + 4 * q4 + 2]), __uint_as_float(r[16 * hs + 4 * q4 + 3]));
-                        __syncwarp();
-                        float4 acc[4];
-                        long long goff[4];
-                        int ch[4];
-                        const int col = c0 + 16 * hs + 4 * (lane & 3);
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const int rl = u * 8 + (lane >> 2);
-                            const long long ro = __shfl_sync(0xffffffffu, my_off, rl);
-                            acc[u] = *reinterpret_cast<const float4*>(patch + rl * kPatchPitch + 4 * (lane & 3));
-                            const bool in = ro >= 0 && col < ncols;
-                            goff[u] = in ? ro + col : -1;
-                            ch[u] = in ? col : 0;
-                        }
-                        cf_chain_store4(e, p.out, acc, goff, ch);
-                    }
-                } else {
-#pragma unroll
-                    for (int g = 0; g < 2; ++g) {   // four 16-byte column quads at a time; consecutive pixels are consecutive words
-                        float4 acc[4];
-                        long long goff[4];
-                        int ch[4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const int q4 = g * 4 + u;
-                            const int col = c0 + 4 * q4;
-                            acc[u] = make_float4(__uint_as_float(r[4 * q4]), __uint_as_float(r[4 * q4 + 1]),
-                                                 __uint_as_float(r[4 * q4 + 2]), __uint_as_float(r[4 * q4 + 3]));
-                            const bool in = valid && (q4 < 4 || full) && col < ncols;
-                            goff[u] = in ? (long long)(pix * 4ull + (unsigned long long)(col >> 2) * p.plane_stride) : -1;
-                            ch[u] = in ? col : 0;
-                        }
-                        cf_chain_store4(e, p.out, acc, goff, ch);
-                    }
-                }
-            }
-            if (nslabs <= first) {   // a warp without a slab still has to hand the buffer back
-                __syncwarp();
-                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty + 8u * buf) : "memory");
-            }
-        }
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 1) {
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
-    }
-}
-
-// ---- input gradient of a <= 4-channel layer: GEMM and gather in one persistent kernel -----------------
-// dx[n, h, w, c] = sum over the taps of matching parity of ycol[tap][n, i, j][c], where ycol = dy x k^T is
-// the plain GEMM of every dy pixel against all taps (N = 4 columns per tap).  Written to memory, ycol is
-// 100 floats per dy pixel - 26 MB at batch 64 for a 3 MB result - and the gather is a second launch.
-// Here a CTA owns 2R output rows of one image: it runs the GEMM for the R + 2 dy rows that contribute to
-// them (two 128-pixel M tiles = 8 rows of 32 pixels, so the rows at the seams are computed twice), parks
-// the products in shared memory as [tap][dy pixel][4] and gathers its own output pixels from there, fused
-// chain included.  Nothing but dy, the weights and dx touches memory, and it is one launch.  Persistent:
-// a CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...; the weights stay resident (read from k
-// itself, K-major rows 4 * tap + c), the dy tiles of the next tile stream in and its MMAs run while this
-// tile is being gathered (one TMEM accumulator per M tile, handed back as soon as it is in shared memory).
-struct Dx3Args {
-    int R;            // dy rows owned per tile (2R output rows)
-    int lo;           // first dy row a tile needs, relative to its first owned row (<= 0)
-    int tiles_per_img, tiles;
-};
-constexpr int kDx3Rows = 8;                               // dy rows per tile (two M tiles of 4 rows x 32 pixels)
-constexpr int kDx3Stages = 4;
-constexpr int kDx3Epi = 512;                              // epilogue threads: 16 warps, four per TMEM lane quadrant (one 32-column slab each)
-constexpr int kDx3Threads = 64 + kDx3Epi;
-constexpr int kDx3YcolBytes = 32 * kDx3Rows * 32 * 16;    // up to 32 taps x 256 dy pixels x 4 floats
-
-template <int KH_, int KW_>   // 5, 5: tap loops unrolled, all loads of a pixel in flight; 0, 0: any kernel size
-__global__ void __launch_bounds__(kDx3Threads, 1)
-conv_dx3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                const __grid_constant__ Params p, const __grid_constant__ Dx3Args g)
-{
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t smem0 = smem_u32(smem_raw);
-    const uint32_t b_res = (smem0 + 1023u) & ~1023u;
-    const long long wait_limit = p.wait_cycles;
-    const int ksteps = p.kchunks;
-    const uint32_t b_bytes = 128u * BK * 4;                       // 128 rows (4 * tap + c) x 32 output channels
-    const uint32_t ring = b_res + (uint32_t)ksteps * b_bytes;
-    const uint32_t ycol_base = ring + (uint32_t)kDx3Stages * A_STAGE_BYTES;
-    const int ntaps = p.KH * p.KW;
-    const uint32_t bar_base = ycol_base + (uint32_t)ntaps * (kDx3Rows * 32 * 16);
-    const uint32_t full_bar = bar_base;                           // [kDx3Stages]
-    const uint32_t empty_bar = bar_base + 8u * kDx3Stages;        // [kDx3Stages]
-    const uint32_t b_bar = bar_base + 16u * kDx3Stages;
-    const uint32_t acc_full = b_bar + 8u;                         // [2] one per M tile
-    const uint32_t acc_empty = acc_full + 16u;                    // [2]
-    const uint32_t tmem_slot = acc_empty + 16u;
-    uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem0));
-    const float4* ycol = reinterpret_cast<const float4*>(smem_raw + (ycol_base - smem0));
-    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kDx3Stages; ++s) {
-            mbar_init(full_bar + 8u * s, 1);
-            mbar_init(empty_bar + 8u * s, 1);
-        }
-        mbar_init(b_bar, 1);
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(acc_full + 8u * b, 1);
-            mbar_init(acc_empty + 8u * b, kDx3Epi / 32);
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
-    }
-    constexpr int tmem_cols = 256;
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(tmem_cols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_d = *tmem_slot_ptr;
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-
-    if (warp == 0) {
-        // ===== producer: the weights once; per tile two M tiles (4 dy rows x 32 pixels each) x the channel chunks =====
-        if (elect_one()) {
-            mbar_expect_tx(b_bar, (uint32_t)ksteps * b_bytes);
-            for (int q = 0; q < ksteps; ++q) tma_load_3d(b_res + (uint32_t)q * b_bytes, &map_b, b_bar, q * BK, 0, 0);
-        }
-        int s = 0, it = 0;
-        uint32_t phase = 0;
-        bool alive = true;
-        for (int tile = blockIdx.x; tile < g.tiles && alive; tile += gridDim.x) {
-            const int n = tile / g.tiles_per_img, t = tile - n * g.tiles_per_img;
-            const int i_base = g.R * t + g.lo;
-            for (int mt = 0; mt < 2 && alive; ++mt)
-                for (int q = 0; q < ksteps; ++q, ++it) {
-                    if (!mbar_wait_warp(empty_bar + 8u * s, phase ^ 1u, 0, it, wait_limit)) { alive = false; break; }
-                    if (elect_one()) {
-                        const uint32_t fb = full_bar + 8u * s;
-                        mbar_expect_tx(fb, (uint32_t)A_STAGE_BYTES);
-                        tma_load_4d(ring + (uint32_t)s * A_STAGE_BYTES, &map_a, fb, q * BK, 0, i_base + 4 * mt, n);
-                    }
-                    if (++s == kDx3Stages) { s = 0; phase ^= 1u; }
-                }
-        }
-    } else if (warp == 1) {
-        // ===== MMA issuer: both operands K-major =====
-        const uint32_t idesc = make_idesc(0, 0, 128, BM);
-        const uint64_t adesc0 = make_smem_desc(ring, 16u, 1024u, kLayoutSw128);
-        const uint64_t bdesc0 = make_smem_desc(b_res, 16u, 1024u, kLayoutSw128);
-        int s = 0, it = 0, n = 0;
-        uint32_t phase = 0;
-        bool alive = mbar_wait_warp(b_bar, 0, 1, -1, wait_limit);
-        for (int tile = blockIdx.x; tile < g.tiles && alive; tile += gridDim.x, ++n) {
-            for (int mt = 0; mt < 2 && alive; ++mt) {
-                // the epilogue has copied this accumulator's previous tile to shared memory (first tile: passes at once)
-                if (!mbar_wait_warp(acc_empty + 8u * mt, ((uint32_t)n & 1u) ^ 1u, 1, it, wait_limit)) { alive = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                for (int q = 0; q < ksteps; ++q, ++it) {
-                    if (!mbar_wait_warp(full_bar + 8u * s, phase, 1, it, wait_limit)) { alive = false; break; }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    if (elect_one()) {
-                        const uint64_t adesc = adesc0 + (uint64_t)((uint32_t)s * (A_STAGE_BYTES >> 4));
-                        const uint64_t bdesc = bdesc0 + (uint64_t)((uint32_t)q * (b_bytes >> 4));
-#pragma unroll
-                        for (int kk = 0; kk < BK / 8; ++kk)
-                            tcgen05_mma_tf32(tmem_d + (uint32_t)(mt * 128), adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc,
-                                             (q > 0 || kk > 0) ? 1u : 0u);
-                        tcgen05_commit(empty_bar + 8u * s);
-                    }
-                    if (++s == kDx3Stages) { s = 0; phase ^= 1u; }
-                }
-                if (elect_one()) tcgen05_commit(acc_full + 8u * mt);   // complete, or abandoned
-            }
-        }
-    } else {
-        // ===== epilogue: accumulators -> shared memory [tap][dy pixel][4], then gather the tile's own output pixels =====
-        const int quad = warp & 3;
-        const int row = quad * 32 + lane;                // dy pixel of the M tile: 32 * (row of the tile) + column
-        const int slab = (warp - 2) >> 2;                // the four warps of a lane quadrant take one 32-column slab each
-        const int tid_e = threadIdx.x - 64;
-        const EpilogueArgs& e = p.ep;
-        const int W = p.W, own = 2 * g.R * W;            // output pixels a tile owns
-        int n_it = 0;
-        for (int tile = blockIdx.x; tile < g.tiles; tile += gridDim.x, ++n_it) {
-            const int n = tile / g.tiles_per_img, t = tile - n * g.tiles_per_img;
-            const int i_base = g.R * t + g.lo;
-            bool ok = true;
-            for (int mt = 0; mt < 2; ++mt) {
-                bool got = mbar_wait(acc_full + 8u * mt, (uint32_t)n_it & 1u, 2, n_it, wait_limit);
-                got = __all_sync(0xffffffffu, got);
-                ok = ok && got;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                {
-                    const int c0 = slab * 32;
-                    if (c0 < 4 * ntaps) {
-                        uint32_t r[32];
-                        tmem_ld_32x32b_x32(tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)(mt * 128 + c0), r);
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                        for (int q = 0; q < 8; ++q) {
-                            const int tap = (c0 >> 2) + q;
-                            if (tap < ntaps) {
-                                const uint32_t addr = ycol_base + (uint32_t)(((tap * kDx3Rows * 32) + mt * 128 + row) * 16);
-                                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(__uint_as_float(r[4 * q])),
-                                             "f"(__uint_as_float(r[4 * q + 1])), "f"(__uint_as_float(r[4 * q + 2])),
-                                             "f"(__uint_as_float(r[4 * q + 3])) : "memory");
-                            }
-                        }
-                    }
-                }
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty + 8u * mt) : "memory");
-            }
-            asm volatile("bar.sync 1, %0;" ::"n"(kDx3Epi) : "memory");
-            // gather: consecutive threads take consecutive output pixels of the tile's 2R rows
-            for (int px = tid_e; px < own; px += kDx3Epi) {
-                const int hl = px / W, w = px - hl * W;
-                const int h = 2 * g.R * t + hl;
-                if (h >= p.H || !ok) continue;
-                float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                const int di0 = (h + p.pt) & 1, dj0 = (w + p.pl) & 1;   // kernel rows / columns of matching parity, ascending
-                if constexpr (KH_ > 0) {
-                    constexpr int TH = (KH_ + 1) / 2, TW = (KW_ + 1) / 2;
-                    float4 v[TH * TW];
-#pragma unroll
-                    for (int a = 0; a < TH; ++a) {
-                        const int di = di0 + 2 * a;
-                        const int hh = h + p.pt - di;
-                        const int i = hh >> 1;
-                        const bool row_ok = di < KH_ && hh >= 0 && i < p.Ho;
-#pragma unroll
-                        for (int b = 0; b < TW; ++b) {
-                            const int dj = dj0 + 2 * b;
-                            const int ww = w + p.pl - dj;
-                            const int j = ww >> 1;
-                            const bool in = row_ok && dj < KW_ && ww >= 0 && j < p.Wo;
-                            v[a * TW + b] = in ? ycol[((di * KW_ + dj) * kDx3Rows + (i - i_base)) * 32 + j]
-                                               : make_float4(0.f, 0.f, 0.f, 0.f);
-                        }
-                    }
-#pragma unroll
-                    for (int q = 0; q < TH * TW; ++q) {
-                        acc[0] = __fadd_rn(acc[0], v[q].x); acc[1] = __fadd_rn(acc[1], v[q].y);
-                        acc[2] = __fadd_rn(acc[2], v[q].z); acc[3] = __fadd_rn(acc[3], v[q].w);
-                    }
-                } else {
-                    for (int di = di0; di < p.KH; di += 2) {
-                        const int i = (h + p.pt - di) >> 1;
-                        if (h + p.pt - di < 0 || i >= p.Ho) continue;
-                        const int rl = i - i_base;
-                        for (int dj = dj0; dj < p.KW; dj += 2) {
-                            const int j = (w + p.pl - dj) >> 1;
-                            if (w + p.pl - dj < 0 || j >= p.Wo) continue;
-                            const float4 v = ycol[((di * p.KW + dj) * kDx3Rows + rl) * 32 + j];
-                            acc[0] = __fadd_rn(acc[0], v.x); acc[1] = __fadd_rn(acc[1], v.y);
-                            acc[2] = __fadd_rn(acc[2], v.z); acc[3] = __fadd_rn(acc[3], v.w);
-                        }
-                    }
-                }
-                const size_t pix = ((size_t)n * p.H + h) * W + w;
-                for (int c = 0; c < p.C; ++c) {
-                    const size_t idx = pix * p.C + c;
-                    p.out[idx] = epilogue_apply(e, acc[c], idx, c);
-                }
-            }
-            asm volatile("bar.sync 1, %0;" ::"n"(kDx3Epi) : "memory");   // the products are consumed: the next tile may overwrite them
-        }
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 1) {
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
-    }
-}
-
-// ---- narrow-channel DK: add the partitions' partial tiles -----------------------------------------
-// partial[m tile][partition][col][row] (col = 32 * kernel row + window slot, row = output channel).
-// Block = 32 rows x 8 lanes of one column: lane l adds partitions l, l+8, ... (all loads in
-// flight), the eight lane sums are then added in lane order - a fixed order for a given partition
-// count, so the result does not depend on timing.  blockIdx.x = column, blockIdx.y = 32-row group.
-__global__ void __launch_bounds__(256)
-dk_narrow_finish_kernel(const float* __restrict__ partial, float* __restrict__ dk, int parts, int bn,
-                        int KH, int KW, int C, int O)
-{
-    pdl_enter();
-    __shared__ float lane_sum[8][32];
-    const int col = blockIdx.x;
-    const int di = col >> 5, dj = (col & 31) >> 2, c = col & 3;
-    if (di >= KH || dj >= KW || c >= C) return;   // padding slot (uniform over the block)
-    const int r = threadIdx.x & 31, l = threadIdx.x >> 5;
-    const int o = blockIdx.y * 32 + r;
-    const int mt = o / BM, row = o % BM;
-    float acc = 0.f;
-    if (o < O) {
-        const float* src = partial + ((size_t)mt * parts * bn + col) * BM + row;
-        for (int sidx = l; sidx < parts; sidx += 8) acc = __fadd_rn(acc, __ldcg(src + (size_t)sidx * bn * BM));
-    }
-    lane_sum[l][r] = acc;
-    __syncthreads();
-    if (l == 0 && o < O) {
-        float t = lane_sum[0][r];
-#pragma unroll
-        for (int q = 1; q < 8; ++q) t = __fadd_rn(t, lane_sum[q][r]);
-        dk[((size_t)(di * KW + dj) * C + c) * O + o] = t;
-    }
-}
-
-// ---- narrow-channel layers (<= 4 input channels: the RGB end of both networks) -------------------
-// A 3-channel NHWC pixel is 12 bytes, which TMA cannot address (16-byte granularity), and a K of
-// 3 per tap would waste the tensor core.  Such an input is first copied into a zero-bordered
-// 4-channel image xp[n][h + pad_top][w + pad_left][4]; in that image the five taps of one kernel
-// row that output pixel (i, j) needs are 32 CONTIGUOUS floats (8 pixels x 4 channels, the last 3
-// pixels unused) starting at xp[n][s*i + di][s*j][0].  A tensor map whose pixel stride (s*16 bytes)
-// is smaller than its 128-byte inner extent hands these overlapping windows to TMA directly, so a
-// whole kernel row becomes one K = 32 step: FWD contracts it against the row's weights repacked as
-// k4[di][4*dj + c][o]; DK contracts the window against dy over pixels and scatters the 32 slots
-// back to dk[di][dj][c][o].
-__global__ void __launch_bounds__(256)
-repack_narrow_kernel(const float* __restrict__ x, float4* __restrict__ xp, int N, int H, int W, int C,
-                     int Hp, int Wp, int pt, int pl)
-{
-    pdl_enter();
-    const size_t total = (size_t)N * Hp * Wp;
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int wp = (int)(i % Wp);
-        const int hp = (int)((i / Wp) % Hp);
-        const int n = (int)(i / ((size_t)Wp * Hp));
-        const int h = hp - pt, w = wp - pl;
-        float v[4] = {0.f, 0.f, 0.f, 0.f};
-        if (h >= 0 && h < H && w >= 0 && w < W) {
-            const float* src = x + (((size_t)n * H + h) * W + w) * C;
-            for (int c = 0; c < C; ++c) v[c] = __ldg(src + c);
-        }
-        xp[i] = make_float4(v[0], v[1], v[2], v[3]);
-    }
-}
-
-// Both repacks of a narrow-channel forward in one launch: blocks [0, gridDim.x - k4_blocks) build
-// the padded 4-channel image, the last k4_blocks blocks the weights k4 [KH][32][O] (row 4*dj + c).
-__global__ void __launch_bounds__(256)
-repack_narrow_k4_kernel(const float* __restrict__ x, float4* __restrict__ xp, int N, int H, int W, int C,
-                        int Hp, int Wp, int pt, int pl, const float* __restrict__ k, float* __restrict__ k4,
-                        int KH, int KW, int O, int k4_blocks)
-{
-    pdl_enter();
-    const int x_blocks = (int)gridDim.x - k4_blocks;
-    if ((int)blockIdx.x >= x_blocks) {
-        const int total = KH * 32 * O;
-        for (int i = ((int)blockIdx.x - x_blocks) * blockDim.x + threadIdx.x; i < total; i += k4_blocks * blockDim.x) {
-            const int o = i % O, slot = (i / O) % 32, di = i / (O * 32);
-            const int dj = slot >> 2, c = slot & 3;
-            k4[i] = (dj < KW && c < C) ? __ldg(k + (((size_t)di * KW + dj) * C + c) * O + o) : 0.f;
-        }
-        return;
-    }
-    const size_t total = (size_t)N * Hp * Wp;
-    const size_t stride = (size_t)x_blocks * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int wp = (int)(i % Wp);
-        const int hp = (int)((i / Wp) % Hp);
-        const int n = (int)(i / ((size_t)Wp * Hp));
-        const int h = hp - pt, w = wp - pl;
-        float v[4] = {0.f, 0.f, 0.f, 0.f};
-        if (h >= 0 && h < H && w >= 0 && w < W) {
-            const float* src = x + (((size_t)n * H + h) * W + w) * C;
-            for (int c = 0; c < C; ++c) v[c] = __ldg(src + c);
-        }
-        xp[i] = make_float4(v[0], v[1], v[2], v[3]);
-    }
-}
-
-// ---- input gradient of a narrow-channel layer (<= 4 input channels) -------------------------------
-// With C <= 4 the implicit GEMM of DX has N = C: every 128 x 32 tile of dy would be fetched for a
-// sliver of tensor work, once per tap.  Instead dy is read ONCE by a plain GEMM against all taps,
-//   ycol[tap][pixel of dy][c] = sum_o dy[pixel, o] * k[tap, c, o]      (N = 4 * KH*KW, padded to 32s)
-// - the FWD kernel on a 1x1 "convolution" with the weights transposed to k2[o][4 * tap + c] - and a
-// gather ("col2im") then adds, for every input pixel, the <= ceil(KH/s)*ceil(KW/s) products that
-// land on it and applies the fused chain.
-__global__ void __launch_bounds__(256)
-repack_k2_kernel(const float* __restrict__ k, float* __restrict__ k2, int taps, int C, int Jp, int O)
-{
-    pdl_enter();
-    const int total = O * Jp;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-        const int j = i % Jp, o = i / Jp;
-        const int tap = j >> 2, c = j & 3;   // four columns per tap, channels beyond C are zero
-        k2[i] = (tap < taps && c < C) ? __ldg(k + ((size_t)tap * C + c) * O + o) : 0.f;
-    }
-}
-
-// ycol is stored tap-major, [tap][pixel of dy][4 channels]: the threads of a warp walk adjacent
-// pixels, so their 16-byte reads of one tap's plane are contiguous.  One thread per output pixel.
-// KH_, KW_, S_ > 0 fix kernel extent and stride at compile time (the DCGAN layers: 5, 5, 2): the tap
-// loops unroll, the divisions turn into shifts and all loads of a pixel are in flight together.
-template <int KH_, int KW_, int S_>
-__global__ void __launch_bounds__(256)
-col2im_kernel(const float4* __restrict__ ycol, float* __restrict__ out, int N, int H, int W, int C, int Ho, int Wo,
-              int KHr, int KWr, int shr, int swr, int pt, int pl, const EpilogueArgs ep)
-{
-    pdl_enter();
-    const int KH = KH_ > 0 ? KH_ : KHr, KW = KW_ > 0 ? KW_ : KWr, sh = S_ > 0 ? S_ : shr, sw = S_ > 0 ? S_ : swr;
-    const size_t total = (size_t)N * H * W;
-    const size_t pixels = (size_t)N * Ho * Wo;
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t pix = (size_t)blockIdx.x * blockDim.x + threadIdx.x; pix < total; pix += stride) {
-        const int w = (int)(pix % W);
-        const int h = (int)((pix / W) % H);
-        const int n = (int)(pix / ((size_t)W * H));
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        const int di0 = (h + pt) % sh, dj0 = (w + pl) % sw;
-        const float4* img = ycol + (size_t)n * Ho * Wo;
-        if constexpr (KH_ > 0) {
-            // all candidate taps of this pixel's parity class, loads first (zero where the tap falls outside)
-            constexpr int SS = S_ > 0 ? S_ : 1;
-            constexpr int TH = (KH_ + SS - 1) / SS, TW = (KW_ + SS - 1) / SS;
-            float4 v[TH * TW];
-#pragma unroll
-            for (int a = 0; a < TH; ++a) {
-                const int di = di0 + a * S_;
-                const int hh = h + pt - di;
-                const int i = hh / S_;
-                const bool row_ok = di < KH_ && hh >= 0 && i < Ho;
-#pragma unroll
-                for (int b = 0; b < TW; ++b) {
-                    const int dj = dj0 + b * S_;
-                    const int ww = w + pl - dj;
-                    const int j = ww / S_;
-                    const bool ok = row_ok && dj < KW_ && ww >= 0 && j < Wo;
-                    v[a * TW + b] = ok ? __ldg(img + (size_t)(di * KW_ + dj) * pixels + (size_t)i * Wo + j)
-                                       : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-            }
-            // same order as the run-time form: kernel rows ascending, columns ascending (absent taps add +0)
-#pragma unroll
-            for (int q = 0; q < TH * TW; ++q) {
-                acc[0] = __fadd_rn(acc[0], v[q].x); acc[1] = __fadd_rn(acc[1], v[q].y);
-                acc[2] = __fadd_rn(acc[2], v[q].z); acc[3] = __fadd_rn(acc[3], v[q].w);
-            }
-        } else {
-            for (int di = di0; di < KH; di += sh) {      // taps whose row parity matches
-                if (h + pt - di < 0) break;
-                const int i = (h + pt - di) / sh;
-                if (i >= Ho) continue;
-                for (int dj = dj0; dj < KW; dj += sw) {
-                    if (w + pl - dj < 0) break;
-                    const int j = (w + pl - dj) / sw;
-                    if (j >= Wo) continue;
-                    const float4 v = __ldg(img + (size_t)(di * KW + dj) * pixels + (size_t)i * Wo + j);
-                    acc[0] = __fadd_rn(acc[0], v.x); acc[1] = __fadd_rn(acc[1], v.y);
-                    acc[2] = __fadd_rn(acc[2], v.z); acc[3] = __fadd_rn(acc[3], v.w);
-                }
-            }
-        }
-        for (int c = 0; c < C; ++c) {
-            const size_t idx = pix * C + c;
-            out[idx] = epilogue_apply(ep, acc[c], idx, c);
-        }
-    }
-}
 
 // ---- host side: tensor maps ---------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
